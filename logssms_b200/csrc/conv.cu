@@ -1,0 +1,117 @@
+// Depthwise causal conv1d over packed portions, with per-request history kept in state slots.
+//
+//   u_t[ch]  = round(xBC_t[ch] * region_scale(ch))                (three regions: x | B | C)
+//   c_t[ch]  = sum_{j<K} w[ch, j] * u_{t-(K-1)+j}[ch] (+ bias[ch])  ; inputs before the portion come
+//              from the request's conv state (zeros when the request starts at position 0)
+//   out_t    = round(silu(round(c_t)))
+//   state'   = the last K-1 scaled inputs u, oldest first
+// (python/logssms/kernel/linear_attention/packed_conv.py:96-140; decode form
+// python/logssms/kernel/linear_attention/conv_decode.py:112-278.)
+//
+// Two launches: the forward kernel only READS the state (grid over token chunks, so a long prompt
+// spreads over many CTAs), the update kernel then rewrites it, one thread per (request, channel).
+#include "lb200/common.cuh"
+using namespace lb200;
+
+namespace {
+constexpr int kChunk = 64;
+
+struct ConvArgs {
+    const void* x; long x_stride;          // [tokens, C] view, row stride in elements
+    const float* weight;                   // [C, K]
+    const float* bias;                     // [C] or null
+    void* state;                           // [slots, C, K-1]
+    void* out;                             // [tokens, C] contiguous
+    const int* cu_seqlens; const int* start_pos; const int* slots;
+    int C; int end0; int end1; float s0; float s1; float s2;
+};
+
+template <typename T>
+__device__ __forceinline__ float scaled_input(const ConvArgs& a, long token, int c, float scale) {
+    return round_to<T>(to_f32(((const T*)a.x)[token * a.x_stride + c]) * scale);
+}
+
+template <typename T, int K>
+__global__ void conv_forward_kernel(ConvArgs a) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const int b = blockIdx.z;
+    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
+    const int t0 = blockIdx.y * kChunk;
+    if (t0 >= len) return;
+    const int t1 = min(len, t0 + kChunk);
+    const float scale = c < a.end0 ? a.s0 : (c < a.end1 ? a.s1 : a.s2);
+    const bool has_history = a.start_pos[b] > 0;
+    const T* st = (const T*)a.state + ((size_t)a.slots[b] * a.C + c) * (K - 1);
+    float w[K], win[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) w[j] = a.weight[(size_t)c * K + j];
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+        const int idx = t0 - (K - 1) + j;                 // relative to the portion's first token
+        win[j] = idx >= 0 ? scaled_input<T>(a, begin + idx, c, scale)
+                          : (has_history ? to_f32(st[K - 1 + idx]) : 0.f);
+    }
+    const float bias = a.bias ? a.bias[c] : 0.f;
+    for (int t = t0; t < t1; ++t) {
+        win[K - 1] = scaled_input<T>(a, begin + t, c, scale);
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < K; ++j) acc += win[j] * w[j];
+        acc = round_to<T>(acc + bias);
+        ((T*)a.out)[(size_t)(begin + t) * a.C + c] = from_f32<T>(silu_f(acc));
+#pragma unroll
+        for (int j = 0; j < K - 1; ++j) win[j] = win[j + 1];
+    }
+}
+
+template <typename T, int K>
+__global__ void conv_state_update_kernel(ConvArgs a) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const int b = blockIdx.y;
+    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
+    if (len <= 0) return;
+    const float scale = c < a.end0 ? a.s0 : (c < a.end1 ? a.s1 : a.s2);
+    const bool has_history = a.start_pos[b] > 0;
+    T* st = (T*)a.state + ((size_t)a.slots[b] * a.C + c) * (K - 1);
+    float next[K];
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+        const int idx = len - (K - 1) + j;
+        next[j] = idx >= 0 ? scaled_input<T>(a, begin + idx, c, scale)
+                           : (has_history ? to_f32(st[K - 1 + idx]) : 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) st[j] = from_f32<T>(next[j]);
+}
+
+template <typename T>
+int launch(const ConvArgs& a, int B, int K, int max_len, cudaStream_t s) {
+    const int threads = 128;
+    dim3 grid_f((a.C + threads - 1) / threads, (max_len + kChunk - 1) / kChunk, B);
+    dim3 grid_u((a.C + threads - 1) / threads, B);
+#define LB_CONV_K(KK)                                                         \
+    case KK:                                                                  \
+        conv_forward_kernel<T, KK><<<grid_f, threads, 0, s>>>(a);             \
+        conv_state_update_kernel<T, KK><<<grid_u, threads, 0, s>>>(a);        \
+        break;
+    switch (K) {
+        LB_CONV_K(2) LB_CONV_K(3) LB_CONV_K(4) LB_CONV_K(5) LB_CONV_K(6) LB_CONV_K(7) LB_CONV_K(8)
+        default: return kBadSize;
+    }
+#undef LB_CONV_K
+    return launch_status();
+}
+}  // namespace
+
+extern "C" int lb_causal_conv1d(const void* x, long x_stride, const float* weight, const float* bias, void* state,
+                                void* out, const int* cu_seqlens, const int* start_pos, const int* slots, int B,
+                                int max_len, int C, int K, int end0, int end1, float s0, float s1, float s2,
+                                int dtype, void* stream) {
+    if (B <= 0 || max_len <= 0) return kOk;
+    if (C <= 0 || K < 2 || K > 8) return kBadSize;
+    ConvArgs a{x, x_stride, weight, bias, state, out, cu_seqlens, start_pos, slots, C, end0, end1, s0, s1, s2};
+    LB_DISPATCH_DTYPE(dtype, return launch<T>(a, B, K, max_len, (cudaStream_t)stream));
+    return kOk;
+}

@@ -1,0 +1,74 @@
+// Shared device/host helpers of the logssms_b200 kernels (sm_100a).
+//
+// Every kernel file exports plain C launchers (`extern "C" int lb_*`) that take raw device
+// pointers, sizes and a stream, and return 0 or an error code; the Python side checks shapes,
+// dtypes and contiguity before the call and turns a non-zero code into an exception.  The same
+// division of labour as the reference's host-side TensorMatcher + LaunchKernel helpers
+// (csrc/include/logssms/tensor.hpp:475, csrc/include/logssms/utils.hpp:189-264), without tvm-ffi.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lb200 {
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// error codes of the launchers (negative: refused before launch; positive: cudaError_t)
+enum : int { kOk = 0, kBadDType = -1, kBadSize = -2, kTooLarge = -3 };
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// value after a store in T and a load back: the "rounded to the activation dtype" of the formulas
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32(from_f32<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a whole block; `scratch` is >= 32 floats of shared memory.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+
+inline int launch_status() { return (int)cudaGetLastError(); }
+
+}  // namespace lb200
+
+#define LB_DISPATCH_DTYPE(dtype, ...)                                   \
+    switch (dtype) {                                                    \
+        case lb200::kF32: { using T = float; __VA_ARGS__; break; }      \
+        case lb200::kBF16: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+        default: return lb200::kBadDType;                               \
+    }

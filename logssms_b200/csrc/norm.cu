@@ -1,0 +1,153 @@
+// Row-wise normalisation and gating kernels: statistics in 32-bit, one CTA per row (or row group).
+//
+//  add_rmsnorm_branches : residual add + RMSNorm with one or two scaled outputs
+//                         (formula of python/logssms/kernel/norm.py:16-35)
+//  gated_rmsnorm        : grouped RMSNorm with SiLU gate, before or after the gate, or the plain
+//                         y * silu(gate) product when the mixer has no norm
+//                         (python/logssms/kernel/norm.py:55-86, python/logssms/kernel/fused.py:9-19)
+//  swiglu               : silu(gate * s) * up on a packed [gate | up] row
+//                         (python/logssms/kernel/fused.py:32-50)
+#include "lb200/common.cuh"
+using namespace lb200;
+
+// r = round(round(x*in0) + round(other*in1))  (only when `other` is given; else r = x)
+// r += residual ; residual_out = round(r) ; n = round(r * rsqrt(mean(r^2)+eps) * w)
+// out0 = round(n*s0) ; out1 = round(n*s1)
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ other, const T* residual_in,
+                                   T* residual_out, const float* __restrict__ weight, T* __restrict__ out0,
+                                   T* __restrict__ out1, int H, float eps, float in0, float in1, float s0, float s1) {
+    extern __shared__ float row[];          // H floats
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = to_f32(x[base + c]);
+        if (other != nullptr) {
+            v = round_to<T>(round_to<T>(v * in0) + round_to<T>(to_f32(other[base + c]) * in1));
+        }
+        if (residual_in != nullptr) v += to_f32(residual_in[base + c]);
+        row[c] = v;
+        ss += v * v;
+        if (residual_out != nullptr) residual_out[base + c] = from_f32<T>(v);
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float n = round_to<T>(row[c] * inv * weight[c]);
+        out0[base + c] = from_f32<T>(n * s0);
+        if (out1 != nullptr) out1[base + c] = from_f32<T>(n * s1);
+    }
+}
+
+extern "C" int lb_add_rmsnorm(const void* x, const void* other, const void* residual_in, void* residual_out,
+                              const float* weight, void* out0, void* out1, int rows, int H, float eps,
+                              float in0, float in1, float s0, float s1, int dtype, void* stream) {
+    if (rows <= 0) return kOk;
+    if (H <= 0) return kBadSize;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return kTooLarge;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    LB_DISPATCH_DTYPE(dtype, {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<T><<<rows, threads, smem, (cudaStream_t)stream>>>(
+            (const T*)x, (const T*)other, (const T*)residual_in, (T*)residual_out, weight, (T*)out0, (T*)out1,
+            H, eps, in0, in1, s0, s1);
+    });
+    return launch_status();
+}
+
+// mode 0: out = y * round(silu(round(gate*s)))               (no norm)
+// mode 1: norm before gate: out = y*rsqrt(mean_g(y^2)+eps)*w * silu(round(gate*s))
+// mode 2: norm after gate : t = y*silu(round(gate*s)); out = t*rsqrt(mean_g(t^2)+eps)*w
+// grid (rows, groups); y row stride = groups*width (contiguous), gate row stride given (a view).
+template <typename T>
+__global__ void gated_rmsnorm_kernel(const T* __restrict__ y, const T* __restrict__ gate, long gate_stride,
+                                     const float* __restrict__ weight, T* __restrict__ out, int width, int groups,
+                                     float eps, float gate_scale, int mode) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int g = blockIdx.y;
+    const T* yr = y + row * (size_t)groups * width + (size_t)g * width;
+    const T* gr = gate + row * (size_t)gate_stride + (size_t)g * width;
+    T* orow = out + row * (size_t)groups * width + (size_t)g * width;
+    if (mode == 0) {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            const float z = round_to<T>(silu_f(round_to<T>(to_f32(gr[c]) * gate_scale)));
+            orow[c] = from_f32<T>(to_f32(yr[c]) * z);
+        }
+        return;
+    }
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = to_f32(yr[c]);
+        if (mode == 2) v *= silu_f(round_to<T>(to_f32(gr[c]) * gate_scale));
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float z = silu_f(round_to<T>(to_f32(gr[c]) * gate_scale));
+        float v = to_f32(yr[c]);
+        if (mode == 2) v *= z;
+        v = v * inv * weight[g * width + c];
+        if (mode == 1) v *= z;
+        orow[c] = from_f32<T>(v);
+    }
+}
+
+extern "C" int lb_gated_rmsnorm(const void* y, const void* gate, long gate_stride, const float* weight, void* out,
+                                int rows, int width, int groups, float eps, float gate_scale, int mode, int dtype,
+                                void* stream) {
+    if (rows <= 0) return kOk;
+    if (width <= 0 || groups <= 0 || mode < 0 || mode > 2) return kBadSize;
+    const int threads = width >= 1024 ? 256 : 128;
+    dim3 grid(rows, groups);
+    LB_DISPATCH_DTYPE(dtype, gated_rmsnorm_kernel<T><<<grid, threads, 0, (cudaStream_t)stream>>>(
+        (const T*)y, (const T*)gate, gate_stride, weight, (T*)out, width, groups, eps, gate_scale, mode));
+    return launch_status();
+}
+
+// out[r, c] = round(silu(round(gate*s))) * up, gate = in[r, c], up = in[r, I + c]; in row stride 2*I.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int I, float act_scale) {
+    const size_t r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= I) return;
+    const float g = round_to<T>(to_f32(in[r * 2 * I + c]) * act_scale);
+    const float a = round_to<T>(silu_f(g));
+    out[r * I + c] = from_f32<T>(a * to_f32(in[r * 2 * I + I + c]));
+}
+
+extern "C" int lb_swiglu(const void* in, void* out, int rows, int I, float act_scale, int dtype, void* stream) {
+    if (rows <= 0) return kOk;
+    if (I <= 0) return kBadSize;
+    dim3 grid((I + 255) / 256, rows);
+    LB_DISPATCH_DTYPE(dtype, swiglu_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)in, (T*)out, I, act_scale));
+    return launch_status();
+}
+
+// out = round(x * s): the output multiplier of a projection when it cannot ride in the product's epilogue.
+template <typename T>
+__global__ void scale_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n, float s) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<T>(to_f32(x[i]) * s);
+}
+
+// out_f32 = float(x) * s: logits leave the model in 32-bit.
+template <typename T>
+__global__ void scale_to_f32_kernel(const T* __restrict__ x, float* __restrict__ out, size_t n, float s) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = to_f32(x[i]) * s;
+}
+
+extern "C" int lb_scale(const void* x, void* out, long n, float s, int to_f32_out, int dtype, void* stream) {
+    if (n <= 0) return kOk;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    LB_DISPATCH_DTYPE(dtype, {
+        if (to_f32_out) scale_to_f32_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)x, (float*)out, (size_t)n, s);
+        else scale_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, (size_t)n, s);
+    });
+    return launch_status();
+}

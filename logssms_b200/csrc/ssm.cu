@@ -1,0 +1,151 @@
+// Selective state-space scan (Mamba2), token by token, with the state kept in 32-bit.
+//
+//   dt_h   = softplus(round(dt_raw_h * dt_scale) + dt_bias_h)        softplus(v) = v if v > 20 else log1p(e^v)
+//   dA_h   = -exp(A_log_h) * dt_h
+//   S_h   <- e^{dA_h} S_h + B_{g(h)} (x) (x_h * dt_h)                 S_h in R^{P x N}
+//   y_h    = S_h C_{g(h)} + D_h x_h                                   (uses the updated state)
+// (python/logssms/kernel/linear_attention/mamba2.py:27-36 and :261-292; recurrence oracle
+// tests/kernel/test_mamba2.py:22-38 of the reference.)
+//
+// This kernel runs a portion of any length from the request's saved state and writes the state back
+// in place; a request whose portion starts at position 0 starts from zeros whatever the slot holds.
+// A single decoded token is a portion of length one.  Grid (head, request, P tile of 16); 128 threads
+// = 16 values of p x 8 lanes over N; each lane owns N/8 state values in registers (float4 strided),
+// the sum over N ends with three shuffles.
+#include "lb200/common.cuh"
+using namespace lb200;
+
+namespace {
+constexpr int kPTile = 16;
+constexpr int kLanesN = 8;
+
+struct SsmArgs {
+    const void* conv; int C;                     // [tokens, C]: x | B | C after the conv
+    const void* dt; long dt_stride;              // [tokens, nh] view
+    const float* A_log; const float* dt_bias; const float* D;
+    float* state;                                // [slots, nh, P, N]
+    void* y;                                     // [tokens, nh * P]
+    const int* cu_seqlens; const int* start_pos; const int* slots;
+    int nh, P, N, G; float dt_scale;
+};
+
+template <typename T> __device__ __forceinline__ void load4(const T* p, float* f);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+// NPT: state values per thread (N <= 8 * NPT).  ALIGNED: 4-element vector loads of B and C are legal.
+template <typename T, int NPT, bool ALIGNED>
+__global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int pi = threadIdx.x / kLanesN, nl = threadIdx.x % kLanesN;
+    const int p = blockIdx.z * kPTile + pi;
+    const bool p_ok = p < a.P;
+    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
+    if (len <= 0) return;
+    const int g = h / (a.nh / a.G);
+    const int inner = a.nh * a.P;
+    const int N = a.N;
+    const float negA = -expf(a.A_log[h]);
+    const float dt_bias = a.dt_bias[h], Dh = a.D[h];
+    float* sp = a.state + (((size_t)a.slots[b] * a.nh + h) * a.P + (p_ok ? p : 0)) * N;
+
+    float S[NPT];
+    const bool fresh = a.start_pos[b] <= 0;
+#pragma unroll
+    for (int i = 0; i < NPT / 4; ++i) {
+        const int n0 = i * 32 + nl * 4;
+        if (!fresh && p_ok && n0 < N) {
+            const float4 v = *reinterpret_cast<const float4*>(sp + n0);
+            S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+        } else {
+            S[4 * i] = S[4 * i + 1] = S[4 * i + 2] = S[4 * i + 3] = 0.f;
+        }
+    }
+    const T* conv = (const T*)a.conv;
+    const T* dtp = (const T*)a.dt;
+#pragma unroll 2
+    for (int t = 0; t < len; ++t) {
+        const size_t tok = (size_t)(begin + t);
+        const T* row = conv + tok * a.C;
+        float dt = round_to<T>(to_f32(dtp[tok * a.dt_stride + h]) * a.dt_scale) + dt_bias;
+        dt = dt > 20.f ? dt : log1pf(expf(dt));
+        const float decay = expf(negA * dt);
+        const float xv = p_ok ? to_f32(row[h * a.P + p]) : 0.f;
+        const float u = xv * dt;
+        const T* Bp = row + inner + g * N;
+        const T* Cp = Bp + a.G * N;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPT / 4; ++i) {
+            const int n0 = i * 32 + nl * 4;
+            if (n0 < N) {
+                float Bv[4], Cv[4];
+                if (ALIGNED) {
+                    load4<T>(Bp + n0, Bv);
+                    load4<T>(Cp + n0, Cv);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { Bv[e] = to_f32(Bp[n0 + e]); Cv[e] = to_f32(Cp[n0 + e]); }
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    S[4 * i + e] = S[4 * i + e] * decay + Bv[e] * u;
+                    acc += S[4 * i + e] * Cv[e];
+                }
+            }
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        if (nl == 0 && p_ok) ((T*)a.y)[tok * inner + h * a.P + p] = from_f32<T>(acc + Dh * xv);
+    }
+    if (p_ok) {
+#pragma unroll
+        for (int i = 0; i < NPT / 4; ++i) {
+            const int n0 = i * 32 + nl * 4;
+            if (n0 < N)
+                *reinterpret_cast<float4*>(sp + n0) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+        }
+    }
+}
+
+template <typename T, int NPT>
+void launch_npt(const SsmArgs& a, int B, bool aligned, cudaStream_t s) {
+    dim3 grid(a.nh, B, (a.P + kPTile - 1) / kPTile);
+    if (aligned) ssm_scan_kernel<T, NPT, true><<<grid, kPTile * kLanesN, 0, s>>>(a);
+    else ssm_scan_kernel<T, NPT, false><<<grid, kPTile * kLanesN, 0, s>>>(a);
+}
+
+template <typename T>
+int launch(const SsmArgs& a, int B, cudaStream_t s) {
+    const int inner = a.nh * a.P;
+    const bool aligned = (inner % 4 == 0) && (a.C % 4 == 0) && (a.N % 4 == 0) &&
+                         (sizeof(T) == 4 || (inner % 4 == 0));
+    if (a.N <= 32) launch_npt<T, 4>(a, B, aligned, s);
+    else if (a.N <= 64) launch_npt<T, 8>(a, B, aligned, s);
+    else if (a.N <= 128) launch_npt<T, 16>(a, B, aligned, s);
+    else if (a.N <= 256) launch_npt<T, 32>(a, B, aligned, s);
+    else return kTooLarge;
+    return launch_status();
+}
+}  // namespace
+
+extern "C" int lb_ssm_scan(const void* conv, int C, const void* dt, long dt_stride, const float* A_log,
+                           const float* dt_bias, const float* D, float* state, void* y, const int* cu_seqlens,
+                           const int* start_pos, const int* slots, int B, int nh, int P, int N, int G,
+                           float dt_scale, int dtype, void* stream) {
+    if (B <= 0) return kOk;
+    if (nh <= 0 || P <= 0 || N <= 0 || G <= 0 || nh % G || N % 4) return kBadSize;
+    if (C != nh * P + 2 * G * N) return kBadSize;
+    SsmArgs a{conv, C, dt, dt_stride, A_log, dt_bias, D, state, y, cu_seqlens, start_pos, slots, nh, P, N, G, dt_scale};
+    LB_DISPATCH_DTYPE(dtype, return launch<T>(a, B, (cudaStream_t)stream));
+    return kOk;
+}

@@ -1,0 +1,86 @@
+"""The one model class: embedding -> scheduled layers -> final norm -> head, all from a ModelSpec."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import build as kernel_build
+from ..ops import kernels as K
+from ..parts import Embedding, LMHead, Part
+from ..registry import BLOCKS, NORMS
+
+
+class DecoderModel(Part):
+    """Runs `spec.layers` in the order of `spec.resolved_schedule()`.
+
+    The schedule is data: an entry names the layer to run (a layer may appear twice) and the cache
+    layer it uses; an entry with `writes_cache=False` reads the keys/values another entry stored.
+    The cache manager is sized from `cache_needs()`: one entry per cache layer."""
+
+    def __init__(self, spec, perturb_init: bool = False):
+        self.spec = spec
+        shared: dict = {}
+        self.embedding = Embedding(spec.vocab_size, spec.hidden_size, spec.embedding_multiplier)
+        self.layers = [BLOCKS.get(b.kind)(b, perturb_init=perturb_init, shared=shared) for b in spec.layers]
+        self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, perturb_init)
+        self.lm_head = LMHead(spec.vocab_size, spec.hidden_size, spec.lm_head_multiplier,
+                              self.embedding if spec.tie_word_embeddings else None)
+        self.schedule = spec.resolved_schedule()
+        for e in self.schedule:
+            if not 0 <= e.layer < len(self.layers):
+                raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.layers)}")
+        self.num_cache_layers = max(e.cache for e in self.schedule) + 1
+
+    def children(self):
+        kids = {self.spec.embedding_name: self.embedding, self.spec.final_norm_name: self.final_norm,
+                self.spec.lm_head_name: self.lm_head}
+        for block_spec, block in zip(self.spec.layers, self.layers):
+            kids[block_spec.prefix] = block
+        return kids
+
+    def cache_needs(self):
+        from ..cache import CacheNeeds
+        needs = [None] * self.num_cache_layers
+        for e in self.schedule:
+            need = self.layers[e.layer].cache_needs()
+            if needs[e.cache] is None:
+                if not e.writes_cache:
+                    raise ValueError(f"schedule entry reads cache layer {e.cache} before anything wrote it")
+                needs[e.cache] = need
+            elif needs[e.cache] != need:
+                raise ValueError(f"cache layer {e.cache} is shared by layers with different needs")
+        return [n if n is not None else CacheNeeds() for n in needs]
+
+    def kernel_libraries(self) -> list[str]:
+        """Names of the CUDA libraries this model's parts call (compiled at first use)."""
+        names: list[str] = []
+
+        def walk(part):
+            names.extend(getattr(part, "kernels", ()))
+            for child in part.children().values():
+                walk(child)
+        walk(self)
+        return list(dict.fromkeys(names))
+
+    def setup(self, rt) -> None:
+        libs = self.kernel_libraries()
+        if rt.dtype == torch.float32:
+            libs.append("gemm_f32")
+        kernel_build.build_many(libs)
+        for block in self.layers:
+            block.setup(rt)
+
+    def forward(self, ctx):
+        """Residual stream after all scheduled layers, as the pair (x, residual) whose sum it is."""
+        x = self.embedding.forward(ctx.token_ids)
+        residual = None
+        for e in self.schedule:
+            x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
+        return x, residual
+
+    def logits(self, x: torch.Tensor, residual, rows: torch.Tensor) -> torch.Tensor:
+        """float32 logits [len(rows), vocab] at the token rows that were asked for."""
+        x = K.gather_rows(x, rows)
+        if residual is not None:
+            residual = K.gather_rows(residual, rows)
+        (h,), _ = self.final_norm.forward(x, residual, want_residual=False)
+        return self.lm_head.forward(h)

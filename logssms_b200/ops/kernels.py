@@ -1,0 +1,332 @@
+"""Python face of the CUDA kernels: checks on the host, then one C call.
+
+Every function here validates what the kernel cannot (device, dtype, layout,
+size limits) and raises a clear error instead of launching; the launchers
+return an error code for what they refuse themselves.  There is no CPU path
+and no library stand-in: a tensor that is not on a CUDA device is an error.
+
+Matrix products are the exception the engine shares with the reference, which
+also leaves them to a library (`F.linear`, python/logssms/layers/linear.py:26):
+bfloat16 products go to cuBLAS through torch, float32 products to the engine's
+own FFMA kernel so that no reduced-precision matrix mode can take part.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+
+import torch
+import torch.nn.functional as F
+
+from . import build
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_ERRORS = {-1: "dtype is neither float32 nor bfloat16", -2: "a size the kernel does not take",
+           -3: "a size beyond the kernel's limit"}
+_fn_cache: dict[tuple[str, str], ctypes._CFuncPtr] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _fn(lib: str, name: str, argtypes):
+    key = (lib, name)
+    f = _fn_cache.get(key)
+    if f is None:
+        f = getattr(build.load(lib), name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _fn_cache[key] = f
+    return f
+
+
+def _check(code: int, name: str, detail: str = "") -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{name} refused the call: {_ERRORS.get(code, code)} {detail}")
+    raise KernelError(f"{name}: CUDA error {code} at launch {detail}")
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {t.dtype}: the kernels take float32 and bfloat16") from None
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("logssms_b200 kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+
+
+# --------------------------------------------------------------------------- embedding
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, multiplier: float,
+                 bad_ids: torch.Tensor | None = None) -> torch.Tensor:
+    _cuda(table, ids)
+    _i32(ids, "ids")
+    _need(table.dim() == 2 and table.is_contiguous(), "embedding table must be a contiguous [vocab, hidden] matrix")
+    V, H = table.shape
+    out = torch.empty((ids.numel(), H), dtype=table.dtype, device=table.device)
+    f = _fn("embed", "lb_embed_gather", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
+                                         c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(table), _ptr(ids), ids.numel(), H, V, multiplier, _ptr(bad_ids), _code(table),
+             _stream()), "embed_gather")
+    return out
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    _cuda(src, rows)
+    _i32(rows, "rows")
+    _need(src.dim() == 2 and src.is_contiguous(), "gather_rows wants a contiguous matrix")
+    out = torch.empty((rows.numel(), src.shape[1]), dtype=src.dtype, device=src.device)
+    f = _fn("embed", "lb_gather_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(src), _ptr(rows), rows.numel(), src.shape[1], _code(src), _stream()), "gather_rows")
+    return out
+
+
+# --------------------------------------------------------------------------- norms
+def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None, *,
+                other: torch.Tensor | None = None, in_scales=(1.0, 1.0), out_scales=(1.0,),
+                want_residual: bool = True):
+    """(outputs, new_residual): residual add + RMSNorm with one or two scaled outputs.
+    The new residual is written in place of `residual` when one is given."""
+    _cuda(x, weight, residual, other)
+    _need(x.dim() == 2 and x.is_contiguous(), "add_rmsnorm wants a contiguous [rows, width] input")
+    rows, H = x.shape
+    _need(weight.dtype == torch.float32 and weight.shape == (H,) and weight.is_contiguous(),
+          "norm weight must be a contiguous float32 vector of the row width")
+    for t, name in ((residual, "residual"), (other, "other")):
+        if t is not None:
+            _need(t.shape == x.shape and t.dtype == x.dtype and t.is_contiguous(), f"{name} must match the input")
+    _need(1 <= len(out_scales) <= 2, "one or two outputs")
+    out0 = torch.empty_like(x)
+    out1 = torch.empty_like(x) if len(out_scales) == 2 else None
+    res_out = residual if residual is not None else (torch.empty_like(x) if want_residual else None)
+    f = _fn("norm", "lb_add_rmsnorm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                       c_int, c_float, c_float, c_float, c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(other), _ptr(residual), _ptr(res_out), _ptr(weight), _ptr(out0), _ptr(out1), rows, H,
+             eps, in_scales[0], in_scales[1], out_scales[0], out_scales[-1], _code(x), _stream()),
+           "add_rmsnorm", f"(width {H})")
+    return ((out0,) if out1 is None else (out0, out1)), res_out
+
+
+GATE_ONLY, NORM_BEFORE_GATE, NORM_AFTER_GATE = 0, 1, 2
+
+
+def gated_rmsnorm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor | None, eps: float, groups: int,
+                  gate_scale: float, mode: int) -> torch.Tensor:
+    """Grouped RMSNorm with SiLU gate (`mode` NORM_BEFORE_GATE / NORM_AFTER_GATE) or the bare
+    y * silu(gate) product (`GATE_ONLY`).  `gate` may be a column view of a wider matrix."""
+    _cuda(y, gate, weight)
+    _need(y.dim() == 2 and y.is_contiguous(), "gated_rmsnorm wants a contiguous [rows, width] input")
+    rows, width = y.shape
+    _need(gate.shape == y.shape and gate.dtype == y.dtype and gate.stride(1) == 1, "gate must match y, unit column stride")
+    _need(width % groups == 0, "width must be a multiple of groups")
+    if mode != GATE_ONLY:
+        _need(weight is not None and weight.dtype == torch.float32 and weight.shape == (width,) and weight.is_contiguous(),
+              "gated norm weight must be a contiguous float32 vector of the row width")
+    out = torch.empty_like(y)
+    f = _fn("norm", "lb_gated_rmsnorm", [c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int,
+                                         c_float, c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(y), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), rows, width // groups, groups, eps,
+             gate_scale, mode, _code(y), _stream()), "gated_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, act_scale: float) -> torch.Tensor:
+    _cuda(gate_up)
+    _need(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0,
+          "swiglu wants a contiguous [rows, 2*I] matrix")
+    rows, two_i = gate_up.shape
+    out = torch.empty((rows, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("norm", "lb_swiglu", [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), rows, two_i // 2, act_scale, _code(gate_up), _stream()), "swiglu")
+    return out
+
+
+def scale(x: torch.Tensor, s: float, to_f32: bool = False) -> torch.Tensor:
+    """round(x * s) in x's dtype, or float32(x) * s with `to_f32`."""
+    _cuda(x)
+    _need(x.is_contiguous(), "scale wants a contiguous tensor")
+    out = torch.empty(x.shape, dtype=torch.float32 if to_f32 else x.dtype, device=x.device)
+    f = _fn("norm", "lb_scale", [c_void_p, c_void_p, c_long, c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(out), x.numel(), s, int(to_f32), _code(x), _stream()), "scale")
+    return out
+
+
+# --------------------------------------------------------------------------- rotary + cache store
+def rope_table(inv_freq: torch.Tensor, rows: int) -> torch.Tensor:
+    """[rows, 2*half] float32: cos | sin of position * inv_freq."""
+    _cuda(inv_freq)
+    _need(inv_freq.dtype == torch.float32 and inv_freq.is_contiguous(), "inv_freq must be contiguous float32")
+    half = inv_freq.numel()
+    table = torch.empty((rows, 2 * half), dtype=torch.float32, device=inv_freq.device)
+    f = _fn("rope", "lb_rope_table", [c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(table), _ptr(inv_freq), rows, half, _stream()), "rope_table")
+    return table
+
+
+def rope_kv_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,
+                  slot_mapping: torch.Tensor, cos_sin: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  key_scale: float, write_kv: bool = True) -> torch.Tensor:
+    """qkv: [tokens, (Hq + 2*Hkv) * head_dim], columns q | k | v (row stride free).  Returns the rotated
+    queries [tokens, Hq, head_dim]; stores scaled+rotated keys and the values at `slot_mapping` (token
+    index in the page pool) unless `write_kv` is off."""
+    _cuda(qkv, positions, slot_mapping, cos_sin, k_cache, v_cache)
+    Hq, Hkv, hd = num_heads, num_kv_heads, head_dim
+    tokens = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.shape[1] == (Hq + 2 * Hkv) * hd and qkv.stride(1) == 1,
+          "qkv must be [tokens, (Hq + 2*Hkv) * head_dim] with unit column stride")
+    _i32(positions, "positions")
+    _i32(slot_mapping, "slot_mapping")
+    _need(positions.numel() == tokens and slot_mapping.numel() == tokens, "one position and one slot per token")
+    _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.dim() == 2,
+          "cos/sin table must be contiguous float32 [positions, rotary_dim]")
+    rotary_dim = cos_sin.shape[1]
+    _need(rotary_dim % 2 == 0 and rotary_dim <= hd, f"rotary_dim {rotary_dim} must be even and within head_dim {hd}")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == qkv.dtype == v_cache.dtype
+          and k_cache.shape[-2:] == (Hkv, hd) and v_cache.shape == k_cache.shape,
+          "k/v cache must be contiguous [..., kv_heads, head_dim] of the activation dtype")
+    q_out = torch.empty((tokens, Hq, hd), dtype=qkv.dtype, device=qkv.device)
+    row_stride = qkv.stride(0) if tokens > 1 else qkv.shape[1]
+    base = qkv.data_ptr()
+    item = qkv.element_size()
+    f = _fn("rope", "lb_rope_kv_store", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int,
+                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                         c_int, c_int, c_void_p])
+    _check(f(base, base + Hq * hd * item, base + (Hq + Hkv) * hd * item, row_stride, _ptr(positions),
+             _ptr(slot_mapping), _ptr(cos_sin), cos_sin.shape[0], _ptr(q_out), _ptr(k_cache), _ptr(v_cache), tokens,
+             Hq, Hkv, hd, rotary_dim, key_scale, int(write_kv), _code(qkv), _stream()), "rope_kv_store")
+    return q_out
+
+
+# --------------------------------------------------------------------------- attention
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                    token_req: torch.Tensor, positions: torch.Tensor, scale: float, window: int = 0) -> torch.Tensor:
+    """q: [tokens, Hq, hd]; caches: [pages, page_size, Hkv, hd]; block_table: [requests, max_pages] int32;
+    token_req / positions: per token its request row and absolute position.  Returns [tokens, Hq, hd]."""
+    _cuda(q, k_cache, v_cache, block_table, token_req, positions)
+    tokens, Hq, hd = q.shape
+    _need(q.is_contiguous(), "q must be contiguous")
+    _need(k_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
+          and k_cache.dtype == q.dtype == v_cache.dtype and k_cache.shape[3] == hd,
+          "caches must be contiguous [pages, page_size, kv_heads, head_dim] of q's dtype")
+    page_size, Hkv = k_cache.shape[1], k_cache.shape[2]
+    _need(hd % 16 == 0 and hd <= 256, f"attention takes head sizes in steps of 16 up to 256, got {hd}")
+    _need(Hq % Hkv == 0, f"query heads ({Hq}) must be a multiple of key/value heads ({Hkv})")
+    _need(block_table.dim() == 2 and block_table.dtype == torch.int32 and block_table.stride(1) == 1,
+          "block table must be a row-major int32 matrix")
+    _i32(token_req, "token_req")
+    _i32(positions, "positions")
+    out = torch.empty_like(q)
+    f = _fn("attention", "lb_paged_attention", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                                c_void_p])
+    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
+             _ptr(token_req), _ptr(positions), tokens, Hq, Hkv, hd, page_size, scale, int(window or 0), _code(q),
+             _stream()), "paged_attention")
+    return out
+
+
+# --------------------------------------------------------------------------- Mamba2
+def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
+                  cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int,
+                  max_len: int, region_ends: tuple[int, int], region_scales: tuple[float, float, float]) -> torch.Tensor:
+    """x: [tokens, C] (column view allowed); weight: [C, K] float32; state: [slots, C, K-1] of x's dtype,
+    read then rewritten in place.  Returns silu(conv) as a contiguous [tokens, C]."""
+    _cuda(x, weight, bias, state, cu_seqlens, start_pos, slots)
+    tokens, C = x.shape
+    K = weight.shape[1]
+    _need(x.stride(1) == 1, "conv input needs unit column stride")
+    _need(weight.dtype == torch.float32 and weight.shape == (C, K) and weight.is_contiguous(), "conv weight must be float32 [C, K]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.shape == (C,) and bias.is_contiguous()), "conv bias must be float32 [C]")
+    _need(2 <= K <= 8, f"conv kernel sizes 2..8 are built, got {K}")
+    _need(state.dtype == x.dtype and state.is_contiguous() and state.shape[1:] == (C, K - 1),
+          "conv state must be contiguous [slots, C, K-1] of the activation dtype")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
+        _i32(t, n)
+    out = torch.empty((tokens, C), dtype=x.dtype, device=x.device)
+    f = _fn("conv", "lb_causal_conv1d", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                         c_float, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_seqlens),
+             _ptr(start_pos), _ptr(slots), num_requests, max_len, C, K, region_ends[0], region_ends[1],
+             region_scales[0], region_scales[1], region_scales[2], _code(x), _stream()), "causal_conv1d")
+    return out
+
+
+def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
+             state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor,
+             num_requests: int, num_heads: int, head_dim: int, state_dim: int, num_groups: int,
+             dt_scale: float) -> torch.Tensor:
+    """conv: [tokens, nh*P + 2*G*N] contiguous (x | B | C); dt: [tokens, nh] view; state: float32
+    [slots, nh, P, N], updated in place.  Returns y [tokens, nh*P]."""
+    _cuda(conv, dt, A_log, dt_bias, D, state, cu_seqlens, start_pos, slots)
+    tokens, C = conv.shape
+    _need(conv.is_contiguous(), "conv output must be contiguous")
+    _need(dt.shape == (tokens, num_heads) and dt.stride(1) == 1 and dt.dtype == conv.dtype, "dt must be a [tokens, heads] view")
+    for t, n in ((A_log, "A_log"), (dt_bias, "dt_bias"), (D, "D")):
+        _need(t.dtype == torch.float32 and t.shape == (num_heads,) and t.is_contiguous(), f"{n} must be float32 [heads]")
+    _need(state.dtype == torch.float32 and state.is_contiguous()
+          and state.shape[1:] == (num_heads, head_dim, state_dim), "SSM state must be float32 [slots, heads, P, N]")
+    _need(state_dim % 4 == 0 and state_dim <= 256, f"state sizes in steps of 4 up to 256 are built, got {state_dim}")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
+        _i32(t, n)
+    y = torch.empty((tokens, num_heads * head_dim), dtype=conv.dtype, device=conv.device)
+    f = _fn("ssm", "lb_ssm_scan", [c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                   c_void_p])
+    _check(f(_ptr(conv), C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(state), _ptr(y),
+             _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), num_requests, num_heads, head_dim, state_dim,
+             num_groups, dt_scale, _code(conv), _stream()), "ssm_scan")
+    return y
+
+
+# --------------------------------------------------------------------------- matrix products
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+    _cuda(a, w, bias)
+    _need(a.dtype == w.dtype == torch.float32, "gemm_f32 takes float32 operands")
+    _need(a.dim() == 2 and a.stride(1) == 1 and w.dim() == 2 and w.is_contiguous() and a.shape[1] == w.shape[1],
+          "gemm_f32 wants a [M, K] (row-strided) and w [N, K]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.shape == (w.shape[0],)), "bias must be float32 [N]")
+    M, K = a.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    f = _fn("gemm_f32", "lb_gemm_f32", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int,
+                                        c_float, c_void_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), _ptr(bias), _ptr(out), N, M, N, K, out_scale, _stream()), "gemm_f32")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """x [M, K] @ w[N, K]^T (+ bias), in x's dtype.
+
+    float32 activations: the engine's own 32-bit kernel.  bfloat16 activations with bfloat16
+    weights: cuBLAS through torch (32-bit accumulation).  bfloat16 activations with a weight that
+    is stored in 32-bit: the 32-bit kernel on widened activations, result rounded once."""
+    _cuda(x, w, bias)
+    if x.dtype == torch.float32:
+        return gemm_f32(x, w.float(), None if bias is None else bias.float())
+    if w.dtype == torch.float32:
+        return gemm_f32(x.float(), w, None if bias is None else bias.float()).to(x.dtype)
+    return F.linear(x, w, None if bias is None else bias.to(x.dtype))

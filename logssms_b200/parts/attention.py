@@ -1,0 +1,68 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import torch
+
+from ..cache import CacheNeeds, KVNeed
+from ..ops import kernels as K
+from ..registry import MIXERS, POSITION_ENCODINGS
+from .base import MATRIX, ParamSpec, Part
+from .rope import NoPositionEncoding
+
+
+@MIXERS.register("attention")
+class Attention(Part):
+    """q/k/v projection -> key multiplier + rotation + store into the page cache (one kernel) ->
+    causal attention over the cache -> output projection.
+
+    Checkpoint tensors `q_proj / k_proj / v_proj .weight` are concatenated (rows q | k | v) at
+    bind time, as the reference merges them at load (python/logssms/models/weight.py:27-31);
+    the flow is python/logssms/layers/attention.py:115-167."""
+    kernels = ("rope", "attention")
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        s = spec
+        self.q_size, self.kv_size = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        self.scale = s.softmax_scale if s.softmax_scale is not None else s.head_dim ** -0.5
+        if s.position is None:
+            self.position = NoPositionEncoding()
+        else:
+            key = ("position", s.position)
+            if shared is not None and key in shared:
+                self.position = shared[key]
+            else:
+                self.position = POSITION_ENCODINGS.get(s.position.kind)(s.position)
+                if shared is not None:
+                    shared[key] = self.position
+        self.qkv_weight = self.o_weight = None
+
+    def param_specs(self):
+        s = self.spec
+        return {
+            "q_proj.weight": ParamSpec((self.q_size, s.hidden_size), MATRIX),
+            "k_proj.weight": ParamSpec((self.kv_size, s.hidden_size), MATRIX),
+            "v_proj.weight": ParamSpec((self.kv_size, s.hidden_size), MATRIX),
+            "o_proj.weight": ParamSpec((s.hidden_size, self.q_size), MATRIX),
+        }
+
+    def bind(self, t):
+        self.qkv_weight = torch.cat([t["q_proj.weight"], t["k_proj.weight"], t["v_proj.weight"]], 0).contiguous()
+        self.o_weight = t["o_proj.weight"]
+
+    def setup(self, rt) -> None:
+        self.position.setup(rt)
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(kv=KVNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window))
+
+    def forward(self, x: torch.Tensor, ctx, cache_layer: int, writes_cache: bool = True) -> torch.Tensor:
+        s = self.spec
+        T = x.shape[0]
+        qkv = K.linear(x, self.qkv_weight)
+        k_cache, v_cache, group = ctx.cache.kv(cache_layer)
+        q = K.rope_kv_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions, ctx.slot_mappings[group],
+                            self.position.table, k_cache, v_cache, s.key_scale, writes_cache)
+        o = K.paged_attention(q, k_cache, v_cache, ctx.block_tables[group], ctx.token_req, ctx.positions,
+                              self.scale, s.window or 0)
+        return K.linear(o.view(T, self.q_size), self.o_weight)

@@ -1,0 +1,70 @@
+"""How a layer's parts are arranged."""
+from __future__ import annotations
+
+import torch
+
+from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+from .base import Part
+
+
+@BLOCKS.register("prenorm_parallel")
+class PreNormParallelBlock(Part):
+    """norm -> one or two mixers side by side on the same normed input (each with its own input
+    scale) -> their scaled sum joins the residual inside the next norm -> feed-forward.  The
+    feed-forward's output joins the residual inside the NEXT block's first norm (or the final
+    norm), so a block returns (x, residual) with x not yet added.
+
+    With two mixers this is Falcon-H1's layer (python/logssms/models/falcon_h1.py:152-185);
+    with one mixer and unit scales it is the plain sequential pre-norm decoder layer."""
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        if not 1 <= len(spec.mixers) <= 2:
+            raise ValueError("prenorm_parallel blocks take one or two mixers")
+        self.spec = spec
+        self.mixers = [MIXERS.get(m.spec.kind)(m.spec, perturb_init=perturb_init, shared=shared) for m in spec.mixers]
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, perturb_init)
+        self.ff_norm = NORMS.get(spec.feed_forward_norm.kind)(spec.feed_forward_norm, perturb_init)
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, perturb_init=perturb_init,
+                                                                      shared=shared)
+
+    def children(self):
+        s = self.spec
+        kids = {s.mixer_norm_name: self.mixer_norm, s.feed_forward_norm_name: self.ff_norm,
+                s.feed_forward_name: self.feed_forward}
+        for slot, mixer in zip(s.mixers, self.mixers):
+            kids[slot.name] = mixer
+        return kids
+
+    def cache_needs(self):
+        """Needs of all mixers of this block, merged into one cache layer."""
+        from ..cache import CacheNeeds
+        kv, states = None, []
+        for mixer in self.mixers:
+            need = mixer.cache_needs()
+            if need.kv is not None:
+                if kv is not None:
+                    raise ValueError("a block holds at most one mixer with a key/value cache")
+                kv = need.kv
+            states.extend(need.states)
+        names = [s.name for s in states]
+        if len(set(names)) != len(names):
+            raise ValueError(f"state names clash inside one block: {names}")
+        return CacheNeeds(kv=kv, states=tuple(states))
+
+    def setup(self, rt) -> None:
+        for part in (*self.mixers, self.feed_forward):
+            part.setup(rt)
+
+    def forward(self, x: torch.Tensor, residual, ctx, cache_layer: int, writes_cache: bool = True):
+        slots = self.spec.mixers
+        ins, residual = self.mixer_norm.forward(x, residual, out_scales=tuple(m.in_scale for m in slots))
+        outs = [mixer.forward(inp, ctx, cache_layer, writes_cache) for mixer, inp in zip(self.mixers, ins)]
+        if len(outs) == 2:
+            (h,), residual = self.ff_norm.forward(outs[0], residual, other=outs[1],
+                                                  in_scales=(slots[0].out_scale, slots[1].out_scale))
+        else:
+            if slots[0].out_scale != 1.0:
+                from ..ops import kernels as K
+                outs[0] = K.scale(outs[0], slots[0].out_scale)
+            (h,), residual = self.ff_norm.forward(outs[0], residual)
+        return self.feed_forward.forward(h), residual

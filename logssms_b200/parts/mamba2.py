@@ -1,0 +1,105 @@
+"""Mamba2 (SSD) mixer: in_proj -> causal conv -> selective scan -> gate / gated norm -> out_proj."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache import CacheNeeds, StateNeed
+from ..ops import kernels as K
+from ..registry import MIXERS
+from .base import MATRIX, VECTOR, ParamSpec, Part, normal_init, ones_init
+
+
+def _a_log_init(gen, shape):
+    return torch.log(1.0 + 15.0 * torch.rand(shape, generator=gen, dtype=torch.float32))          # log U[1, 16]
+
+
+def _dt_bias_init(gen, shape):
+    lo, hi = math.log(1e-3), math.log(1e-1)
+    dt = torch.exp(lo + (hi - lo) * torch.rand(shape, generator=gen, dtype=torch.float32))        # log-uniform step
+    return dt + torch.log(-torch.expm1(-dt))                                                       # softplus^-1(dt)
+
+
+@MIXERS.register("mamba2")
+class Mamba2(Part):
+    """Per-request state: the conv window (last K-1 scaled inputs per channel, activation dtype) and
+    the SSM state [heads, P, N] in float32 (the reference keeps it in the activation dtype,
+    python/logssms/cache/radix/state_pool.py:25-32).
+
+    Flow and constants: python/logssms/layers/mamba2.py:70-149; kernels' formulas:
+    python/logssms/kernel/linear_attention/packed_conv.py:96-140,
+    python/logssms/kernel/linear_attention/mamba2.py:27-36 and :261-292,
+    python/logssms/kernel/norm.py:55-86."""
+    kernels = ("conv", "ssm", "norm")
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        self._perturb = perturb_init
+        self.in_w = self.in_b = self.conv_w = self.conv_b = None
+        self.A_log = self.dt_bias = self.D = self.norm_w = self.out_w = self.out_b = None
+
+    def param_specs(self):
+        s = self.spec
+        jitter = 0.1 if self._perturb else 0.0
+        bias_init = normal_init(0.02 if self._perturb else 0.0)
+        specs = {
+            "in_proj.weight": ParamSpec((s.proj_size, s.hidden_size), MATRIX),
+            "conv1d.weight": ParamSpec((s.conv_dim, 1, s.conv_kernel), VECTOR, normal_init(0.2)),
+            "A_log": ParamSpec((s.num_heads,), VECTOR, _a_log_init, torch.float32),
+            "dt_bias": ParamSpec((s.num_heads,), VECTOR, _dt_bias_init),
+            "D": ParamSpec((s.num_heads,), VECTOR, ones_init(jitter)),
+            "out_proj.weight": ParamSpec((s.hidden_size, s.inner_size), MATRIX),
+        }
+        if s.proj_bias:
+            specs["in_proj.bias"] = ParamSpec((s.proj_size,), VECTOR, bias_init)
+        if s.conv_bias:
+            specs["conv1d.bias"] = ParamSpec((s.conv_dim,), VECTOR, bias_init)
+        if s.gated_norm:
+            specs["norm.weight"] = ParamSpec((s.inner_size,), VECTOR, ones_init(jitter))
+        if s.out_bias:
+            specs["out_proj.bias"] = ParamSpec((s.hidden_size,), VECTOR, bias_init)
+        return specs
+
+    def bind(self, t):
+        s = self.spec
+        self.in_w, self.out_w = t["in_proj.weight"], t["out_proj.weight"]
+        act = self.in_w.dtype
+        self.in_b = t.get("in_proj.bias")
+        self.out_b = t.get("out_proj.bias")
+        if act != torch.float32:
+            self.in_b = None if self.in_b is None else self.in_b.to(act)
+            self.out_b = None if self.out_b is None else self.out_b.to(act)
+        self.conv_w = t["conv1d.weight"].reshape(s.conv_dim, s.conv_kernel).contiguous()
+        self.conv_b = t.get("conv1d.bias")
+        self.A_log, self.dt_bias, self.D = t["A_log"], t["dt_bias"], t["D"]
+        self.norm_w = t.get("norm.weight")
+
+    def setup(self, rt) -> None:
+        pass
+
+    def cache_needs(self) -> CacheNeeds:
+        s = self.spec
+        return CacheNeeds(states=(
+            StateNeed("conv", (s.conv_dim, s.conv_kernel - 1), None),
+            StateNeed("ssm", (s.num_heads, s.head_dim, s.state_dim), torch.float32),
+        ))
+
+    def forward(self, x: torch.Tensor, ctx, cache_layer: int, writes_cache: bool = True) -> torch.Tensor:
+        s = self.spec
+        m = s.multipliers
+        inner, C = s.inner_size, s.conv_dim
+        proj = K.linear(x, self.in_w, self.in_b)
+        z, xbc, dt = proj[:, :inner], proj[:, inner:inner + C], proj[:, inner + C:]
+        states = ctx.cache.states[cache_layer]
+        conv = K.causal_conv1d(xbc, self.conv_w, self.conv_b, states["conv"], ctx.cu_seqlens, ctx.start_pos,
+                               ctx.slots, ctx.num_requests, ctx.max_len,
+                               (inner, inner + s.num_groups * s.state_dim), (m[1], m[2], m[3]))
+        y = K.ssm_scan(conv, dt, self.A_log, self.dt_bias, self.D, states["ssm"], ctx.cu_seqlens, ctx.start_pos,
+                       ctx.slots, ctx.num_requests, s.num_heads, s.head_dim, s.state_dim, s.num_groups, m[4])
+        if s.gated_norm:
+            mode = K.NORM_BEFORE_GATE if s.norm_before_gate else K.NORM_AFTER_GATE
+            y = K.gated_rmsnorm(y, z, self.norm_w, s.norm_eps, s.num_groups, m[0], mode)
+        else:
+            y = K.gated_rmsnorm(y, z, None, s.norm_eps, 1, m[0], K.GATE_ONLY)
+        return K.linear(y, self.out_w, self.out_b)

@@ -1,0 +1,40 @@
+"""Gated (SwiGLU) feed-forward."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels as K
+from ..registry import FEED_FORWARDS
+from .base import MATRIX, ParamSpec, Part
+
+
+@FEED_FORWARDS.register("gated_mlp")
+class GatedMLP(Part):
+    """down(silu(gate * s0) * up) * s1.  `gate_proj` and `up_proj` are concatenated at bind time
+    (python/logssms/models/weight.py:32-33); flow python/logssms/layers/mlp.py:50-61."""
+    kernels = ("norm",)
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        self.gate_up = self.down = None
+
+    def param_specs(self):
+        s = self.spec
+        return {
+            "gate_proj.weight": ParamSpec((s.intermediate_size, s.hidden_size), MATRIX),
+            "up_proj.weight": ParamSpec((s.intermediate_size, s.hidden_size), MATRIX),
+            "down_proj.weight": ParamSpec((s.hidden_size, s.intermediate_size), MATRIX),
+        }
+
+    def bind(self, t):
+        self.gate_up = torch.cat([t["gate_proj.weight"], t["up_proj.weight"]], 0).contiguous()
+        self.down = t["down_proj.weight"]
+
+    def setup(self, rt) -> None:
+        pass
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        s = self.spec
+        h = K.swiglu(K.linear(x, self.gate_up), s.activation_scale)
+        out = K.linear(h, self.down)
+        return out if s.output_scale == 1.0 else K.scale(out, s.output_scale)

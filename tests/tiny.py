@@ -1,0 +1,81 @@
+"""Two tiny Falcon-H1 configurations that differ in every size and option, and helpers that
+write a random model folder for them and ask the plain implementation for its logits."""
+from __future__ import annotations
+
+import copy
+import os
+
+import torch
+
+from logssms_b200.config import make_model_config
+from logssms_b200.weights import read_checkpoint, write_random_model
+
+from plain.falcon_h1_plain import falcon_h1_logits
+
+TINY_A = {
+    "architectures": ["FalconH1ForCausalLM"], "model_type": "falcon_h1",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 128, "vocab_size": 256, "rms_norm_eps": 1e-5,
+    "max_position_embeddings": 2048, "rope_theta": 1e4, "tie_word_embeddings": True,
+    "mamba_d_ssm": 64, "mamba_n_heads": 4, "mamba_d_head": 16, "mamba_d_state": 16, "mamba_n_groups": 1,
+    "mamba_d_conv": 4, "mamba_chunk_size": 8, "mamba_conv_bias": False, "mamba_proj_bias": False,
+    "projectors_bias": False, "mamba_rms_norm": False, "mamba_norm_before_gate": False,
+    "embedding_multiplier": 1.0, "lm_head_multiplier": 1.0, "attention_in_multiplier": 1.0,
+    "attention_out_multiplier": 1.0, "key_multiplier": 1.0, "ssm_in_multiplier": 1.0, "ssm_out_multiplier": 1.0,
+    "ssm_multipliers": [1.0, 1.0, 1.0, 1.0, 1.0], "mlp_multipliers": [1.0, 1.0],
+    "hidden_act": "silu", "attention_bias": False, "mlp_bias": False,
+}
+
+TINY_B = {
+    "architectures": ["FalconH1ForCausalLM"], "model_type": "falcon_h1",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 3, "num_key_value_heads": 1,
+    "head_dim": 32, "intermediate_size": 200, "vocab_size": 517, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 4096, "rope_theta": 1e11, "tie_word_embeddings": False,
+    "mamba_d_ssm": 144, "mamba_n_heads": 6, "mamba_d_head": 24, "mamba_d_state": 32, "mamba_n_groups": 2,
+    "mamba_d_conv": 3, "mamba_chunk_size": 16, "mamba_conv_bias": True, "mamba_proj_bias": True,
+    "projectors_bias": True, "mamba_rms_norm": True, "mamba_norm_before_gate": True,
+    "embedding_multiplier": 5.0, "lm_head_multiplier": 0.25, "attention_in_multiplier": 1.5,
+    "attention_out_multiplier": 0.8, "key_multiplier": 0.5, "ssm_in_multiplier": 1.2, "ssm_out_multiplier": 0.7,
+    "ssm_multipliers": [0.6, 1.1, 0.9, 1.3, 0.8], "mlp_multipliers": [0.9, 1.1],
+    "hidden_act": "silu", "attention_bias": False, "mlp_bias": False,
+}
+
+# a third shape: gated norm applied AFTER the gate, partial rotation, llama3 frequency scaling
+TINY_C = {
+    **copy.deepcopy(TINY_B),
+    "num_hidden_layers": 2, "mamba_norm_before_gate": False, "partial_rotary_factor": 0.5,
+    "rope_theta": 1e5,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "num_attention_heads": 4, "num_key_value_heads": 4, "head_dim": 48, "vocab_size": 300,
+}
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def make_model_dir(path: str, raw: dict, seed: int = 0, dtype=torch.float32, perturb: bool = True) -> str:
+    """Write config.json + model.safetensors with seeded random weights into `path`."""
+    return write_random_model(make_model_config(raw), str(path), seed=seed, dtype=dtype, perturb=perturb)
+
+
+def plain_logits(model_dir: str, ids, dtype: str) -> torch.Tensor:
+    """Logits of every position of `ids` from the plain implementation.  For the float32 engine the
+    oracle computes in float64; for the bfloat16 engine in float32 with the bfloat16 rounding points."""
+    import json
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    tensors = read_checkpoint(model_dir)
+    if dtype == "float32":
+        return falcon_h1_logits(cfg, tensors, ids, compute=torch.float64).float()
+    return falcon_h1_logits(cfg, tensors, ids, compute=torch.float32, act=torch.bfloat16).float()
+
+
+# tolerances, set once: largest error anywhere, relative to the largest reference logit of the comparison
+TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    got, want = got.double().cpu(), want.double().cpu()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert torch.isfinite(got).all(), "engine produced non-finite logits"
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
