@@ -187,6 +187,10 @@ class CacheManager:
             want = g.pages_for(new_length)
             have = int(g.num_pages_of[rc.row])
             if want > have:
+                beyond_reservation = (want - have) - rc.reserved.get(gi, 0)
+                if beyond_reservation > self.available_pages(gi):      # never eat what others were promised
+                    raise OutOfPages(f"group {gi}: request row {rc.row} needs {want - have} more pages, "
+                                     f"{self.available_pages(gi)} are free and unpromised")
                 pages = g.pool.alloc(want - have)
                 g.block_table[rc.row, have:want] = pages
                 g.num_pages_of[rc.row] = want

@@ -1,0 +1,185 @@
+"""The scheduler above the step function: admit, cut prompts into portions, decode, finish, free.
+
+Rules (the reference's, python/logssms/scheduler/prefill.py:94-152 and :294-324,
+python/logssms/scheduler/scheduler.py:194-205, python/logssms/scheduler/ar.py:114-117,
+with its "mixed" policy as the only one):
+
+  * Admission is first-come-first-served and stops at the first request that does not fit; nobody
+    overtakes.  A request fits when a request row is free and every page group can set aside the
+    pages of its whole life (prompt + max_tokens).  Pages are reserved at admission, so a running
+    request can never run out of pages; there is no preemption and no swapping.
+  * What happens when pages run out: waiting requests wait until finished requests give pages
+    back.  A request that could not fit even into an empty pool, or whose prompt does not leave room
+    for one new token within max_seq_len, is finished at once with reason "rejected".
+    `max_tokens` is clamped so that prompt + max_tokens <= max_seq_len.
+  * Every step takes one token from each decoding request, then fills what is left of the token
+    budget (`max_step_tokens`) with prompt portions, oldest request first; a prompt that does not
+    fit is cut at the budget, anywhere, and goes on in the next step.
+  * A request ends after `max_tokens` new tokens or at an end-of-sequence token (unless
+    `ignore_eos`); its row, pages and state slot go back at once.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Iterable, Sequence
+
+import torch
+
+from ..sampling import Sampler, SamplingParams
+from .step import StepEntry
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass(eq=False)
+class Request:
+    number: int
+    prompt: list[int]
+    params: SamplingParams
+    max_tokens: int                      # after clamping
+    state: str = WAITING
+    cache: object | None = None          # RequestCache while running
+    computed: int = 0                    # tokens (prompt and generated) that have gone through the model
+    output: list[int] = field(default_factory=list)
+    finish_reason: str | None = None
+    seed: int = 0
+
+    @property
+    def prompt_done(self) -> bool:
+        return self.computed >= len(self.prompt)
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + self.max_tokens
+
+
+@dataclass
+class StepDecision:
+    """What one step runs: (request, first token index, number of tokens, sample afterwards?)."""
+    decodes: list[Request]
+    portions: list[tuple[Request, int, int, bool]]
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.decodes) + sum(n for _, _, n, _ in self.portions)
+
+
+class Scheduler:
+    def __init__(self, engine, *, max_step_tokens: int = 8192, sampler=None, eos_token_ids: Iterable[int] = ()):
+        if max_step_tokens < 1:
+            raise ValueError("max_step_tokens must be at least 1")
+        self.engine = engine
+        self.cache = engine.cache
+        self.max_step_tokens = max_step_tokens
+        self.sampler = sampler if sampler is not None else Sampler(engine.device)
+        self.eos = frozenset(eos_token_ids)
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.finished: list[Request] = []
+        self._count = 0
+        self.steps = 0
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, prompt: Sequence[int], params: SamplingParams | None = None) -> Request:
+        params = params or SamplingParams()
+        prompt = [int(t) for t in prompt]
+        max_seq = self.cache.max_seq_len
+        req = Request(self._count, prompt, params, max(0, min(params.max_tokens, max_seq - len(prompt))))
+        req.seed = self.sampler.seed_for(params, req.number) if hasattr(self.sampler, "seed_for") else 0
+        self._count += 1
+        if not prompt:
+            return self._finish(req, "rejected: empty prompt")
+        if len(prompt) >= max_seq:
+            return self._finish(req, f"rejected: prompt of {len(prompt)} tokens leaves no room within max_seq_len {max_seq}")
+        if req.max_tokens == 0:
+            return self._finish(req, "length")
+        if not self.cache.fits_at_all(req.total_len):
+            return self._finish(req, f"rejected: {req.total_len} tokens can never fit the page pool")
+        self.waiting.append(req)
+        return req
+
+    # ------------------------------------------------------------------ one step
+    def schedule(self) -> StepDecision:
+        decodes = [r for r in self.running if r.prompt_done]
+        budget = self.max_step_tokens - len(decodes)
+        portions: list[tuple[Request, int, int, bool]] = []
+
+        def give_portion(r: Request) -> None:
+            nonlocal budget
+            left = len(r.prompt) - r.computed
+            n = min(left, budget)
+            if n > 0:
+                portions.append((r, r.computed, n, n == left))
+                budget -= n
+
+        for r in self.running:                       # prompts already under way, oldest first
+            if not r.prompt_done and budget > 0:
+                give_portion(r)
+        while self.waiting and budget > 0:           # then newcomers, in arrival order, no overtaking
+            r = self.waiting[0]
+            if not self.cache.can_admit(r.total_len):
+                break
+            self.waiting.popleft()
+            r.cache = self.cache.admit(r.total_len)
+            r.state = RUNNING
+            self.running.append(r)
+            give_portion(r)
+        return StepDecision(decodes, portions)
+
+    def step(self) -> list[Request]:
+        """Run one step; return the requests that finished in it."""
+        decision = self.schedule()
+        if decision.num_tokens == 0:
+            if self.waiting and not self.running:
+                raise RuntimeError("scheduler is stuck: requests wait but nothing runs and nothing fits")
+            return []
+        entries, sampled = [], []
+        for r in decision.decodes:
+            entries.append(StepEntry(r.cache, [r.output[-1]], [0]))
+            sampled.append(r)
+        for r, first, n, last in decision.portions:
+            entries.append(StepEntry(r.cache, r.prompt[first:first + n], [n - 1] if last else []))
+            if last:
+                sampled.append(r)
+        logits = self.engine.step(entries)
+        self.steps += 1
+        for r in decision.decodes:
+            r.computed += 1
+        for r, _, n, _ in decision.portions:
+            r.computed += n
+        done: list[Request] = []
+        if sampled:
+            tokens = self.sampler.sample(logits, [r.params for r in sampled], [r.seed for r in sampled],
+                                         [len(r.output) for r in sampled])
+            for r, tok in zip(sampled, tokens.tolist()):
+                r.output.append(int(tok))
+                if int(tok) in self.eos and not r.params.ignore_eos:
+                    done.append(self._finish(r, "stop"))
+                elif len(r.output) >= r.max_tokens:
+                    done.append(self._finish(r, "length"))
+        return done
+
+    def abort(self, req: Request) -> None:
+        if req.state == WAITING:
+            self.waiting.remove(req)
+        if req.state != FINISHED:
+            self._finish(req, "abort")
+
+    def _finish(self, req: Request, reason: str) -> Request:
+        if req.cache is not None:
+            self.cache.release(req.cache)
+            req.cache = None
+        if req in self.running:
+            self.running.remove(req)
+        req.state, req.finish_reason = FINISHED, reason
+        self.finished.append(req)
+        return req
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def run(self) -> None:
+        while self.has_work:
+            self.step()

@@ -1,0 +1,161 @@
+"""The cache manager on the CPU: no page lost, held twice or freed twice, under random orders."""
+import random
+
+import pytest
+import torch
+
+from logssms_b200.cache import CacheManager, CacheNeeds, FreeList, KVNeed, OutOfPages, StateNeed
+
+FULL = KVNeed(2, 16)
+WINDOW = KVNeed(2, 16, window=40)
+
+
+def manager(needs, pages=12, page=16, max_requests=4, max_seq=256, **kw):
+    return CacheManager(needs, page_size=page, num_pages=pages, max_requests=max_requests, max_seq_len=max_seq,
+                        dtype=torch.float32, device="cpu", **kw)
+
+
+def test_free_list_refuses_misuse():
+    fl = FreeList(3)
+    a = fl.alloc(2)
+    with pytest.raises(OutOfPages):
+        fl.alloc(2)
+    fl.free(a[:1])
+    with pytest.raises(ValueError, match="twice"):
+        fl.free(a[:1])
+    with pytest.raises(ValueError, match="does not exist"):
+        fl.free([7])
+    fl.check()
+    assert fl.num_free == 2 and fl.num_held == 1
+
+
+def test_groups_are_formed_by_need():
+    needs = [CacheNeeds(kv=FULL), CacheNeeds(kv=WINDOW), CacheNeeds(kv=FULL, states=(StateNeed("s", (3, 2)),)),
+             CacheNeeds(states=(StateNeed("only", (5,), torch.float32),))]
+    m = manager(needs)
+    assert len(m.groups) == 2
+    assert m.groups[0].layers == [0, 2] and m.groups[1].layers == [1]
+    assert m.groups[0].storage.shape == (2, 2, 12, 16, 2, 16)
+    assert m.states[2]["s"].shape == (4, 3, 2) and m.states[3]["only"].dtype == torch.float32
+    k, v, gi = m.kv(2)
+    assert gi == 0 and k.shape == (12, 16, 2, 16)
+
+
+def test_pages_follow_length_and_return_at_release():
+    m = manager([CacheNeeds(kv=FULL)])
+    a = m.admit()
+    m.extend(a, 17)
+    assert m.groups[0].pool.num_held == 2
+    m.extend(a, 32)
+    assert m.groups[0].pool.num_held == 2
+    m.extend(a, 33)
+    assert m.groups[0].pool.num_held == 3
+    assert m.slot_of(0, a, 20) == int(m.groups[0].block_table[a.row, 1]) * 16 + 4
+    m.check_integrity()
+    m.release(a)
+    assert m.groups[0].pool.num_held == 0 and m.rows.num_free == 4
+    with pytest.raises(ValueError, match="twice"):
+        m.release(a)
+    m.check_integrity()
+
+
+def test_window_group_gives_pages_back_as_the_window_passes():
+    m = manager([CacheNeeds(kv=FULL), CacheNeeds(kv=WINDOW)], pages=16)
+    a = m.admit()
+    m.extend(a, 100)                              # one step of 100 tokens: nothing behind it yet
+    full, win = m.groups
+    assert full.pool.num_held == 7 and win.pool.num_held == 7
+    m.extend(a, 101)                              # next token at position 100 sees keys >= 61: pages 0..2 go
+    assert win.pool.num_held == 7 - 3 and full.pool.num_held == 7
+    assert (win.block_table[a.row, :3] == -1).all() and win.block_table[a.row, 3] >= 0
+    m.check_integrity()
+    for n in range(102, 200):
+        m.extend(a, n)
+        m.check_integrity()
+        assert win.pool.num_held <= 4             # window 40 + one token spans at most 4 pages of 16
+    m.release(a)
+    m.check_integrity()
+    assert win.pool.num_held == 0 and full.pool.num_held == 0
+
+
+def test_reservation_blocks_admission_not_running_requests():
+    m = manager([CacheNeeds(kv=FULL)], pages=10)
+    a = m.admit(reserve_tokens=100)               # 7 pages set aside
+    assert not m.can_admit(80) and m.can_admit(48)
+    b = m.admit(reserve_tokens=48)                # 3 pages
+    assert not m.can_admit(1)
+    with pytest.raises(OutOfPages):
+        m.admit(1)
+    m.extend(a, 100)
+    m.extend(b, 48)                               # both can always grow to what they reserved
+    m.check_integrity()
+    m.release(a)
+    assert m.can_admit(100)
+    m.release(b)
+    m.check_integrity()
+    assert not m.fits_at_all(10 * 16 + 1) and m.fits_at_all(160)
+
+
+def test_unreserved_growth_fails_loudly_when_the_pool_is_dry():
+    m = manager([CacheNeeds(kv=FULL)], pages=3)
+    a, b = m.admit(), m.admit()
+    m.extend(a, 32)
+    m.extend(b, 16)
+    with pytest.raises(OutOfPages):
+        m.extend(b, 17)
+    with pytest.raises(OutOfPages):
+        m.extend(a, 10_000)
+    with pytest.raises(ValueError, match="shrinks"):
+        m.extend(a, 5)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_of_requests_keep_every_page_accounted(seed):
+    rng = random.Random(seed)
+    m = manager([CacheNeeds(kv=FULL), CacheNeeds(kv=WINDOW, states=(StateNeed("s", (2,)),))], pages=20,
+                max_requests=5, max_seq=200)
+    live = []
+    for _ in range(400):
+        action = rng.random()
+        if action < 0.25 and m.rows.num_free:
+            reserve = rng.choice([0, 0, rng.randrange(1, 120)])
+            if m.can_admit(reserve):
+                live.append([m.admit(reserve), reserve])
+        elif action < 0.85 and live:
+            rc, reserve = rng.choice(live)
+            limit = reserve if reserve else 200
+            new_len = min(limit, rc.length + rng.choice([1, 1, 1, 2, 7, 30]))
+            try:
+                m.extend(rc, new_len)
+            except OutOfPages:
+                assert reserve == 0                # a reserved request never runs dry
+        elif live:
+            rc, _ = live.pop(rng.randrange(len(live)))
+            m.release(rc)
+        m.check_integrity()
+        for g in m.groups:
+            held = sum(int(g.num_pages_of[rc.row] - g.first_page[rc.row]) for rc, _ in live)
+            assert held == g.pool.num_held
+    for rc, _ in live:
+        m.release(rc)
+    m.check_integrity()
+    assert all(g.pool.num_free == 20 for g in m.groups) and m.rows.num_free == 5
+
+
+def test_integrity_check_sees_a_corrupted_table():
+    m = manager([CacheNeeds(kv=FULL)])
+    a, b = m.admit(), m.admit()
+    m.extend(a, 20)
+    m.extend(b, 20)
+    m.groups[0].block_table[b.row, 0] = m.groups[0].block_table[a.row, 0]
+    with pytest.raises(AssertionError):
+        m.check_integrity()
+
+
+def test_poison_marks_freed_memory():
+    m = manager([CacheNeeds(kv=FULL, states=(StateNeed("s", (2,)),))], poison_on_free=True)
+    a = m.admit()
+    m.extend(a, 5)
+    page = int(m.groups[0].block_table[a.row, 0])
+    m.release(a)
+    assert torch.isnan(m.groups[0].storage[:, :, page]).all() and torch.isnan(m.states[0]["s"][a.row]).all()
