@@ -45,6 +45,25 @@ class LLM:
         self.scheduler = Scheduler(self.engine, max_step_tokens=max_prefill_tokens, sampler=self.sampler,
                                    eos_token_ids=eos_token_ids)
 
+    # ------------------------------------------------------------------ step-wise use
+    def add_request(self, prompt_ids: Sequence[int], sampling_params: SamplingParams | None = None):
+        """Queue one prompt (token ids); returns the scheduler's `Request`, whose `output` grows as
+        `step()` is called."""
+        return self.scheduler.add_request(prompt_ids, sampling_params)
+
+    def step(self, device_loop: bool = True):
+        """Run one scheduled step (prompt portions and one token of every decoding request); returns
+        the requests that finished in it."""
+        return self.scheduler.step()
+
+    def abort(self, request) -> None:
+        self.scheduler.abort(request)
+
+    @property
+    def d2h_bytes(self) -> int:
+        """Bytes of sampled token ids read back to the host so far."""
+        return self.scheduler.d2h_bytes
+
     def generate(self, prompts, sampling_params: SamplingParams | Sequence[SamplingParams] | None = None) -> list[Output]:
         """`prompts`: a list of token-id lists, or of strings when the model folder has a tokenizer.
         Returns one `Output` per prompt, in order."""

@@ -79,6 +79,7 @@ class Scheduler:
         self.finished: list[Request] = []
         self._count = 0
         self.steps = 0
+        self.d2h_bytes = 0
 
     # ------------------------------------------------------------------ intake
     def add_request(self, prompt: Sequence[int], params: SamplingParams | None = None) -> Request:
@@ -152,6 +153,7 @@ class Scheduler:
         if sampled:
             tokens = self.sampler.sample(logits, [r.params for r in sampled], [r.seed for r in sampled],
                                          [len(r.output) for r in sampled])
+            self.d2h_bytes += tokens.numel() * tokens.element_size()
             for r, tok in zip(sampled, tokens.tolist()):
                 r.output.append(int(tok))
                 if int(tok) in self.eos and not r.params.ignore_eos:

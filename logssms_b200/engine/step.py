@@ -94,6 +94,7 @@ class Engine:
         self._ring = _PinnedRing()
         self._staging: torch.Tensor | None = None
         self.steps_run = 0
+        self.h2d_bytes = 0          # bytes of step tables copied host -> device so far
 
     def _pages_that_fit(self, needs, max_requests: int, memory_ratio: float) -> int:
         """Pages for `memory_ratio` of the device after weights and state slots, capped at what
@@ -193,6 +194,7 @@ class Engine:
             half = total
         dev = self._staging[self._staging_half * half: self._staging_half * half + total]
         dev.copy_(pinned[:total], non_blocking=True)
+        self.h2d_bytes += total * 4
         self._ring.mark(slot)
 
         def view(i, shape=None):

@@ -24,6 +24,7 @@ _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _ERRORS = {-1: "dtype is neither float32 nor bfloat16", -2: "a size the kernel does not take",
            -3: "a size beyond the kernel's limit"}
 _fn_cache: dict[tuple[str, str], ctypes._CFuncPtr] = {}
+launch_count = 0        # kernels of this package launched so far (a launcher adds what it launches)
 
 
 class KernelError(RuntimeError):
@@ -41,8 +42,10 @@ def _fn(lib: str, name: str, argtypes):
     return f
 
 
-def _check(code: int, name: str, detail: str = "") -> None:
+def _check(code: int, name: str, detail: str = "", launches: int = 1) -> None:
+    global launch_count
     if code == 0:
+        launch_count += launches
         return
     if code < 0:
         raise KernelError(f"{name} refused the call: {_ERRORS.get(code, code)} {detail}")
@@ -271,7 +274,7 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
                                          c_float, c_int, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_seqlens),
              _ptr(start_pos), _ptr(slots), num_requests, max_len, C, K, region_ends[0], region_ends[1],
-             region_scales[0], region_scales[1], region_scales[2], _code(x), _stream()), "causal_conv1d")
+             region_scales[0], region_scales[1], region_scales[2], _code(x), _stream()), "causal_conv1d", launches=2)
     return out
 
 
