@@ -206,4 +206,5 @@ class Engine:
             num_tokens=T, num_requests=B, max_len=int(lens.max()), token_ids=view(0), positions=view(1),
             token_req=view(2), cu_seqlens=view(3), start_pos=view(4), slots=view(5),
             block_tables=block_tables, slot_mappings=slot_mappings, logit_rows=view(6), cache=self.cache,
+            max_context=int((starts + lens).max()),
         )

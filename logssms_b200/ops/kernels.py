@@ -251,6 +251,63 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return out
 
 
+def attention_splits(num_tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
+    """How many ranges each context is cut into so that the grid covers the SMs a few times over."""
+    G = num_heads // num_kv_heads
+    tile = 8 if G >= 8 else (4 if G > 2 else G)
+    items = max(1, num_tokens * num_kv_heads * (-(-G // tile)))
+    return max(1, min(_SPLIT_TARGET_CTAS // items, -(-max_context // 64), 256))
+
+
+_SPLIT_TARGET_CTAS = 592        # 4 CTAs on each of the 148 SMs
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                     token_req: torch.Tensor, positions: torch.Tensor, scale: float, window: int = 0, *,
+                     splits: int = 1, token_list: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                     scratch: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+    """Split-KV attention, each token on its own over its request's pages (see `paged_attention` for
+    the arguments).  `token_list` (int32) restricts the call to those tokens; the other rows of `out`
+    are left as they are.  `scratch`: float32 buffers (>= tokens*Hq*splits*hd and >= tokens*Hq*splits*2
+    elements) for the ranges' partial results; allocated here when missing."""
+    _cuda(q, k_cache, v_cache, block_table, token_req, positions, token_list)
+    tokens, Hq, hd = q.shape
+    _need(q.is_contiguous(), "q must be contiguous")
+    _need(k_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
+          and k_cache.dtype == q.dtype == v_cache.dtype and k_cache.shape[3] == hd,
+          "caches must be contiguous [pages, page_size, kv_heads, head_dim] of q's dtype")
+    page_size, Hkv = k_cache.shape[1], k_cache.shape[2]
+    _need(hd % 16 == 0 and hd <= 256, f"attention takes head sizes in steps of 16 up to 256, got {hd}")
+    _need(Hq % Hkv == 0, f"query heads ({Hq}) must be a multiple of key/value heads ({Hkv})")
+    _need(block_table.dim() == 2 and block_table.dtype == torch.int32 and block_table.stride(1) == 1,
+          "block table must be a row-major int32 matrix")
+    _i32(token_req, "token_req")
+    _i32(positions, "positions")
+    sel = tokens
+    if token_list is not None:
+        _i32(token_list, "token_list")
+        sel = token_list.numel()
+    if out is None:
+        out = torch.empty_like(q)
+    _need(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+    part_o = part_ml = None
+    if splits > 1:
+        if scratch is None:
+            scratch = (torch.empty(sel * Hq * splits * hd, dtype=torch.float32, device=q.device),
+                       torch.empty(sel * Hq * splits * 2, dtype=torch.float32, device=q.device))
+        part_o, part_ml = scratch
+        _need(part_o.dtype == torch.float32 == part_ml.dtype and part_o.numel() >= sel * Hq * splits * hd
+              and part_ml.numel() >= sel * Hq * splits * 2, "attention scratch is too small or not float32")
+    f = _fn("attention_decode", "lb_attention_decode",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
+             _ptr(token_req), _ptr(positions), _ptr(token_list), sel, Hq, Hkv, hd, page_size, scale, int(window or 0),
+             int(splits), _ptr(part_o), _ptr(part_ml), _code(q), _stream()), "attention_decode",
+           launches=2 if splits > 1 else 1)
+    return out
+
+
 # --------------------------------------------------------------------------- Mamba2
 def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
                   cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int,

@@ -36,4 +36,6 @@ class StepContext:
     slot_mappings: list[torch.Tensor]    # per page group: [T] token index into the group's page pool
     logit_rows: torch.Tensor             # [n] token indices whose logits are wanted
     cache: Any                           # the CacheManager
+    max_context: int = 0                 # most keys any token of this step sees (host)
+    attention_splits: int = 0            # fixed number of key ranges per context (0: chosen per call)
     extras: dict = field(default_factory=dict)

@@ -1,0 +1,402 @@
+"""Every CUDA kernel alone against its plain reference, at sizes other than the tiny models'.
+
+References are the per-part functions of tests/plain (or a few lines of torch where the kernel has
+no counterpart there), computed on the CPU in float64 for the 32-bit kernels and in float32 with
+bfloat16 rounding points for the bfloat16 kernels.
+"""
+import math
+
+import pytest
+import torch
+
+from plain import falcon_h1_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+
+
+def K():
+    from logssms_b200.ops import kernels
+    return kernels
+
+
+def dev(t):
+    return t.cuda()
+
+
+def close(got, want, dtype, scale=None, tol=None):
+    got, want = got.double().cpu(), want.double().cpu()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert torch.isfinite(got).all()
+    denom = want.abs().max().clamp_min(1e-30) if scale is None else scale
+    err = float((got - want).abs().max() / denom)
+    assert err <= (TOL[dtype] if tol is None else tol), f"error {err:.3g}"
+
+
+def rnd_of(dtype):
+    return P._rounder(None if dtype == torch.float32 else dtype)
+
+
+def ref_dtype(dtype):
+    return torch.float64 if dtype == torch.float32 else torch.float32
+
+
+def randn(gen, *shape, dtype=torch.float32, scale=1.0):
+    return (torch.randn(*shape, generator=gen) * scale).to(dtype)
+
+
+# --------------------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather_and_gather_rows(dtype):
+    g = torch.Generator().manual_seed(0)
+    V, H = 301, 200
+    table = randn(g, V, H, dtype=dtype)
+    ids = torch.randint(0, V, (37,), generator=g, dtype=torch.int32)
+    out = K().embed_gather(dev(table), dev(ids), 3.5)
+    want = rnd_of(dtype)(table.to(ref_dtype(dtype))[ids.long()] * 3.5)
+    close(out, want, dtype, tol=1e-7 if dtype == torch.float32 else 1e-6)   # one rounding of the product
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32)
+    picked = K().gather_rows(out, dev(rows))
+    assert torch.equal(picked.cpu(), out.cpu()[rows.long()])
+
+
+# --------------------------------------------------------------------------- norms
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [40, 1000, 3000])
+@pytest.mark.parametrize("two_inputs", [False, True])
+def test_add_rmsnorm(dtype, H, two_inputs):
+    g = torch.Generator().manual_seed(H)
+    rows = 7
+    x, other, res = (randn(g, rows, H, dtype=dtype) for _ in range(3))
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    rd = ref_dtype(dtype)
+    outs, new_res = K().add_rmsnorm(dev(x), dev(w), 1e-5, dev(res.clone()), other=dev(other) if two_inputs else None,
+                                    in_scales=(0.8, 0.7), out_scales=(1.5, 1.2))
+    want_outs, want_res = P.rms_norm_branches(x.to(rd), w.to(rd), 1e-5, res.to(rd), other.to(rd) if two_inputs else None,
+                                              (0.8, 0.7), (1.5, 1.2), rnd_of(dtype))
+    close(new_res, want_res, dtype)
+    for a, b in zip(outs, want_outs):
+        close(a, b, dtype)
+    # first layer: no residual yet, one output
+    (o,), r = K().add_rmsnorm(dev(x), dev(w), 1e-5)
+    (wo,), wr = P.rms_norm_branches(x.to(rd), w.to(rd), 1e-5, rnd=rnd_of(dtype))
+    close(o, wo, dtype)
+    close(r, wr, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("mode", ["gate_only", "before", "after"])
+def test_gated_rmsnorm(dtype, mode):
+    g = torch.Generator().manual_seed(1)
+    rows, groups, width = 5, 3, 120
+    k = K()
+    y = randn(g, rows, groups * width, dtype=dtype)
+    wide = randn(g, rows, groups * width + 50, dtype=dtype)
+    gate = wide[:, 20:20 + groups * width]                       # a column view, as the mixer passes it
+    w = 1 + 0.1 * torch.randn(groups * width, generator=g)
+    rd = ref_dtype(dtype)
+    gate_dev = dev(wide)[:, 20:20 + groups * width]
+    if mode == "gate_only":
+        out = k.gated_rmsnorm(dev(y), gate_dev, None, 1e-6, 1, 0.6, k.GATE_ONLY)
+        want = P.silu_gate(y.to(rd), gate.to(rd), 0.6, rnd_of(dtype))
+    else:
+        out = k.gated_rmsnorm(dev(y), gate_dev, dev(w), 1e-6, groups, 0.6,
+                              k.NORM_BEFORE_GATE if mode == "before" else k.NORM_AFTER_GATE)
+        want = P.gated_group_norm(y.to(rd), gate.to(rd), w.to(rd), 1e-6, groups, mode == "before", 0.6, rnd_of(dtype))
+    close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_and_scale(dtype):
+    g = torch.Generator().manual_seed(2)
+    rows, I = 9, 333
+    gu = randn(g, rows, 2 * I, dtype=dtype)
+    rd, rnd = ref_dtype(dtype), rnd_of(dtype)
+    out = K().swiglu(dev(gu), 0.9)
+    gg, uu = gu.to(rd)[:, :I], gu.to(rd)[:, I:]
+    close(out, rnd(rnd(P.silu(rnd(gg * 0.9))) * uu), dtype)
+    close(K().scale(dev(gu), 1.1), rnd(gu.to(rd) * 1.1), dtype)
+    f32 = K().scale(dev(gu), 0.25, to_f32=True)
+    assert f32.dtype == torch.float32
+    close(f32, gu.to(rd) * 0.25, torch.float32)
+
+
+# --------------------------------------------------------------------------- rotation + cache store
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,rotary", [(16, 16), (48, 24), (80, 80), (128, 64)])
+def test_rope_kv_store(dtype, hd, rotary):
+    g = torch.Generator().manual_seed(hd)
+    k = K()
+    Hq, Hkv, T, page, pages = 6, 3, 11, 16, 5
+    theta = 1e4
+    inv = P.rope_inv_freq(rotary, theta)
+    table = k.rope_table(dev(inv), 200)
+    pos_all = torch.arange(200, dtype=torch.float32)[:, None] * inv[None]
+    close(table, torch.cat([pos_all.cos(), pos_all.sin()], 1), torch.float32, tol=2e-6)
+    qkv = randn(g, T, (Hq + 2 * Hkv) * hd + 8, dtype=dtype)[:, :(Hq + 2 * Hkv) * hd]      # row-strided view
+    positions = torch.randint(0, 200, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(page * pages, generator=g)[:T].to(torch.int32)
+    slots[3] = -1                                                                        # a token without a slot
+    kc = torch.zeros(pages, page, Hkv, hd, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    qkv_dev = dev(torch.cat([qkv, qkv.new_zeros(T, 8)], 1))[:, :(Hq + 2 * Hkv) * hd]
+    kcd, vcd = dev(kc), dev(vc)
+    q_out = k.rope_kv_store(qkv_dev, Hq, Hkv, hd, dev(positions), dev(slots), table, kcd, vcd, 0.5)
+    rd, rnd = ref_dtype(dtype), rnd_of(dtype)
+    q, kk, v = qkv.to(rd).split([Hq * hd, Hkv * hd, Hkv * hd], 1)
+    want_q = P.rope_apply(q.reshape(T, Hq, hd), positions, inv, rotary, rnd)
+    want_k = P.rope_apply(rnd(kk.reshape(T, Hkv, hd) * 0.5), positions, inv, rotary, rnd)
+    close(q_out, want_q, dtype)
+    want_kc, want_vc = kc.to(rd).reshape(-1, Hkv, hd), vc.to(rd).reshape(-1, Hkv, hd)
+    for t in range(T):
+        if slots[t] >= 0:
+            want_kc[slots[t]] = want_k[t]
+            want_vc[slots[t]] = v.reshape(T, Hkv, hd)[t]
+    close(kcd.reshape(-1, Hkv, hd), want_kc, dtype)
+    close(vcd.reshape(-1, Hkv, hd), want_vc, dtype, tol=0 if dtype == torch.float32 else 1e-6)
+
+
+# --------------------------------------------------------------------------- attention over pages
+def paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new_tokens, plant=False):
+    """Requests of `lengths` tokens whose last `new_tokens[r]` tokens are this step's queries, keys and
+    values scattered over shuffled pages.  Returns device inputs and, per query row, (request, position)."""
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    kc = torch.full((total_pages, page, Hkv, hd), float("nan"), dtype=dtype)
+    vc = torch.full_like(kc, float("nan"))
+    max_pages = max(-(-n // page) for n in lengths) + 2
+    bt = torch.full((len(lengths), max_pages), -1, dtype=torch.int32)
+    keys, values, rows = [], [], []
+    for r, n in enumerate(lengths):
+        k = randn(g, n, Hkv, hd, dtype=dtype)
+        v = randn(g, n, Hkv, hd, dtype=dtype)
+        if plant and n > 40:
+            k[3] *= 6.0                                  # one far key that the query below will pick
+        for p in range(-(-n // page)):
+            page_id = perm.pop()
+            bt[r, p] = page_id
+            lo, hi = p * page, min(n, (p + 1) * page)
+            kc[page_id, :hi - lo] = k[lo:hi]
+            vc[page_id, :hi - lo] = v[lo:hi]
+        keys.append(k)
+        values.append(v)
+        rows += [(r, pos) for pos in range(n - new_tokens[r], n)]
+    q = randn(g, len(rows), Hq, hd, dtype=dtype)
+    if plant:
+        for i, (r, pos) in enumerate(rows):
+            if lengths[r] > 40 and pos >= 3:
+                q[i] = (keys[r][3].float().repeat_interleave(Hq // Hkv, 0) * 0.5).to(dtype)
+    token_req = torch.tensor([r for r, _ in rows], dtype=torch.int32)
+    positions = torch.tensor([p for _, p in rows], dtype=torch.int32)
+    return dict(q=q, kc=kc, vc=vc, bt=bt, token_req=token_req, positions=positions, keys=keys, values=values, rows=rows)
+
+
+def attention_reference(case, scale, window, rd):
+    q = case["q"].to(rd)
+    Hq, Hkv = q.shape[1], case["keys"][0].shape[1]
+    out = torch.zeros_like(q)
+    for i, (r, pos) in enumerate(case["rows"]):
+        lo = max(0, pos - window + 1) if window else 0
+        k = case["keys"][r].to(rd)[lo:pos + 1].repeat_interleave(Hq // Hkv, 1)
+        v = case["values"][r].to(rd)[lo:pos + 1].repeat_interleave(Hq // Hkv, 1)
+        s = torch.einsum("hd,shd->hs", q[i], k) * scale
+        out[i] = torch.einsum("hs,shd->hd", torch.softmax(s, -1), v)
+    return out
+
+
+ATTN_SHAPES = [  # Hq, Hkv, hd, page
+    (4, 2, 16, 16), (3, 1, 32, 64), (8, 2, 64, 64), (6, 6, 48, 16), (16, 1, 80, 32), (5, 1, 128, 64), (2, 1, 256, 16),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", ATTN_SHAPES)
+@pytest.mark.parametrize("kernel", ["general", "split1", "split5", "split_auto"])
+def test_paged_attention_kernels(dtype, shape, kernel):
+    Hq, Hkv, hd, page = shape
+    g = torch.Generator().manual_seed(hd + Hq)
+    lengths, new = [70, 1, 333, 64, 129], [5, 1, 1, 64, 2]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new)
+    k = K()
+    scale = hd ** -0.5
+    args = (dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(case["token_req"]), dev(case["positions"]), scale)
+    if kernel == "general":
+        out = k.paged_attention(*args)
+    else:
+        splits = {"split1": 1, "split5": 5}.get(kernel) or k.attention_splits(len(case["rows"]), Hq, Hkv, max(lengths))
+        out = k.attention_decode(*args, splits=splits)
+    close(out, rnd_of(dtype)(attention_reference(case, scale, 0, ref_dtype(dtype))), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [1, 7])
+def test_attention_finds_a_far_key_and_honours_a_window(dtype, splits):
+    g = torch.Generator().manual_seed(5)
+    Hq, Hkv, hd, page = 8, 2, 64, 64
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, [700, 50, 257], [3, 2, 1], plant=True)
+    k = K()
+    scale = hd ** -0.5
+    args = (dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(case["token_req"]), dev(case["positions"]), scale)
+    rd = ref_dtype(dtype)
+    want = attention_reference(case, scale, 0, rd)
+    # the planted key really dominates: the output is close to that key's value row
+    v3 = case["values"][0].to(rd)[3].repeat_interleave(Hq // Hkv, 0)
+    assert float((want[0] - v3).abs().max()) < 0.05
+    close(k.attention_decode(*args, splits=splits), rnd_of(dtype)(want), dtype)
+    close(k.paged_attention(*args), rnd_of(dtype)(want), dtype)
+    for window in (1, 64, 65, 300):
+        want_w = rnd_of(dtype)(attention_reference(case, scale, window, rd))
+        close(k.attention_decode(*args, window, splits=splits), want_w, dtype)
+        close(k.paged_attention(*args, window), want_w, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_decode_token_list_leaves_other_rows(dtype):
+    g = torch.Generator().manual_seed(6)
+    Hq, Hkv, hd, page = 4, 1, 32, 16
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, [90, 40], [6, 3])
+    k = K()
+    scale = hd ** -0.5
+    out = torch.full_like(dev(case["q"]), 7.0)
+    picked = torch.tensor([8, 0, 5], dtype=torch.int32)
+    k.attention_decode(dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(case["token_req"]),
+                       dev(case["positions"]), scale, splits=3, token_list=dev(picked), out=out)
+    want = rnd_of(dtype)(attention_reference(case, scale, 0, ref_dtype(dtype)))
+    mask = torch.zeros(len(case["rows"]), dtype=torch.bool)
+    mask[picked.long()] = True
+    close(out[dev(mask)], want[mask], dtype)
+    assert bool((out[dev(~mask)] == 7.0).all())
+
+
+# --------------------------------------------------------------------------- Mamba2: conv and scan
+def packed_batch(lens, starts):
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    return cu, torch.tensor(starts, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Kc", [2, 3, 4])
+def test_causal_conv1d_portions_resume_from_state(dtype, Kc):
+    """Three requests; each is run as two portions (the second resumes from the saved window) and must
+    equal the conv over the whole sequence.  Lengths include portions shorter than the kernel."""
+    g = torch.Generator().manual_seed(Kc)
+    k = K()
+    C, e0, e1 = 50, 30, 40
+    scales = (1.1, 0.9, 1.3)
+    full = [70, 5, 131]
+    first = [69, 1, 64]
+    w = randn(g, C, Kc, scale=0.3)
+    b = randn(g, C, scale=0.1)
+    xs = [randn(g, n, C + 6, dtype=dtype)[:, 3:3 + C] for n in full]
+    rd, rnd = ref_dtype(dtype), rnd_of(dtype)
+    scale_vec = torch.cat([torch.full((e0,), scales[0]), torch.full((e1 - e0,), scales[1]), torch.full((C - e1,), scales[2])])
+    want = [P.causal_conv_silu(rnd(x.to(rd) * scale_vec.to(rd)), w.to(rd), b.to(rd), rnd) for x in xs]
+    state = torch.full((5, C, Kc - 1), float("nan"), dtype=dtype).cuda()
+    slots = torch.tensor([4, 0, 2], dtype=torch.int32)
+    got = [[] for _ in full]
+    for part in range(2):
+        pieces = [x[:f] if part == 0 else x[f:] for x, f in zip(xs, first)]
+        lens = [p.shape[0] for p in pieces]
+        starts = [0 if part == 0 else f for f in first]
+        cu, sp = packed_batch(lens, starts)
+        wide = torch.cat([torch.cat(pieces).contiguous(), torch.zeros(sum(lens), 9, dtype=dtype)], 1).cuda()
+        out = k.causal_conv1d(wide[:, :C], dev(w), dev(b), state, dev(cu), dev(sp), dev(slots), 3, max(lens),
+                              (e0, e1), scales)
+        for r in range(3):
+            got[r].append(out[int(cu[r]):int(cu[r + 1])].cpu())
+    for r in range(3):
+        close(torch.cat(got[r]), want[r], dtype)
+    # the saved window is the last K-1 scaled inputs, oldest first
+    for r in range(3):
+        tail = rnd(xs[r].to(rd) * scale_vec.to(rd))[-(Kc - 1):].T
+        close(state[int(slots[r])], tail, dtype, tol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(4, 16, 16, 1), (6, 24, 32, 2), (3, 64, 128, 1), (2, 40, 256, 2), (5, 8, 20, 5)])
+def test_ssm_scan_portions_resume_from_state(dtype, shape):
+    nh, Pd, N, G = shape
+    g = torch.Generator().manual_seed(nh * N)
+    k = K()
+    inner, C = nh * Pd, nh * Pd + 2 * G * N
+    full, first = [45, 2, 71], [44, 1, 16]
+    A_log = torch.log(1 + 15 * torch.rand(nh, generator=g))
+    dt_bias = randn(g, nh, scale=0.5) - 2.0
+    D = 1 + 0.1 * torch.randn(nh, generator=g)
+    convs = [randn(g, n, C, dtype=dtype) for n in full]
+    dts = [randn(g, n, nh + 3, dtype=dtype)[:, 1:1 + nh] for n in full]
+    rd, rnd = ref_dtype(dtype), rnd_of(dtype)
+    want = []
+    for c, d in zip(convs, dts):
+        n = c.shape[0]
+        x, B, Cm = c.to(rd).split([inner, G * N, G * N], 1)
+        y = P.ssm_recurrence(x.reshape(n, nh, Pd), d.to(rd), A_log.to(rd), dt_bias.to(rd), B.reshape(n, G, N),
+                             Cm.reshape(n, G, N), D.to(rd), 0.8, rnd)
+        want.append(y.reshape(n, inner))
+    state = torch.full((4, nh, Pd, N), float("nan"), dtype=torch.float32).cuda()
+    slots = torch.tensor([3, 1, 0], dtype=torch.int32)
+    got = [[] for _ in full]
+    for part in range(2):
+        cs = [c[:f] if part == 0 else c[f:] for c, f in zip(convs, first)]
+        ds = [d[:f] if part == 0 else d[f:] for d, f in zip(dts, first)]
+        lens = [c.shape[0] for c in cs]
+        cu, sp = packed_batch(lens, [0 if part == 0 else f for f in first])
+        dt_wide = torch.cat([torch.cat(ds), torch.zeros(sum(lens), 5, dtype=dtype)], 1).cuda()
+        y = k.ssm_scan(torch.cat(cs).cuda(), dt_wide[:, :nh], dev(A_log), dev(dt_bias), dev(D), state, dev(cu),
+                       dev(sp), dev(slots), 3, nh, Pd, N, G, 0.8)
+        for r in range(3):
+            got[r].append(y[int(cu[r]):int(cu[r + 1])].cpu())
+    for r in range(3):
+        close(torch.cat(got[r]), want[r], dtype)
+
+
+# --------------------------------------------------------------------------- 32-bit matrix product
+def test_gemm_f32_is_true_32_bit():
+    g = torch.Generator().manual_seed(9)
+    M, N, Kd = 37, 150, 1000
+    a = randn(g, M, Kd + 4)[:, :Kd]
+    w, b = randn(g, N, Kd), randn(g, N)
+    out = K().gemm_f32(dev(torch.cat([a, torch.zeros(M, 4)], 1))[:, :Kd], dev(w), dev(b), 0.5)
+    want = (a.double() @ w.double().T + b.double()) * 0.5
+    # a reduced-precision matrix mode (10-bit mantissa inputs) would err by ~1e-3 here
+    close(out, want, torch.float32, tol=3e-6)
+
+
+# --------------------------------------------------------------------------- sampling
+def test_sample_greedy_is_argmax_lowest_index():
+    from logssms_b200.sampling import sample_tokens
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(6, 1003, generator=g)
+    logits[2, 77] = logits[2, 500] = 9.0                    # a tie: the lower index wins
+    out = sample_tokens(dev(logits), None, None, None, None, None).cpu()
+    want = logits.argmax(-1)
+    want[2] = 77
+    assert out.tolist() == want.tolist()
+
+
+def test_sample_temperature_frequencies_and_reproducibility():
+    from logssms_b200.sampling import sample_tokens
+    rows = 4000
+    base = torch.tensor([1.0, 0.0, -1.0, 2.0, 0.5])
+    logits = dev(base.repeat(rows, 1).contiguous())
+    temp = dev(torch.full((rows,), 0.7))
+    topk = dev(torch.zeros(rows, dtype=torch.int32))
+    topp = dev(torch.ones(rows))
+    seeds = dev(torch.full((rows,), 1234, dtype=torch.int64))
+    counters = dev(torch.arange(rows, dtype=torch.int64))
+    a = sample_tokens(logits, temp, topk, topp, seeds, counters).cpu()
+    b = sample_tokens(logits, temp, topk, topp, seeds, counters).cpu()
+    assert torch.equal(a, b)
+    freq = torch.bincount(a.long(), minlength=5).double() / rows
+    want = torch.softmax(base.double() / 0.7, 0)
+    assert float((freq - want).abs().max()) < 0.03
+    # top_k = 2 keeps the two most likely tokens only; top_p = 0.5 keeps the most likely one (p = 0.66)
+    a2 = sample_tokens(logits, temp, dev(torch.full((rows,), 2, dtype=torch.int32)), topp, seeds, counters).cpu()
+    assert set(a2.tolist()) == {0, 3}
+    a3 = sample_tokens(logits, temp, topk, dev(torch.full((rows,), 0.5)), seeds, counters).cpu()
+    assert set(a3.tolist()) == {3}
+    # temperature -> 0 is greedy
+    a4 = sample_tokens(logits, dev(torch.full((rows,), 1e-6)), topk, topp, seeds, counters).cpu()
+    assert set(a4.tolist()) == {3}
