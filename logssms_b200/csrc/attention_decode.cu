@@ -266,3 +266,80 @@ extern "C" int lb_attention_decode(const void* q, const void* k_cache, const voi
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, sel_tokens, (cudaStream_t)stream));
     return kOk;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same attention without any allocation: the ranges' partial results live in a fixed array of
+// this library's device data segment.  Declaration, limits and rules: lb200/attention_decode_static.h.
+// No counterpart in the reference.
+#include <mutex>
+#include <stdio.h>
+
+#include "lb200/attention_decode_static.h"
+
+namespace {
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_static_scratch[LB_ATTN_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_addr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+int refuse(char* err, size_t err_len, int code, const char* fmt, long a = 0, long b = 0) {
+    if (err != nullptr && err_len > 0) snprintf(err, err_len, fmt, a, b);
+    return code;
+}
+
+// Device address of the array on the current device; looked up once per device.
+int static_scratch_address(float** addr, char* err, size_t err_len) {
+    int device = -1;
+    cudaError_t rc = cudaGetDevice(&device);
+    if (rc != cudaSuccess) return refuse(err, err_len, (int)rc, "cudaGetDevice failed: CUDA error %ld", (long)rc);
+    if (device < 0 || device >= kMaxDevices)
+        return refuse(err, err_len, kTooLarge, "device index %ld is beyond the %ld this entry point tracks", device, kMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[device] == nullptr) {
+        float* p = nullptr;
+        rc = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+        if (rc != cudaSuccess || p == nullptr)
+            return refuse(err, err_len, rc != cudaSuccess ? (int)rc : (int)cudaErrorInvalidSymbol,
+                          "cudaGetSymbolAddress of the static scratch failed: CUDA error %ld", (long)rc);
+        g_static_scratch_addr[device] = p;
+    }
+    *addr = g_static_scratch_addr[device];
+    return kOk;
+}
+}  // namespace
+
+extern "C" int lb_attention_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          const int* block_table, int bt_stride, const int* token_req,
+                                          const int* positions, const int* token_list, int sel_tokens, int Hq,
+                                          int Hkv, int hd, int page_size, float scale, int window, int splits,
+                                          int dtype, void* stream, char* err, size_t err_len) {
+    if (err != nullptr && err_len > 0) err[0] = '\0';
+    if (sel_tokens <= 0) return kOk;
+    if (hd <= 0 || hd > 256 || hd % 16 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || splits < 1)
+        return refuse(err, err_len, kBadSize, "a size the kernel does not take (head_dim %ld in steps of 16 up to 256, "
+                      "query heads a multiple of key/value heads, splits %ld >= 1)", hd, splits);
+    if (splits > 65535 || (long)Hkv * ((Hq / Hkv + 7) / 8 + 1) > 65535)
+        return refuse(err, err_len, kTooLarge, "too many ranges (%ld) or key/value heads (%ld) for one grid", splits, Hkv);
+    if (dtype != kF32 && dtype != kBF16) return refuse(err, err_len, kBadDType, "dtype code %ld is neither float32 (0) nor bfloat16 (1)", dtype);
+    const size_t slots = (size_t)sel_tokens * (size_t)Hq * (size_t)splits;
+    const size_t need = slots * (size_t)(hd + 2);
+    if (need > (size_t)LB_ATTN_STATIC_SCRATCH_FLOATS)
+        return refuse(err, err_len, LB_ERR_STATIC_SCRATCH,
+                      "this call needs %ld floats of scratch, the static array holds %ld: use fewer ranges or tokens per call",
+                      (long)need, (long)LB_ATTN_STATIC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch, err, err_len);
+    if (rc != kOk) return rc;
+    // partial outputs first (slots * hd floats, 256-byte aligned start), then the (max, sum) pairs
+    float* part_o = scratch;
+    float* part_ml = scratch + slots * (size_t)hd;
+    DecodeArgs a{q, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, token_list, part_o, part_ml,
+                 Hq, Hkv, hd, page_size, window, splits, 1, scale};
+    int launched = kOk;
+    if (dtype == kF32) launched = launch<float>(a, sel_tokens, (cudaStream_t)stream);
+    else launched = launch<__nv_bfloat16>(a, sel_tokens, (cudaStream_t)stream);
+    if (launched != kOk) return refuse(err, err_len, launched, "kernel launch failed: CUDA error %ld", launched);
+    return kOk;
+}
