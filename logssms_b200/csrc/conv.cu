@@ -8,8 +8,10 @@
 // (python/logssms/kernel/linear_attention/packed_conv.py:96-140; decode form
 // python/logssms/kernel/linear_attention/conv_decode.py:112-278.)
 //
-// Two launches: the forward kernel only READS the state (grid over token chunks, so a long prompt
-// spreads over many CTAs), the update kernel then rewrites it, one thread per (request, channel).
+// Long portions take two launches: the forward kernel only READS the state (grid over token chunks, so
+// a long prompt spreads over many CTAs), the update kernel then rewrites it, one thread per (request,
+// channel).  When no portion is longer than one chunk (every decode step) a thread is the only reader
+// of its (request, channel) state, so the forward kernel rewrites it itself and the step is one launch.
 #include "lb200/common.cuh"
 using namespace lb200;
 
@@ -31,7 +33,7 @@ __device__ __forceinline__ float scaled_input(const ConvArgs& a, long token, int
     return round_to<T>(to_f32(((const T*)a.x)[token * a.x_stride + c]) * scale);
 }
 
-template <typename T, int K>
+template <typename T, int K, bool UPDATE>
 __global__ void conv_forward_kernel(ConvArgs a) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= a.C) return;
@@ -63,6 +65,11 @@ __global__ void conv_forward_kernel(ConvArgs a) {
 #pragma unroll
         for (int j = 0; j < K - 1; ++j) win[j] = win[j + 1];
     }
+    if (UPDATE) {                                         // single chunk: win holds the last K-1 inputs
+        T* st_w = (T*)a.state + ((size_t)a.slots[b] * a.C + c) * (K - 1);
+#pragma unroll
+        for (int j = 0; j < K - 1; ++j) st_w[j] = from_f32<T>(win[j]);
+    }
 }
 
 template <typename T, int K>
@@ -93,8 +100,12 @@ int launch(const ConvArgs& a, int B, int K, int max_len, cudaStream_t s) {
     dim3 grid_u((a.C + threads - 1) / threads, B);
 #define LB_CONV_K(KK)                                                         \
     case KK:                                                                  \
-        conv_forward_kernel<T, KK><<<grid_f, threads, 0, s>>>(a);             \
-        conv_state_update_kernel<T, KK><<<grid_u, threads, 0, s>>>(a);        \
+        if (max_len <= kChunk) {                                              \
+            conv_forward_kernel<T, KK, true><<<grid_f, threads, 0, s>>>(a);   \
+        } else {                                                              \
+            conv_forward_kernel<T, KK, false><<<grid_f, threads, 0, s>>>(a);  \
+            conv_state_update_kernel<T, KK><<<grid_u, threads, 0, s>>>(a);    \
+        }                                                                     \
         break;
     switch (K) {
         LB_CONV_K(2) LB_CONV_K(3) LB_CONV_K(4) LB_CONV_K(5) LB_CONV_K(6) LB_CONV_K(7) LB_CONV_K(8)

@@ -1,0 +1,195 @@
+// Projections of a decode step: y[M, N] = x[M, K] W[N, K]^T for a handful of rows (M <= 64), bfloat16.
+//
+// With so few rows the product is bound by reading W once from HBM, so the kernel is built as a weight
+// streamer: every CTA owns 16 output features (16 rows of W; 16 gate + 16 up rows for the SwiGLU form),
+// its 8 warps split K between them, and every thread pulls its share of W straight from global memory
+// into registers with 16-byte loads that bypass L1 (each byte of W is used once).  The rows of x are a
+// few KB shared by all CTAs; they are read through L1/L2 as needed.  The arithmetic rides on the
+// warp-level tensor-core instruction (mma.sync m16n8k16, bfloat16 in, float32 accumulate) with W as the
+// 16-row operand and x as the 8-column operand ("swap A/B"), so 8 batch rows cost one instruction per
+// 16 x 16 block of W.  tcgen05 has nothing to offer here: its smallest tile has 64 rows and needs W in
+// shared memory first, while this kernel's limit is the HBM stream.
+//
+// K order inside an instruction is free as long as both operands agree: a thread loads 8 consecutive
+// k (16 bytes) of its W row and of its x row and feeds them to two instructions, so all loads are
+// 16-byte vectors.
+//
+// Epilogues (all on the float32 sums, rounding where the unfused chain rounds):
+//   plain : out = round(round(acc + bias) * out_scale)                      bfloat16
+//   f32   : out = float(round(acc + bias)) * out_scale                      float32 (logits)
+//   swiglu: g = round(acc_gate), u = round(acc_up);
+//           out = round(round(silu(round(g * act_scale))) * u)              bfloat16
+// (python/logssms/layers/linear.py:26, python/logssms/kernel/fused.py:32-50 for the gate chain.)
+#include "lb200/common.cuh"
+using namespace lb200;
+
+namespace {
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kFeat = 16;            // output features per CTA (per half for swiglu)
+constexpr int kChunk = 32;           // k per load step: 4 lanes x 8 elements
+constexpr int kUnroll = 4;           // chunks in flight per warp
+
+struct SkinnyArgs {
+    const __nv_bfloat16* x; long ldx;
+    const __nv_bfloat16* w;                      // [N (or 2*N for swiglu: gate rows then up rows), K]
+    const __nv_bfloat16* bias;                   // [N] or null
+    void* out; long ldo;
+    int M, N, K;
+    float out_scale, act_scale;
+};
+
+__device__ __forceinline__ uint4 load_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+enum Epilogue : int { kPlain = 0, kOutF32 = 1, kSwiglu = 2 };
+
+// MT: tiles of 8 batch rows.  HALVES: 1, or 2 for swiglu (gate and up rows of the same feature).
+template <int MT, int EPI>
+__global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
+    constexpr int HALVES = EPI == kSwiglu ? 2 : 1;
+    constexpr int MP = MT * 8 + 1;
+    extern __shared__ float red_raw[];
+    float (*red)[HALVES][kFeat][MP] = reinterpret_cast<float (*)[HALVES][kFeat][MP]>(red_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * kFeat;
+    const int K = a.K;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    // rows of W this thread reads (clamped at the edge; masked at the store)
+    const __nv_bfloat16* wrow[HALVES][2];
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int n = min(n0 + g + 8 * r, a.N - 1);
+            wrow[h][r] = a.w + ((size_t)h * a.N + n) * K;
+        }
+    const __nv_bfloat16* xrow[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) xrow[m] = a.x + (size_t)min(m * 8 + g, a.M - 1) * a.ldx;
+
+    float acc[HALVES][MT][4];
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[h][m][e] = 0.f;
+
+    const int chunks = (K + kChunk - 1) / kChunk;
+    const int per_warp = (chunks + kWarps - 1) / kWarps;
+    const int c_begin = warp * per_warp, c_end = min(chunks, c_begin + per_warp);
+    for (int c0 = c_begin; c0 < c_end; c0 += kUnroll) {
+        uint4 wv[kUnroll][HALVES][2];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int k = (c0 + u) * kChunk + t * 8;
+            const bool ok = (c0 + u) < c_end && k < K;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) wv[u][h][r] = ok ? load_stream(wrow[h][r] + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int k = (c0 + u) * kChunk + t * 8;
+            const bool ok = (c0 + u) < c_end && k < K;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const uint4 xv = ok ? __ldg(reinterpret_cast<const uint4*>(xrow[m] + k)) : zero;
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) {
+                    mma_bf16(acc[h][m], wv[u][h][0].x, wv[u][h][1].x, wv[u][h][0].y, wv[u][h][1].y, xv.x, xv.y);
+                    mma_bf16(acc[h][m], wv[u][h][0].z, wv[u][h][1].z, wv[u][h][0].w, wv[u][h][1].w, xv.z, xv.w);
+                }
+            }
+        }
+    }
+    // accumulator element e of tile m: feature g + 8*(e/2), batch row m*8 + 2t + (e&1)
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) red[warp][h][g + 8 * (e >> 1)][m * 8 + 2 * t + (e & 1)] = acc[h][m][e];
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.M * kFeat; i += kThreads) {
+        const int m = i / kFeat, f = i % kFeat;
+        const int n = n0 + f;
+        if (n >= a.N) continue;
+        float s[HALVES];
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) v += red[w][h][f][m];
+            s[h] = v;
+        }
+        if (EPI == kSwiglu) {
+            const float gate = round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(s[0]) * a.act_scale);
+            const float act = round_to<__nv_bfloat16>(silu_f(gate));
+            const float up = round_to<__nv_bfloat16>(s[HALVES - 1]);
+            ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n] = __float2bfloat16_rn(act * up);
+        } else {
+            float v = s[0];
+            if (a.bias != nullptr) v += __bfloat162float(a.bias[n]);
+            v = round_to<__nv_bfloat16>(v);
+            if (EPI == kOutF32) ((float*)a.out)[(size_t)m * a.ldo + n] = v * a.out_scale;
+            else ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n] =
+                a.out_scale == 1.f ? __float2bfloat16_rn(v) : __float2bfloat16_rn(v * a.out_scale);
+        }
+    }
+}
+
+template <int EPI>
+int launch_mt(const SkinnyArgs& a, cudaStream_t s) {
+    const dim3 grid((a.N + kFeat - 1) / kFeat);
+    const int mt = (a.M + 7) / 8;
+    constexpr int halves = EPI == kSwiglu ? 2 : 1;
+#define LB_SKINNY(MT)                                                                                       \
+    {                                                                                                       \
+        const size_t smem = sizeof(float) * kWarps * halves * kFeat * (MT * 8 + 1);                         \
+        if (smem > 48 * 1024)                                                                               \
+            cudaFuncSetAttribute(skinny_linear_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        skinny_linear_kernel<MT, EPI><<<grid, kThreads, smem, s>>>(a);                                      \
+    }
+    if (mt <= 1) LB_SKINNY(1)
+    else if (mt <= 2) LB_SKINNY(2)
+    else if (mt <= 4) LB_SKINNY(4)
+    else LB_SKINNY(8)
+#undef LB_SKINNY
+    return launch_status();
+}
+}  // namespace
+
+// x: [M, K] bfloat16 rows (row stride ldx, a multiple of 8 elements, 16-byte aligned base);
+// w: [N, K] bfloat16 contiguous ([2N, K] for the swiglu epilogue: gate rows, then up rows); K a
+// multiple of 8; M <= 64.  epilogue: 0 plain (bfloat16 out), 1 float32 out, 2 swiglu (bfloat16 out).
+extern "C" int lb_linear_skinny(const void* x, long ldx, const void* w, const void* bias, void* out, long ldo, int M,
+                                int N, int K, float out_scale, float act_scale, int epilogue, void* stream) {
+    if (M <= 0 || N <= 0) return kOk;
+    if (K <= 0 || K % 8 || ldx % 8) return kBadSize;
+    if (M > 64) return kTooLarge;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return kBadSize;
+    SkinnyArgs a{(const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, out, ldo,
+                 M, N, K, out_scale, act_scale};
+    switch (epilogue) {
+        case kPlain: return launch_mt<kPlain>(a, (cudaStream_t)stream);
+        case kOutF32: return launch_mt<kOutF32>(a, (cudaStream_t)stream);
+        case kSwiglu: return launch_mt<kSwiglu>(a, (cudaStream_t)stream);
+        default: return kBadSize;
+    }
+}

@@ -4,6 +4,7 @@
 //   dA_h   = -exp(A_log_h) * dt_h
 //   S_h   <- e^{dA_h} S_h + B_{g(h)} (x) (x_h * dt_h)                 S_h in R^{P x N}
 //   y_h    = S_h C_{g(h)} + D_h x_h                                   (uses the updated state)
+//   y_h   <- round(y_h) * round(silu(round(z_h * gate_scale)))          (optional: the gate of a mixer without norm)
 // (python/logssms/kernel/linear_attention/mamba2.py:27-36 and :261-292; recurrence oracle
 // tests/kernel/test_mamba2.py:22-38 of the reference.)
 //
@@ -27,6 +28,7 @@ struct SsmArgs {
     void* y;                                     // [tokens, nh * P]
     const int* cu_seqlens; const int* start_pos; const int* slots;
     int nh, P, N, G; float dt_scale;
+    const void* gate; long gate_stride; float gate_scale;   // optional [tokens, nh * P] view: y *= silu(gate * scale)
 };
 
 template <typename T> __device__ __forceinline__ void load4(const T* p, float* f);
@@ -105,7 +107,14 @@ __global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
         acc += __shfl_xor_sync(0xffffffffu, acc, 2);
         acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-        if (nl == 0 && p_ok) ((T*)a.y)[tok * inner + h * a.P + p] = from_f32<T>(acc + Dh * xv);
+        if (nl == 0 && p_ok) {
+            float yv = acc + Dh * xv;
+            if (a.gate != nullptr) {                      // the mixer's gate when it has no norm (fused.py:9-19)
+                const float zg = round_to<T>(to_f32(((const T*)a.gate)[tok * a.gate_stride + h * a.P + p]) * a.gate_scale);
+                yv = round_to<T>(yv) * round_to<T>(silu_f(zg));
+            }
+            ((T*)a.y)[tok * inner + h * a.P + p] = from_f32<T>(yv);
+        }
     }
     if (p_ok) {
 #pragma unroll
@@ -141,11 +150,13 @@ int launch(const SsmArgs& a, int B, cudaStream_t s) {
 extern "C" int lb_ssm_scan(const void* conv, int C, const void* dt, long dt_stride, const float* A_log,
                            const float* dt_bias, const float* D, float* state, void* y, const int* cu_seqlens,
                            const int* start_pos, const int* slots, int B, int nh, int P, int N, int G,
-                           float dt_scale, int dtype, void* stream) {
+                           float dt_scale, const void* gate, long gate_stride, float gate_scale, int dtype,
+                           void* stream) {
     if (B <= 0) return kOk;
     if (nh <= 0 || P <= 0 || N <= 0 || G <= 0 || nh % G || N % 4) return kBadSize;
     if (C != nh * P + 2 * G * N) return kBadSize;
-    SsmArgs a{conv, C, dt, dt_stride, A_log, dt_bias, D, state, y, cu_seqlens, start_pos, slots, nh, P, N, G, dt_scale};
+    SsmArgs a{conv, C, dt, dt_stride, A_log, dt_bias, D, state, y, cu_seqlens, start_pos, slots, nh, P, N, G, dt_scale,
+              gate, gate_stride, gate_scale};
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, B, (cudaStream_t)stream));
     return kOk;
 }

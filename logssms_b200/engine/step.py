@@ -23,6 +23,7 @@ import torch
 from ..cache import CacheManager, RequestCache
 from ..config import load_model_config
 from ..models import build_model
+from ..ops import kernels as K
 from ..parts import Runtime, StepContext
 from ..weights import load_weights
 
@@ -68,7 +69,8 @@ class Engine:
 
     def __init__(self, model_dir: str, dtype="bfloat16", *, max_requests: int = 64, max_seq_len: int = 8192,
                  page_size: int = 64, num_pages: int | None = None, memory_ratio: float = 0.9,
-                 device: str = "cuda:0", poison_on_free: bool = False, max_step_tokens: int = 1 << 30):
+                 device: str = "cuda:0", poison_on_free: bool = False, max_step_tokens: int = 1 << 30,
+                 use_graphs: bool = True, max_graphs: int = 16):
         if not torch.cuda.is_available():
             raise RuntimeError("logssms_b200 needs a CUDA device (built for sm_100a); there is no CPU path")
         try:
@@ -93,6 +95,10 @@ class Engine:
         self.vocab_size = self.model.spec.vocab_size
         self._ring = _PinnedRing()
         self._staging: torch.Tensor | None = None
+        self._staging_half = 0
+        self.use_graphs = use_graphs
+        self.max_graphs = max_graphs
+        self._graphs: dict[int, _DecodeGraph] = {}
         self.steps_run = 0
         self.h2d_bytes = 0          # bytes of step tables copied host -> device so far
 
@@ -120,20 +126,56 @@ class Engine:
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens as one batch; return float32 logits [wanted, vocab] in the order
-        of the entries and of each entry's `want`."""
-        ctx = self._plan(entries)
-        if ctx is None:
+        of the entries and of each entry's `want`.
+
+        A step of single decoded tokens that all want their logits is replayed from a CUDA graph
+        (one per batch size, captured the second time that size is seen); the returned tensor is then
+        the graph's own output buffer, valid until the next step of the same size."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self._decode_step(entries)
+        ctx = self._plan(entries)
         x, residual = self.model.forward(ctx)
         self.steps_run += 1
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.logits(x, residual, ctx.logit_rows)
 
-    def _plan(self, entries: Sequence[StepEntry]) -> StepContext | None:
-        entries = [e for e in entries if len(e.tokens) > 0]
-        if not entries:
-            return None
+    def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        B = len(entries)
+        slot = self._graphs.get(B)
+        if slot is None:
+            if len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))
+            slot = self._graphs[B] = _DecodeGraph()
+        slot.seen += 1
+        if slot.graph is None and slot.seen < 2:
+            ctx = self._plan(entries)              # first time: eager (this also builds and loads every kernel)
+            x, residual = self.model.forward(ctx)
+            self.steps_run += 1
+            return self.model.logits(x, residual, ctx.logit_rows)
+        ctx = self._plan(entries, slot)
+        if slot.graph is None:
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = K.launch_count
+            with torch.cuda.graph(graph):
+                x, residual = self.model.forward(ctx)
+                slot.logits = self.model.logits(x, residual, ctx.logit_rows)
+            slot.launches = K.launch_count - before
+            K.launch_count = before
+            slot.graph = graph
+        slot.graph.replay()
+        K.launch_count += slot.launches
+        self.steps_run += 1
+        return slot.logits
+
+    def _plan(self, entries: Sequence[StepEntry], static: "_DecodeGraph | None" = None) -> StepContext:
+        """Host side of a step: checks, room in the cache, and every per-step integer packed into one
+        pinned buffer and copied to the device at once.  With `static` (a decode graph's slot) the
+        tables keep a fixed width and a fixed place on the device, so that a captured graph finds them."""
         B = len(entries)
         seen = set()
         for e in entries:
@@ -163,9 +205,10 @@ class Engine:
         logit_rows = np.asarray([cu[b] + w for b, e in enumerate(entries) for w in e.want], dtype=np.int64)
         groups = self.cache.groups
         ps = self.page_size
+        max_context = int((starts + lens).max())
+        P = self.cache.max_pages_per_request if static is not None else -(-max_context // ps)
         tables, mappings = [], []
         for g in groups:
-            P = int(-(-(starts + lens).max() // ps))
             bt = g.block_table[rows, :P]
             page_of_token = bt[token_req, positions // ps].astype(np.int64)
             if (page_of_token < 0).any():
@@ -179,32 +222,51 @@ class Engine:
         sizes = [int(s.size) for s in sections]
         offsets = np.concatenate([[0], np.cumsum([(n + 3) // 4 * 4 for n in sizes])])
         total = int(offsets[-1])
-        pinned, slot = self._ring.take(total)
+        pinned, ring_slot = self._ring.take(total)
         host = pinned.numpy()
         for s, off, n in zip(sections, offsets[:-1], sizes):
             host[off:off + n] = s
-        if self._staging is None or self._staging.numel() < total:
-            self._staging = torch.empty(max(total, 4096) * 2, dtype=torch.int32, device=self.device)
-            self._staging_half = 0
-        # alternate halves so that a step's tables are not overwritten while an earlier step may still run
-        self._staging_half ^= 1
-        half = self._staging.numel() // 2
-        if total > half:
-            self._staging = torch.empty(total * 2, dtype=torch.int32, device=self.device)
-            half = total
-        dev = self._staging[self._staging_half * half: self._staging_half * half + total]
+        if static is not None:
+            if static.tables is None:
+                static.tables = torch.empty(total, dtype=torch.int32, device=self.device)
+            dev = static.tables
+        else:
+            if self._staging is None or self._staging.numel() < 2 * total:
+                self._staging = torch.empty(max(total, 4096) * 2, dtype=torch.int32, device=self.device)
+            # alternate halves so that a step's tables are not overwritten while an earlier step may still run
+            self._staging_half ^= 1
+            half = self._staging.numel() // 2
+            dev = self._staging[self._staging_half * half: self._staging_half * half + total]
         dev.copy_(pinned[:total], non_blocking=True)
         self.h2d_bytes += total * 4
-        self._ring.mark(slot)
+        self._ring.mark(ring_slot)
+        if static is not None and static.ctx is not None:
+            return static.ctx
 
         def view(i, shape=None):
             t = dev[int(offsets[i]): int(offsets[i]) + sizes[i]]
             return t if shape is None else t.view(shape)
         block_tables = [view(8 + 2 * gi, (B, tables[gi].shape[1])) for gi in range(len(groups))]
         slot_mappings = [view(7 + 2 * gi) for gi in range(len(groups))]
-        return StepContext(
+        ctx = StepContext(
             num_tokens=T, num_requests=B, max_len=int(lens.max()), token_ids=view(0), positions=view(1),
             token_req=view(2), cu_seqlens=view(3), start_pos=view(4), slots=view(5),
             block_tables=block_tables, slot_mappings=slot_mappings, logit_rows=view(6), cache=self.cache,
-            max_context=int((starts + lens).max()),
+            max_context=max_context if static is None else self.max_seq_len,
         )
+        if static is not None:
+            static.ctx = ctx
+        return ctx
+
+
+class _DecodeGraph:
+    """A captured decode step for one batch size: its table buffer on the device, the step context
+    whose tensors are views of that buffer, the graph, and the logits it writes."""
+
+    def __init__(self):
+        self.seen = 0
+        self.tables: torch.Tensor | None = None
+        self.ctx: StepContext | None = None
+        self.graph = None
+        self.logits: torch.Tensor | None = None
+        self.launches = 0

@@ -331,17 +331,22 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
                                          c_float, c_int, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_seqlens),
              _ptr(start_pos), _ptr(slots), num_requests, max_len, C, K, region_ends[0], region_ends[1],
-             region_scales[0], region_scales[1], region_scales[2], _code(x), _stream()), "causal_conv1d", launches=2)
+             region_scales[0], region_scales[1], region_scales[2], _code(x), _stream()), "causal_conv1d",
+           launches=1 if max_len <= 64 else 2)
     return out
 
 
 def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
              state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor,
              num_requests: int, num_heads: int, head_dim: int, state_dim: int, num_groups: int,
-             dt_scale: float) -> torch.Tensor:
+             dt_scale: float, gate: torch.Tensor | None = None, gate_scale: float = 1.0) -> torch.Tensor:
     """conv: [tokens, nh*P + 2*G*N] contiguous (x | B | C); dt: [tokens, nh] view; state: float32
-    [slots, nh, P, N], updated in place.  Returns y [tokens, nh*P]."""
-    _cuda(conv, dt, A_log, dt_bias, D, state, cu_seqlens, start_pos, slots)
+    [slots, nh, P, N], updated in place.  Returns y [tokens, nh*P]; with `gate` ([tokens, nh*P] view)
+    the result is y * silu(gate * gate_scale), the gate of a mixer that has no norm."""
+    _cuda(conv, dt, A_log, dt_bias, D, state, cu_seqlens, start_pos, slots, gate)
+    if gate is not None:
+        _need(gate.shape == (conv.shape[0], num_heads * head_dim) and gate.stride(1) == 1 and gate.dtype == conv.dtype,
+              "gate must be a [tokens, heads * head_dim] view of the activation dtype")
     tokens, C = conv.shape
     _need(conv.is_contiguous(), "conv output must be contiguous")
     _need(dt.shape == (tokens, num_heads) and dt.stride(1) == 1 and dt.dtype == conv.dtype, "dt must be a [tokens, heads] view")
@@ -354,11 +359,12 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
         _i32(t, n)
     y = torch.empty((tokens, num_heads * head_dim), dtype=conv.dtype, device=conv.device)
     f = _fn("ssm", "lb_ssm_scan", [c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                   c_void_p])
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                   c_long, c_float, c_int, c_void_p])
     _check(f(_ptr(conv), C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(state), _ptr(y),
              _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), num_requests, num_heads, head_dim, state_dim,
-             num_groups, dt_scale, _code(conv), _stream()), "ssm_scan")
+             num_groups, dt_scale, _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale, _code(conv),
+             _stream()), "ssm_scan")
     return y
 
 
@@ -378,15 +384,68 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
-    """x [M, K] @ w[N, K]^T (+ bias), in x's dtype.
+SKINNY_MAX_ROWS = 64       # at or below this many rows a bfloat16 product goes to the weight-streaming kernel
 
-    float32 activations: the engine's own 32-bit kernel.  bfloat16 activations with bfloat16
-    weights: cuBLAS through torch (32-bit accumulation).  bfloat16 activations with a weight that
-    is stored in 32-bit: the 32-bit kernel on widened activations, result rounded once."""
+
+def _skinny_ok(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= SKINNY_MAX_ROWS
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.shape[1] % 8 == 0 and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous())))
+
+
+_PLAIN, _OUT_F32, _SWIGLU = 0, 1, 2
+
+
+def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out_scale: float = 1.0,
+                  out_f32: bool = False, swiglu_scale: float | None = None) -> torch.Tensor:
+    """The weight-streaming product for at most 64 bfloat16 rows: x [M, K] @ w[N, K]^T, with the bias,
+    output multiplier, float32 output or SwiGLU (w = [gate rows; up rows]) done on the sums."""
+    _cuda(x, w, bias)
+    _need(_skinny_ok(x, w, bias), "linear_skinny takes at most 64 bfloat16 rows, K a multiple of 8, 16-byte aligned operands")
+    M, Kdim = x.shape
+    _need(w.dim() == 2 and w.shape[1] == Kdim, "weight must be [N, K]")
+    N = w.shape[0]
+    mode = _PLAIN
+    if swiglu_scale is not None:
+        _need(N % 2 == 0 and bias is None and not out_f32 and out_scale == 1.0, "the SwiGLU form takes [gate; up] rows and nothing else")
+        N //= 2
+        mode = _SWIGLU
+    elif out_f32:
+        mode = _OUT_F32
+    _need(bias is None or bias.shape == (N,), "bias must be [N]")
+    out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    f = _fn("linear_skinny", "lb_linear_skinny", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int,
+                                                  c_int, c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(bias), _ptr(out), N, M, N, Kdim, out_scale,
+             swiglu_scale if swiglu_scale is not None else 1.0, mode, _stream()), "linear_skinny")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out_scale: float = 1.0,
+           out_f32: bool = False) -> torch.Tensor:
+    """round(round(x [M, K] @ w[N, K]^T + bias) * out_scale) in x's dtype, or as float32 with `out_f32`.
+
+    float32 activations: the engine's own 32-bit kernel.  bfloat16: at most 64 rows go to the
+    weight-streaming kernel (a decode step is bound by reading the weights once); more rows go to
+    cuBLAS through torch (32-bit accumulation).  bfloat16 activations with a weight that is stored in
+    32-bit: the 32-bit kernel on widened activations, result rounded once."""
     _cuda(x, w, bias)
     if x.dtype == torch.float32:
-        return gemm_f32(x, w.float(), None if bias is None else bias.float())
+        return gemm_f32(x, w.float(), None if bias is None else bias.float(), out_scale)
     if w.dtype == torch.float32:
-        return gemm_f32(x.float(), w, None if bias is None else bias.float()).to(x.dtype)
-    return F.linear(x, w, None if bias is None else bias.to(x.dtype))
+        y = gemm_f32(x.float(), w, None if bias is None else bias.float()).to(x.dtype)
+    elif _skinny_ok(x, w, bias):
+        return linear_skinny(x, w, bias, out_scale=out_scale, out_f32=out_f32)
+    else:
+        y = F.linear(x, w, None if bias is None else bias.to(x.dtype))
+    if out_f32 or out_scale != 1.0:
+        y = scale(y, out_scale, to_f32=out_f32)
+    return y
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_scale: float) -> torch.Tensor:
+    """silu(round(gate * act_scale)) * up with [gate | up] = x @ w_gate_up^T (w rows: gate, then up)."""
+    if _skinny_ok(x, w_gate_up, None):
+        return linear_skinny(x, w_gate_up, swiglu_scale=act_scale)
+    return swiglu(linear(x, w_gate_up), act_scale)

@@ -30,6 +30,7 @@ class Embedding(Part):
 class LMHead(Part):
     """logits = float32((h W^T) * multiplier); W is the embedding table when the model ties them
     (python/logssms/layers/embedding.py:94-106, python/logssms/models/falcon_h1.py:237)."""
+    kernels = ("norm", "linear_skinny")
 
     def __init__(self, vocab_size: int, hidden_size: int, multiplier: float, tied_to: Embedding | None):
         self.vocab_size, self.hidden_size, self.multiplier, self.tied_to = vocab_size, hidden_size, multiplier, tied_to
@@ -48,4 +49,4 @@ class LMHead(Part):
         return self.tied_to.weight if self.tied_to is not None else self._weight
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return K.scale(K.linear(h, self.weight), self.multiplier, to_f32=True)
+        return K.linear(h, self.weight, out_scale=self.multiplier, out_f32=True)

@@ -31,7 +31,7 @@ class Mamba2(Part):
     python/logssms/kernel/linear_attention/packed_conv.py:96-140,
     python/logssms/kernel/linear_attention/mamba2.py:27-36 and :261-292,
     python/logssms/kernel/norm.py:55-86."""
-    kernels = ("conv", "ssm", "norm")
+    kernels = ("conv", "ssm", "norm", "linear_skinny")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
         self.spec = spec
@@ -95,11 +95,11 @@ class Mamba2(Part):
         conv = K.causal_conv1d(xbc, self.conv_w, self.conv_b, states["conv"], ctx.cu_seqlens, ctx.start_pos,
                                ctx.slots, ctx.num_requests, ctx.max_len,
                                (inner, inner + s.num_groups * s.state_dim), (m[1], m[2], m[3]))
-        y = K.ssm_scan(conv, dt, self.A_log, self.dt_bias, self.D, states["ssm"], ctx.cu_seqlens, ctx.start_pos,
-                       ctx.slots, ctx.num_requests, s.num_heads, s.head_dim, s.state_dim, s.num_groups, m[4])
+        scan = (conv, dt, self.A_log, self.dt_bias, self.D, states["ssm"], ctx.cu_seqlens, ctx.start_pos, ctx.slots,
+                ctx.num_requests, s.num_heads, s.head_dim, s.state_dim, s.num_groups, m[4])
         if s.gated_norm:
             mode = K.NORM_BEFORE_GATE if s.norm_before_gate else K.NORM_AFTER_GATE
-            y = K.gated_rmsnorm(y, z, self.norm_w, s.norm_eps, s.num_groups, m[0], mode)
+            y = K.gated_rmsnorm(K.ssm_scan(*scan), z, self.norm_w, s.norm_eps, s.num_groups, m[0], mode)
         else:
-            y = K.gated_rmsnorm(y, z, None, s.norm_eps, 1, m[0], K.GATE_ONLY)
+            y = K.ssm_scan(*scan, gate=z, gate_scale=m[0])      # the bare gate rides in the scan's epilogue
         return K.linear(y, self.out_w, self.out_b)

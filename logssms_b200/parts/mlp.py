@@ -12,7 +12,7 @@ from .base import MATRIX, ParamSpec, Part
 class GatedMLP(Part):
     """down(silu(gate * s0) * up) * s1.  `gate_proj` and `up_proj` are concatenated at bind time
     (python/logssms/models/weight.py:32-33); flow python/logssms/layers/mlp.py:50-61."""
-    kernels = ("norm",)
+    kernels = ("norm", "linear_skinny")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
         self.spec = spec
@@ -35,6 +35,5 @@ class GatedMLP(Part):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         s = self.spec
-        h = K.swiglu(K.linear(x, self.gate_up), s.activation_scale)
-        out = K.linear(h, self.down)
-        return out if s.output_scale == 1.0 else K.scale(out, s.output_scale)
+        h = K.linear_swiglu(x, self.gate_up, s.activation_scale)
+        return K.linear(h, self.down, out_scale=s.output_scale)

@@ -364,6 +364,77 @@ def test_gemm_f32_is_true_32_bit():
     close(out, want, torch.float32, tol=3e-6)
 
 
+# --------------------------------------------------------------------------- products of a few rows
+@pytest.mark.parametrize("M", [1, 7, 8, 13, 33, 64])
+@pytest.mark.parametrize("N,Kd", [(16, 64), (100, 1000), (3352, 1024), (1030, 2048)])
+def test_linear_skinny_plain_bias_scale_and_f32(M, N, Kd):
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = randn(g, M, Kd + 8, dtype=torch.bfloat16)[:, :Kd]          # a row-strided view
+    w = randn(g, N, Kd, dtype=torch.bfloat16, scale=0.05)
+    b = randn(g, N, dtype=torch.bfloat16)
+    k = K()
+    xd = dev(torch.cat([x, torch.zeros(M, 8, dtype=torch.bfloat16)], 1))[:, :Kd]
+    rnd = rnd_of(torch.bfloat16)
+    acc = x.float() @ w.float().T
+    close(k.linear_skinny(xd, dev(w)), rnd(acc), torch.bfloat16, tol=4e-3)           # one bfloat16 ulp of the largest
+    close(k.linear_skinny(xd, dev(w), dev(b), out_scale=0.7), rnd(rnd(acc + b.float()) * 0.7), torch.bfloat16, tol=8e-3)
+    out32 = k.linear_skinny(xd, dev(w), out_scale=0.25, out_f32=True)
+    assert out32.dtype == torch.float32
+    close(out32, rnd(acc) * 0.25, torch.bfloat16, tol=4e-3)
+    # the dispatcher sends these sizes to the same kernel, and more rows to the library
+    assert torch.equal(k.linear(xd, dev(w)), k.linear_skinny(xd, dev(w)))
+
+
+@pytest.mark.parametrize("M", [1, 8, 20, 64])
+@pytest.mark.parametrize("I,Kd", [(16, 64), (200, 96), (2048, 1024)])
+def test_linear_skinny_swiglu_matches_the_unfused_chain(M, I, Kd):
+    g = torch.Generator().manual_seed(M + I)
+    x = randn(g, M, Kd, dtype=torch.bfloat16)
+    w = randn(g, 2 * I, Kd, dtype=torch.bfloat16, scale=0.1)
+    k = K()
+    rnd = rnd_of(torch.bfloat16)
+    gu = rnd(x.float() @ w.float().T)
+    gate = rnd(gu[:, :I] * 0.9)
+    want = rnd(rnd(P.silu(gate)) * gu[:, I:])
+    close(k.linear_skinny(dev(x), dev(w), swiglu_scale=0.9), want, torch.bfloat16, tol=1e-2)
+    close(k.linear_swiglu(dev(x), dev(w), 0.9), want, torch.bfloat16, tol=1e-2)
+
+
+def test_linear_many_rows_goes_to_the_library_with_the_same_epilogues():
+    g = torch.Generator().manual_seed(4)
+    x = randn(g, 130, 256, dtype=torch.bfloat16)
+    w = randn(g, 2 * 96, 256, dtype=torch.bfloat16, scale=0.1)
+    k = K()
+    rnd = rnd_of(torch.bfloat16)
+    acc = rnd(x.float() @ w.float().T)
+    close(k.linear(dev(x), dev(w), out_scale=1.1), rnd(acc * 1.1), torch.bfloat16, tol=8e-3)
+    close(k.linear_swiglu(dev(x), dev(w), 0.9), rnd(rnd(P.silu(rnd(acc[:, :96] * 0.9))) * acc[:, 96:]), torch.bfloat16, tol=1e-2)
+
+
+def test_ssm_scan_with_the_gate_in_its_epilogue():
+    g = torch.Generator().manual_seed(12)
+    nh, Pd, N, G = 6, 24, 32, 2
+    inner = nh * Pd
+    k = K()
+    for dtype in DTYPES:
+        n = 9
+        conv = randn(g, n, inner + 2 * G * N, dtype=dtype)
+        z = randn(g, n, inner + 3, dtype=dtype)
+        dt = randn(g, n, nh, dtype=dtype)
+        A_log, dt_bias, D = torch.rand(nh, generator=g), torch.randn(nh, generator=g) - 2, torch.randn(nh, generator=g)
+        cu, sp = packed_batch([5, 4], [0, 0])
+        args = (dev(A_log), dev(dt_bias), dev(D))
+        rest = (dev(cu), dev(sp), dev(torch.tensor([1, 0], dtype=torch.int32)), 2, nh, Pd, N, G, 0.8)
+        st1 = torch.zeros(2, nh, Pd, N).cuda()
+        st2 = torch.zeros(2, nh, Pd, N).cuda()
+        y = k.ssm_scan(dev(conv), dev(dt), *args, st1, *rest)
+        zd = dev(z)[:, :inner]
+        fused = k.ssm_scan(dev(conv), dev(dt), *args, st2, *rest, gate=zd, gate_scale=0.6)
+        unfused = k.gated_rmsnorm(y, zd, None, 1e-5, 1, 0.6, k.GATE_ONLY)
+        assert torch.equal(fused, unfused)
+        assert torch.equal(st1, st2)
+
+
 # --------------------------------------------------------------------------- sampling
 def test_sample_greedy_is_argmax_lowest_index():
     from logssms_b200.sampling import sample_tokens
