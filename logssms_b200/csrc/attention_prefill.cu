@@ -1,0 +1,232 @@
+// Causal grouped-query attention for prompt portions over the paged cache, on tensor cores (bfloat16).
+//
+// One CTA per (tile of 64 query tokens of one request, query head), 4 warps x 16 query rows.  The
+// keys a tile may see (everything the request has in the cache up to the tile's last token, which
+// includes earlier portions and the keys this step stored) are walked in tiles of 64: K and V rows
+// are gathered page by page into shared memory with 16-byte cp.async (double buffered), S = Q K^T and
+// O += P V run on mma.sync m16n8k16 (bfloat16 in, float32 accumulate), the softmax is the online
+// form with float32 maximum, sum and output, masked by absolute position (causal, optional sliding
+// window).  P is rounded to bfloat16 for the second product, as every flash-attention kernel does.
+// Head sizes: multiples of 16 up to 256; any page size; any head counts (a CTA reads its key/value
+// head's rows again for each query head of the group; they come from L2).
+//
+// Formula: python/logssms/layers/attention_backend/fi.py:175-190 (causal, scale head_dim^-1/2);
+// chunked prompts: the query at absolute position p sees keys 0..p.
+#include "lb200/common.cuh"
+using namespace lb200;
+
+namespace {
+constexpr int kQTile = 64, kKTile = 64, kWarps = 4, kThreads = kWarps * 32;
+typedef __nv_bfloat16 bf16;
+
+struct PrefillArgs {
+    const bf16* q; const bf16* k_cache; const bf16* v_cache; bf16* out;
+    const int* block_table; int bt_stride;
+    const int* cu_seqlens; const int* start_pos;
+    const int* tiles;                      // [n_tiles][2]: request index in the batch, first token of the tile in its portion
+    int Hq, Hkv, hd, page_size, window;
+    float scale_log2;                      // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;           // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// HDT: head_dim / 16, rounded up to the instantiated size (4, 8 or 16); loops are cut at the real hd.
+template <int HDT>
+__global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int hd = a.hd;
+    const int ld = hd + 8;                               // row stride in elements: an odd number of 16-byte pieces
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [64][ld]
+    bf16* k_s = q_s + kQTile * ld;                       // [2][64][ld]
+    bf16* v_s = k_s + 2 * kKTile * ld;                   // [2][64][ld]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
+    const int h = blockIdx.y, kvh = h / (a.Hq / a.Hkv);
+    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
+    const int rows = min(kQTile, len - q0);              // valid query rows of this tile
+    const int pos0 = a.start_pos[b] + q0;                // absolute position of row 0
+    const int last_pos = pos0 + rows - 1;
+    const int lo = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int* bt = a.block_table + (size_t)b * a.bt_stride;
+    const int pieces = hd / 8;
+
+    // Q tile -> shared memory (rows beyond the portion: zeros)
+    for (int i = threadIdx.x; i < kQTile * pieces; i += kThreads) {
+        const int r = i / pieces, c = i % pieces;
+        const bf16* src = a.q + ((size_t)(begin + q0 + min(r, rows - 1)) * a.Hq + h) * hd + c * 8;
+        cp_async16(q_s + r * ld + c * 8, src, r < rows);
+    }
+    const int kt_begin = lo / kKTile, kt_end = last_pos / kKTile + 1;
+    auto load_kv = [&](int kt, int buf) {
+        bf16* kd = k_s + buf * kKTile * ld;
+        bf16* vd = v_s + buf * kKTile * ld;
+        for (int i = threadIdx.x; i < kKTile * pieces; i += kThreads) {
+            const int r = i / pieces, c = i % pieces;
+            const int j = kt * kKTile + r;
+            const bool valid = j >= lo && j <= last_pos;
+            size_t off = 0;
+            if (valid) off = (((size_t)bt[j / a.page_size] * a.page_size + (j % a.page_size)) * a.Hkv + kvh) * hd + c * 8;
+            cp_async16(kd + r * ld + c * 8, a.k_cache + off, valid);
+            cp_async16(vd + r * ld + c * 8, a.v_cache + off, valid);
+        }
+    };
+    load_kv(kt_begin, 0);
+    cp_async_commit();
+
+    float o[HDT * 2][4];
+#pragma unroll
+    for (int i = 0; i < HDT * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows g and g + 8 of this warp's 16
+    const int row0 = warp * 16 + g, row1 = row0 + 8;
+    const int p0 = pos0 + row0, p1 = pos0 + row1;                  // absolute positions (rows beyond `rows` are never stored)
+    const int lo0 = a.window > 0 ? p0 - a.window + 1 : 0, lo1 = a.window > 0 ? p1 - a.window + 1 : 0;
+
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
+        const int buf = (kt - kt_begin) & 1;
+        if (kt + 1 < kt_end) load_kv(kt + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* kb = k_s + buf * kKTile * ld;
+        const bf16* vb = v_s + buf * kKTile * ld;
+        if (warp * 16 < rows) {
+            // S = Q K^T for this warp's 16 rows and the tile's 64 keys
+            float s[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < HDT; ++kk) {
+                if (kk * 16 < hd) {
+                    unsigned qa[4];
+                    ldsm_x4(qa, q_s + (warp * 16 + (lane & 15)) * ld + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                    for (int n2 = 0; n2 < 4; ++n2) {           // two key tiles of 8 per ldmatrix
+                        unsigned kf[4];
+                        const int mi = lane >> 3;
+                        ldsm_x4(kf, kb + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * ld + kk * 16 + (mi & 1) * 8);
+                        mma_bf16(s[2 * n2], qa, kf[0], kf[1]);
+                        mma_bf16(s[2 * n2 + 1], qa, kf[2], kf[3]);
+                    }
+                }
+            }
+            // mask by absolute position, running maximum
+            const int j0 = kt * kKTile;
+            float mx0 = m0, mx1 = m1;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + n * 8 + 2 * t + (e & 1);
+                    const bool top = e < 2;
+                    const bool ok = top ? (j <= p0 && j >= lo0) : (j <= p1 && j >= lo1);
+                    const float v = ok ? s[n][e] * a.scale_log2 : -INFINITY;
+                    s[n][e] = v;
+                    if (top) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            // a row that has seen no key yet keeps maximum -inf: use 0 as the reference so that exp2(-inf - 0) = 0
+            const float ref0 = mx0 == -INFINITY ? 0.f : mx0, ref1 = mx1 == -INFINITY ? 0.f : mx1;
+            const float alpha0 = exp2f(m0 - ref0), alpha1 = exp2f(m1 - ref1);
+            m0 = mx0; m1 = mx1;
+            float sum0 = 0.f, sum1 = 0.f;
+            unsigned pa[4][4];                                  // P as the A operand: 4 k-steps of 16 keys
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const float e0 = exp2f(s[n][0] - ref0), e1 = exp2f(s[n][1] - ref0);
+                const float e2 = exp2f(s[n][2] - ref1), e3 = exp2f(s[n][3] - ref1);
+                sum0 += e0 + e1; sum1 += e2 + e3;
+                pa[n >> 1][(n & 1) * 2] = pack_bf16(e0, e1);
+                pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(e2, e3);
+            }
+            l0 = l0 * alpha0 + sum0;
+            l1 = l1 * alpha1 + sum1;
+#pragma unroll
+            for (int i = 0; i < HDT * 2; ++i) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                for (int d2 = 0; d2 < HDT; ++d2) {               // two output tiles of 8 columns per ldmatrix
+                    if (d2 * 16 < hd) {
+                        unsigned vf[4];
+                        const int mi = lane >> 3;
+                        ldsm_x4_t(vf, vb + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * ld + d2 * 16 + (mi >> 1) * 8);
+                        mma_bf16(o[2 * d2], pa[kk], vf[0], vf[1]);
+                        mma_bf16(o[2 * d2 + 1], pa[kk], vf[2], vf[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+#pragma unroll
+    for (int i = 0; i < HDT * 2; ++i) {
+        const int d = i * 8 + 2 * t;
+        if (d < hd) {
+            if (row0 < rows)
+                *reinterpret_cast<unsigned*>(a.out + ((size_t)(begin + q0 + row0) * a.Hq + h) * hd + d) =
+                    pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+            if (row1 < rows)
+                *reinterpret_cast<unsigned*>(a.out + ((size_t)(begin + q0 + row1) * a.Hq + h) * hd + d) =
+                    pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+        }
+    }
+}
+
+template <int HDT>
+int launch_hdt(const PrefillArgs& a, int n_tiles, cudaStream_t s) {
+    const size_t smem = (size_t)(kQTile + 4 * kKTile) * (a.hd + 8) * sizeof(bf16);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(attn_prefill_kernel<HDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_prefill_kernel<HDT><<<dim3(n_tiles, a.Hq), kThreads, smem, s>>>(a);
+    return launch_status();
+}
+}  // namespace
+
+// q, out: [tokens, Hq, hd] bfloat16; caches [pages, page_size, Hkv, hd]; tiles: int32 [n_tiles, 2]
+// (request index, first token of the tile within the request's portion; 64 tokens per tile).
+extern "C" int lb_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                    const int* block_table, int bt_stride, const int* cu_seqlens,
+                                    const int* start_pos, const int* tiles, int n_tiles, int Hq, int Hkv, int hd,
+                                    int page_size, float scale, int window, int dtype, void* stream) {
+    if (n_tiles <= 0) return kOk;
+    if (dtype != kBF16) return kBadDType;
+    if (hd <= 0 || hd > 256 || hd % 16 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0) return kBadSize;
+    if (Hq > 65535) return kTooLarge;
+    PrefillArgs a{(const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table, bt_stride,
+                  cu_seqlens, start_pos, tiles, Hq, Hkv, hd, page_size, window, scale * 1.4426950408889634f};
+    if (hd <= 64) return launch_hdt<4>(a, n_tiles, (cudaStream_t)stream);
+    if (hd <= 128) return launch_hdt<8>(a, n_tiles, (cudaStream_t)stream);
+    return launch_hdt<16>(a, n_tiles, (cudaStream_t)stream);
+}

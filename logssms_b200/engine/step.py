@@ -253,6 +253,7 @@ class Engine:
             token_req=view(2), cu_seqlens=view(3), start_pos=view(4), slots=view(5),
             block_tables=block_tables, slot_mappings=slot_mappings, logit_rows=view(6), cache=self.cache,
             max_context=max_context if static is None else self.max_seq_len,
+            host_lens=None if static is not None else lens, host_starts=None if static is not None else starts,
         )
         if static is not None:
             static.ctx = ctx

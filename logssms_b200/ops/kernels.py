@@ -308,6 +308,43 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return out
 
 
+def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                      cu_seqlens: torch.Tensor, start_pos: torch.Tensor, tiles: torch.Tensor, num_tiles: int,
+                      scale: float, window: int = 0, *, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tensor-core attention for prompt portions (bfloat16).  `tiles`: int32 [n, 2] = (request index,
+    first token of a 64-token tile within that request's portion).  Rows of `out` that no tile covers
+    are left as they are.  Other arguments as for `paged_attention`."""
+    _cuda(q, k_cache, v_cache, block_table, cu_seqlens, start_pos, tiles)
+    tokens, Hq, hd = q.shape
+    _need(q.dtype == torch.bfloat16, "attention_prefill is the bfloat16 kernel; float32 runs the general kernel")
+    _need(q.is_contiguous(), "q must be contiguous")
+    _need(k_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
+          and k_cache.dtype == q.dtype == v_cache.dtype and k_cache.shape[3] == hd,
+          "caches must be contiguous [pages, page_size, kv_heads, head_dim] of q's dtype")
+    page_size, Hkv = k_cache.shape[1], k_cache.shape[2]
+    _need(hd % 16 == 0 and hd <= 256, f"attention takes head sizes in steps of 16 up to 256, got {hd}")
+    _need(Hq % Hkv == 0, f"query heads ({Hq}) must be a multiple of key/value heads ({Hkv})")
+    _need(block_table.dim() == 2 and block_table.dtype == torch.int32 and block_table.stride(1) == 1,
+          "block table must be a row-major int32 matrix")
+    _i32(cu_seqlens, "cu_seqlens")
+    _i32(start_pos, "start_pos")
+    _i32(tiles, "tiles")
+    _need(tiles.numel() >= 2 * num_tiles, "tiles holds fewer pairs than num_tiles")
+    if out is None:
+        out = torch.empty_like(q)
+    _need(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+    f = _fn("attention_prefill", "lb_attention_prefill",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
+             _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), num_tiles, Hq, Hkv, hd, page_size, scale,
+             int(window or 0), _code(q), _stream()), "attention_prefill")
+    return out
+
+
+ATTENTION_TILE = 64        # query tokens per CTA of the prefill kernel
+
+
 # --------------------------------------------------------------------------- Mamba2
 def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
                   cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int,

@@ -18,7 +18,7 @@ class Attention(Part):
     Checkpoint tensors `q_proj / k_proj / v_proj .weight` are concatenated (rows q | k | v) at
     bind time, as the reference merges them at load (python/logssms/models/weight.py:27-31);
     the flow is python/logssms/layers/attention.py:115-167."""
-    kernels = ("rope", "attention_decode", "linear_skinny")
+    kernels = ("rope", "attention_decode", "attention_prefill", "linear_skinny")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
         self.spec = spec
@@ -63,7 +63,18 @@ class Attention(Part):
         k_cache, v_cache, group = ctx.cache.kv(cache_layer)
         q = K.rope_kv_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions, ctx.slot_mappings[group],
                             self.position.table, k_cache, v_cache, s.key_scale, writes_cache)
-        splits = ctx.attention_splits or K.attention_splits(T, s.num_heads, s.num_kv_heads, ctx.max_context)
-        o = K.attention_decode(q, k_cache, v_cache, ctx.block_tables[group], ctx.token_req, ctx.positions,
-                               self.scale, s.window or 0, splits=splits)
+        tables = ctx.block_tables[group]
+        window = s.window or 0
+        o = None
+        token_list, n_short = None, T
+        if q.dtype == torch.bfloat16 and ctx.has_long_portions:
+            # long portions on the tensor-core kernel; what is left (decoded tokens, short portions) token by token
+            tiles, n_tiles = ctx.long_portion_tiles(K.ATTENTION_TILE)
+            o = K.attention_prefill(q, k_cache, v_cache, tables, ctx.cu_seqlens, ctx.start_pos, tiles, n_tiles,
+                                    self.scale, window)
+            token_list, n_short = ctx.short_portion_tokens()
+        if n_short > 0:
+            splits = ctx.attention_splits or K.attention_splits(n_short, s.num_heads, s.num_kv_heads, ctx.max_context)
+            o = K.attention_decode(q, k_cache, v_cache, tables, ctx.token_req, ctx.positions, self.scale, window,
+                                   splits=splits, token_list=token_list, out=o)
         return K.linear(o.view(T, self.q_size), self.o_weight)

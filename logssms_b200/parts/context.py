@@ -4,7 +4,10 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any
 
+import numpy as np
 import torch
+
+SHORT_PORTION = 8      # a portion of at most this many tokens is run token by token (the decode kernels)
 
 
 @dataclass(frozen=True)
@@ -38,4 +41,42 @@ class StepContext:
     cache: Any                           # the CacheManager
     max_context: int = 0                 # most keys any token of this step sees (host)
     attention_splits: int = 0            # fixed number of key ranges per context (0: chosen per call)
+    host_lens: Any = None                # numpy [B]: tokens each request brings (None: unknown, treat all as short)
+    host_starts: Any = None              # numpy [B]: tokens each request had before this step
     extras: dict = field(default_factory=dict)
+
+    # ---- work lists that kernels for long portions need; built on the host on first use, then cached
+    @property
+    def has_long_portions(self) -> bool:
+        return self.host_lens is not None and self.max_len > SHORT_PORTION
+
+    def _upload(self, array) -> torch.Tensor:
+        return torch.from_numpy(np.ascontiguousarray(array, dtype=np.int32)).to(self.token_ids.device, non_blocking=True)
+
+    def long_portion_tiles(self, tile: int) -> tuple[torch.Tensor, int]:
+        """int32 [n, 2] on the device: (request index in the batch, first token within its portion) for
+        every run of `tile` tokens of every portion longer than SHORT_PORTION."""
+        key = ("tiles", tile)
+        if key not in self.extras:
+            pairs = [(b, t0) for b, n in enumerate(self.host_lens) if n > SHORT_PORTION for t0 in range(0, int(n), tile)]
+            self.extras[key] = (self._upload(np.asarray(pairs, dtype=np.int32).reshape(-1, 2)), len(pairs))
+        return self.extras[key]
+
+    def short_portion_tokens(self) -> tuple[torch.Tensor, int]:
+        """int32 token indices (rows of this step's batch) of all portions of at most SHORT_PORTION tokens."""
+        key = "short_tokens"
+        if key not in self.extras:
+            cu = np.concatenate([[0], np.cumsum(self.host_lens)])
+            idx = [t for b, n in enumerate(self.host_lens) if n <= SHORT_PORTION for t in range(int(cu[b]), int(cu[b + 1]))]
+            self.extras[key] = (self._upload(np.asarray(idx, dtype=np.int32)), len(idx))
+        return self.extras[key]
+
+    def requests_by_portion(self) -> tuple[torch.Tensor, int, torch.Tensor, int]:
+        """(long request indices, their count, short request indices, their count), int32 on the device."""
+        key = "requests_by_portion"
+        if key not in self.extras:
+            long_r = [b for b, n in enumerate(self.host_lens) if n > SHORT_PORTION]
+            short_r = [b for b, n in enumerate(self.host_lens) if n <= SHORT_PORTION]
+            self.extras[key] = (self._upload(np.asarray(long_r, dtype=np.int32)), len(long_r),
+                                self._upload(np.asarray(short_r, dtype=np.int32)), len(short_r))
+        return self.extras[key]

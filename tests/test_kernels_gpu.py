@@ -270,6 +270,55 @@ def test_attention_decode_token_list_leaves_other_rows(dtype):
     assert bool((out[dev(~mask)] == 7.0).all())
 
 
+def prefill_inputs(case, lengths, new):
+    cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32)
+    start = torch.tensor([n - m for n, m in zip(lengths, new)], dtype=torch.int32)
+    tiles = torch.tensor([(b, t0) for b, m in enumerate(new) for t0 in range(0, m, 64)], dtype=torch.int32)
+    return cu, start, tiles
+
+
+@pytest.mark.parametrize("shape", ATTN_SHAPES)
+def test_attention_prefill_kernel_over_pages_and_earlier_portions(shape):
+    Hq, Hkv, hd, page = shape
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(hd * 3 + Hq)
+    lengths, new = [70, 333, 64, 129, 200, 9], [70, 100, 64, 65, 13, 9]      # whole prompts and later portions
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new)
+    cu, start, tiles = prefill_inputs(case, lengths, new)
+    k = K()
+    scale = hd ** -0.5
+    out = k.attention_prefill(dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(cu), dev(start),
+                              dev(tiles), tiles.shape[0], scale)
+    close(out, rnd_of(dtype)(attention_reference(case, scale, 0, ref_dtype(dtype))), dtype)
+
+
+def test_attention_prefill_finds_a_far_key_honours_a_window_and_leaves_other_rows():
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(15)
+    Hq, Hkv, hd, page = 8, 2, 64, 64
+    lengths, new = [700, 50, 257], [130, 50, 70]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new, plant=True)
+    cu, start, tiles = prefill_inputs(case, lengths, new)
+    k = K()
+    scale = hd ** -0.5
+    args = (dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(cu), dev(start))
+    rd = ref_dtype(dtype)
+    want = attention_reference(case, scale, 0, rd)
+    v3 = case["values"][0].to(rd)[3].repeat_interleave(Hq // Hkv, 0)
+    assert float((want[0] - v3).abs().max()) < 0.05          # the planted far key dominates
+    close(k.attention_prefill(*args, dev(tiles), tiles.shape[0], scale), rnd_of(dtype)(want), dtype)
+    for window in (1, 64, 65, 300):
+        want_w = rnd_of(dtype)(attention_reference(case, scale, window, rd))
+        close(k.attention_prefill(*args, dev(tiles), tiles.shape[0], scale, window), want_w, dtype)
+    # only the second request's tile: the other rows stay as they were
+    out = torch.full_like(dev(case["q"]), 7.0)
+    only = torch.tensor([[1, 0]], dtype=torch.int32)
+    k.attention_prefill(*args, dev(only), 1, scale, out=out)
+    lo, hi = int(cu[1]), int(cu[2])
+    close(out[lo:hi], rnd_of(dtype)(want)[lo:hi], dtype)
+    assert bool((out[:lo] == 7.0).all()) and bool((out[hi:] == 7.0).all())
+
+
 # --------------------------------------------------------------------------- Mamba2: conv and scan
 def packed_batch(lens, starts):
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
