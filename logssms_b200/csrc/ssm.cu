@@ -10,7 +10,8 @@
 //
 // This kernel runs a portion of any length from the request's saved state and writes the state back
 // in place; a request whose portion starts at position 0 starts from zeros whatever the slot holds.
-// A single decoded token is a portion of length one.  Grid (head, request, P tile of 16); 128 threads
+// A single decoded token is a portion of length one.  `req_list` restricts the launch to some requests of
+// the batch (B then counts the list).  Grid (head, request, P tile of 16); 128 threads
 // = 16 values of p x 8 lanes over N; each lane owns N/8 state values in registers (float4 strided),
 // the sum over N ends with three shuffles.
 #include "lb200/common.cuh"
@@ -29,6 +30,7 @@ struct SsmArgs {
     const int* cu_seqlens; const int* start_pos; const int* slots;
     int nh, P, N, G; float dt_scale;
     const void* gate; long gate_stride; float gate_scale;   // optional [tokens, nh * P] view: y *= silu(gate * scale)
+    const int* req_list;                         // optional: the requests (indices in the batch) to run
 };
 
 template <typename T> __device__ __forceinline__ void load4(const T* p, float* f);
@@ -46,7 +48,7 @@ template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bflo
 // NPT: state values per thread (N <= 8 * NPT).  ALIGNED: 4-element vector loads of B and C are legal.
 template <typename T, int NPT, bool ALIGNED>
 __global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
-    const int h = blockIdx.x, b = blockIdx.y;
+    const int h = blockIdx.x, b = a.req_list ? a.req_list[blockIdx.y] : blockIdx.y;
     const int pi = threadIdx.x / kLanesN, nl = threadIdx.x % kLanesN;
     const int p = blockIdx.z * kPTile + pi;
     const bool p_ok = p < a.P;
@@ -150,13 +152,13 @@ int launch(const SsmArgs& a, int B, cudaStream_t s) {
 extern "C" int lb_ssm_scan(const void* conv, int C, const void* dt, long dt_stride, const float* A_log,
                            const float* dt_bias, const float* D, float* state, void* y, const int* cu_seqlens,
                            const int* start_pos, const int* slots, int B, int nh, int P, int N, int G,
-                           float dt_scale, const void* gate, long gate_stride, float gate_scale, int dtype,
-                           void* stream) {
+                           float dt_scale, const void* gate, long gate_stride, float gate_scale,
+                           const int* req_list, int dtype, void* stream) {
     if (B <= 0) return kOk;
     if (nh <= 0 || P <= 0 || N <= 0 || G <= 0 || nh % G || N % 4) return kBadSize;
     if (C != nh * P + 2 * G * N) return kBadSize;
     SsmArgs a{conv, C, dt, dt_stride, A_log, dt_bias, D, state, y, cu_seqlens, start_pos, slots, nh, P, N, G, dt_scale,
-              gate, gate_stride, gate_scale};
+              gate, gate_stride, gate_scale, req_list};
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, B, (cudaStream_t)stream));
     return kOk;
 }

@@ -376,11 +376,19 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
 def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
              state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor,
              num_requests: int, num_heads: int, head_dim: int, state_dim: int, num_groups: int,
-             dt_scale: float, gate: torch.Tensor | None = None, gate_scale: float = 1.0) -> torch.Tensor:
+             dt_scale: float, gate: torch.Tensor | None = None, gate_scale: float = 1.0, *,
+             request_list: torch.Tensor | None = None, num_listed: int = 0,
+             out: torch.Tensor | None = None) -> torch.Tensor:
     """conv: [tokens, nh*P + 2*G*N] contiguous (x | B | C); dt: [tokens, nh] view; state: float32
     [slots, nh, P, N], updated in place.  Returns y [tokens, nh*P]; with `gate` ([tokens, nh*P] view)
-    the result is y * silu(gate * gate_scale), the gate of a mixer that has no norm."""
-    _cuda(conv, dt, A_log, dt_bias, D, state, cu_seqlens, start_pos, slots, gate)
+    the result is y * silu(gate * gate_scale), the gate of a mixer that has no norm.  `request_list`
+    (int32 indices into the batch, `num_listed` of them) restricts the call to those requests; the rows
+    of `out` that belong to other requests are left as they are."""
+    _cuda(conv, dt, A_log, dt_bias, D, state, cu_seqlens, start_pos, slots, gate, request_list, out)
+    if request_list is not None:
+        _i32(request_list, "request_list")
+        _need(request_list.numel() >= num_listed, "request_list is shorter than num_listed")
+        num_requests = num_listed
     if gate is not None:
         _need(gate.shape == (conv.shape[0], num_heads * head_dim) and gate.stride(1) == 1 and gate.dtype == conv.dtype,
               "gate must be a [tokens, heads * head_dim] view of the activation dtype")
@@ -394,14 +402,62 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
     _need(state_dim % 4 == 0 and state_dim <= 256, f"state sizes in steps of 4 up to 256 are built, got {state_dim}")
     for t, n in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
         _i32(t, n)
-    y = torch.empty((tokens, num_heads * head_dim), dtype=conv.dtype, device=conv.device)
+    y = out if out is not None else torch.empty((tokens, num_heads * head_dim), dtype=conv.dtype, device=conv.device)
+    _need(y.shape == (tokens, num_heads * head_dim) and y.dtype == conv.dtype and y.is_contiguous(), "out must be [tokens, heads * head_dim]")
     f = _fn("ssm", "lb_ssm_scan", [c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                   c_long, c_float, c_int, c_void_p])
+                                   c_long, c_float, c_void_p, c_int, c_void_p])
     _check(f(_ptr(conv), C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(state), _ptr(y),
              _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), num_requests, num_heads, head_dim, state_dim,
-             num_groups, dt_scale, _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale, _code(conv),
-             _stream()), "ssm_scan")
+             num_groups, dt_scale, _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale,
+             _ptr(request_list), _code(conv), _stream()), "ssm_scan")
+    return y
+
+
+def ssd_chunk_len(chunk_size: int, head_dim: int, state_dim: int) -> int:
+    """Chunk length the tensor-core SSD kernels will use for these sizes (at most `chunk_size`), or 0
+    when they do not take them (then the token-by-token scan runs everything)."""
+    lib = build.load("ssd")
+    f = lib.lb_ssd_chunk_len
+    f.argtypes, f.restype = [c_int, c_int, c_int], c_int
+    return int(f(int(chunk_size), int(head_dim), int(state_dim)))
+
+
+def ssd_prefill(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
+                state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor,
+                chunks: torch.Tensor, num_chunks: int, req_chunks: torch.Tensor, num_long: int, chunk_len: int,
+                num_heads: int, head_dim: int, state_dim: int, num_groups: int, dt_scale: float,
+                gate: torch.Tensor | None = None, gate_scale: float = 1.0, *, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Chunked scan of the listed prompt portions (bfloat16, tensor cores).  `chunks`: int32 [n, 2] =
+    (request index, first token of the chunk within its portion); `req_chunks`: int32 [m, 3] = (request
+    index, its first chunk, its number of chunks).  Arguments otherwise as `ssm_scan`; rows of `out`
+    outside the listed requests are left as they are."""
+    _cuda(conv, dt, A_log, dt_bias, D, state, cu_seqlens, start_pos, slots, chunks, req_chunks, gate, out)
+    tokens, C = conv.shape
+    _need(conv.dtype == torch.bfloat16 and conv.is_contiguous(), "ssd_prefill takes a contiguous bfloat16 conv output")
+    _need(dt.shape == (tokens, num_heads) and dt.stride(1) == 1 and dt.dtype == conv.dtype, "dt must be a [tokens, heads] view")
+    for t, n in ((A_log, "A_log"), (dt_bias, "dt_bias"), (D, "D")):
+        _need(t.dtype == torch.float32 and t.shape == (num_heads,) and t.is_contiguous(), f"{n} must be float32 [heads]")
+    _need(state.dtype == torch.float32 and state.is_contiguous()
+          and state.shape[1:] == (num_heads, head_dim, state_dim), "SSM state must be float32 [slots, heads, P, N]")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots"), (chunks, "chunks"), (req_chunks, "req_chunks")):
+        _i32(t, n)
+    _need(chunks.numel() >= 2 * num_chunks and req_chunks.numel() >= 3 * num_long, "work lists are shorter than their counts")
+    if gate is not None:
+        _need(gate.shape == (tokens, num_heads * head_dim) and gate.stride(1) == 1 and gate.dtype == conv.dtype,
+              "gate must be a [tokens, heads * head_dim] view of the activation dtype")
+    y = out if out is not None else torch.empty((tokens, num_heads * head_dim), dtype=conv.dtype, device=conv.device)
+    _need(y.shape == (tokens, num_heads * head_dim) and y.dtype == conv.dtype and y.is_contiguous(), "out must be [tokens, heads * head_dim]")
+    scratch = torch.empty((max(num_chunks, 1), num_heads, head_dim, state_dim), dtype=torch.float32, device=conv.device)
+    chunk_a = torch.empty((max(num_chunks, 1), num_heads), dtype=torch.float32, device=conv.device)
+    f = _fn("ssd", "lb_ssd_prefill", [c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                      c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_float, c_int, c_void_p])
+    _check(f(_ptr(conv), C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(state), _ptr(y),
+             _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(req_chunks), num_long,
+             _ptr(scratch), _ptr(chunk_a), num_heads, head_dim, state_dim, num_groups, chunk_len, dt_scale,
+             _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale, _code(conv), _stream()),
+           "ssd_prefill", f"(head_dim {head_dim}, state_dim {state_dim}, chunk {chunk_len})", launches=3)
     return y
 
 

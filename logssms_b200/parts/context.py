@@ -71,6 +71,22 @@ class StepContext:
             self.extras[key] = (self._upload(np.asarray(idx, dtype=np.int32)), len(idx))
         return self.extras[key]
 
+    def long_portion_chunks(self, chunk: int) -> tuple[torch.Tensor, int, torch.Tensor, int]:
+        """Work lists of a chunked scan over the long portions: int32 [n, 2] (request index, first token of
+        the chunk within its portion) with its count, and int32 [m, 3] (request index, its first chunk,
+        its number of chunks) with its count."""
+        key = ("chunks", chunk)
+        if key not in self.extras:
+            chunks, per_request = [], []
+            for b, n in enumerate(self.host_lens):
+                if n > SHORT_PORTION:
+                    first = len(chunks)
+                    chunks += [(b, t0) for t0 in range(0, int(n), chunk)]
+                    per_request.append((b, first, len(chunks) - first))
+            self.extras[key] = (self._upload(np.asarray(chunks, dtype=np.int32).reshape(-1, 2)), len(chunks),
+                                self._upload(np.asarray(per_request, dtype=np.int32).reshape(-1, 3)), len(per_request))
+        return self.extras[key]
+
     def requests_by_portion(self) -> tuple[torch.Tensor, int, torch.Tensor, int]:
         """(long request indices, their count, short request indices, their count), int32 on the device."""
         key = "requests_by_portion"

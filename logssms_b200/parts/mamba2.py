@@ -31,13 +31,14 @@ class Mamba2(Part):
     python/logssms/kernel/linear_attention/packed_conv.py:96-140,
     python/logssms/kernel/linear_attention/mamba2.py:27-36 and :261-292,
     python/logssms/kernel/norm.py:55-86."""
-    kernels = ("conv", "ssm", "norm", "linear_skinny")
+    kernels = ("conv", "ssm", "ssd", "norm", "linear_skinny")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
         self.spec = spec
         self._perturb = perturb_init
         self.in_w = self.in_b = self.conv_w = self.conv_b = None
         self.A_log = self.dt_bias = self.D = self.norm_w = self.out_w = self.out_b = None
+        self._chunk_len = 0
 
     def param_specs(self):
         s = self.spec
@@ -76,7 +77,8 @@ class Mamba2(Part):
         self.norm_w = t.get("norm.weight")
 
     def setup(self, rt) -> None:
-        pass
+        s = self.spec
+        self._chunk_len = K.ssd_chunk_len(s.chunk_size, s.head_dim, s.state_dim) if rt.dtype == torch.bfloat16 else 0
 
     def cache_needs(self) -> CacheNeeds:
         s = self.spec
@@ -95,11 +97,19 @@ class Mamba2(Part):
         conv = K.causal_conv1d(xbc, self.conv_w, self.conv_b, states["conv"], ctx.cu_seqlens, ctx.start_pos,
                                ctx.slots, ctx.num_requests, ctx.max_len,
                                (inner, inner + s.num_groups * s.state_dim), (m[1], m[2], m[3]))
-        scan = (conv, dt, self.A_log, self.dt_bias, self.D, states["ssm"], ctx.cu_seqlens, ctx.start_pos, ctx.slots,
-                ctx.num_requests, s.num_heads, s.head_dim, s.state_dim, s.num_groups, m[4])
+        gate = None if s.gated_norm else z          # the bare gate rides in the scan's epilogue
+        head = (conv, dt, self.A_log, self.dt_bias, self.D, states["ssm"], ctx.cu_seqlens, ctx.start_pos, ctx.slots)
+        sizes = (s.num_heads, s.head_dim, s.state_dim, s.num_groups, m[4])
+        y = None
+        short_list, n_short = None, ctx.num_requests
+        if x.dtype == torch.bfloat16 and ctx.has_long_portions and self._chunk_len:
+            # long portions in chunks on the tensor cores; decoded tokens and short portions token by token
+            chunks, n_chunks, per_request, n_long = ctx.long_portion_chunks(self._chunk_len)
+            y = K.ssd_prefill(*head, chunks, n_chunks, per_request, n_long, self._chunk_len, *sizes, gate, m[0])
+            _, _, short_list, n_short = ctx.requests_by_portion()
+        if n_short > 0:
+            y = K.ssm_scan(*head, ctx.num_requests, *sizes, gate, m[0], request_list=short_list, num_listed=n_short, out=y)
         if s.gated_norm:
             mode = K.NORM_BEFORE_GATE if s.norm_before_gate else K.NORM_AFTER_GATE
-            y = K.gated_rmsnorm(K.ssm_scan(*scan), z, self.norm_w, s.norm_eps, s.num_groups, m[0], mode)
-        else:
-            y = K.ssm_scan(*scan, gate=z, gate_scale=m[0])      # the bare gate rides in the scan's epilogue
+            y = K.gated_rmsnorm(y, z, self.norm_w, s.norm_eps, s.num_groups, m[0], mode)
         return K.linear(y, self.out_w, self.out_b)

@@ -401,6 +401,86 @@ def test_ssm_scan_portions_resume_from_state(dtype, shape):
         close(torch.cat(got[r]), want[r], dtype)
 
 
+def chunk_lists(lens, L):
+    chunks, per_request = [], []
+    for b, n in enumerate(lens):
+        first = len(chunks)
+        chunks += [(b, t0) for t0 in range(0, n, L)]
+        per_request.append((b, first, len(chunks) - first))
+    return torch.tensor(chunks, dtype=torch.int32), torch.tensor(per_request, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("shape", [(4, 16, 16, 1, 8), (6, 24, 32, 2, 16), (3, 64, 128, 1, 128), (2, 40, 256, 2, 64),
+                                   (2, 128, 64, 1, 32), (5, 8, 24, 5, 256)])
+def test_ssd_prefill_in_chunks_resumes_from_state_and_matches_the_recurrence(shape):
+    nh, Pd, N, G, chunk = shape
+    dtype = torch.bfloat16
+    k = K()
+    L = k.ssd_chunk_len(chunk, Pd, N)
+    assert 0 < L <= chunk
+    g = torch.Generator().manual_seed(nh * 31 + N)
+    inner = nh * Pd
+    full, first = [150, 40, 300], [70, 17, 129]
+    convs = [randn(g, n, inner + 2 * G * N, dtype=dtype) for n in full]
+    dts = [randn(g, n, nh, dtype=dtype) for n in full]
+    zs = [randn(g, n, inner, dtype=dtype) for n in full]
+    A_log = torch.log(1 + 15 * torch.rand(nh, generator=g))
+    dt_bias = torch.randn(nh, generator=g) - 3.0
+    D = torch.randn(nh, generator=g)
+    rd, rnd = ref_dtype(dtype), rnd_of(dtype)
+    want = []
+    for c, d in zip(convs, dts):
+        n = c.shape[0]
+        x, B, Cm = c.to(rd).split([inner, G * N, G * N], 1)
+        want.append(P.ssm_recurrence(x.reshape(n, nh, Pd), d.to(rd), A_log.to(rd), dt_bias.to(rd), B.reshape(n, G, N),
+                                     Cm.reshape(n, G, N), D.to(rd), 0.8, rnd).reshape(n, inner))
+    state = torch.full((4, nh, Pd, N), float("nan"), dtype=torch.float32).cuda()
+    state_seq = torch.full((4, nh, Pd, N), float("nan"), dtype=torch.float32).cuda()
+    slots = torch.tensor([3, 1, 0], dtype=torch.int32)
+    got, got_gated = [[] for _ in full], [[] for _ in full]
+    for part in range(2):
+        cut = lambda ts: [t[:f] if part == 0 else t[f:] for t, f in zip(ts, first)]
+        cs, ds, zz = cut(convs), cut(dts), cut(zs)
+        lens = [c.shape[0] for c in cs]
+        cu, sp = packed_batch(lens, [0 if part == 0 else f for f in first])
+        chunks, per_request = chunk_lists(lens, L)
+        common = (dev(A_log), dev(dt_bias), dev(D))
+        conv_d, dt_d, z_d = torch.cat(cs).cuda(), torch.cat(ds).cuda(), torch.cat(zz).cuda()
+        lists = (dev(cu), dev(sp), dev(slots), dev(chunks), chunks.shape[0], dev(per_request), per_request.shape[0], L)
+        st_before = state.clone()
+        y = k.ssd_prefill(conv_d, dt_d, *common, state, *lists, nh, Pd, N, G, 0.8)
+        yg = k.ssd_prefill(conv_d, dt_d, *common, st_before, *lists, nh, Pd, N, G, 0.8, z_d, 0.6)
+        assert torch.equal(yg, k.gated_rmsnorm(y, z_d, None, 1e-5, 1, 0.6, k.GATE_ONLY))
+        k.ssm_scan(conv_d, dt_d, *common, state_seq, dev(cu), dev(sp), dev(slots), 3, nh, Pd, N, G, 0.8)
+        for r in range(3):
+            got[r].append(y[int(cu[r]):int(cu[r + 1])].cpu())
+    for r in range(3):
+        close(torch.cat(got[r]), want[r], dtype)
+    live = [3, 1, 0]
+    close(state[live], state_seq[live], dtype)           # the state left behind equals the token-by-token kernel's
+
+
+def test_ssm_scan_request_list_leaves_other_rows():
+    g = torch.Generator().manual_seed(13)
+    nh, Pd, N, G = 4, 16, 16, 1
+    inner = nh * Pd
+    k = K()
+    lens = [3, 5, 2]
+    n = sum(lens)
+    conv = randn(g, n, inner + 2 * G * N, dtype=torch.bfloat16).cuda()
+    dt = randn(g, n, nh, dtype=torch.bfloat16).cuda()
+    consts = [dev(torch.rand(nh, generator=g)), dev(torch.randn(nh, generator=g) - 2), dev(torch.randn(nh, generator=g))]
+    cu, sp = packed_batch(lens, [0, 0, 0])
+    slots = dev(torch.tensor([0, 1, 2], dtype=torch.int32))
+    st_all, st_some = torch.zeros(3, nh, Pd, N).cuda(), torch.zeros(3, nh, Pd, N).cuda()
+    y_all = k.ssm_scan(conv, dt, *consts, st_all, dev(cu), dev(sp), slots, 3, nh, Pd, N, G, 1.0)
+    out = torch.full_like(y_all, 7.0)
+    picked = dev(torch.tensor([2, 0], dtype=torch.int32))
+    k.ssm_scan(conv, dt, *consts, st_some, dev(cu), dev(sp), slots, 3, nh, Pd, N, G, 1.0, request_list=picked, num_listed=2, out=out)
+    assert torch.equal(out[:3], y_all[:3]) and torch.equal(out[8:], y_all[8:]) and bool((out[3:8] == 7.0).all())
+    assert torch.equal(st_some[[0, 2]], st_all[[0, 2]]) and bool((st_some[1] == 0).all())
+
+
 # --------------------------------------------------------------------------- 32-bit matrix product
 def test_gemm_f32_is_true_32_bit():
     g = torch.Generator().manual_seed(9)
