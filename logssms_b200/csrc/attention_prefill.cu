@@ -26,6 +26,7 @@ struct PrefillArgs {
     const int* tiles;                      // [n_tiles][2]: request index in the batch, first token of the tile in its portion
     int Hq, Hkv, hd, page_size, window;
     float scale_log2;                      // softmax scale * log2(e)
+    int n_items, per_wave;                 // tiles * query heads; CTAs that start together (one per SM)
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -63,8 +64,14 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
     bf16* k_s = q_s + kQTile * ld;                       // [2][64][ld]
     bf16* v_s = k_s + 2 * kKTile * ld;                   // [2][64][ld]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
-    const int h = blockIdx.y, kvh = h / (a.Hq / a.Hkv);
+    // The host lists the tiles heaviest first.  CTAs are handed to the SMs in rounds of one per SM; every
+    // second round takes its items in reverse, so that the SM that got the heaviest item of one round
+    // gets the lightest of the next (causal tiles differ by up to the whole context in cost).
+    const int wave = blockIdx.x / a.per_wave, wave_pos = blockIdx.x % a.per_wave, wave_begin = wave * a.per_wave;
+    const int item = (wave & 1) ? wave_begin + (min(a.per_wave, a.n_items - wave_begin) - 1 - wave_pos) : (int)blockIdx.x;
+    const int tile = item / a.Hq;
+    const int b = a.tiles[2 * tile], q0 = a.tiles[2 * tile + 1];
+    const int h = item % a.Hq, kvh = h / (a.Hq / a.Hkv);
     const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
     const int rows = min(kQTile, len - q0);              // valid query rows of this tile
     const int pos0 = a.start_pos[b] + q0;                // absolute position of row 0
@@ -209,7 +216,7 @@ int launch_hdt(const PrefillArgs& a, int n_tiles, cudaStream_t s) {
     const size_t smem = (size_t)(kQTile + 4 * kKTile) * (a.hd + 8) * sizeof(bf16);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(attn_prefill_kernel<HDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attn_prefill_kernel<HDT><<<dim3(n_tiles, a.Hq), kThreads, smem, s>>>(a);
+    attn_prefill_kernel<HDT><<<dim3(a.n_items), kThreads, smem, s>>>(a);
     return launch_status();
 }
 }  // namespace
@@ -223,9 +230,17 @@ extern "C" int lb_attention_prefill(const void* q, const void* k_cache, const vo
     if (n_tiles <= 0) return kOk;
     if (dtype != kBF16) return kBadDType;
     if (hd <= 0 || hd > 256 || hd % 16 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0) return kBadSize;
-    if (Hq > 65535) return kTooLarge;
+    if ((long)n_tiles * Hq > 0x7fffffffL) return kTooLarge;
+    static int num_sms = 0;
+    if (num_sms == 0) {
+        int device = 0, count = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = 148;
+        num_sms = count;
+    }
     PrefillArgs a{(const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table, bt_stride,
-                  cu_seqlens, start_pos, tiles, Hq, Hkv, hd, page_size, window, scale * 1.4426950408889634f};
+                  cu_seqlens, start_pos, tiles, Hq, Hkv, hd, page_size, window, scale * 1.4426950408889634f,
+                  n_tiles * Hq, num_sms};
     if (hd <= 64) return launch_hdt<4>(a, n_tiles, (cudaStream_t)stream);
     if (hd <= 128) return launch_hdt<8>(a, n_tiles, (cudaStream_t)stream);
     return launch_hdt<16>(a, n_tiles, (cudaStream_t)stream);

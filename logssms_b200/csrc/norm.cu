@@ -120,9 +120,36 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int
     out[r * I + c] = from_f32<T>(a * to_f32(in[r * 2 * I + I + c]));
 }
 
+// the same for bfloat16 rows whose width is a multiple of 8: eight columns per thread, 16-byte accesses
+__global__ void swiglu_vec_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int I, float act_scale) {
+    typedef __nv_bfloat16 T;
+    const size_t r = blockIdx.y;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= I) return;
+    const uint4 gv = *reinterpret_cast<const uint4*>(in + r * 2 * I + c);
+    const uint4 uv = *reinterpret_cast<const uint4*>(in + r * 2 * I + I + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+        const float a0 = round_to<T>(silu_f(round_to<T>(g.x * act_scale)));
+        const float a1 = round_to<T>(silu_f(round_to<T>(g.y * act_scale)));
+        o2[e] = __floats2bfloat162_rn(a0 * u.x, a1 * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + r * I + c) = ov;
+}
+
 extern "C" int lb_swiglu(const void* in, void* out, int rows, int I, float act_scale, int dtype, void* stream) {
     if (rows <= 0) return kOk;
     if (I <= 0) return kBadSize;
+    if (dtype == kBF16 && I % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+        dim3 grid((I / 8 + 127) / 128, rows);
+        swiglu_vec_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, I, act_scale);
+        return launch_status();
+    }
     dim3 grid((I + 255) / 256, rows);
     LB_DISPATCH_DTYPE(dtype, swiglu_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)in, (T*)out, I, act_scale));
     return launch_status();
@@ -142,8 +169,26 @@ __global__ void scale_to_f32_kernel(const T* __restrict__ x, float* __restrict__
     if (i < n) out[i] = to_f32(x[i]) * s;
 }
 
+__global__ void scale_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, size_t n8, float s) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const uint4 v = reinterpret_cast<const uint4*>(x)[i];
+    const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(v2[e]); o2[e] = __floats2bfloat162_rn(f.x * s, f.y * s); }
+    reinterpret_cast<uint4*>(out)[i] = o;
+}
+
 extern "C" int lb_scale(const void* x, void* out, long n, float s, int to_f32_out, int dtype, void* stream) {
     if (n <= 0) return kOk;
+    if (dtype == kBF16 && !to_f32_out && n % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        const size_t n8 = (size_t)n / 8;
+        scale_vec_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n8, s);
+        return launch_status();
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     LB_DISPATCH_DTYPE(dtype, {
         if (to_f32_out) scale_to_f32_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)x, (float*)out, (size_t)n, s);

@@ -56,6 +56,11 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
 }
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 p = __bfloat1622float2(h[i]); f[2 * i] = p.x; f[2 * i + 1] = p.y; }
+}
 __host__ __device__ constexpr int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 // dt_s and the inclusive running sum a_s of dA over the chunk, for s < Lpad (s >= Lc: dt = 0, a = a_{Lc-1}).
@@ -102,16 +107,24 @@ __global__ void __launch_bounds__(kStateThreads) ssd_chunk_state_kernel(SsdArgs 
     chunk_decay(a, tok0, Lc, Lpad, h, dt_s, a_s, tot);
     const float aL = a_s[Lc - 1];
     const int g = h / (a.nh / a.G), inner = a.nh * P;
-    for (int i = threadIdx.x; i < Lpad * Ppad; i += kStateThreads) {
-        const int s = i / Ppad, p = i % Ppad;
-        float v = 0.f;
+    const int ppieces = Ppad / 8;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < Lpad * ppieces; i += kStateThreads) {
+        const int s = i / ppieces, p = (i % ppieces) * 8;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
         if (s < Lc && p < P) {
-            const float u = round_to<bf16>(__bfloat162float(a.conv[(size_t)(tok0 + s) * a.C + h * P + p]) * dt_s[s]);
-            v = u * expf(aL - a_s[s]);
+            float f[8];
+            unpack8(*reinterpret_cast<const uint4*>(a.conv + (size_t)(tok0 + s) * a.C + h * P + p), f);
+            const float dts = dt_s[s], wgt = expf(aL - a_s[s]);
+            unsigned* o = reinterpret_cast<unsigned*>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                o[e] = pack_bf16(round_to<bf16>(f[2 * e] * dts) * wgt, round_to<bf16>(f[2 * e + 1] * dts) * wgt);
         }
-        x_s[s * ldx + p] = __float2bfloat16_rn(v);
+        *reinterpret_cast<uint4*>(x_s + s * ldx + p) = packed;
     }
     const int npieces = Npad / 8;
+#pragma unroll 4
     for (int i = threadIdx.x; i < Lpad * npieces; i += kStateThreads) {
         const int s = i / npieces, c = i % npieces;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -164,12 +177,25 @@ __global__ void __launch_bounds__(256) ssd_state_pass_kernel(SsdArgs a) {
     float* sp = a.state + ((size_t)a.slots[b] * a.nh + h) * per_head + i;
     float4 S = make_float4(0.f, 0.f, 0.f, 0.f);
     if (a.start_pos[b] > 0) S = *reinterpret_cast<const float4*>(sp);
-    for (int c = c0; c < c0 + nc; ++c) {
-        float4* cell = reinterpret_cast<float4*>(a.scratch + ((size_t)c * a.nh + h) * per_head + i);
-        const float4 d = *cell;
-        const float decay = expf(a.chunk_a[(size_t)c * a.nh + h]);
-        *cell = S;                                               // what the chunk starts from
-        S.x = S.x * decay + d.x; S.y = S.y * decay + d.y; S.z = S.z * decay + d.z; S.w = S.w * decay + d.w;
+    constexpr int kAhead = 4;                                    // chunks whose dS and decay are fetched together
+    for (int c = c0; c < c0 + nc; c += kAhead) {
+        float4 d[kAhead];
+        float decay[kAhead];
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            if (c + u < c0 + nc) {
+                d[u] = *reinterpret_cast<const float4*>(a.scratch + ((size_t)(c + u) * a.nh + h) * per_head + i);
+                decay[u] = a.chunk_a[(size_t)(c + u) * a.nh + h];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            if (c + u < c0 + nc) {
+                *reinterpret_cast<float4*>(a.scratch + ((size_t)(c + u) * a.nh + h) * per_head + i) = S;   // what the chunk starts from
+                const float e = expf(decay[u]);
+                S.x = S.x * e + d[u].x; S.y = S.y * e + d[u].y; S.z = S.z * e + d[u].z; S.w = S.w * e + d[u].w;
+            }
+        }
     }
     *reinterpret_cast<float4*>(sp) = S;
 }
@@ -197,6 +223,7 @@ __global__ void __launch_bounds__(MAXT) ssd_chunk_scan_kernel(SsdArgs a) {
     const int g = h / (a.nh / a.G), inner = a.nh * P;
     const int threads = blockDim.x;
     const int npieces = Npad / 8;
+#pragma unroll 2
     for (int i = threadIdx.x; i < Lpad * npieces; i += threads) {
         const int s = i / npieces, c = i % npieces;
         uint4 vb = make_uint4(0u, 0u, 0u, 0u), vc = vb;
@@ -208,16 +235,32 @@ __global__ void __launch_bounds__(MAXT) ssd_chunk_scan_kernel(SsdArgs a) {
         *reinterpret_cast<uint4*>(b_s + s * ldn + c * 8) = vb;
         *reinterpret_cast<uint4*>(c_s + s * ldn + c * 8) = vc;
     }
-    for (int i = threadIdx.x; i < Lpad * Ppad; i += threads) {
-        const int s = i / Ppad, p = i % Ppad;
-        float v = 0.f;
-        if (s < Lc && p < P) v = __bfloat162float(a.conv[(size_t)(tok0 + s) * a.C + h * P + p]) * dt_s[s];
-        u_s[s * ldp + p] = __float2bfloat16_rn(v);
+    const int ppieces = Ppad / 8;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < Lpad * ppieces; i += threads) {
+        const int s = i / ppieces, p = (i % ppieces) * 8;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (s < Lc && p < P) {
+            float f[8];
+            unpack8(*reinterpret_cast<const uint4*>(a.conv + (size_t)(tok0 + s) * a.C + h * P + p), f);
+            const float dts = dt_s[s];
+            unsigned* o = reinterpret_cast<unsigned*>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = pack_bf16(f[2 * e] * dts, f[2 * e + 1] * dts);
+        }
+        *reinterpret_cast<uint4*>(u_s + s * ldp + p) = packed;
     }
     const float* sin = a.scratch + ((size_t)chunk * a.nh + h) * P * N;
-    for (int i = threadIdx.x; i < Ppad * Npad; i += threads) {
-        const int p = i / Npad, n = i % Npad;
-        s_s[p * ldn + n] = __float2bfloat16_rn((p < P && n < N) ? sin[(size_t)p * N + n] : 0.f);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < Ppad * npieces; i += threads) {
+        const int p = i / npieces, n = (i % npieces) * 8;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (p < P && n < N) {
+            const float4 lo = *reinterpret_cast<const float4*>(sin + (size_t)p * N + n);
+            const float4 hi = *reinterpret_cast<const float4*>(sin + (size_t)p * N + n + 4);
+            packed = make_uint4(pack_bf16(lo.x, lo.y), pack_bf16(lo.z, lo.w), pack_bf16(hi.x, hi.y), pack_bf16(hi.z, hi.w));
+        }
+        *reinterpret_cast<uint4*>(s_s + p * ldn + n) = packed;
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;

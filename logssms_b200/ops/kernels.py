@@ -369,7 +369,7 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
     _check(f(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_seqlens),
              _ptr(start_pos), _ptr(slots), num_requests, max_len, C, K, region_ends[0], region_ends[1],
              region_scales[0], region_scales[1], region_scales[2], _code(x), _stream()), "causal_conv1d",
-           launches=1 if max_len <= 64 else 2)
+           launches=1 if max_len <= 16 else 2)
     return out
 
 

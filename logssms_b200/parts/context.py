@@ -55,10 +55,12 @@ class StepContext:
 
     def long_portion_tiles(self, tile: int) -> tuple[torch.Tensor, int]:
         """int32 [n, 2] on the device: (request index in the batch, first token within its portion) for
-        every run of `tile` tokens of every portion longer than SHORT_PORTION."""
+        every run of `tile` tokens of every portion longer than SHORT_PORTION, the tile that sees the
+        most keys first (a causal tile's cost grows with its position)."""
         key = ("tiles", tile)
         if key not in self.extras:
             pairs = [(b, t0) for b, n in enumerate(self.host_lens) if n > SHORT_PORTION for t0 in range(0, int(n), tile)]
+            pairs.sort(key=lambda bt: -(int(self.host_starts[bt[0]]) + min(bt[1] + tile, int(self.host_lens[bt[0]]))))
             self.extras[key] = (self._upload(np.asarray(pairs, dtype=np.int32).reshape(-1, 2)), len(pairs))
         return self.extras[key]
 

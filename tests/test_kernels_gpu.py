@@ -109,9 +109,10 @@ def test_gated_rmsnorm(dtype, mode):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_swiglu_and_scale(dtype):
+@pytest.mark.parametrize("I", [333, 328])                  # odd width / a multiple of 8 (the 16-byte form)
+def test_swiglu_and_scale(dtype, I):
     g = torch.Generator().manual_seed(2)
-    rows, I = 9, 333
+    rows = 9
     gu = randn(g, rows, 2 * I, dtype=dtype)
     rd, rnd = ref_dtype(dtype), rnd_of(dtype)
     out = K().swiglu(dev(gu), 0.9)
@@ -327,18 +328,19 @@ def packed_batch(lens, starts):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("Kc", [2, 3, 4])
-def test_causal_conv1d_portions_resume_from_state(dtype, Kc):
+@pytest.mark.parametrize("layout", [(50, 30, 40, 3, 6), (64, 32, 48, 8, 16)])       # odd sizes / 16-byte aligned
+def test_causal_conv1d_portions_resume_from_state(dtype, Kc, layout):
     """Three requests; each is run as two portions (the second resumes from the saved window) and must
     equal the conv over the whole sequence.  Lengths include portions shorter than the kernel."""
     g = torch.Generator().manual_seed(Kc)
     k = K()
-    C, e0, e1 = 50, 30, 40
+    C, e0, e1, lead, extra = layout
     scales = (1.1, 0.9, 1.3)
     full = [70, 5, 131]
     first = [69, 1, 64]
     w = randn(g, C, Kc, scale=0.3)
     b = randn(g, C, scale=0.1)
-    xs = [randn(g, n, C + 6, dtype=dtype)[:, 3:3 + C] for n in full]
+    xs = [randn(g, n, C + extra, dtype=dtype)[:, lead:lead + C] for n in full]
     rd, rnd = ref_dtype(dtype), rnd_of(dtype)
     scale_vec = torch.cat([torch.full((e0,), scales[0]), torch.full((e1 - e0,), scales[1]), torch.full((C - e1,), scales[2])])
     want = [P.causal_conv_silu(rnd(x.to(rd) * scale_vec.to(rd)), w.to(rd), b.to(rd), rnd) for x in xs]
@@ -350,8 +352,9 @@ def test_causal_conv1d_portions_resume_from_state(dtype, Kc):
         lens = [p.shape[0] for p in pieces]
         starts = [0 if part == 0 else f for f in first]
         cu, sp = packed_batch(lens, starts)
-        wide = torch.cat([torch.cat(pieces).contiguous(), torch.zeros(sum(lens), 9, dtype=dtype)], 1).cuda()
-        out = k.causal_conv1d(wide[:, :C], dev(w), dev(b), state, dev(cu), dev(sp), dev(slots), 3, max(lens),
+        wide = torch.cat([torch.zeros(sum(lens), lead, dtype=dtype), torch.cat(pieces).contiguous(),
+                          torch.zeros(sum(lens), extra - lead, dtype=dtype)], 1).cuda()
+        out = k.causal_conv1d(wide[:, lead:lead + C], dev(w), dev(b), state, dev(cu), dev(sp), dev(slots), 3, max(lens),
                               (e0, e1), scales)
         for r in range(3):
             got[r].append(out[int(cu[r]):int(cu[r + 1])].cpu())
