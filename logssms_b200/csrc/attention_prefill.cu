@@ -27,6 +27,7 @@ struct PrefillArgs {
     int Hq, Hkv, hd, page_size, window;
     float scale_log2;                      // softmax scale * log2(e)
     int n_items, per_wave;                 // tiles * query heads; CTAs that start together (one per SM)
+    int page_shift;                        // log2(page_size), or -1 when it is no power of two
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -87,17 +88,23 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
         cp_async16(q_s + r * ld + c * 8, src, r < rows);
     }
     const int kt_begin = lo / kKTile, kt_end = last_pos / kKTile + 1;
+    // two threads per key row: one page lookup per row and tile, then 16-byte pieces side by side
+    const int ld_row = threadIdx.x >> 1, ld_half = threadIdx.x & 1;
+    const int ld_c0 = ld_half * ((pieces + 1) / 2), ld_c1 = ld_half ? pieces : (pieces + 1) / 2;
     auto load_kv = [&](int kt, int buf) {
-        bf16* kd = k_s + buf * kKTile * ld;
-        bf16* vd = v_s + buf * kKTile * ld;
-        for (int i = threadIdx.x; i < kKTile * pieces; i += kThreads) {
-            const int r = i / pieces, c = i % pieces;
-            const int j = kt * kKTile + r;
-            const bool valid = j >= lo && j <= last_pos;
-            size_t off = 0;
-            if (valid) off = (((size_t)bt[j / a.page_size] * a.page_size + (j % a.page_size)) * a.Hkv + kvh) * hd + c * 8;
-            cp_async16(kd + r * ld + c * 8, a.k_cache + off, valid);
-            cp_async16(vd + r * ld + c * 8, a.v_cache + off, valid);
+        const int j = kt * kKTile + ld_row;
+        const bool valid = j >= lo && j <= last_pos;
+        size_t off = 0;
+        if (valid) {
+            const int page = a.page_shift >= 0 ? (j >> a.page_shift) : j / a.page_size;
+            const int in_page = j - page * a.page_size;
+            off = (((size_t)bt[page] * a.page_size + in_page) * a.Hkv + kvh) * hd;
+        }
+        bf16* kd = k_s + (buf * kKTile + ld_row) * ld;
+        bf16* vd = v_s + (buf * kKTile + ld_row) * ld;
+        for (int c = ld_c0; c < ld_c1; ++c) {
+            cp_async16(kd + c * 8, a.k_cache + off + c * 8, valid);
+            cp_async16(vd + c * 8, a.v_cache + off + c * 8, valid);
         }
     };
     load_kv(kt_begin, 0);
@@ -139,26 +146,34 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
                     }
                 }
             }
-            // mask by absolute position, running maximum
+            // mask by absolute position (only on tiles that some row does not see whole), running maximum
             const int j0 = kt * kKTile;
-            float mx0 = m0, mx1 = m1;
+            const bool whole = j0 + kKTile - 1 <= pos0 && (a.window <= 0 || j0 >= pos0 + kQTile - a.window);
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+            if (!whole) {
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = j0 + n * 8 + 2 * t + (e & 1);
+                        const bool ok = e < 2 ? (j <= p0 && j >= lo0) : (j <= p1 && j >= lo1);
+                        if (!ok) s[n][e] = -INFINITY;
+                    }
+                }
+            }
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int j = j0 + n * 8 + 2 * t + (e & 1);
-                    const bool top = e < 2;
-                    const bool ok = top ? (j <= p0 && j >= lo0) : (j <= p1 && j >= lo1);
-                    const float v = ok ? s[n][e] * a.scale_log2 : -INFINITY;
-                    s[n][e] = v;
-                    if (top) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-                }
+                mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
             }
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            // a row that has seen no key yet keeps maximum -inf: use 0 as the reference so that exp2(-inf - 0) = 0
+            // m0, m1: running maxima of the scaled scores (log2 units); a row that has seen no key keeps -inf,
+            // and 0 then stands in as the reference so that exp2(-inf - 0) = 0
+            mx0 = fmaxf(m0, mx0 * a.scale_log2);
+            mx1 = fmaxf(m1, mx1 * a.scale_log2);
             const float ref0 = mx0 == -INFINITY ? 0.f : mx0, ref1 = mx1 == -INFINITY ? 0.f : mx1;
             const float alpha0 = exp2f(m0 - ref0), alpha1 = exp2f(m1 - ref1);
             m0 = mx0; m1 = mx1;
@@ -166,8 +181,8 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
             unsigned pa[4][4];                                  // P as the A operand: 4 k-steps of 16 keys
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
-                const float e0 = exp2f(s[n][0] - ref0), e1 = exp2f(s[n][1] - ref0);
-                const float e2 = exp2f(s[n][2] - ref1), e3 = exp2f(s[n][3] - ref1);
+                const float e0 = exp2f(fmaf(s[n][0], a.scale_log2, -ref0)), e1 = exp2f(fmaf(s[n][1], a.scale_log2, -ref0));
+                const float e2 = exp2f(fmaf(s[n][2], a.scale_log2, -ref1)), e3 = exp2f(fmaf(s[n][3], a.scale_log2, -ref1));
                 sum0 += e0 + e1; sum1 += e2 + e3;
                 pa[n >> 1][(n & 1) * 2] = pack_bf16(e0, e1);
                 pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(e2, e3);
@@ -240,7 +255,8 @@ extern "C" int lb_attention_prefill(const void* q, const void* k_cache, const vo
     }
     PrefillArgs a{(const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table, bt_stride,
                   cu_seqlens, start_pos, tiles, Hq, Hkv, hd, page_size, window, scale * 1.4426950408889634f,
-                  n_tiles * Hq, num_sms};
+                  n_tiles * Hq, num_sms, -1};
+    for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
     if (hd <= 64) return launch_hdt<4>(a, n_tiles, (cudaStream_t)stream);
     if (hd <= 128) return launch_hdt<8>(a, n_tiles, (cudaStream_t)stream);
     return launch_hdt<16>(a, n_tiles, (cudaStream_t)stream);

@@ -96,7 +96,7 @@ __global__ void conv_state_update_kernel(ConvArgs a) {
 // The same for bfloat16 with eight channels per thread and 16-byte loads and stores: channels, the region
 // edges and the row stride must be multiples of 8 and the input 16-byte aligned.  A thread walks
 // kVecChunk tokens; their rows are fetched in batches so that several loads are in flight.
-constexpr int kVecChunk = 16;
+constexpr int kVecChunk = 8;
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -155,7 +155,8 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
                 float acc = 0.f;
 #pragma unroll
                 for (int j = 0; j < K; ++j) acc += win[e][j] * w[e][j];
-                acc = silu_f(round_to<T>(acc + bias[e]));
+                acc = round_to<T>(acc + bias[e]);
+                acc = __fdividef(acc, 1.f + __expf(-acc));      // SiLU; the result is rounded to bfloat16 next
                 if (e & 1) o[e >> 1].y = __float2bfloat16_rn(acc); else o[e >> 1].x = __float2bfloat16_rn(acc);
 #pragma unroll
                 for (int j = 0; j < K - 1; ++j) win[e][j] = win[e][j + 1];

@@ -6,7 +6,7 @@
 //   chunk state   dS   = sum_s e^{a_L - a_s} B_s (x) u_s                       [P x N]   (kernel 1, one CTA per chunk and head)
 //   state pass    S_in(c+1) = e^{a_L(c)} S_in(c) + dS(c), from the request's saved state (zeros at
 //                 position 0); the state after the last chunk goes back to the slot     (kernel 2, float32)
-//   chunk scan    y_t  = e^{a_t} C_t . S_in + sum_{s<=t} (C_t . B_s) e^{a_t - a_s} u_s + D x_t           (kernel 3)
+//   chunk scan    y_t  = e^{a_t} C_t . S_in + sum_{s<=t} [(C_t . B_s) e^{a_t - a_s} dt_s] x_s + D x_t      (kernel 3)
 //
 // (python/logssms/kernel/linear_attention/mamba2.py:148-194 and vendor/fla/chunk_o.py:79-136 of the
 // reference, which fixes L = 64; here L is the configuration's chunk size.)  All three products of
@@ -31,7 +31,8 @@ struct SsdArgs {
     const int* cu_seqlens; const int* start_pos; const int* slots;
     const int* chunks;                           // [n_chunks][2]: request index, first token of the chunk in its portion
     const int* req_chunks;                       // [n_long][3]: request index, first chunk, number of chunks
-    float* scratch;                              // [n_chunks, nh, P, N]: dS, then S_in
+    float* scratch;                              // [n_chunks, nh, P, N]: dS of every chunk
+    bf16* s_in;                                  // [n_chunks, nh, P, N]: the state every chunk starts from, rounded
     float* chunk_a;                              // [n_chunks, nh]: a_L of the chunk
     int nh, P, N, G, L;
     float dt_scale;
@@ -55,6 +56,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;           // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;");
+    asm volatile("cp.async.wait_group 0;");
 }
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -191,7 +200,9 @@ __global__ void __launch_bounds__(256) ssd_state_pass_kernel(SsdArgs a) {
 #pragma unroll
         for (int u = 0; u < kAhead; ++u) {
             if (c + u < c0 + nc) {
-                *reinterpret_cast<float4*>(a.scratch + ((size_t)(c + u) * a.nh + h) * per_head + i) = S;   // what the chunk starts from
+                // what the chunk starts from, as the bfloat16 operand of C . S_in
+                *reinterpret_cast<uint2*>(a.s_in + ((size_t)(c + u) * a.nh + h) * per_head + i) =
+                    make_uint2(pack_bf16(S.x, S.y), pack_bf16(S.z, S.w));
                 const float e = expf(decay[u]);
                 S.x = S.x * e + d[u].x; S.y = S.y * e + d[u].y; S.z = S.z * e + d[u].z; S.w = S.w * e + d[u].w;
             }
@@ -217,51 +228,32 @@ __global__ void __launch_bounds__(MAXT) ssd_chunk_scan_kernel(SsdArgs a) {
     float* tot = a_s + Lpad;                                    // [32]
     bf16* c_s = reinterpret_cast<bf16*>(tot + 32);              // [Lpad][ldn]
     bf16* b_s = c_s + Lpad * ldn;                               // [Lpad][ldn]
-    bf16* u_s = b_s + Lpad * ldn;                               // [Lpad][ldp]   x * dt
+    bf16* u_s = b_s + Lpad * ldn;                               // [Lpad][ldp]   x (dt rides in the masked scores)
     bf16* s_s = u_s + Lpad * ldp;                               // [Ppad][ldn]   S_in
     chunk_decay(a, tok0, Lc, Lpad, h, dt_s, a_s, tot);
     const int g = h / (a.nh / a.G), inner = a.nh * P;
     const int threads = blockDim.x;
-    const int npieces = Npad / 8;
-#pragma unroll 2
+    // all four tiles come in 16-byte cp.async pieces (zeros outside the chunk and the real sizes)
+    const int npieces = Npad / 8, ppieces = Ppad / 8;
     for (int i = threadIdx.x; i < Lpad * npieces; i += threads) {
         const int s = i / npieces, c = i % npieces;
-        uint4 vb = make_uint4(0u, 0u, 0u, 0u), vc = vb;
-        if (s < Lc && c * 8 < N) {
-            const bf16* row = a.conv + (size_t)(tok0 + s) * a.C + inner + g * N + c * 8;
-            vb = *reinterpret_cast<const uint4*>(row);
-            vc = *reinterpret_cast<const uint4*>(row + a.G * N);
-        }
-        *reinterpret_cast<uint4*>(b_s + s * ldn + c * 8) = vb;
-        *reinterpret_cast<uint4*>(c_s + s * ldn + c * 8) = vc;
+        const bool ok = s < Lc && c * 8 < N;
+        const bf16* row = a.conv + (size_t)(tok0 + (ok ? s : 0)) * a.C + inner + g * N + (ok ? c * 8 : 0);
+        cp_async16(b_s + s * ldn + c * 8, row, ok);
+        cp_async16(c_s + s * ldn + c * 8, row + a.G * N, ok);
     }
-    const int ppieces = Ppad / 8;
-#pragma unroll 4
     for (int i = threadIdx.x; i < Lpad * ppieces; i += threads) {
         const int s = i / ppieces, p = (i % ppieces) * 8;
-        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-        if (s < Lc && p < P) {
-            float f[8];
-            unpack8(*reinterpret_cast<const uint4*>(a.conv + (size_t)(tok0 + s) * a.C + h * P + p), f);
-            const float dts = dt_s[s];
-            unsigned* o = reinterpret_cast<unsigned*>(&packed);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) o[e] = pack_bf16(f[2 * e] * dts, f[2 * e + 1] * dts);
-        }
-        *reinterpret_cast<uint4*>(u_s + s * ldp + p) = packed;
+        const bool ok = s < Lc && p < P;
+        cp_async16(u_s + s * ldp + p, a.conv + (size_t)(tok0 + (ok ? s : 0)) * a.C + h * P + (ok ? p : 0), ok);
     }
-    const float* sin = a.scratch + ((size_t)chunk * a.nh + h) * P * N;
-#pragma unroll 4
+    const bf16* sin = a.s_in + ((size_t)chunk * a.nh + h) * P * N;
     for (int i = threadIdx.x; i < Ppad * npieces; i += threads) {
         const int p = i / npieces, n = (i % npieces) * 8;
-        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-        if (p < P && n < N) {
-            const float4 lo = *reinterpret_cast<const float4*>(sin + (size_t)p * N + n);
-            const float4 hi = *reinterpret_cast<const float4*>(sin + (size_t)p * N + n + 4);
-            packed = make_uint4(pack_bf16(lo.x, lo.y), pack_bf16(lo.z, lo.w), pack_bf16(hi.x, hi.y), pack_bf16(hi.z, hi.w));
-        }
-        *reinterpret_cast<uint4*>(s_s + p * ldn + n) = packed;
+        const bool ok = p < P && n < N;
+        cp_async16(s_s + p * ldn + n, sin + (ok ? (size_t)p * N + n : 0), ok);
     }
+    cp_async_wait_all();
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;
     const int r0 = warp * 16;
@@ -316,7 +308,7 @@ __global__ void __launch_bounds__(MAXT) ssd_chunk_scan_kernel(SsdArgs a) {
                 const int trow = r0 + lg + 8 * (e >> 1);
                 const int s = sb * 16 + j * 8 + 2 * lt + (e & 1);
                 const float at = (e >> 1) ? at1 : at0;
-                m[e] = (s <= trow && s < Lc) ? gs[j][e] * expf(at - a_s[s]) : 0.f;
+                m[e] = (s <= trow && s < Lc) ? gs[j][e] * expf(at - a_s[s]) * dt_s[s] : 0.f;
             }
             pa[2 * j] = pack_bf16(m[0], m[1]);
             pa[2 * j + 1] = pack_bf16(m[2], m[3]);
@@ -395,7 +387,7 @@ extern "C" int lb_ssd_chunk_len(int chunk, int P, int N) {
 extern "C" int lb_ssd_prefill(const void* conv, int C, const void* dt, long dt_stride, const float* A_log,
                               const float* dt_bias, const float* D, float* state, void* y, const int* cu_seqlens,
                               const int* start_pos, const int* slots, const int* chunks, int n_chunks,
-                              const int* req_chunks, int n_long, float* scratch, float* chunk_a, int nh, int P, int N,
+                              const int* req_chunks, int n_long, float* scratch, void* s_in, float* chunk_a, int nh, int P, int N,
                               int G, int L, float dt_scale, const void* gate, long gate_stride, float gate_scale,
                               int dtype, void* stream) {
     if (n_chunks <= 0 || n_long <= 0) return kOk;
@@ -405,7 +397,7 @@ extern "C" int lb_ssd_prefill(const void* conv, int C, const void* dt, long dt_s
     if (P > 128 || N > 256 || L > 256 || nh > 65535) return kTooLarge;
     if (scan_smem(L, P, N) > kSmemLimit || state_smem(L, P, N) > kSmemLimit) return kTooLarge;
     SsdArgs a{(const bf16*)conv, C, (const bf16*)dt, dt_stride, A_log, dt_bias, D, state, (bf16*)y, cu_seqlens,
-              start_pos, slots, chunks, req_chunks, scratch, chunk_a, nh, P, N, G, L, dt_scale,
+              start_pos, slots, chunks, req_chunks, scratch, (bf16*)s_in, chunk_a, nh, P, N, G, L, dt_scale,
               (const bf16*)gate, gate_stride, gate_scale};
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem1 = state_smem(L, P, N);

@@ -369,7 +369,7 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
     _check(f(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_seqlens),
              _ptr(start_pos), _ptr(slots), num_requests, max_len, C, K, region_ends[0], region_ends[1],
              region_scales[0], region_scales[1], region_scales[2], _code(x), _stream()), "causal_conv1d",
-           launches=1 if max_len <= 16 else 2)
+           launches=1 if max_len <= 8 else 2)
     return out
 
 
@@ -450,12 +450,13 @@ def ssd_prefill(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bi
     _need(y.shape == (tokens, num_heads * head_dim) and y.dtype == conv.dtype and y.is_contiguous(), "out must be [tokens, heads * head_dim]")
     scratch = torch.empty((max(num_chunks, 1), num_heads, head_dim, state_dim), dtype=torch.float32, device=conv.device)
     chunk_a = torch.empty((max(num_chunks, 1), num_heads), dtype=torch.float32, device=conv.device)
+    s_in = torch.empty(scratch.shape, dtype=torch.bfloat16, device=conv.device)
     f = _fn("ssd", "lb_ssd_prefill", [c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                       c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_float, c_int, c_void_p])
     _check(f(_ptr(conv), C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(state), _ptr(y),
              _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(req_chunks), num_long,
-             _ptr(scratch), _ptr(chunk_a), num_heads, head_dim, state_dim, num_groups, chunk_len, dt_scale,
+             _ptr(scratch), _ptr(s_in), _ptr(chunk_a), num_heads, head_dim, state_dim, num_groups, chunk_len, dt_scale,
              _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale, _code(conv), _stream()),
            "ssd_prefill", f"(head_dim {head_dim}, state_dim {state_dim}, chunk {chunk_len})", launches=3)
     return y
