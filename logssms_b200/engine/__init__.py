@@ -1,5 +1,6 @@
-from .step import Engine, StepEntry
+from .plan import StepEntry, StepPlanner
+from .step import Engine
 from .scheduler import Request, Scheduler, StepDecision
 from .llm import LLM, Output
 
-__all__ = ["Engine", "StepEntry", "Request", "Scheduler", "StepDecision", "LLM", "Output"]
+__all__ = ["Engine", "StepEntry", "StepPlanner", "Request", "Scheduler", "StepDecision", "LLM", "Output"]
