@@ -1,6 +1,145 @@
-"""The reference arm of bench.py: the unmodified reference, installed under baseline/_ref."""
+"""The reference arm of bench.py: the unmodified dakingffo/LogSSMs, installed under baseline/_ref.
+
+It runs the reference's own `Scheduler` (python/logssms/scheduler/scheduler.py) and `Engine` through
+their public constructors and the scheduler's own loop (`overlap_loop`, the body of `run_forever`), fed
+in process the way the reference's own end-to-end test feeds it (tests/mtp/test_mtp_e2e.py:63-127:
+`receive_msg` / `send_result` replaced by in-memory lists, everything else stock).  Weights are the
+reference's `use_dummy_weight` random weights on the same config.json as our arm, prompts the same
+seeded token ids.  Nothing of logssms_b200 is on this path.
+
+What is timed is what our arm times: K scheduler iterations in the steady decode state (one new token
+per request and iteration, sampling and the host read-back of the ids included), on the device with
+CUDA events, after W warm-up iterations.
+"""
 from __future__ import annotations
+
+import json
+import os
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+
+def _write_model_folder(model: dict, path: str) -> None:
+    """config.json plus the smallest tokenizer the scheduler's `load_tokenizer` accepts (the benchmark
+    feeds token ids; the tokenizer only supplies an end-of-sequence id, which `ignore_eos` overrides)."""
+    os.makedirs(path, exist_ok=True)
+    cfg = dict(model)
+    cfg.setdefault("torch_dtype", "bfloat16")
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    from tokenizers import Tokenizer, models
+    vocab = {f"t{i}": i for i in range(256)}
+    vocab["<eos>"] = 256
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="t0"))
+    tok.save(os.path.join(path, "tokenizer.json"))
+    with open(os.path.join(path, "tokenizer_config.json"), "w") as f:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "eos_token": "<eos>", "unk_token": "t0"}, f)
 
 
 def run(args, model: dict, context: int, max_seq_len: int) -> dict:
-    raise RuntimeError("reference arm not wired yet")
+    if not os.path.isdir(os.path.join(REF, "logssms")):
+        raise RuntimeError("baseline/_ref holds no installed reference (pip install --target baseline/_ref did not run)")
+    sys.path.insert(0, REF)
+    import numpy as np
+    import torch
+    from logssms.core import SamplingParams
+    from logssms.distributed import DistributedInfo
+    from logssms.message import UserMsg
+    from logssms.scheduler import SchedulerConfig
+    from logssms.scheduler.scheduler import Scheduler
+
+    tmp = tempfile.mkdtemp(prefix="logssms_ref_bench_")
+    _write_model_folder(model, tmp)
+    batch = args.batch
+    new_tokens = args.warmup + args.steps + 8
+    rng = np.random.default_rng(1234)
+    msgs = [UserMsg(uid=i, input_ids=torch.from_numpy(rng.integers(0, model["vocab_size"], context - 1).astype(np.int32)),
+                    sampling_params=SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True))
+            for i in range(batch)]
+
+    class InProcessScheduler(Scheduler):
+        def __init__(self, config, pending):
+            self._pending = list(pending)
+            self.results: list = []
+            super().__init__(config)
+            self.receive_msg = self._take
+            self.send_result = self.results.extend
+
+        def _take(self, blocking: bool = False):
+            out, self._pending = self._pending, []
+            return out
+
+    config = SchedulerConfig(model_path=tmp, tp_info=DistributedInfo(0, 1), dtype=torch.bfloat16, max_running_req=64,
+                             use_dummy_weight=True, max_seq_len_override=max_seq_len,
+                             max_prefill_tokens=args.prefill_budget)      # cache type, attention backend, graphs: the defaults
+    t0 = time.time()
+    sched = InProcessScheduler(config, msgs)
+    print(f"[bench] reference engine up in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    with torch.inference_mode():
+        data = None
+        deadline = time.time() + 600
+        # prompts first: iterate until every request has produced its first token
+        while len({m.uid for m in sched.results}) < batch:
+            data = sched.overlap_loop(data)
+            if time.time() > deadline:
+                raise RuntimeError("reference scheduler did not finish the prompts within 600 s")
+        for _ in range(args.warmup):
+            data = sched.overlap_loop(data)
+        torch.cuda.synchronize()
+        before = len(sched.results)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wall0 = time.perf_counter()
+        start.record()
+        for _ in range(args.steps):
+            data = sched.overlap_loop(data)
+        stop.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - wall0
+        produced = len(sched.results) - before
+    ms = start.elapsed_time(stop)
+    if produced < batch * (args.steps - 1):
+        raise RuntimeError(f"reference produced {produced} tokens in {args.steps} iterations of batch {batch}: not in steady decode")
+    return {
+        "impl": "reference", "metric": "decode tok/s (batch 8, 2,048-token contexts; 0.5B-class Falcon-H1)",
+        "value": produced / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded uniform token ids, the reference's dummy weights)",
+        "config": {"model": "Falcon-H1-0.5B-class", "layers": model["num_hidden_layers"], "global_batch": batch,
+                   "seq_len": context, "context_budget": max_seq_len, "parallelism": "single GPU",
+                   "path": "Scheduler.overlap_loop, default cache type and attention backend"},
+        "e2e": {"value": produced / wall, "unit": "tokens/s"},
+    }
+
+
+def main() -> int:
+    """Child process of `bench.py --impl reference`: prints the JSON line, or the reason it could not."""
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model-json", required=True)
+    ap.add_argument("--context", type=int, required=True)
+    ap.add_argument("--max-seq-len", type=int, required=True)
+    ap.add_argument("--steps", type=int, required=True)
+    ap.add_argument("--warmup", type=int, required=True)
+    ap.add_argument("--batch", type=int, required=True)
+    ap.add_argument("--prefill-budget", type=int, default=8192)
+    args = ap.parse_args()
+    with open(args.model_json) as f:
+        model = json.load(f)
+    try:
+        line = run(args, model, args.context, args.max_seq_len)
+    except BaseException as exc:                 # also SystemExit / KeyboardInterrupt raised inside the reference
+        import traceback
+        traceback.print_exc()
+        text = f"{type(exc).__name__}: {exc}".splitlines()
+        detail = next((t.strip() for t in text[1:] if "error" in t.lower() and "FAILED" not in t), "")
+        line = {"impl": "reference", "unavailable": (text[0] + (" | " + detail if detail else ""))[:400]}
+    print("RESULT " + json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

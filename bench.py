@@ -85,6 +85,9 @@ class ClockSampler:
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
+        deadline = time.time() + 5.0                      # the first sample takes nvidia-smi a moment
+        while not self.lines and time.time() < deadline:
+            time.sleep(0.05)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -103,7 +106,10 @@ class ClockSampler:
 
     def summary(self, lo: int = 0, hi: int | None = None) -> dict:
         sm, mx, reasons = [], [], set()
-        for line in self.lines[lo:hi]:
+        span = self.lines[lo:hi]
+        if not span:                                      # a region shorter than one sampling period: its neighbours
+            span = self.lines[max(lo - 2, 0):(hi or len(self.lines)) + 2]
+        for line in span:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -286,8 +292,31 @@ def run_ours(args) -> dict:
 
 # --------------------------------------------------------------------------- the reference arm
 def run_reference(args) -> dict:
-    from baseline.reference_arm import run as run_ref
-    return run_ref(args, MODEL, CONTEXT, MAX_SEQ_LEN)
+    """The reference runs in a child process (its own CUDA context, streams and JIT caches), with a time
+    limit; whatever goes wrong there becomes the `unavailable` line."""
+    tmp = tempfile.mkdtemp(prefix="logssms_ref_cfg_")
+    try:
+        cfg = dict(MODEL)
+        if args.layers:
+            cfg["num_hidden_layers"] = args.layers
+        path = os.path.join(tmp, "model.json")
+        with open(path, "w") as f:
+            json.dump(cfg, f)
+        cmd = [sys.executable, os.path.join(ROOT, "baseline", "reference_arm.py"), "--model-json", path,
+               "--context", str(CONTEXT), "--max-seq-len", str(MAX_SEQ_LEN), "--steps", str(args.steps),
+               "--warmup", str(args.warmup), "--batch", str(args.batch), "--prefill-budget", str(args.prefill_budget)]
+        try:
+            proc = subprocess.run(cmd, capture_output=True, text=True, timeout=args.reference_timeout)
+        except subprocess.TimeoutExpired:
+            return {"impl": "reference", "unavailable": f"the reference did not finish within {args.reference_timeout} s"}
+        sys.stderr.write(proc.stderr[-6000:])
+        for line in reversed(proc.stdout.splitlines()):
+            if line.startswith("RESULT "):
+                return json.loads(line[len("RESULT "):])
+        tail = (proc.stderr or proc.stdout).strip().splitlines()[-1:] or ["no output"]
+        return {"impl": "reference", "unavailable": f"the reference process ended with code {proc.returncode}: {tail[0][:240]}"}
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
 
 
 def main() -> int:
@@ -299,6 +328,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (both are reported)")
     ap.add_argument("--prefill-budget", type=int, default=8192, help="token budget of one scheduled step")
+    ap.add_argument("--reference-timeout", type=int, default=900, help="seconds the reference arm may take")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print("bench.py: this engine runs on one GPU; --gpus N>1 is not built")
