@@ -187,25 +187,37 @@ __global__ void __launch_bounds__(kThreads) attn_split_kernel(DecodeArgs a) {
     }
 }
 
-// grid (selected tokens, query heads); one thread per output column.
+// grid (selected tokens, query heads); one thread per output column.  The ranges' (max, sum) pairs are
+// read once into shared memory, where every range gets its weight exp(max_s - max); the columns are then
+// weighted sums of independent, coalesced loads.
+constexpr int kMaxMergeSplits = 1024;
+
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   T* __restrict__ out, const int* __restrict__ token_list, int Hq, int hd, int splits) {
+    pdl_trigger();
+    extern __shared__ float w_s[];                     // [splits] weights, then [32] for the reductions
+    float* red = w_s + splits;
     const int sel = blockIdx.x, h = blockIdx.y;
     const size_t t = token_list ? token_list[sel] : sel;
     const size_t base = ((size_t)sel * Hq + h) * splits;
     float mt = -INFINITY;
-    for (int s = 0; s < splits; ++s) mt = fmaxf(mt, part_ml[(base + s) * 2]);
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) mt = fmaxf(mt, part_ml[(base + s) * 2]);
+    mt = block_max(mt, red);
+    float lt = 0.f;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float ms = part_ml[(base + s) * 2];
+        const float f = ms == -INFINITY ? 0.f : expf(ms - mt);      // an empty range has weight 0
+        w_s[s] = f;
+        lt += part_ml[(base + s) * 2 + 1] * f;
+    }
+    lt = block_sum(lt, red);                           // (its barriers also publish w_s)
+    const float inv = 1.f / lt;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float lt = 0.f, o = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            if (ms == -INFINITY) continue;                 // an empty range wrote no output
-            const float f = expf(ms - mt);
-            lt += part_ml[(base + s) * 2 + 1] * f;
-            o += part_o[(base + s) * hd + d] * f;
-        }
-        out[(t * Hq + h) * hd + d] = from_f32<T>(o / lt);
+        float o = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) o = fmaf(part_o[(base + s) * hd + d], w_s[s], o);
+        out[(t * Hq + h) * hd + d] = from_f32<T>(o * inv);
     }
 }
 
@@ -244,7 +256,8 @@ int launch(DecodeArgs a, int sel_tokens, cudaStream_t s) {
     if (rc != 0 || a.splits == 1) return rc;
     dim3 grid(sel_tokens, a.Hq);
     const int threads = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);
-    attn_merge_kernel<T><<<grid, threads, 0, s>>>(a.part_o, a.part_ml, (T*)a.out, a.token_list, a.Hq, a.hd, a.splits);
+    attn_merge_kernel<T><<<grid, threads, (a.splits + 32) * sizeof(float), s>>>(a.part_o, a.part_ml, (T*)a.out, a.token_list,
+                                                                                a.Hq, a.hd, a.splits);
     return launch_status();
 }
 }  // namespace
@@ -260,7 +273,7 @@ extern "C" int lb_attention_decode(const void* q, const void* k_cache, const voi
     if (hd <= 0 || hd > 256 || hd % 16 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || splits < 1)
         return kBadSize;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return kBadSize;
-    if (splits > 65535 || (long)Hkv * ((Hq / Hkv + 7) / 8 + 1) > 65535) return kTooLarge;
+    if (splits > kMaxMergeSplits || (long)Hkv * ((Hq / Hkv + 7) / 8 + 1) > 65535) return kTooLarge;
     DecodeArgs a{q, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, token_list, part_o, part_ml,
                  Hq, Hkv, hd, page_size, window, splits, 1, scale};
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, sel_tokens, (cudaStream_t)stream));
@@ -320,7 +333,7 @@ extern "C" int lb_attention_decode_static(const void* q, const void* k_cache, co
     if (hd <= 0 || hd > 256 || hd % 16 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || splits < 1)
         return refuse(err, err_len, kBadSize, "a size the kernel does not take (head_dim %ld in steps of 16 up to 256, "
                       "query heads a multiple of key/value heads, splits %ld >= 1)", hd, splits);
-    if (splits > 65535 || (long)Hkv * ((Hq / Hkv + 7) / 8 + 1) > 65535)
+    if (splits > kMaxMergeSplits || (long)Hkv * ((Hq / Hkv + 7) / 8 + 1) > 65535)
         return refuse(err, err_len, kTooLarge, "too many ranges (%ld) or key/value heads (%ld) for one grid", splits, Hkv);
     if (dtype != kF32 && dtype != kBF16) return refuse(err, err_len, kBadDType, "dtype code %ld is neither float32 (0) nor bfloat16 (1)", dtype);
     const size_t slots = (size_t)sel_tokens * (size_t)Hq * (size_t)splits;

@@ -23,6 +23,7 @@ __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ t
 // Row gather without scaling: out[i, :] = src[rows[i], :] (used to pick the positions whose logits are wanted).
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ src, const int* __restrict__ rows, int H) {
+    pdl_trigger();
     const T* s = src + (size_t)rows[blockIdx.x] * H;
     T* d = out + (size_t)blockIdx.x * H;
     for (int c = threadIdx.x; c < H; c += blockDim.x) d[c] = s[c];

@@ -92,8 +92,8 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     const int chunks = (K + kChunk - 1) / kChunk;
     const int per_warp = (chunks + kWarps - 1) / kWarps;
     const int c_begin = warp * per_warp, c_end = min(chunks, c_begin + per_warp);
-    for (int c0 = c_begin; c0 < c_end; c0 += kUnroll) {
-        uint4 wv[kUnroll][HALVES][2];
+    uint4 wv[kUnroll][HALVES][2];
+    auto load_w = [&](int c0) {
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int k = (c0 + u) * kChunk + t * 8;
@@ -103,6 +103,14 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
 #pragma unroll
                 for (int r = 0; r < 2; ++r) wv[u][h][r] = ok ? load_stream(wrow[h][r] + k) : zero;
         }
+    };
+    // The weights do not depend on the kernel before this one: their first batch is on its way while
+    // that kernel still runs; x (its output) is touched only after the wait.
+    pdl_trigger();
+    load_w(c_begin);
+    pdl_wait();
+    for (int c0 = c_begin; c0 < c_end; c0 += kUnroll) {
+        if (c0 != c_begin) load_w(c0);
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int k = (c0 + u) * kChunk + t * 8;
@@ -164,14 +172,15 @@ int launch_mt(const SkinnyArgs& a, cudaStream_t s) {
         const size_t smem = sizeof(float) * kWarps * halves * kFeat * (MT * 8 + 1);                         \
         if (smem > 48 * 1024)                                                                               \
             cudaFuncSetAttribute(skinny_linear_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        skinny_linear_kernel<MT, EPI><<<grid, kThreads, smem, s>>>(a);                                      \
+        rc = launch_pdl(skinny_linear_kernel<MT, EPI>, grid, dim3(kThreads), smem, s, a);                   \
     }
+    int rc = 0;
     if (mt <= 1) LB_SKINNY(1)
     else if (mt <= 2) LB_SKINNY(2)
     else if (mt <= 4) LB_SKINNY(4)
     else LB_SKINNY(8)
 #undef LB_SKINNY
-    return launch_status();
+    return rc != 0 ? rc : launch_status();
 }
 }  // namespace
 

@@ -17,6 +17,7 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ other, const T* residual_in,
                                    T* residual_out, const float* __restrict__ weight, T* __restrict__ out0,
                                    T* __restrict__ out1, int H, float eps, float in0, float in1, float s0, float s1) {
+    pdl_trigger();
     extern __shared__ float row[];          // H floats
     __shared__ float red[32];
     const size_t base = (size_t)blockIdx.x * H;
@@ -66,6 +67,7 @@ template <typename T>
 __global__ void gated_rmsnorm_kernel(const T* __restrict__ y, const T* __restrict__ gate, long gate_stride,
                                      const float* __restrict__ weight, T* __restrict__ out, int width, int groups,
                                      float eps, float gate_scale, int mode) {
+    pdl_trigger();
     __shared__ float red[32];
     const size_t row = blockIdx.x;
     const int g = blockIdx.y;

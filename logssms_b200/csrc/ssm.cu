@@ -48,6 +48,7 @@ template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bflo
 // NPT: state values per thread (N <= 8 * NPT).  ALIGNED: 4-element vector loads of B and C are legal.
 template <typename T, int NPT, bool ALIGNED>
 __global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
+    pdl_trigger();
     const int h = blockIdx.x, b = a.req_list ? a.req_list[blockIdx.y] : blockIdx.y;
     const int pi = threadIdx.x / kLanesN, nl = threadIdx.x % kLanesN;
     const int p = blockIdx.z * kPTile + pi;

@@ -63,6 +63,7 @@ class Engine:
         self.use_graphs = use_graphs
         self.max_graphs = max_graphs
         self._graphs: dict[int, _DecodeGraph] = {}
+        self._side_stream: torch.cuda.Stream | None = None
         self.steps_run = 0
 
     def _pages_that_fit(self, needs, max_requests: int, memory_ratio: float) -> int:
@@ -129,9 +130,13 @@ class Engine:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = K.launch_count
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(self.device)
+            ctx.extras["side_stream"] = self._side_stream      # blocks may fork their mixers onto it while capturing
             with torch.cuda.graph(graph):
                 x, residual = self.model.forward(ctx)
                 slot.logits = self.model.logits(x, residual, ctx.logit_rows)
+            del ctx.extras["side_stream"]
             slot.launches = K.launch_count - before
             K.launch_count = before
             slot.graph = graph

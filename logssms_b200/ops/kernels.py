@@ -481,8 +481,9 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
 SKINNY_MAX_ROWS = 64       # at or below this many rows a bfloat16 product goes to the weight-streaming kernel
 
 
-def _skinny_ok(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> bool:
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= SKINNY_MAX_ROWS
+def _skinny_ok(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, max_rows: int | None = None) -> bool:
+    max_rows = SKINNY_MAX_ROWS if max_rows is None else max_rows
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= max_rows
             and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.shape[1] % 8 == 0 and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous())))
@@ -496,7 +497,7 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = 
     """The weight-streaming product for at most 64 bfloat16 rows: x [M, K] @ w[N, K]^T, with the bias,
     output multiplier, float32 output or SwiGLU (w = [gate rows; up rows]) done on the sums."""
     _cuda(x, w, bias)
-    _need(_skinny_ok(x, w, bias), "linear_skinny takes at most 64 bfloat16 rows, K a multiple of 8, 16-byte aligned operands")
+    _need(_skinny_ok(x, w, bias, 64), "linear_skinny takes at most 64 bfloat16 rows, K a multiple of 8, 16-byte aligned operands")
     M, Kdim = x.shape
     _need(w.dim() == 2 and w.shape[1] == Kdim, "weight must be [N, K]")
     N = w.shape[0]

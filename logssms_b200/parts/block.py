@@ -58,7 +58,23 @@ class PreNormParallelBlock(Part):
     def forward(self, x: torch.Tensor, residual, ctx, cache_layer: int, writes_cache: bool = True):
         slots = self.spec.mixers
         ins, residual = self.mixer_norm.forward(x, residual, out_scales=tuple(m.in_scale for m in slots))
-        outs = [mixer.forward(inp, ctx, cache_layer, writes_cache) for mixer, inp in zip(self.mixers, ins)]
+        side = ctx.extras.get("side_stream") if len(self.mixers) == 2 else None
+        if side is None:
+            outs = [mixer.forward(inp, ctx, cache_layer, writes_cache) for mixer, inp in zip(self.mixers, ins)]
+        else:
+            # Inside a graph capture the two mixers go to two streams, so that the graph may run their
+            # kernels side by side (each alone leaves most of the 148 SMs idle at small batch).
+            main = torch.cuda.current_stream()
+            fork = torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                second = self.mixers[1].forward(ins[1], ctx, cache_layer, writes_cache)
+                join = torch.cuda.Event()
+                join.record(side)
+            first = self.mixers[0].forward(ins[0], ctx, cache_layer, writes_cache)
+            main.wait_event(join)
+            outs = [first, second]
         if len(outs) == 2:
             (h,), residual = self.ff_norm.forward(outs[0], residual, other=outs[1],
                                                   in_scales=(slots[0].out_scale, slots[1].out_scale))

@@ -514,7 +514,10 @@ def test_linear_skinny_plain_bias_scale_and_f32(M, N, Kd):
     assert out32.dtype == torch.float32
     close(out32, rnd(acc) * 0.25, torch.bfloat16, tol=4e-3)
     # the dispatcher sends these sizes to the same kernel, and more rows to the library
-    assert torch.equal(k.linear(xd, dev(w)), k.linear_skinny(xd, dev(w)))
+    if M <= k.SKINNY_MAX_ROWS:
+        assert torch.equal(k.linear(xd, dev(w)), k.linear_skinny(xd, dev(w)))
+    else:
+        close(k.linear(xd, dev(w)), rnd(acc), torch.bfloat16, tol=8e-3)
 
 
 @pytest.mark.parametrize("M", [1, 8, 20, 64])
