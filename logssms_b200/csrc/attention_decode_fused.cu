@@ -1,0 +1,370 @@
+// One launch for the attention of a decode step: every token of the batch is the only new token of its
+// request.  What otherwise takes three launches (rotate + store, split-KV attention, merge) is one:
+//
+//   * the CTA reads its query heads straight from the q|k|v projection and rotates them while loading;
+//   * the CTA whose key range ends at the token's own position rotates the new key (after the key
+//     multiplier), keeps it and the new value in shared memory for its own use, and (one CTA per
+//     key/value head) stores both into the page cache;
+//   * keys and values of a 32-key tile are all requested before any arithmetic starts (the kernel lives
+//     on memory-level parallelism: a decode step is bound by reading the cache once);
+//   * with several ranges per token, the CTA that finishes last (a counter per token and head group,
+//     bumped after a fence) merges the ranges' partial results, so no second launch is needed.  The
+//     counter returns to zero for the next call.  Nobody ever waits on anybody.
+//
+// Rotation: python/logssms/kernel/fused.py:161-256 (key scaled and rounded before the rotation,
+// half-split pairing); attention: python/logssms/layers/attention_backend/fi.py:175-190.
+// Softmax statistics and accumulators are float32, exp is expf.  Head sizes: multiples of 16 up to 256.
+#include "lb200/common.cuh"
+using namespace lb200;
+
+namespace {
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+
+struct FusedArgs {
+    const void* qkv; long row_stride;              // [tokens, (Hq + 2 Hkv) * hd], columns q | k | v
+    void* k_cache; void* v_cache; void* out;       // caches [pages, page_size, Hkv, hd]; out [tokens, Hq, hd]
+    const int* block_table; int bt_stride;
+    const int* token_req; const int* positions; const int* slot_mapping;
+    const float* cos_sin; int table_rows; int rotary_dim;
+    float* part_o; float* part_ml; int* counters;
+    int Hq, Hkv, hd, page_size, window, splits, head_tiles, write_kv;
+    float scale, key_scale;
+};
+
+// eight consecutive elements held raw in registers until they are needed
+template <typename T> struct Raw8;
+template <> struct Raw8<__nv_bfloat16> {
+    uint4 v;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void zero() { v = make_uint4(0u, 0u, 0u, 0u); }
+    __device__ __forceinline__ void get(float* f) const {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+};
+template <> struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = *reinterpret_cast<const float4*>(p); b = *reinterpret_cast<const float4*>(p + 4);
+    }
+    __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ __forceinline__ void get(float* f) const {
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+};
+
+// rotated value of column c of a head row `src` (values already scaled/rounded by `pre`)
+template <typename T>
+__device__ __forceinline__ float rotated(const T* src, int c, int rotary_dim, const float* cs, float pre, bool round_pre) {
+    float val = to_f32(src[c]) * pre;
+    if (round_pre) val = round_to<T>(val);
+    if (c < rotary_dim) {
+        const int half = rotary_dim >> 1;
+        const int f = c < half ? c : c - half;
+        float partner = to_f32(src[c < half ? c + half : c - half]) * pre;
+        if (round_pre) partner = round_to<T>(partner);
+        val = val * cs[f] + (c < half ? -partner : partner) * cs[half + f];
+    }
+    return round_to<T>(val);
+}
+
+// GT: query heads per CTA.  CHP: 8-element pieces per head row, rounded up to a power of two (2..32).
+template <typename T, int GT, int CHP>
+__global__ void __launch_bounds__(kThreads) attn_decode_fused_kernel(FusedArgs a) {
+    extern __shared__ float smem[];
+    const int hd = a.hd;
+    float* q_s = smem;                                   // [GT][hd]  rotated queries, pre-scaled
+    float* kn_s = q_s + GT * hd;                         // [hd]      the token's own key (rotated)
+    float* vn_s = kn_s + hd;                             // [hd]      the token's own value
+    float* mrg = vn_s + hd;                              // [kWarps][GT][hd + 2]
+    __shared__ int last_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t t = blockIdx.x;
+    const int kvh = blockIdx.y / a.head_tiles, ht = blockIdx.y % a.head_tiles;
+    const int G = a.Hq / a.Hkv;
+    const int h0 = kvh * G + ht * GT;
+    const int nheads = min(GT, G - ht * GT);
+    const int split = blockIdx.z;
+    const int pos = a.positions[t];
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int n = pos - lo + 1;
+    // a range is never shorter than one tile per warp; ranges beyond the context have no CTA work at all
+    const int chunk = (max((n + a.splits - 1) / a.splits, kWarps * 32) + 31) / 32 * 32;
+    const int used = (n + chunk - 1) / chunk;            // ranges that hold keys
+    if (split >= used) return;
+    const int begin = lo + split * chunk;
+    const int end = min(begin + chunk, pos + 1);
+    const bool use_new = a.write_kv != 0;                // else the own position was stored by another layer
+    const bool owns_new = use_new && begin <= pos && pos < end;     // this CTA's range holds the token's own key
+    const int* bt = a.block_table + (size_t)a.token_req[t] * a.bt_stride;
+    const T* row = (const T*)a.qkv + t * a.row_stride;
+    const float* cs = a.cos_sin + (size_t)min(max(pos, 0), a.table_rows - 1) * a.rotary_dim;
+
+    for (int i = threadIdx.x; i < GT * hd; i += kThreads) {
+        const int g = i / hd, c = i % hd;
+        q_s[i] = g < nheads ? rotated<T>(row + (size_t)(h0 + g) * hd, c, a.rotary_dim, cs, 1.f, false) * a.scale : 0.f;
+    }
+    if (owns_new) {
+        const T* ksrc = row + (size_t)(a.Hq + kvh) * hd;
+        const T* vsrc = row + (size_t)(a.Hq + a.Hkv + kvh) * hd;
+        const long slot = a.slot_mapping[t];
+        const bool store = ht == 0 && slot >= 0;
+        for (int c = threadIdx.x; c < hd; c += kThreads) {
+            const float kv = rotated<T>(ksrc, c, a.rotary_dim, cs, a.key_scale, true);
+            const float vv = to_f32(vsrc[c]);
+            kn_s[c] = kv; vn_s[c] = vv;
+            if (store) {
+                ((T*)a.k_cache)[((size_t)slot * a.Hkv + kvh) * hd + c] = from_f32<T>(kv);
+                ((T*)a.v_cache)[((size_t)slot * a.Hkv + kvh) * hd + c] = vsrc[c];
+            }
+        }
+    }
+    __syncthreads();
+
+    constexpr int KPI = 32 / CHP;                        // keys per value-load instruction
+    constexpr int KB = CHP < 8 ? CHP : 8;                // pieces of a key row fetched together
+    constexpr int VB = CHP < 8 ? CHP : 8;                // value-load instructions fetched together
+    const int piece = lane % CHP, ksub = lane / CHP;
+    const bool piece_ok = piece * 8 < hd;
+    const int pieces = hd / 8;
+    float acc[GT][8];
+    float m[GT], l[GT];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+    }
+    const T* kc = (const T*)a.k_cache;
+    const T* vc = (const T*)a.v_cache;
+
+    for (int j0 = begin + warp * 32; j0 < end; j0 += kWarps * 32) {
+        const int j = j0 + lane;
+        const bool valid = j < end;
+        const bool from_cache = valid && !(use_new && j == pos);       // the token's own key and value come from shared memory
+        long krow = 0;
+        if (from_cache) krow = (long)bt[j / a.page_size] * a.page_size + (j % a.page_size);
+        const int count = min(32, end - j0);
+        const int own_key = (use_new && pos >= j0 && pos < j0 + 32) ? pos - j0 : -1;   // lane of the own key in this tile
+
+        float s[GT];
+#pragma unroll
+        for (int g = 0; g < GT; ++g) s[g] = 0.f;
+        Raw8<T> vreg[VB];
+#pragma unroll 1
+        for (int kb = 0; kb < CHP; kb += KB) {
+            // this batch of key pieces, and on the first pass the first batch of value pieces, all in flight together
+            Raw8<T> kreg[KB];
+#pragma unroll
+            for (int c = 0; c < KB; ++c) {
+                if (from_cache && kb + c < pieces) kreg[c].load(kc + ((size_t)krow * a.Hkv + kvh) * hd + (kb + c) * 8);
+                else kreg[c].zero();
+            }
+            if (kb == 0) {
+#pragma unroll
+                for (int i = 0; i < VB; ++i) {
+                    const int key = i * KPI + ksub;
+                    const long rj = __shfl_sync(0xffffffffu, krow, key);
+                    if (key < count && key != own_key && piece_ok) vreg[i].load(vc + ((size_t)rj * a.Hkv + kvh) * hd + piece * 8);
+                    else vreg[i].zero();
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < KB; ++c) {
+                if (kb + c < pieces) {
+                    float f[8];
+                    kreg[c].get(f);
+                    if (valid && !from_cache) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) f[e] = kn_s[(kb + c) * 8 + e];
+                    }
+#pragma unroll
+                    for (int g = 0; g < GT; ++g) {
+                        const float* qg = q_s + g * hd + (kb + c) * 8;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) s[g] = fmaf(qg[e], f[e], s[g]);
+                    }
+                }
+            }
+        }
+        float p[GT];
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+            const float m_new = fmaxf(m[g], warp_max(valid ? s[g] : -INFINITY));
+            const float alpha = expf(m[g] - m_new);          // m = -inf at first: exp(-inf) = 0
+            p[g] = valid ? expf(s[g] - m_new) : 0.f;
+            l[g] = l[g] * alpha + p[g];
+            m[g] = m_new;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] *= alpha;
+        }
+#pragma unroll 1
+        for (int vb = 0; vb < CHP; vb += VB) {
+            if (vb > 0) {
+#pragma unroll
+                for (int i = 0; i < VB; ++i) {
+                    const int key = (vb + i) * KPI + ksub;
+                    const long rj = __shfl_sync(0xffffffffu, krow, key);
+                    if (key < count && key != own_key && piece_ok) vreg[i].load(vc + ((size_t)rj * a.Hkv + kvh) * hd + piece * 8);
+                    else vreg[i].zero();
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < VB; ++i) {
+                const int key = (vb + i) * KPI + ksub;
+                float pj[GT];
+#pragma unroll
+                for (int g = 0; g < GT; ++g) pj[g] = __shfl_sync(0xffffffffu, p[g], key);
+                if (key < count && piece_ok) {
+                    float f[8];
+                    vreg[i].get(f);
+                    if (key == own_key) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) f[e] = vn_s[piece * 8 + e];
+                    }
+#pragma unroll
+                    for (int g = 0; g < GT; ++g)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj[g], f[e], acc[g][e]);
+                }
+            }
+        }
+    }
+    // lanes that hold the same columns -> lane `piece`
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        l[g] = warp_sum(l[g]);
+#pragma unroll
+        for (int o = CHP; o < 32; o <<= 1)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+    }
+    const int stride = hd + 2;
+    if (lane < CHP && piece_ok) {
+#pragma unroll
+        for (int g = 0; g < GT; ++g)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) mrg[(warp * GT + g) * stride + piece * 8 + e] = acc[g][e];
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < GT; ++g) { mrg[(warp * GT + g) * stride + hd] = m[g]; mrg[(warp * GT + g) * stride + hd + 1] = l[g]; }
+    }
+    __syncthreads();
+    const size_t group = t * (size_t)(a.Hkv * a.head_tiles) + blockIdx.y;      // (token, kv head, head tile)
+    for (int i = threadIdx.x; i < nheads * hd; i += kThreads) {
+        const int g = i / hd, d = i % hd;
+        float mt = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mt = fmaxf(mt, mrg[(w * GT + g) * stride + hd]);
+        float lt = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float mw = mrg[(w * GT + g) * stride + hd];
+            const float f = mw == -INFINITY ? 0.f : expf(mw - mt);
+            lt += mrg[(w * GT + g) * stride + hd + 1] * f;
+            o += mrg[(w * GT + g) * stride + d] * f;
+        }
+        const int h = h0 + g;
+        if (used == 1) {
+            ((T*)a.out)[(t * a.Hq + h) * hd + d] = from_f32<T>(o / lt);
+        } else {
+            const size_t slot = ((size_t)t * a.Hq + h) * a.splits + split;
+            a.part_o[slot * hd + d] = o;
+            if (d == 0) { a.part_ml[slot * 2] = mt; a.part_ml[slot * 2 + 1] = lt; }
+        }
+    }
+    if (used == 1) return;
+    // the last CTA of this (token, head group) to get here merges all ranges
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int done = atomicAdd(a.counters + group, 1);
+        last_flag = done == used - 1;
+        if (last_flag) a.counters[group] = 0;              // ready for the next call
+    }
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < nheads * hd; i += kThreads) {
+        const int g = i / hd, d = i % hd;
+        const int h = h0 + g;
+        const size_t base = ((size_t)t * a.Hq + h) * a.splits;
+        float mt = -INFINITY;
+        for (int s2 = 0; s2 < used; ++s2) mt = fmaxf(mt, __ldcg(a.part_ml + (base + s2) * 2));
+        float lt = 0.f, o = 0.f;
+        for (int s2 = 0; s2 < used; ++s2) {
+            const float ms = __ldcg(a.part_ml + (base + s2) * 2);
+            const float f = expf(ms - mt);
+            lt += __ldcg(a.part_ml + (base + s2) * 2 + 1) * f;
+            o += __ldcg(a.part_o + (base + s2) * hd + d) * f;
+        }
+        ((T*)a.out)[(t * a.Hq + h) * hd + d] = from_f32<T>(o / lt);
+    }
+}
+
+template <typename T, int GT>
+int launch_chp(const FusedArgs& a, int tokens, cudaStream_t s) {
+    const int pieces = a.hd / 8;
+    dim3 grid(tokens, a.Hkv * a.head_tiles, a.splits);
+    const size_t smem = (size_t)(GT * a.hd + 2 * a.hd + kWarps * GT * (a.hd + 2)) * sizeof(float);
+#define LB_CHP(N)                                                                                          \
+    {                                                                                                      \
+        if (smem > 48 * 1024)                                                                              \
+            cudaFuncSetAttribute(attn_decode_fused_kernel<T, GT, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        attn_decode_fused_kernel<T, GT, N><<<grid, kThreads, smem, s>>>(a);                                \
+    }
+    if (pieces <= 2) LB_CHP(2)
+    else if (pieces <= 4) LB_CHP(4)
+    else if (pieces <= 8) LB_CHP(8)
+    else if (pieces <= 16) LB_CHP(16)
+    else LB_CHP(32)
+#undef LB_CHP
+    return launch_status();
+}
+
+template <typename T>
+int launch(FusedArgs a, int tokens, cudaStream_t s) {
+    const int G = a.Hq / a.Hkv;
+    const int gt = G >= 8 ? 8 : (G > 2 ? 4 : (G == 2 ? 2 : 1));
+    a.head_tiles = (G + gt - 1) / gt;
+    switch (gt) {
+        case 1: return launch_chp<T, 1>(a, tokens, s);
+        case 2: return launch_chp<T, 2>(a, tokens, s);
+        case 4: return launch_chp<T, 4>(a, tokens, s);
+        default: return launch_chp<T, 8>(a, tokens, s);
+    }
+}
+}  // namespace
+
+// Number of counters the call needs: tokens * Hkv * head tiles (head tiles = ceil((Hq / Hkv) / heads per CTA)).
+extern "C" int lb_attention_decode_fused_counters(int tokens, int Hq, int Hkv) {
+    if (tokens <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return 0;
+    const int G = Hq / Hkv;
+    const int gt = G >= 8 ? 8 : (G > 2 ? 4 : (G == 2 ? 2 : 1));
+    return tokens * Hkv * ((G + gt - 1) / gt);
+}
+
+// qkv: [tokens, (Hq + 2 Hkv) * hd] rows (row stride in elements); every token is the only new token of its
+// request; `counters`: zero-initialised int32, at least lb_attention_decode_fused_counters(...) entries, left
+// at zero by the call; part_o / part_ml as for lb_attention_decode (may be null when splits == 1).
+extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void* k_cache, void* v_cache, void* out,
+                                         const int* block_table, int bt_stride, const int* token_req,
+                                         const int* positions, const int* slot_mapping, const float* cos_sin,
+                                         int table_rows, int rotary_dim, int tokens, int Hq, int Hkv, int hd,
+                                         int page_size, float scale, float key_scale, int window, int write_kv,
+                                         int splits, float* part_o, float* part_ml, int* counters, int dtype,
+                                         void* stream) {
+    if (tokens <= 0) return kOk;
+    if (hd <= 0 || hd > 256 || hd % 16 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || splits < 1) return kBadSize;
+    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return kBadSize;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return kBadSize;
+    if (splits > 65535 || (long)Hkv * ((Hq / Hkv + 7) / 8 + 1) > 65535) return kTooLarge;
+    FusedArgs a{qkv, row_stride, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, slot_mapping,
+                cos_sin, table_rows, rotary_dim, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
+                write_kv, scale, key_scale};
+    LB_DISPATCH_DTYPE(dtype, return launch<T>(a, tokens, (cudaStream_t)stream));
+    return kOk;
+}

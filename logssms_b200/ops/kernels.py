@@ -308,6 +308,79 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return out
 
 
+_decode_counters: dict[torch.device, torch.Tensor] = {}
+
+
+def _counters_for(device: torch.device, n: int) -> torch.Tensor:
+    """Zeroed int32 counters kept per device; the fused decode kernel leaves them at zero."""
+    t = _decode_counters.get(device)
+    if t is None or t.numel() < n:
+        t = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+        _decode_counters[device] = t
+    return t
+
+
+def decode_step_splits(num_tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
+    """Most key ranges per token for `attention_decode_step`: enough CTAs to fill every SM several times
+    over, never more ranges than 128-key pieces of the longest context (the kernel itself uses fewer
+    ranges for a short context)."""
+    G = num_heads // num_kv_heads
+    tile = 8 if G >= 8 else (4 if G > 2 else G)
+    items = max(1, num_tokens * num_kv_heads * (-(-G // tile)))
+    return max(1, min(_STEP_TARGET_CTAS // items, -(-max_context // 128), 256))
+
+
+_STEP_TARGET_CTAS = 1184        # 8 CTAs on each of the 148 SMs
+
+
+def attention_decode_step(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,
+                          slot_mapping: torch.Tensor, cos_sin: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                          block_table: torch.Tensor, token_req: torch.Tensor, scale: float, key_scale: float,
+                          window: int = 0, write_kv: bool = True, *, splits: int = 1) -> torch.Tensor:
+    """The whole attention of a decode step in one launch: every row of `qkv` ([tokens, (Hq + 2 Hkv) * hd],
+    columns q | k | v) is the only new token of its request.  Rotates q and the new key, stores the new
+    key/value at `slot_mapping` (unless `write_kv` is off: then the position was stored by another layer
+    and is read from the cache), attends over the request's pages and merges the key ranges.
+    Returns [tokens, Hq, hd]."""
+    _cuda(qkv, positions, slot_mapping, cos_sin, k_cache, v_cache, block_table, token_req)
+    Hq, Hkv, hd = num_heads, num_kv_heads, head_dim
+    tokens = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.shape[1] == (Hq + 2 * Hkv) * hd and qkv.stride(1) == 1,
+          "qkv must be [tokens, (Hq + 2*Hkv) * head_dim] with unit column stride")
+    for t_, n_ in ((positions, "positions"), (slot_mapping, "slot_mapping"), (token_req, "token_req")):
+        _i32(t_, n_)
+        _need(t_.numel() == tokens, f"one entry of {n_} per token")
+    _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.dim() == 2,
+          "cos/sin table must be contiguous float32 [positions, rotary_dim]")
+    rotary_dim = cos_sin.shape[1]
+    _need(rotary_dim % 2 == 0 and rotary_dim <= hd, f"rotary_dim {rotary_dim} must be even and within head_dim {hd}")
+    _need(k_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
+          and k_cache.dtype == qkv.dtype == v_cache.dtype and k_cache.shape[2:] == (Hkv, hd),
+          "caches must be contiguous [pages, page_size, kv_heads, head_dim] of the activation dtype")
+    _need(hd % 16 == 0 and hd <= 256, f"attention takes head sizes in steps of 16 up to 256, got {hd}")
+    _need(Hq % Hkv == 0, f"query heads ({Hq}) must be a multiple of key/value heads ({Hkv})")
+    _need(block_table.dim() == 2 and block_table.dtype == torch.int32 and block_table.stride(1) == 1,
+          "block table must be a row-major int32 matrix")
+    page_size = k_cache.shape[1]
+    out = torch.empty((tokens, Hq, hd), dtype=qkv.dtype, device=qkv.device)
+    part_o = part_ml = counters = None
+    splits = int(splits)
+    if splits > 1:
+        part_o = torch.empty(tokens * Hq * splits * hd, dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty(tokens * Hq * splits * 2, dtype=torch.float32, device=qkv.device)
+        counters = _counters_for(qkv.device, tokens * Hq)
+    row_stride = qkv.stride(0) if tokens > 1 else qkv.shape[1]
+    f = _fn("attention_decode_fused", "lb_attention_decode_fused",
+            [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
+             c_void_p, c_int, c_void_p])
+    _check(f(_ptr(qkv), row_stride, _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
+             _ptr(token_req), _ptr(positions), _ptr(slot_mapping), _ptr(cos_sin), cos_sin.shape[0], rotary_dim, tokens,
+             Hq, Hkv, hd, page_size, scale, key_scale, int(window or 0), int(write_kv), splits, _ptr(part_o),
+             _ptr(part_ml), _ptr(counters), _code(qkv), _stream()), "attention_decode_step")
+    return out
+
+
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                       cu_seqlens: torch.Tensor, start_pos: torch.Tensor, tiles: torch.Tensor, num_tiles: int,
                       scale: float, window: int = 0, *, out: torch.Tensor | None = None) -> torch.Tensor:

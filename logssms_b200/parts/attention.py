@@ -18,7 +18,7 @@ class Attention(Part):
     Checkpoint tensors `q_proj / k_proj / v_proj .weight` are concatenated (rows q | k | v) at
     bind time, as the reference merges them at load (python/logssms/models/weight.py:27-31);
     the flow is python/logssms/layers/attention.py:115-167."""
-    kernels = ("rope", "attention_decode", "attention_prefill", "linear_skinny")
+    kernels = ("rope", "attention_decode", "attention_decode_fused", "attention_prefill", "linear_skinny")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
         self.spec = spec
@@ -61,6 +61,14 @@ class Attention(Part):
         T = x.shape[0]
         qkv = K.linear(x, self.qkv_weight)
         k_cache, v_cache, group = ctx.cache.kv(cache_layer)
+        if ctx.max_len == 1:
+            # a decode step: rotation, cache store, attention over the pages and the merge of key ranges in one launch
+            splits = ctx.attention_splits or K.decode_step_splits(T, s.num_heads, s.num_kv_heads, ctx.max_context)
+            o = K.attention_decode_step(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions,
+                                        ctx.slot_mappings[group], self.position.table, k_cache, v_cache,
+                                        ctx.block_tables[group], ctx.token_req, self.scale, s.key_scale, s.window or 0,
+                                        writes_cache, splits=splits)
+            return K.linear(o.view(T, self.q_size), self.o_weight)
         q = K.rope_kv_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions, ctx.slot_mappings[group],
                             self.position.table, k_cache, v_cache, s.key_scale, writes_cache)
         tables = ctx.block_tables[group]

@@ -271,6 +271,44 @@ def test_attention_decode_token_list_leaves_other_rows(dtype):
     assert bool((out[dev(~mask)] == 7.0).all())
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", ATTN_SHAPES)
+@pytest.mark.parametrize("splits", [1, 3, 40])
+def test_attention_decode_step_rotates_stores_attends_and_merges(dtype, shape, splits):
+    """One launch against the three-kernel chain: rotate + store, attention, merge."""
+    Hq, Hkv, hd, page = shape
+    g = torch.Generator().manual_seed(hd + Hq + splits)
+    lengths = [70, 1, 333, 64, 129, 700]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, [1] * len(lengths))
+    k = K()
+    tokens = len(lengths)
+    qkv = randn(g, tokens, (Hq + 2 * Hkv) * hd + 8, dtype=dtype)[:, :(Hq + 2 * Hkv) * hd]        # a row-strided view
+    rotary = hd // 2 if hd % 32 == 0 else hd
+    inv = 1.0 / (1e4 ** (torch.arange(0, rotary, 2, dtype=torch.float32) / rotary))
+    table = k.rope_table(dev(inv), 1024)
+    positions = case["positions"]
+    slots = torch.tensor([int(case["bt"][r, p // page]) * page + p % page for r, p in case["rows"]], dtype=torch.int32)
+    qkv_d = dev(torch.cat([qkv, torch.zeros(tokens, 8, dtype=dtype)], 1))[:, :(Hq + 2 * Hkv) * hd]
+    scale = hd ** -0.5
+    for window in (0, 100):
+        kc1, vc1, kc2, vc2 = dev(case["kc"]), dev(case["vc"]), dev(case["kc"]), dev(case["vc"])
+        q = k.rope_kv_store(qkv_d, Hq, Hkv, hd, dev(positions), dev(slots), table, kc1, vc1, 0.5)
+        want = k.attention_decode(q, kc1, vc1, dev(case["bt"]), dev(case["token_req"]), dev(positions), scale, window, splits=2)
+        got = k.attention_decode_step(qkv_d, Hq, Hkv, hd, dev(positions), dev(slots), table, kc2, vc2, dev(case["bt"]),
+                                      dev(case["token_req"]), scale, 0.5, window, splits=splits)
+        close(got, want, dtype)
+        held = torch.isfinite(kc1.float())                                    # pages nobody owns stay NaN in the case
+        assert torch.equal(torch.isfinite(kc2.float()), held)
+        assert torch.equal(kc2[held], kc1[held]) and torch.equal(vc2[held], vc1[held])   # the same keys and values were stored
+        # write_kv off: nothing is stored, and the own position is read from the cache (stored by someone else)
+        kc3, vc3 = kc1.clone(), vc1.clone()
+        again = k.attention_decode_step(qkv_d, Hq, Hkv, hd, dev(positions), dev(slots), table, kc3, vc3, dev(case["bt"]),
+                                        dev(case["token_req"]), scale, 0.5, window, write_kv=False, splits=splits)
+        close(again, want, dtype)
+        assert torch.equal(kc3[held], kc1[held])
+    assert int(k._counters_for(torch.device("cuda", torch.cuda.current_device()), 1).abs().sum()) == 0
+
+
 def prefill_inputs(case, lengths, new):
     cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32)
     start = torch.tensor([n - m for n, m in zip(lengths, new)], dtype=torch.int32)
