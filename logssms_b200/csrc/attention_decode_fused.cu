@@ -325,6 +325,277 @@ int launch_chp(const FusedArgs& a, int tokens, cudaStream_t s) {
     return launch_status();
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same step on tensor cores (bfloat16, head_dim <= 128, at most 16 query heads per key/value head).
+// The query heads that share a key/value head are the 16 rows of an mma.sync m16n8k16 tile; every warp
+// walks its own 32-key tiles of the CTA's range: K and V rows arrive by 16-byte cp.async into the warp's
+// own double buffer (the next tile is in flight while this one is used), S = Q K^T and O += P V are
+// tensor-core products, the softmax statistics stay float32.  Per 32 keys this costs ~200 instructions
+// where the kernel above needs ~2000, and the copies keep the memory system busy with few warps.
+typedef __nv_bfloat16 bf16;
+constexpr int kKT = 32;                                  // keys per tile
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;                        // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// HDT: head_dim / 16 rounded up to the instantiated size (4 or 8).
+template <int HDT>
+__global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int hd = a.hd, ld = hd + 8;                    // row stride: an odd number of 16-byte pieces
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [16][ld]   rotated queries (rows beyond the group: zeros)
+    bf16* kn_s = q_s + 16 * ld;                          // [ld]       the token's own key (rotated)
+    bf16* vn_s = kn_s + ld;                              // [ld]       the token's own value
+    bf16* tiles = vn_s + ld;                             // [kWarps][2 stages][K, V][kKT][ld]
+    float* mrg = reinterpret_cast<float*>(tiles + (size_t)kWarps * 4 * kKT * ld);   // [kWarps][16][hd + 2]
+    __shared__ int last_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;
+    const size_t t = blockIdx.x;
+    const int kvh = blockIdx.y;
+    const int G = a.Hq / a.Hkv, h0 = kvh * G;
+    const int split = blockIdx.z;
+    const int pos = a.positions[t];
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int n = pos - lo + 1;
+    const int chunk = (max((n + a.splits - 1) / a.splits, kWarps * kKT) + kKT - 1) / kKT * kKT;
+    const int used = (n + chunk - 1) / chunk;
+    if (split >= used) return;
+    const int begin = lo + split * chunk;
+    const int end = min(begin + chunk, pos + 1);
+    const bool use_new = a.write_kv != 0;
+    const bool owns_new = use_new && begin <= pos && pos < end;
+    const int* bt = a.block_table + (size_t)a.token_req[t] * a.bt_stride;
+    const bf16* row = (const bf16*)a.qkv + t * a.row_stride;
+    const float* cs = a.cos_sin + (size_t)min(max(pos, 0), a.table_rows - 1) * a.rotary_dim;
+    const int pieces = hd / 8;
+
+    for (int i = threadIdx.x; i < 16 * hd; i += kThreads) {
+        const int g = i / hd, c = i % hd;
+        q_s[g * ld + c] = __float2bfloat16_rn(g < G ? rotated<bf16>(row + (size_t)(h0 + g) * hd, c, a.rotary_dim, cs, 1.f, false) : 0.f);
+    }
+    if (owns_new) {
+        const bf16* ksrc = row + (size_t)(a.Hq + kvh) * hd;
+        const bf16* vsrc = row + (size_t)(a.Hq + a.Hkv + kvh) * hd;
+        const long slot = a.slot_mapping[t];
+        for (int c = threadIdx.x; c < hd; c += kThreads) {
+            const bf16 kv = __float2bfloat16_rn(rotated<bf16>(ksrc, c, a.rotary_dim, cs, a.key_scale, true));
+            kn_s[c] = kv; vn_s[c] = vsrc[c];
+            if (slot >= 0) {
+                ((bf16*)a.k_cache)[((size_t)slot * a.Hkv + kvh) * hd + c] = kv;
+                ((bf16*)a.v_cache)[((size_t)slot * a.Hkv + kvh) * hd + c] = vsrc[c];
+            }
+        }
+    }
+    __syncthreads();
+
+    bf16* my_tiles = tiles + (size_t)warp * 4 * kKT * ld;
+    const bf16* kc = (const bf16*)a.k_cache;
+    const bf16* vc = (const bf16*)a.v_cache;
+    // Lane l looks up the cache row of key j0 + l once; the copies then run with consecutive lanes on
+    // consecutive 16-byte pieces of the same row, so that one instruction covers whole 128-byte lines.
+    auto fetch = [&](int j0, int stage) {
+        const int j = j0 + lane;
+        const bool mine = j < end && !(use_new && j == pos);
+        long long off = -1;
+        if (mine) {
+            const int page = j / a.page_size;
+            off = (((long long)bt[page] * a.page_size + (j - page * a.page_size)) * a.Hkv + kvh) * hd;
+        }
+        bf16* kd = my_tiles + (size_t)(stage * 2) * kKT * ld;
+        bf16* vd = kd + kKT * ld;
+        for (int i = lane; i < kKT * pieces; i += 32) {
+            const int r = i / pieces, c = i - r * pieces;
+            const long long roff = __shfl_sync(0xffffffffu, off, r);
+            const bool valid = roff >= 0;
+            cp_async16(kd + r * ld + c * 8, kc + (valid ? roff : 0) + c * 8, valid);
+            cp_async16(vd + r * ld + c * 8, vc + (valid ? roff : 0) + c * 8, valid);
+        }
+    };
+    float o[HDT * 2][4];
+#pragma unroll
+    for (int i = 0; i < HDT * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;     // rows lg and lg + 8 (query heads)
+    const float scale_log2 = a.scale * 1.4426950408889634f;
+    const int first = begin + warp * kKT;
+    if (first < end) fetch(first, 0);
+    cp_async_commit();
+    int stage = 0;
+    for (int j0 = first; j0 < end; j0 += kWarps * kKT, stage ^= 1) {
+        const int next = j0 + kWarps * kKT;
+        if (next < end) fetch(next, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        bf16* kb = my_tiles + (size_t)(stage * 2) * kKT * ld;
+        bf16* vb = kb + kKT * ld;
+        if (use_new && pos >= j0 && pos < j0 + kKT) {     // the token's own key and value take their row of the tile
+            for (int c = lane; c < hd; c += 32) { kb[(pos - j0) * ld + c] = kn_s[c]; vb[(pos - j0) * ld + c] = vn_s[c]; }
+            __syncwarp();
+        }
+        float s[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < HDT; ++kk) {
+            if (kk * 16 < hd) {
+                unsigned qa[4];
+                ldsm_x4(qa, q_s + (lane & 15) * ld + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int n2 = 0; n2 < 2; ++n2) {
+                    unsigned kf[4];
+                    ldsm_x4(kf, kb + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * ld + kk * 16 + (mi & 1) * 8);
+                    mma_bf16(s[2 * n2], qa, kf[0], kf[1]);
+                    mma_bf16(s[2 * n2 + 1], qa, kf[2], kf[3]);
+                }
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nn = 0; nn < 4; ++nn) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j0 + nn * 8 + 2 * lt + (e & 1);
+                if (j >= end) s[nn][e] = -INFINITY;
+            }
+            mx0 = fmaxf(mx0, fmaxf(s[nn][0], s[nn][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[nn][2], s[nn][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        mx0 = fmaxf(m0, mx0 * scale_log2);               // every tile of a warp holds at least one key: finite
+        mx1 = fmaxf(m1, mx1 * scale_log2);
+        const float alpha0 = exp2f(m0 - mx0), alpha1 = exp2f(m1 - mx1);
+        m0 = mx0; m1 = mx1;
+        float sum0 = 0.f, sum1 = 0.f;
+        unsigned pa[2][4];
+#pragma unroll
+        for (int nn = 0; nn < 4; ++nn) {
+            const float e0 = exp2f(fmaf(s[nn][0], scale_log2, -mx0)), e1 = exp2f(fmaf(s[nn][1], scale_log2, -mx0));
+            const float e2 = exp2f(fmaf(s[nn][2], scale_log2, -mx1)), e3 = exp2f(fmaf(s[nn][3], scale_log2, -mx1));
+            sum0 += e0 + e1; sum1 += e2 + e3;
+            pa[nn >> 1][(nn & 1) * 2] = pack_bf16(e0, e1);
+            pa[nn >> 1][(nn & 1) * 2 + 1] = pack_bf16(e2, e3);
+        }
+        l0 = l0 * alpha0 + sum0;
+        l1 = l1 * alpha1 + sum1;
+#pragma unroll
+        for (int i = 0; i < HDT * 2; ++i) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+            for (int d2 = 0; d2 < HDT; ++d2) {
+                if (d2 * 16 < hd) {
+                    unsigned vf[4];
+                    ldsm_x4_t(vf, vb + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * ld + d2 * 16 + (mi >> 1) * 8);
+                    mma_bf16(o[2 * d2], pa[kk], vf[0], vf[1]);
+                    mma_bf16(o[2 * d2 + 1], pa[kk], vf[2], vf[3]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    // per warp: rows (query heads) x columns -> shared memory, in natural-exponent units for the merge
+    const int stride = hd + 2;
+    const float ln2 = 0.6931471805599453f;
+#pragma unroll
+    for (int i = 0; i < HDT * 2; ++i) {
+        const int d = i * 8 + 2 * lt;
+        if (d < hd) {
+            mrg[(warp * 16 + lg) * stride + d] = o[i][0]; mrg[(warp * 16 + lg) * stride + d + 1] = o[i][1];
+            mrg[(warp * 16 + lg + 8) * stride + d] = o[i][2]; mrg[(warp * 16 + lg + 8) * stride + d + 1] = o[i][3];
+        }
+    }
+    if (lt == 0) {
+        mrg[(warp * 16 + lg) * stride + hd] = m0 * ln2; mrg[(warp * 16 + lg) * stride + hd + 1] = l0;
+        mrg[(warp * 16 + lg + 8) * stride + hd] = m1 * ln2; mrg[(warp * 16 + lg + 8) * stride + hd + 1] = l1;
+    }
+    __syncthreads();
+    const size_t group = t * (size_t)a.Hkv + kvh;
+    for (int i = threadIdx.x; i < G * hd; i += kThreads) {
+        const int g = i / hd, d = i % hd;
+        float mt = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mt = fmaxf(mt, mrg[(w * 16 + g) * stride + hd]);
+        float lsum = 0.f, osum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float mw = mrg[(w * 16 + g) * stride + hd];
+            const float f = mw == -INFINITY ? 0.f : expf(mw - mt);
+            lsum += mrg[(w * 16 + g) * stride + hd + 1] * f;
+            osum += mrg[(w * 16 + g) * stride + d] * f;
+        }
+        const int h = h0 + g;
+        if (used == 1) {
+            ((bf16*)a.out)[(t * a.Hq + h) * hd + d] = __float2bfloat16_rn(osum / lsum);
+        } else {
+            const size_t slot = ((size_t)t * a.Hq + h) * a.splits + split;
+            a.part_o[slot * hd + d] = osum;
+            if (d == 0) { a.part_ml[slot * 2] = mt; a.part_ml[slot * 2 + 1] = lsum; }
+        }
+    }
+    if (used == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int done = atomicAdd(a.counters + group, 1);
+        last_flag = done == used - 1;
+        if (last_flag) a.counters[group] = 0;
+    }
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < G * hd; i += kThreads) {
+        const int g = i / hd, d = i % hd;
+        const size_t base = ((size_t)t * a.Hq + h0 + g) * a.splits;
+        float mt = -INFINITY;
+        for (int s2 = 0; s2 < used; ++s2) mt = fmaxf(mt, __ldcg(a.part_ml + (base + s2) * 2));
+        float lsum = 0.f, osum = 0.f;
+        for (int s2 = 0; s2 < used; ++s2) {
+            const float f = expf(__ldcg(a.part_ml + (base + s2) * 2) - mt);
+            lsum += __ldcg(a.part_ml + (base + s2) * 2 + 1) * f;
+            osum += __ldcg(a.part_o + (base + s2) * hd + d) * f;
+        }
+        ((bf16*)a.out)[(t * a.Hq + h0 + g) * hd + d] = __float2bfloat16_rn(osum / lsum);
+    }
+}
+
+template <int HDT>
+int launch_mma(const FusedArgs& a, int tokens, cudaStream_t s) {
+    const int ld = a.hd + 8;
+    const size_t smem = (size_t)(16 + 2 + kWarps * 4 * kKT) * ld * sizeof(bf16) + (size_t)kWarps * 16 * (a.hd + 2) * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(attn_decode_mma_kernel<HDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_decode_mma_kernel<HDT><<<dim3(tokens, a.Hkv, a.splits), kThreads, smem, s>>>(a);
+    return launch_status();
+}
+
 template <typename T>
 int launch(FusedArgs a, int tokens, cudaStream_t s) {
     const int G = a.Hq / a.Hkv;
@@ -365,6 +636,8 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
     FusedArgs a{qkv, row_stride, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, slot_mapping,
                 cos_sin, table_rows, rotary_dim, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
                 write_kv, scale, key_scale};
+    if (dtype == kBF16 && hd <= 128 && Hq / Hkv <= 16)
+        return hd <= 64 ? launch_mma<4>(a, tokens, (cudaStream_t)stream) : launch_mma<8>(a, tokens, (cudaStream_t)stream);
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, tokens, (cudaStream_t)stream));
     return kOk;
 }

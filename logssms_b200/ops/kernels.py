@@ -330,7 +330,7 @@ def decode_step_splits(num_tokens: int, num_heads: int, num_kv_heads: int, max_c
     return max(1, min(_STEP_TARGET_CTAS // items, -(-max_context // 128), 256))
 
 
-_STEP_TARGET_CTAS = 1184        # 8 CTAs on each of the 148 SMs
+_STEP_TARGET_CTAS = 296         # one round of two CTAs on each of the 148 SMs: long ranges keep the copies streaming
 
 
 def attention_decode_step(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,
