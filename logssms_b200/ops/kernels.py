@@ -590,6 +590,58 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = 
     return out
 
 
+_gemm_error: dict[torch.device, torch.Tensor] = {}
+USE_TCGEN05 = True         # bfloat16 products of more than 64 rows: the engine's tcgen05 kernel (False: cuBLAS through torch)
+
+
+def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] > 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.shape[1] % 8 == 0 and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous())))
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out_scale: float = 1.0,
+                 out_f32: bool = False, swiglu_scale: float | None = None) -> torch.Tensor:
+    """x [M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory), with the
+    bias, output multiplier, float32 output or SwiGLU (w = [gate rows; up rows]) done on the sums.
+    `check_gemm_errors()` reports a kernel whose internal wait gave up."""
+    _cuda(x, w, bias)
+    _need(_tcgen05_ok(x, w, bias), "gemm_tcgen05 takes bfloat16 operands, K a multiple of 8, 16-byte aligned")
+    M, Kdim = x.shape
+    _need(w.dim() == 2 and w.shape[1] == Kdim, "weight must be [N, K]")
+    N = w.shape[0]
+    mode = _PLAIN
+    if swiglu_scale is not None:
+        _need(N % 2 == 0 and bias is None and not out_f32 and out_scale == 1.0, "the SwiGLU form takes [gate; up] rows and nothing else")
+        N //= 2
+        mode = _SWIGLU
+    elif out_f32:
+        mode = _OUT_F32
+    _need(bias is None or bias.shape == (N,), "bias must be [N]")
+    out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    err = _gemm_error.get(x.device)
+    if err is None:
+        err = _gemm_error[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    f = _fn("gemm_tcgen05", "lb_gemm_tcgen05", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int,
+                                                c_float, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(bias), _ptr(out), N, M, N, Kdim, out_scale,
+             swiglu_scale if swiglu_scale is not None else 1.0, mode, _ptr(err), _stream()), "gemm_tcgen05")
+    return out
+
+
+def check_gemm_errors(device=None) -> None:
+    """Raise if a tcgen05 product gave up on one of its bounded waits since the last check (synchronises)."""
+    for dev, err in _gemm_error.items():
+        if device is not None and torch.device(device) != dev:
+            continue
+        code = int(err.item())
+        if code:
+            err.zero_()
+            raise KernelError(f"gemm_tcgen05: a wait inside the kernel gave up (role {(code >> 24) & 0x3F}, "
+                              f"block {(code >> 12) & 0xFFF}, k-block {code & 0xFFF})")
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out_scale: float = 1.0,
            out_f32: bool = False) -> torch.Tensor:
     """round(round(x [M, K] @ w[N, K]^T + bias) * out_scale) in x's dtype, or as float32 with `out_f32`.
@@ -605,6 +657,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
         y = gemm_f32(x.float(), w, None if bias is None else bias.float()).to(x.dtype)
     elif _skinny_ok(x, w, bias):
         return linear_skinny(x, w, bias, out_scale=out_scale, out_f32=out_f32)
+    elif USE_TCGEN05 and _tcgen05_ok(x, w, bias):
+        return gemm_tcgen05(x, w, bias, out_scale=out_scale, out_f32=out_f32)
     else:
         y = F.linear(x, w, None if bias is None else bias.to(x.dtype))
     if out_f32 or out_scale != 1.0:
@@ -616,4 +670,6 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_scale: float) ->
     """silu(round(gate * act_scale)) * up with [gate | up] = x @ w_gate_up^T (w rows: gate, then up)."""
     if _skinny_ok(x, w_gate_up, None):
         return linear_skinny(x, w_gate_up, swiglu_scale=act_scale)
+    if USE_TCGEN05 and _tcgen05_ok(x, w_gate_up, None):
+        return gemm_tcgen05(x, w_gate_up, swiglu_scale=act_scale)
     return swiglu(linear(x, w_gate_up), act_scale)

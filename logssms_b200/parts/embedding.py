@@ -30,7 +30,7 @@ class Embedding(Part):
 class LMHead(Part):
     """logits = float32((h W^T) * multiplier); W is the embedding table when the model ties them
     (python/logssms/layers/embedding.py:94-106, python/logssms/models/falcon_h1.py:237)."""
-    kernels = ("norm", "linear_skinny")
+    kernels = ("norm", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, vocab_size: int, hidden_size: int, multiplier: float, tied_to: Embedding | None):
         self.vocab_size, self.hidden_size, self.multiplier, self.tied_to = vocab_size, hidden_size, multiplier, tied_to

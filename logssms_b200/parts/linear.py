@@ -8,7 +8,7 @@ from .base import MATRIX, VECTOR, ParamSpec, Part, normal_init
 
 
 class Linear(Part):
-    kernels = ("linear_skinny",)
+    kernels = ("linear_skinny", "gemm_tcgen05",)
 
     def __init__(self, in_features: int, out_features: int, bias: bool = False, bias_init=None):
         self.in_features, self.out_features, self.has_bias = in_features, out_features, bias

@@ -584,6 +584,44 @@ def test_linear_many_rows_goes_to_the_library_with_the_same_epilogues():
     close(k.linear_swiglu(dev(x), dev(w), 0.9), rnd(rnd(P.silu(rnd(acc[:, :96] * 0.9))) * acc[:, 96:]), torch.bfloat16, tol=1e-2)
 
 
+@pytest.mark.parametrize("shape", [(128, 128, 64), (130, 200, 72), (65, 72, 1000), (300, 1024, 2048), (2048, 3352, 1024)])
+def test_gemm_tcgen05_plain_bias_scale_and_f32(shape):
+    M, N, Kd = shape
+    g = torch.Generator().manual_seed(M + N)
+    x = randn(g, M, Kd + 8, dtype=torch.bfloat16)[:, :Kd]          # a row-strided view
+    w = randn(g, N, Kd, dtype=torch.bfloat16, scale=0.05)
+    b = randn(g, N, dtype=torch.bfloat16)
+    k = K()
+    xd = dev(torch.cat([x, torch.zeros(M, 8, dtype=torch.bfloat16)], 1))[:, :Kd]
+    rnd = rnd_of(torch.bfloat16)
+    acc = x.float() @ w.float().T
+    close(k.gemm_tcgen05(xd, dev(w)), rnd(acc), torch.bfloat16, tol=8e-3)            # one bfloat16 ulp of the largest
+    close(k.gemm_tcgen05(xd, dev(w), dev(b), out_scale=0.7), rnd(rnd(acc + b.float()) * 0.7), torch.bfloat16, tol=1.6e-2)
+    out32 = k.gemm_tcgen05(xd, dev(w), out_scale=0.25, out_f32=True)
+    assert out32.dtype == torch.float32
+    close(out32, rnd(acc) * 0.25, torch.bfloat16, tol=8e-3)
+    k.check_gemm_errors()
+    # exact structure: one hot rows of x pick single rows of w, whatever tile and k-block they sit in
+    eye = torch.zeros(M, Kd, dtype=torch.bfloat16)
+    cols = torch.randint(0, Kd, (M,), generator=g)
+    eye[torch.arange(M), cols] = 1.0
+    assert torch.equal(k.gemm_tcgen05(dev(eye), dev(w)).cpu(), w[:, cols].T.contiguous())
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 64), (200, 200, 96), (2048, 2048, 1024)])
+def test_gemm_tcgen05_swiglu_matches_the_unfused_chain(shape):
+    M, I, Kd = shape
+    g = torch.Generator().manual_seed(M + I)
+    x = randn(g, M, Kd, dtype=torch.bfloat16)
+    w = randn(g, 2 * I, Kd, dtype=torch.bfloat16, scale=0.1)
+    k = K()
+    rnd = rnd_of(torch.bfloat16)
+    gu = rnd(x.float() @ w.float().T)
+    want = rnd(rnd(P.silu(rnd(gu[:, :I] * 0.9))) * gu[:, I:])
+    close(k.gemm_tcgen05(dev(x), dev(w), swiglu_scale=0.9), want, torch.bfloat16, tol=1.6e-2)
+    k.check_gemm_errors()
+
+
 def test_ssm_scan_with_the_gate_in_its_epilogue():
     g = torch.Generator().manual_seed(12)
     nh, Pd, N, G = 6, 24, 32, 2
