@@ -12,7 +12,8 @@
 //   warps 2-5 read the accumulator with tcgen05.ld (32 lanes x 32 columns at a time; warp w may touch lanes
 //             32 (w mod 4) .. +31, i.e. rows of the tile), apply the epilogue and store
 //   Two CTAs fit on an SM (97 KB shared memory, 128 of 512 tensor-memory columns each), so one CTA's epilogue
-//   overlaps the other's main loop.
+//   overlaps the other's main loop.  A product with so few 128-wide tiles that SMs would stay idle runs with
+//   64-wide tiles (one W box per stage, 4 stages) instead.
 //
 // Epilogues, rounding where the unfused chain rounds (python/logssms/layers/linear.py:26,
 // python/logssms/kernel/fused.py:32-50):
@@ -30,10 +31,10 @@
 using namespace lb200;
 
 namespace {
-constexpr int BM = 128, BN = 128, BK = 64, kStages = 3;
+constexpr int BM = 128, BK = 64;                          // the N extent of a tile is a template parameter: 128 or 64
 constexpr int kThreads = 192;
-constexpr uint32_t kABytes = BM * BK * 2, kBHalfBytes = (BN / 2) * BK * 2, kStageBytes = kABytes + 2 * kBHalfBytes;
-constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kABytes = BM * BK * 2, kBHalfBytes = 64 * BK * 2;     // W arrives in boxes of 64 rows
+constexpr uint32_t stage_bytes(int bn) { return kABytes + (bn / 64) * kBHalfBytes; }
 constexpr uint32_t kSpinLimit = 1u << 22;                 // polls of try_wait before a wait gives up
 
 struct GemmArgs {
@@ -103,8 +104,11 @@ __device__ __forceinline__ void report(int* error, int role, int kb) {
     if (error != nullptr) atomicCAS(error, 0, (role << 24) | ((blockIdx.x & 0xFFF) << 12) | (kb & 0xFFF) | 0x40000000);
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+template <int kStages, int BN>
+__global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+    constexpr uint32_t kStageBytes = stage_bytes(BN);
+    constexpr uint32_t kTmemCols = BN;                    // accumulator columns (a power of two >= 32)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms: 1024-byte aligned
     uint64_t* full = reinterpret_cast<uint64_t*>(base + kStages * kStageBytes);
@@ -146,7 +150,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 mbar_expect_tx(full + s, kStageBytes);
                 tma_load_2d(a_tile, &map_a, full + s, kb * BK, m0);
                 tma_load_2d(a_tile + kABytes, &map_b, full + s, kb * BK, w_row0);
-                tma_load_2d(a_tile + kABytes + kBHalfBytes, &map_b, full + s, kb * BK, w_row1);
+                if (BN == 128) tma_load_2d(a_tile + kABytes + kBHalfBytes, &map_b, full + s, kb * BK, w_row1);
             }
             if (*failed) {                                 // let the copies already under way land before the CTA leaves
                 for (int kb = max(0, issued - kStages); kb < issued; ++kb) mbar_wait(full + kb % kStages, (kb / kStages) & 1);
@@ -175,43 +179,65 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_after();
         if (__all_sync(0xffffffffu, ok && !*failed)) {     // tcgen05.ld wants the whole warp: decide together
             const int quarter = warp & 3;                  // the lanes of tensor memory this warp may read
-            const int row = m0 + quarter * 32 + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-            if (g.epilogue == kSwiglu) {
+            // The stage ring is idle now (every product has been committed): this warp's 32 rows pass through
+            // its own slice of it, so that the stores to global memory are whole 16-byte pieces of a row.
+            const int out_cols = g.epilogue == kSwiglu ? BN / 2 : BN;          // columns of the output tile
+            const int col0 = tile_n * out_cols;
+            const int esz = g.epilogue == kOutF32 ? 4 : 2;
+            const int row_bytes = out_cols * esz + 16;                          // padded: rows land in different banks
+            uint8_t* stage_rows = base + (size_t)quarter * 32 * (BN * 4 + 16);
+            uint8_t* my_row = stage_rows + (size_t)lane * row_bytes;
 #pragma unroll 1
-                for (int c = 0; c < BN / 2; c += 32) {
-                    uint32_t gate[32], up[32];
-                    tmem_ld32(lane_addr + c, gate);
+            for (int c = 0; c < out_cols; c += 32) {
+                uint32_t acc[32];
+                tmem_ld32(lane_addr + c, acc);
+                if (g.epilogue == kSwiglu) {
+                    uint32_t up[32];
                     tmem_ld32(lane_addr + BN / 2 + c, up);
-                    if (row < g.M) {
-                        __nv_bfloat16* dst = (__nv_bfloat16*)g.out + (size_t)row * g.ldo + tile_n * (BN / 2) + c;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (tile_n * (BN / 2) + c + j < g.N) {
-                                const float gv = round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(__uint_as_float(gate[j])) * g.act_scale);
-                                const float act = round_to<__nv_bfloat16>(silu_f(gv));
-                                dst[j] = __float2bfloat16_rn(act * round_to<__nv_bfloat16>(__uint_as_float(up[j])));
-                            }
+                    for (int j = 0; j < 32; j += 2) {
+                        float o2[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float gv = round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(__uint_as_float(acc[j + e])) * g.act_scale);
+                            const float act = round_to<__nv_bfloat16>(silu_f(gv));
+                            o2[e] = act * round_to<__nv_bfloat16>(__uint_as_float(up[j + e]));
                         }
+                        *reinterpret_cast<__nv_bfloat162*>(my_row + (c + j) * 2) = __floats2bfloat162_rn(o2[0], o2[1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float v2[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            float v = __uint_as_float(acc[j + e]);
+                            if (g.bias != nullptr && col0 + c + j + e < g.N) v += __bfloat162float(g.bias[col0 + c + j + e]);
+                            v2[e] = round_to<__nv_bfloat16>(v) * g.out_scale;
+                        }
+                        if (g.epilogue == kOutF32) *reinterpret_cast<float2*>(my_row + (c + j) * 4) = make_float2(v2[0], v2[1]);
+                        else *reinterpret_cast<__nv_bfloat162*>(my_row + (c + j) * 2) = __floats2bfloat162_rn(v2[0], v2[1]);
                     }
                 }
-            } else {
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    uint32_t acc[32];
-                    tmem_ld32(lane_addr + c, acc);
-                    if (row < g.M) {
-                        const int n0 = tile_n * BN + c;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (n0 + j < g.N) {
-                                float v = __uint_as_float(acc[j]);
-                                if (g.bias != nullptr) v += __bfloat162float(g.bias[n0 + j]);
-                                v = round_to<__nv_bfloat16>(v);
-                                if (g.epilogue == kOutF32) ((float*)g.out)[(size_t)row * g.ldo + n0 + j] = v * g.out_scale;
-                                else ((__nv_bfloat16*)g.out)[(size_t)row * g.ldo + n0 + j] = __float2bfloat16_rn(v * g.out_scale);
-                            }
-                        }
+            }
+            __syncwarp();
+            // rows of the warp, 16 bytes per lane; whole pieces when the row start and N allow it, else element by element
+            const int pieces = out_cols * esz / 16;
+            const bool vec_ok = ((g.ldo * esz) % 16 == 0) && (((uintptr_t)g.out) % 16 == 0) && ((col0 * esz) % 16 == 0);
+            for (int i = lane; i < 32 * pieces; i += 32) {
+                const int r = i / pieces, pc = i % pieces;
+                const int grow = m0 + quarter * 32 + r;
+                if (grow >= g.M) continue;
+                const int first_col = col0 + pc * (16 / esz);
+                const uint8_t* src = stage_rows + (size_t)r * row_bytes + pc * 16;
+                uint8_t* dst = (uint8_t*)g.out + ((size_t)grow * g.ldo + first_col) * esz;
+                if (vec_ok && first_col + 16 / esz <= g.N) {
+                    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+                } else {
+                    for (int e = 0; e < 16 / esz && first_col + e < g.N; ++e) {
+                        if (esz == 4) reinterpret_cast<float*>(dst)[e] = reinterpret_cast<const float*>(src)[e];
+                        else reinterpret_cast<__nv_bfloat16*>(dst)[e] = reinterpret_cast<const __nv_bfloat16*>(src)[e];
                     }
                 }
             }
@@ -264,18 +290,30 @@ extern "C" int lb_gemm_tcgen05(const void* a, long lda, const void* w, const voi
     CUtensorMap map_a, map_b;
     int rc = make_map(&map_a, a, M, K, lda, BM);
     if (rc != 0) return rc;
-    rc = make_map(&map_b, w, epilogue == kSwiglu ? 2L * N : N, K, K, BN / 2);
+    rc = make_map(&map_b, w, epilogue == kSwiglu ? 2L * N : N, K, K, 64);
     if (rc != 0) return rc;
     GemmArgs g{out, ldo, (const __nv_bfloat16*)bias, M, N, K, out_scale, act_scale, epilogue, error};
-    const int per_tile_n = epilogue == kSwiglu ? BN / 2 : BN;
-    const long tiles = (long)((M + BM - 1) / BM) * ((N + per_tile_n - 1) / per_tile_n);
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const long tiles_m = (M + BM - 1) / BM;
+    // 128-wide tiles unless they would not even give every SM one CTA; then 64-wide ones (twice as many).
+    // SwiGLU always takes 64 gate + 64 up rows of W per tile.
+    const bool narrow = epilogue != kSwiglu && tiles_m * ((N + 127) / 128) <= sms;
+    const int per_tile_n = (epilogue == kSwiglu || narrow) ? 64 : 128;
+    const long tiles = tiles_m * ((N + per_tile_n - 1) / per_tile_n);
     if (tiles > 0x7fffffffL) return kTooLarge;
-    const size_t smem = (size_t)kStages * kStageBytes + 1024 + 256;
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_tcgen05_kernel<3, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * (int)stage_bytes(128) + 1280);
+        cudaFuncSetAttribute(gemm_tcgen05_kernel<4, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (int)stage_bytes(64) + 1280);
         configured = true;
     }
-    gemm_tcgen05_kernel<<<(unsigned)tiles, kThreads, smem, (cudaStream_t)stream>>>(map_a, map_b, g);
+    if (narrow) {
+        const size_t smem = 4 * (size_t)stage_bytes(64) + 1280;         // 4 x 24 KB: two CTAs per SM
+        gemm_tcgen05_kernel<4, 64><<<(unsigned)tiles, kThreads, smem, (cudaStream_t)stream>>>(map_a, map_b, g);
+    } else {
+        const size_t smem = 3 * (size_t)stage_bytes(128) + 1280;        // 3 x 32 KB: two CTAs per SM
+        gemm_tcgen05_kernel<3, 128><<<(unsigned)tiles, kThreads, smem, (cudaStream_t)stream>>>(map_a, map_b, g);
+    }
     return launch_status();
 }

@@ -13,6 +13,7 @@ own FFMA kernel so that no reduced-precision matrix mode can take part.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_long, c_void_p
 
 import torch
@@ -591,7 +592,12 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = 
 
 
 _gemm_error: dict[torch.device, torch.Tensor] = {}
-USE_TCGEN05 = True         # bfloat16 products of more than 64 rows: the engine's tcgen05 kernel (False: cuBLAS through torch)
+# Which kernel takes bfloat16 products of more than 64 rows.  "auto": the engine's tcgen05 kernel where its
+# fused epilogue pays (gate|up with SwiGLU: 31 us against 18 + 9 us for the library product plus the SwiGLU
+# kernel at 2048 x 4096 x 1024, one 16 MB round trip less), the library (cuBLAS through torch) for plain
+# products, where it is still about twice as fast as the tcgen05 kernel.  "tcgen05": everything on the
+# engine's kernel.  "library": everything on cuBLAS.
+GEMM_MODE = os.environ.get("LOGSSMS_B200_GEMM", "auto")
 
 
 def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> bool:
@@ -657,7 +663,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
         y = gemm_f32(x.float(), w, None if bias is None else bias.float()).to(x.dtype)
     elif _skinny_ok(x, w, bias):
         return linear_skinny(x, w, bias, out_scale=out_scale, out_f32=out_f32)
-    elif USE_TCGEN05 and _tcgen05_ok(x, w, bias):
+    elif GEMM_MODE == "tcgen05" and _tcgen05_ok(x, w, bias):
         return gemm_tcgen05(x, w, bias, out_scale=out_scale, out_f32=out_f32)
     else:
         y = F.linear(x, w, None if bias is None else bias.to(x.dtype))
@@ -670,6 +676,6 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_scale: float) ->
     """silu(round(gate * act_scale)) * up with [gate | up] = x @ w_gate_up^T (w rows: gate, then up)."""
     if _skinny_ok(x, w_gate_up, None):
         return linear_skinny(x, w_gate_up, swiglu_scale=act_scale)
-    if USE_TCGEN05 and _tcgen05_ok(x, w_gate_up, None):
+    if GEMM_MODE in ("auto", "tcgen05") and _tcgen05_ok(x, w_gate_up, None):
         return gemm_tcgen05(x, w_gate_up, swiglu_scale=act_scale)
     return swiglu(linear(x, w_gate_up), act_scale)
