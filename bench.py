@@ -290,6 +290,66 @@ def run_ours(args) -> dict:
         shutil.rmtree(tmp, ignore_errors=True)
 
 
+# --------------------------------------------------------------------------- a short run for profilers
+def run_probe(args) -> int:
+    """`--probe decode|prefill`: a few steps of one kind on a model of `--layers` layers (default 4), with
+    the CUDA profiler range switched on around the last ones, for `ncu --profile-from-start off`.  Prints a
+    line with the device time of the unprofiled steps; nothing here is a benchmark value."""
+    import numpy as np
+    import torch
+
+    from logssms_b200.config import make_model_config
+    from logssms_b200.engine import LLM, StepEntry
+    from logssms_b200.sampling import SamplingParams
+    from logssms_b200.weights import write_random_model
+
+    cfg = dict(MODEL)
+    cfg["num_hidden_layers"] = args.layers or 4
+    tmp = tempfile.mkdtemp(prefix="logssms_b200_probe_")
+    try:
+        write_random_model(make_model_config(cfg), tmp, seed=0, dtype=torch.bfloat16)
+        llm = LLM(tmp, "bfloat16", max_running_requests=64, max_seq_len_override=MAX_SEQ_LEN, max_prefill_tokens=8192)
+        rng = np.random.default_rng(0)
+        if args.probe == "decode":
+            sp = SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True)
+            reqs = [llm.add_request(rng.integers(0, cfg["vocab_size"], CONTEXT - 1).tolist(), sp) for _ in range(args.batch)]
+            while not all(r.prompt_done for r in reqs):
+                llm.step()
+            for _ in range(5):
+                llm.step()
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(10):
+                llm.step()
+            stop.record()
+            torch.cuda.synchronize()
+            print(f"probe decode: batch {args.batch}, {cfg['num_hidden_layers']} layers, {start.elapsed_time(stop) / 10:.3f} ms/step", flush=True)
+            torch.cuda.profiler.start()
+            llm.step()
+            llm.step()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        else:
+            ids = rng.integers(0, cfg["vocab_size"], PREFILL_TOKENS).tolist()
+            for i in range(3):
+                req = llm.engine.new_request()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                llm.engine.step([StepEntry(req, ids, [PREFILL_TOKENS - 1])])
+                torch.cuda.synchronize()
+                print(f"probe prefill: {PREFILL_TOKENS} tokens, {cfg['num_hidden_layers']} layers, {(time.perf_counter() - t0) * 1e3:.3f} ms", flush=True)
+                llm.engine.release(req)
+            req = llm.engine.new_request()
+            torch.cuda.profiler.start()
+            llm.engine.step([StepEntry(req, ids, [PREFILL_TOKENS - 1])])
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        return 0
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
 # --------------------------------------------------------------------------- the reference arm
 def run_reference(args) -> dict:
     """The reference runs in a child process (its own CUDA context, streams and JIT caches), with a time
@@ -329,12 +389,16 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (both are reported)")
     ap.add_argument("--prefill-budget", type=int, default=8192, help="token budget of one scheduled step")
     ap.add_argument("--reference-timeout", type=int, default=900, help="seconds the reference arm may take")
+    ap.add_argument("--probe", choices=["decode", "prefill"], default=None,
+                    help="a short run of one kind of step for a profiler (see profiles/); prints no benchmark line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print("bench.py: this engine runs on one GPU; --gpus N>1 is not built")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.probe:
+        return run_probe(args)
     if args.impl == "reference":
         try:
             line = run_reference(args)
