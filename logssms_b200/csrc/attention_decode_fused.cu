@@ -391,25 +391,6 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     const float* cs = a.cos_sin + (size_t)min(max(pos, 0), a.table_rows - 1) * a.rotary_dim;
     const int pieces = hd / 8;
 
-    for (int i = threadIdx.x; i < 16 * hd; i += kThreads) {
-        const int g = i / hd, c = i % hd;
-        q_s[g * ld + c] = __float2bfloat16_rn(g < G ? rotated<bf16>(row + (size_t)(h0 + g) * hd, c, a.rotary_dim, cs, 1.f, false) : 0.f);
-    }
-    if (owns_new) {
-        const bf16* ksrc = row + (size_t)(a.Hq + kvh) * hd;
-        const bf16* vsrc = row + (size_t)(a.Hq + a.Hkv + kvh) * hd;
-        const long slot = a.slot_mapping[t];
-        for (int c = threadIdx.x; c < hd; c += kThreads) {
-            const bf16 kv = __float2bfloat16_rn(rotated<bf16>(ksrc, c, a.rotary_dim, cs, a.key_scale, true));
-            kn_s[c] = kv; vn_s[c] = vsrc[c];
-            if (slot >= 0) {
-                ((bf16*)a.k_cache)[((size_t)slot * a.Hkv + kvh) * hd + c] = kv;
-                ((bf16*)a.v_cache)[((size_t)slot * a.Hkv + kvh) * hd + c] = vsrc[c];
-            }
-        }
-    }
-    __syncthreads();
-
     bf16* my_tiles = tiles + (size_t)warp * 4 * kKT * ld;
     const bf16* kc = (const bf16*)a.k_cache;
     const bf16* vc = (const bf16*)a.v_cache;
@@ -439,8 +420,27 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;     // rows lg and lg + 8 (query heads)
     const float scale_log2 = a.scale * 1.4426950408889634f;
     const int first = begin + warp * kKT;
-    if (first < end) fetch(first, 0);
+    if (first < end) fetch(first, 0);                    // the first tile is on its way while the queries are prepared
     cp_async_commit();
+    for (int i = threadIdx.x; i < 16 * hd; i += kThreads) {
+        const int g = i / hd, c = i % hd;
+        q_s[g * ld + c] = __float2bfloat16_rn(g < G ? rotated<bf16>(row + (size_t)(h0 + g) * hd, c, a.rotary_dim, cs, 1.f, false) : 0.f);
+    }
+    if (owns_new) {
+        const bf16* ksrc = row + (size_t)(a.Hq + kvh) * hd;
+        const bf16* vsrc = row + (size_t)(a.Hq + a.Hkv + kvh) * hd;
+        const long slot = a.slot_mapping[t];
+        for (int c = threadIdx.x; c < hd; c += kThreads) {
+            const bf16 kv = __float2bfloat16_rn(rotated<bf16>(ksrc, c, a.rotary_dim, cs, a.key_scale, true));
+            kn_s[c] = kv; vn_s[c] = vsrc[c];
+            if (slot >= 0) {
+                ((bf16*)a.k_cache)[((size_t)slot * a.Hkv + kvh) * hd + c] = kv;
+                ((bf16*)a.v_cache)[((size_t)slot * a.Hkv + kvh) * hd + c] = vsrc[c];
+            }
+        }
+    }
+    __syncthreads();
+
     int stage = 0;
     for (int j0 = first; j0 < end; j0 += kWarps * kKT, stage ^= 1) {
         const int next = j0 + kWarps * kKT;

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <utility>
 
 namespace lb200 {
@@ -76,10 +77,11 @@ template <typename... KArgs, typename... Args>
 inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    static const bool enabled = [] { const char* e = getenv("LOGSSMS_B200_PDL"); return e == nullptr || e[0] != '0'; }();
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    cfg.attrs = attr; cfg.numAttrs = enabled ? 1 : 0;        // LOGSSMS_B200_PDL=0: plain stream order (to measure what it buys)
     return (int)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 

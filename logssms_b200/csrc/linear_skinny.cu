@@ -37,6 +37,11 @@ struct SkinnyArgs {
     void* out; long ldo;
     int M, N, K;
     float out_scale, act_scale;
+    // optional prologue: x is not given but made here, as the RMSNorm of a residual sum
+    //   v = [round(round(nx * in0) + round(nother * in1))  or  nx] + nres ; residual_out = round(v) (one CTA writes it)
+    //   x = round(round(v * rsqrt(mean(v^2) + eps) * nweight) * nscale)
+    const __nv_bfloat16* nx; const __nv_bfloat16* nother; const __nv_bfloat16* nres; __nv_bfloat16* nres_out;
+    const float* nweight; float neps, nin0, nin1, nscale;
 };
 
 __device__ __forceinline__ uint4 load_stream(const void* p) {
@@ -56,12 +61,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 enum Epilogue : int { kPlain = 0, kOutF32 = 1, kSwiglu = 2 };
 
 // MT: tiles of 8 batch rows.  HALVES: 1, or 2 for swiglu (gate and up rows of the same feature).
-template <int MT, int EPI>
+// NORM: x is produced in shared memory by the fused residual-add + RMSNorm prologue (K <= 2048, M <= 16).
+template <int MT, int EPI, bool NORM>
 __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     constexpr int HALVES = EPI == kSwiglu ? 2 : 1;
     constexpr int MP = MT * 8 + 1;
     extern __shared__ float red_raw[];
     float (*red)[HALVES][kFeat][MP] = reinterpret_cast<float (*)[HALVES][kFeat][MP]>(red_raw);
+    // normalised rows, bfloat16, row stride K + 8 (behind the reduction buffer, 16-byte aligned)
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(red_raw + ((kWarps * HALVES * kFeat * MP + 3) / 4) * 4);
+    const int ldxs = a.K + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * kFeat;
@@ -79,7 +88,8 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
         }
     const __nv_bfloat16* xrow[MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) xrow[m] = a.x + (size_t)min(m * 8 + g, a.M - 1) * a.ldx;
+    for (int m = 0; m < MT; ++m)
+        xrow[m] = NORM ? xs + (size_t)(m * 8 + g) * ldxs : a.x + (size_t)min(m * 8 + g, a.M - 1) * a.ldx;
 
     float acc[HALVES][MT][4];
 #pragma unroll
@@ -109,6 +119,71 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     pdl_trigger();
     load_w(c_begin);
     pdl_wait();
+    if (NORM) {
+        // one warp per row; a lane keeps its 8-element pieces of the row in registers between the two passes
+        constexpr int kMaxPieces = 8;                     // K <= 32 lanes * 8 pieces * 8 elements = 2048
+        const int pieces = K / 8;
+        for (int r = warp; r < MT * 8; r += kWarps) {
+            __nv_bfloat16* dst = xs + (size_t)r * ldxs;
+            if (r >= a.M) {
+                for (int pc = lane; pc < pieces; pc += 32) *reinterpret_cast<uint4*>(dst + pc * 8) = zero;
+                continue;
+            }
+            float v[kMaxPieces][8];
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < kMaxPieces; ++i) {
+                const int pc = lane + 32 * i;
+                if (pc < pieces) {
+                    const size_t off = (size_t)r * K + pc * 8;
+                    const uint4 xv = *reinterpret_cast<const uint4*>(a.nx + off);
+                    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+                    uint4 ov = zero, rv = zero;
+                    if (a.nother != nullptr) ov = *reinterpret_cast<const uint4*>(a.nother + off);
+                    if (a.nres != nullptr) rv = *reinterpret_cast<const uint4*>(a.nres + off);
+                    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+                    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+                    uint4 outv;
+                    __nv_bfloat162* out2 = reinterpret_cast<__nv_bfloat162*>(&outv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float2 f = __bfloat1622float2(x2[e]);
+                        if (a.nother != nullptr) {
+                            const float2 fo = __bfloat1622float2(o2[e]);
+                            f.x = round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(f.x * a.nin0) + round_to<__nv_bfloat16>(fo.x * a.nin1));
+                            f.y = round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(f.y * a.nin0) + round_to<__nv_bfloat16>(fo.y * a.nin1));
+                        }
+                        if (a.nres != nullptr) { const float2 fr = __bfloat1622float2(r2[e]); f.x += fr.x; f.y += fr.y; }
+                        v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y;
+                        ss += f.x * f.x + f.y * f.y;
+                        out2[e] = __floats2bfloat162_rn(f.x, f.y);
+                    }
+                    if (a.nres_out != nullptr && blockIdx.x == 0) *reinterpret_cast<uint4*>(a.nres_out + off) = outv;
+                }
+            }
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)K + a.neps);
+#pragma unroll
+            for (int i = 0; i < kMaxPieces; ++i) {
+                const int pc = lane + 32 * i;
+                if (pc < pieces) {
+                    const float4 w0 = *reinterpret_cast<const float4*>(a.nweight + pc * 8);
+                    const float4 w1 = *reinterpret_cast<const float4*>(a.nweight + pc * 8 + 4);
+                    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                    uint4 outv;
+                    __nv_bfloat162* out2 = reinterpret_cast<__nv_bfloat162*>(&outv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float n0 = round_to<__nv_bfloat16>(v[i][2 * e] * inv * w[2 * e]);
+                        const float n1 = round_to<__nv_bfloat16>(v[i][2 * e + 1] * inv * w[2 * e + 1]);
+                        out2[e] = __floats2bfloat162_rn(n0 * a.nscale, n1 * a.nscale);
+                    }
+                    *reinterpret_cast<uint4*>(dst + pc * 8) = outv;
+                }
+            }
+        }
+        __syncthreads();
+    }
     for (int c0 = c_begin; c0 < c_end; c0 += kUnroll) {
         if (c0 != c_begin) load_w(c0);
 #pragma unroll
@@ -117,7 +192,8 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
             const bool ok = (c0 + u) < c_end && k < K;
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-                const uint4 xv = ok ? __ldg(reinterpret_cast<const uint4*>(xrow[m] + k)) : zero;
+                const uint4 xv = ok ? (NORM ? *reinterpret_cast<const uint4*>(xrow[m] + k)
+                                            : __ldg(reinterpret_cast<const uint4*>(xrow[m] + k))) : zero;
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
                     mma_bf16(acc[h][m], wv[u][h][0].x, wv[u][h][1].x, wv[u][h][0].y, wv[u][h][1].y, xv.x, xv.y);
@@ -162,25 +238,37 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     }
 }
 
-template <int EPI>
+template <int EPI, bool NORM>
 int launch_mt(const SkinnyArgs& a, cudaStream_t s) {
     const dim3 grid((a.N + kFeat - 1) / kFeat);
     const int mt = (a.M + 7) / 8;
     constexpr int halves = EPI == kSwiglu ? 2 : 1;
 #define LB_SKINNY(MT)                                                                                       \
     {                                                                                                       \
-        const size_t smem = sizeof(float) * kWarps * halves * kFeat * (MT * 8 + 1);                         \
+        size_t smem = sizeof(float) * ((kWarps * halves * kFeat * (MT * 8 + 1) + 3) / 4 * 4);               \
+        if (NORM) smem += (size_t)MT * 8 * (a.K + 8) * sizeof(__nv_bfloat16);                               \
         if (smem > 48 * 1024)                                                                               \
-            cudaFuncSetAttribute(skinny_linear_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        rc = launch_pdl(skinny_linear_kernel<MT, EPI>, grid, dim3(kThreads), smem, s, a);                   \
+            cudaFuncSetAttribute(skinny_linear_kernel<MT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        rc = launch_pdl(skinny_linear_kernel<MT, EPI, NORM>, grid, dim3(kThreads), smem, s, a);             \
     }
     int rc = 0;
     if (mt <= 1) LB_SKINNY(1)
     else if (mt <= 2) LB_SKINNY(2)
+    else if (NORM) return kTooLarge;
     else if (mt <= 4) LB_SKINNY(4)
     else LB_SKINNY(8)
 #undef LB_SKINNY
     return rc != 0 ? rc : launch_status();
+}
+
+template <bool NORM>
+int launch_epi(const SkinnyArgs& a, int epilogue, cudaStream_t s) {
+    switch (epilogue) {
+        case kPlain: return launch_mt<kPlain, NORM>(a, s);
+        case kOutF32: return launch_mt<kOutF32, NORM>(a, s);
+        case kSwiglu: return launch_mt<kSwiglu, NORM>(a, s);
+        default: return kBadSize;
+    }
 }
 }  // namespace
 
@@ -194,11 +282,25 @@ extern "C" int lb_linear_skinny(const void* x, long ldx, const void* w, const vo
     if (M > 64) return kTooLarge;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return kBadSize;
     SkinnyArgs a{(const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, out, ldo,
-                 M, N, K, out_scale, act_scale};
-    switch (epilogue) {
-        case kPlain: return launch_mt<kPlain>(a, (cudaStream_t)stream);
-        case kOutF32: return launch_mt<kOutF32>(a, (cudaStream_t)stream);
-        case kSwiglu: return launch_mt<kSwiglu>(a, (cudaStream_t)stream);
-        default: return kBadSize;
-    }
+                 M, N, K, out_scale, act_scale, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, 1.f, 1.f, 1.f};
+    return launch_epi<false>(a, epilogue, (cudaStream_t)stream);
+}
+
+// The same product with x made on the fly: x = round(rmsnorm(v; norm_weight, eps) * norm_scale) with
+// v = [round(round(nx * in0) + round(nother * in1)) or nx] + nres.  nx / nother / nres / res_out: contiguous
+// [M, K] bfloat16 (nother, nres, res_out may be null); res_out (the new residual, round(v)) must not alias
+// nres: other CTAs still read it.  M <= 16, K a multiple of 8 up to 2048, norm_weight float32 [K].
+extern "C" int lb_linear_skinny_normed(const void* nx, const void* nother, const void* nres, void* res_out,
+                                       const float* norm_weight, float eps, float in0, float in1, float norm_scale,
+                                       const void* w, const void* bias, void* out, long ldo, int M, int N, int K,
+                                       float out_scale, float act_scale, int epilogue, void* stream) {
+    if (M <= 0 || N <= 0) return kOk;
+    if (K <= 0 || K % 8) return kBadSize;
+    if (M > 16 || K > 2048) return kTooLarge;
+    if (((uintptr_t)nx | (uintptr_t)w | (uintptr_t)nother | (uintptr_t)nres | (uintptr_t)res_out | (uintptr_t)norm_weight) & 15) return kBadSize;
+    if (res_out != nullptr && res_out == nres) return kBadSize;
+    SkinnyArgs a{nullptr, 0, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, out, ldo, M, N, K, out_scale, act_scale,
+                 (const __nv_bfloat16*)nx, (const __nv_bfloat16*)nother, (const __nv_bfloat16*)nres, (__nv_bfloat16*)res_out,
+                 norm_weight, eps, in0, in1, norm_scale};
+    return launch_epi<true>(a, epilogue, (cudaStream_t)stream);
 }

@@ -374,10 +374,14 @@ int launch_scan(const SsdArgs& a, int n_chunks, cudaStream_t s) {
 inline bool wide(int P, int N) { return N > 128 || P > 64; }
 }  // namespace
 
-// Largest chunk length <= `chunk` (halving) whose shared-memory tiles fit; 0 when the sizes are not taken.
+// Chunk length the kernels use for a configured chunk size: at most `chunk`, at most kPreferredChunk (the work
+// inside a chunk grows with its square, the work between chunks does not, and shorter chunks leave room for
+// three CTAs per SM; the result does not depend on the cut beyond float32 rounding), halved until the
+// shared-memory tiles fit; 0 when the sizes are not taken.
+constexpr int kPreferredChunk = 64;
 extern "C" int lb_ssd_chunk_len(int chunk, int P, int N) {
     if (P <= 0 || N <= 0 || P % 8 || N % 8 || P > 128 || N > 256 || chunk <= 0) return 0;
-    int L = chunk > 256 ? 256 : chunk;
+    int L = chunk > kPreferredChunk ? kPreferredChunk : chunk;
     if (wide(P, N) && L > 128) L = 128;
     while (L > 16 && (scan_smem(L, P, N) > kSmemLimit || state_smem(L, P, N) > kSmemLimit)) L = (L + 1) / 2;
     if (scan_smem(L, P, N) > kSmemLimit || state_smem(L, P, N) > kSmemLimit) return 0;

@@ -17,6 +17,11 @@ with its "mixed" policy as the only one):
     fit is cut at the budget, anywhere, and goes on in the next step.
   * A request ends after `max_tokens` new tokens or at an end-of-sequence token (unless
     `ignore_eos`); its row, pages and state slot go back at once.
+  * Host and device overlap in the steady state of decoding: sampled ids are copied to pinned host memory
+    without waiting, and while the same requests go on decoding the next step is launched from the ids
+    still on the device before the host reads the previous ones.  A request that ends at an end-of-sequence
+    token is then noticed one step late: the step that was already launched for it is discarded (the
+    reference finishes such requests one step late as well, python/logssms/scheduler/scheduler.py:164-180).
 """
 from __future__ import annotations
 
@@ -55,6 +60,15 @@ class Request:
 
 
 @dataclass
+class _InFlight:
+    """Sampled ids of a step that the host has not read yet."""
+    requests: list
+    tokens: torch.Tensor          # int32 on the device, one per request
+    pinned: torch.Tensor          # their copy in pinned host memory (valid after `event`)
+    event: "torch.cuda.Event | None"      # None: the ids are already on the host (a sampler that runs there)
+
+
+@dataclass
 class StepDecision:
     """What one step runs: (request, first token index, number of tokens, sample afterwards?)."""
     decodes: list[Request]
@@ -80,6 +94,9 @@ class Scheduler:
         self._count = 0
         self.steps = 0
         self.d2h_bytes = 0
+        self._inflight: _InFlight | None = None
+        self._pinned: list[torch.Tensor] = []
+        self.overlap = True           # launch the next decode step before reading the previous step's ids
 
     # ------------------------------------------------------------------ intake
     def add_request(self, prompt: Sequence[int], params: SamplingParams | None = None) -> Request:
@@ -129,12 +146,24 @@ class Scheduler:
         return StepDecision(decodes, portions)
 
     def step(self) -> list[Request]:
-        """Run one step; return the requests that finished in it."""
+        """Run one step; return the requests that are known to have finished since the last call."""
+        inflight = self._inflight
+        if inflight is not None and self.overlap and self._goes_on(inflight):
+            # the same requests decode on: launch their next step from the ids on the device, then read the previous ids
+            reqs = inflight.requests
+            logits = self.engine.step([StepEntry(r.cache, [0], [0]) for r in reqs], device_tokens=inflight.tokens)
+            self.steps += 1
+            for r in reqs:
+                r.computed += 1
+            self._inflight = self._sample(logits, reqs, pending=1)
+            return self._read(inflight)
+        done = self._read(inflight) if inflight is not None else []
+        self._inflight = None
         decision = self.schedule()
         if decision.num_tokens == 0:
             if self.waiting and not self.running:
                 raise RuntimeError("scheduler is stuck: requests wait but nothing runs and nothing fits")
-            return []
+            return done
         entries, sampled = [], []
         for r in decision.decodes:
             entries.append(StepEntry(r.cache, [r.output[-1]], [0]))
@@ -149,18 +178,66 @@ class Scheduler:
             r.computed += 1
         for r, _, n, _ in decision.portions:
             r.computed += n
-        done: list[Request] = []
         if sampled:
-            tokens = self.sampler.sample(logits, [r.params for r in sampled], [r.seed for r in sampled],
-                                         [len(r.output) for r in sampled])
-            self.d2h_bytes += tokens.numel() * tokens.element_size()
-            for r, tok in zip(sampled, tokens.tolist()):
-                r.output.append(int(tok))
-                if int(tok) in self.eos and not r.params.ignore_eos:
-                    done.append(self._finish(r, "stop"))
-                elif len(r.output) >= r.max_tokens:
-                    done.append(self._finish(r, "length"))
+            self._inflight = self._sample(logits, sampled, pending=0)
+            if not (self.overlap and self._goes_on(self._inflight)):
+                done += self._read(self._inflight)         # nothing to overlap with: read at once
+                self._inflight = None
         return done
+
+    def _sample(self, logits: torch.Tensor, reqs: list, pending: int) -> _InFlight:
+        """Sample one id per request and start its copy to pinned host memory; nobody waits here."""
+        tokens = self.sampler.sample(logits, [r.params for r in reqs], [r.seed for r in reqs],
+                                     [len(r.output) + pending for r in reqs])
+        n = tokens.numel()
+        if not tokens.is_cuda:
+            return _InFlight(list(reqs), tokens, tokens, None)
+        pinned = self._pinned.pop() if self._pinned else None
+        if pinned is None or pinned.numel() < n:
+            pinned = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
+        pinned[:n].copy_(tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return _InFlight(list(reqs), tokens, pinned, event)
+
+    def _goes_on(self, inflight: _InFlight) -> bool:
+        """Will the next step be exactly one more token for each of these requests, whatever their pending ids
+        turn out to be (an end-of-sequence id aside)?  Then it can be launched before they are read."""
+        if inflight.event is None:
+            return False
+        if self.waiting and self.cache.can_admit(self.waiting[0].total_len):
+            return False
+        decoding = [r for r in self.running if r.prompt_done]
+        if len(decoding) != len(self.running) or len(decoding) != len(inflight.requests):
+            return False
+        for r, q in zip(decoding, inflight.requests):
+            if r is not q or r.state != RUNNING or len(r.output) + 2 > r.max_tokens:
+                return False               # the pending id is this request's last: read it first
+        return True
+
+    def _read(self, inflight: _InFlight) -> list[Request]:
+        """Wait for a step's ids, hand them to their requests, finish those that end."""
+        n = len(inflight.requests)
+        if inflight.event is not None:
+            inflight.event.synchronize()
+            self._pinned.append(inflight.pinned)
+        ids = inflight.pinned[:n].tolist()
+        self.d2h_bytes += n * 4
+        done: list[Request] = []
+        for r, tok in zip(inflight.requests, ids):
+            if r.state == FINISHED:
+                continue                   # ended one step ago (end-of-sequence id, abort): this id is discarded
+            r.output.append(int(tok))
+            if int(tok) in self.eos and not r.params.ignore_eos:
+                done.append(self._finish(r, "stop"))
+            elif len(r.output) >= r.max_tokens:
+                done.append(self._finish(r, "length"))
+        return done
+
+    def drain(self) -> list[Request]:
+        """Read what is still in flight (end of a run, or before the caller looks at the outputs)."""
+        inflight, self._inflight = self._inflight, None
+        return self._read(inflight) if inflight is not None else []
 
     def abort(self, req: Request) -> None:
         if req.state == WAITING:
@@ -180,8 +257,9 @@ class Scheduler:
 
     @property
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._inflight is not None)
 
     def run(self) -> None:
         while self.has_work:
             self.step()
+        self.drain()

@@ -14,6 +14,7 @@ in the reference's `BatchIndices` (python/logssms/utils/batch.py:43-101).
 """
 from __future__ import annotations
 
+import os
 from typing import Sequence
 
 import torch
@@ -93,9 +94,12 @@ class Engine:
 
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Run the entries' tokens as one batch; return float32 logits [wanted, vocab] in the order
         of the entries and of each entry's `want`.
+
+        `device_tokens` (int32 on the device, one per entry; decode steps only) replaces the entries' token
+        ids: the ids sampled by the step before need not visit the host before they are fed back.
 
         A step of single decoded tokens that all want their logits is replayed from a CUDA graph
         (one per batch size, captured the second time that size is seen); the returned tensor is then
@@ -104,15 +108,19 @@ class Engine:
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return self._decode_step(entries)
+            return self._decode_step(entries, device_tokens)
         ctx = self.planner.plan(entries)
+        if device_tokens is not None:
+            if ctx.num_tokens != len(entries) or device_tokens.numel() != ctx.num_tokens:
+                raise ValueError("device_tokens feeds steps of one token per entry only")
+            ctx.token_ids.copy_(device_tokens)
         x, residual = self.model.forward(ctx)
         self.steps_run += 1
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.logits(x, residual, ctx.logit_rows)
 
-    def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _decode_step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         B = len(entries)
         slot = self._graphs.get(B)
         if slot is None:
@@ -122,21 +130,26 @@ class Engine:
         slot.seen += 1
         if slot.graph is None and slot.seen < 2:
             ctx = self.planner.plan(entries)              # first time: eager (this also builds and loads every kernel)
+            if device_tokens is not None:
+                ctx.token_ids.copy_(device_tokens)
             x, residual = self.model.forward(ctx)
             self.steps_run += 1
             return self.model.logits(x, residual, ctx.logit_rows)
         ctx = self.planner.plan(entries, slot)
+        if device_tokens is not None:
+            ctx.token_ids.copy_(device_tokens)            # before the capture / replay, on the same stream
         if slot.graph is None:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = K.launch_count
             if self._side_stream is None:
                 self._side_stream = torch.cuda.Stream(self.device)
-            ctx.extras["side_stream"] = self._side_stream      # blocks may fork their mixers onto it while capturing
+            if os.environ.get("LOGSSMS_B200_FORK_MIXERS", "1") != "0":
+                ctx.extras["side_stream"] = self._side_stream  # blocks may fork their mixers onto it while capturing
             with torch.cuda.graph(graph):
                 x, residual = self.model.forward(ctx)
                 slot.logits = self.model.logits(x, residual, ctx.logit_rows)
-            del ctx.extras["side_stream"]
+            ctx.extras.pop("side_stream", None)
             slot.launches = K.launch_count - before
             K.launch_count = before
             slot.graph = graph

@@ -82,5 +82,6 @@ class DecoderModel(Part):
         x = K.gather_rows(x, rows)
         if residual is not None:
             residual = K.gather_rows(residual, rows)
-        (h,), _ = self.final_norm.forward(x, residual, want_residual=False)
+        defer = {"defer": True} if getattr(self.final_norm, "can_defer", False) else {}
+        (h,), _ = self.final_norm.forward(x, residual, want_residual=False, **defer)
         return self.lm_head.forward(h)

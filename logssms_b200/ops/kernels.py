@@ -58,7 +58,9 @@ def _ptr(t: torch.Tensor | None):
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of torch's current stream on the current device (the C call: the Python `Stream` object
+    costs microseconds, and every launch asks)."""
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def _code(t: torch.Tensor) -> int:
@@ -111,9 +113,10 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------- norms
 def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None, *,
                 other: torch.Tensor | None = None, in_scales=(1.0, 1.0), out_scales=(1.0,),
-                want_residual: bool = True):
+                want_residual: bool = True, residual_out: torch.Tensor | None = None, in_place: bool = True):
     """(outputs, new_residual): residual add + RMSNorm with one or two scaled outputs.
-    The new residual is written in place of `residual` when one is given."""
+    The new residual is written in place of `residual` when one is given, unless `in_place` is off
+    (then into `residual_out`, or a new tensor)."""
     _cuda(x, weight, residual, other)
     _need(x.dim() == 2 and x.is_contiguous(), "add_rmsnorm wants a contiguous [rows, width] input")
     rows, H = x.shape
@@ -125,7 +128,10 @@ def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: tor
     _need(1 <= len(out_scales) <= 2, "one or two outputs")
     out0 = torch.empty_like(x)
     out1 = torch.empty_like(x) if len(out_scales) == 2 else None
-    res_out = residual if residual is not None else (torch.empty_like(x) if want_residual else None)
+    if in_place:
+        res_out = residual if residual is not None else (torch.empty_like(x) if want_residual else None)
+    else:
+        res_out = (residual_out if residual_out is not None else torch.empty_like(x)) if want_residual else None
     f = _fn("norm", "lb_add_rmsnorm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                        c_int, c_float, c_float, c_float, c_float, c_float, c_int, c_void_p])
     _check(f(_ptr(x), _ptr(other), _ptr(residual), _ptr(res_out), _ptr(weight), _ptr(out0), _ptr(out1), rows, H,
@@ -552,6 +558,65 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
+class NormedRows:
+    """Rows that are still to be normalised: what `add_rmsnorm` would compute, handed to the product that
+    consumes them so that the few-row kernel can do the norm in its prologue (a decode step is bound by the
+    number of dependent launches).  `residual_out` is shared by all consumers of one norm; the first product
+    that runs writes it.  `tensor()` falls back to the norm kernel for any other use."""
+    __slots__ = ("x", "other", "residual", "weight", "eps", "in_scales", "scale", "shared", "_tensor")
+
+    def __init__(self, x, other, residual, weight, eps, in_scales, scale, shared):
+        self.x, self.other, self.residual, self.weight, self.eps = x, other, residual, weight, eps
+        self.in_scales, self.scale, self.shared = in_scales, scale, shared
+        self._tensor = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            write = self.shared["residual_out"] is not None and not self.shared["written"]
+            (self._tensor,), res = add_rmsnorm(self.x, self.weight, self.eps, self.residual, other=self.other,
+                                               in_scales=self.in_scales, out_scales=(self.scale,), want_residual=write,
+                                               residual_out=self.shared["residual_out"] if write else None, in_place=False)
+            if write:
+                self.shared["written"] = True
+        return self._tensor
+
+
+def deferred_norm_ok(x: torch.Tensor) -> bool:
+    """Can a norm over these rows ride in the prologue of the products that consume it?"""
+    return (x.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= 16 and x.shape[1] % 8 == 0
+            and x.shape[1] <= 2048 and x.is_contiguous())
+
+
+def _skinny_normed(nr: NormedRows, w: torch.Tensor, bias, out_scale: float, out_f32: bool, swiglu_scale) -> torch.Tensor:
+    M, Kdim = nr.x.shape
+    N = w.shape[0]
+    mode = _PLAIN
+    if swiglu_scale is not None:
+        N //= 2
+        mode = _SWIGLU
+    elif out_f32:
+        mode = _OUT_F32
+    out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=w.device)
+    write = nr.shared["residual_out"] is not None and not nr.shared["written"]
+    f = _fn("linear_skinny", "lb_linear_skinny_normed",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_float, c_void_p, c_void_p,
+             c_void_p, c_long, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(nr.x), _ptr(nr.other), _ptr(nr.residual), _ptr(nr.shared["residual_out"]) if write else None,
+             _ptr(nr.weight), nr.eps, nr.in_scales[0], nr.in_scales[1], nr.scale, _ptr(w), _ptr(bias), _ptr(out), N, M, N,
+             Kdim, out_scale, swiglu_scale if swiglu_scale is not None else 1.0, mode, _stream()), "linear_skinny_normed")
+    if write:
+        nr.shared["written"] = True
+    return out
+
+
 SKINNY_MAX_ROWS = 64       # at or below this many rows a bfloat16 product goes to the weight-streaming kernel
 
 
@@ -655,7 +720,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
     float32 activations: the engine's own 32-bit kernel.  bfloat16: at most 64 rows go to the
     weight-streaming kernel (a decode step is bound by reading the weights once); more rows go to
     cuBLAS through torch (32-bit accumulation).  bfloat16 activations with a weight that is stored in
-    32-bit: the 32-bit kernel on widened activations, result rounded once."""
+    32-bit: the 32-bit kernel on widened activations, result rounded once.  `x` may be `NormedRows`."""
+    if isinstance(x, NormedRows):
+        if (w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == x.shape[1] and w.data_ptr() % 16 == 0
+                and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous()))):
+            return _skinny_normed(x, w, bias, out_scale, out_f32, None)
+        x = x.tensor()
     _cuda(x, w, bias)
     if x.dtype == torch.float32:
         return gemm_f32(x, w.float(), None if bias is None else bias.float(), out_scale)
@@ -673,7 +743,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_scale: float) -> torch.Tensor:
-    """silu(round(gate * act_scale)) * up with [gate | up] = x @ w_gate_up^T (w rows: gate, then up)."""
+    """silu(round(gate * act_scale)) * up with [gate | up] = x @ w_gate_up^T (w rows: gate, then up).
+    `x` may be `NormedRows`."""
+    if isinstance(x, NormedRows):
+        if (w_gate_up.dtype == torch.bfloat16 and w_gate_up.is_contiguous() and w_gate_up.shape[1] == x.shape[1]
+                and w_gate_up.shape[0] % 2 == 0 and w_gate_up.data_ptr() % 16 == 0):
+            return _skinny_normed(x, w_gate_up, None, 1.0, False, act_scale)
+        x = x.tensor()
     if _skinny_ok(x, w_gate_up, None):
         return linear_skinny(x, w_gate_up, swiglu_scale=act_scale)
     if GEMM_MODE in ("auto", "tcgen05") and _tcgen05_ok(x, w_gate_up, None):

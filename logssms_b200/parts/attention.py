@@ -18,6 +18,7 @@ class Attention(Part):
     Checkpoint tensors `q_proj / k_proj / v_proj .weight` are concatenated (rows q | k | v) at
     bind time, as the reference merges them at load (python/logssms/models/weight.py:27-31);
     the flow is python/logssms/layers/attention.py:115-167."""
+    takes_normed_rows = True      # forward() passes its input straight into a product
     kernels = ("rope", "attention_decode", "attention_decode_fused", "attention_prefill", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):

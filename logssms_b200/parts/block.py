@@ -57,7 +57,13 @@ class PreNormParallelBlock(Part):
 
     def forward(self, x: torch.Tensor, residual, ctx, cache_layer: int, writes_cache: bool = True):
         slots = self.spec.mixers
-        ins, residual = self.mixer_norm.forward(x, residual, out_scales=tuple(m.in_scale for m in slots))
+        # parts whose first step is a product say so (`takes_normed_rows`): the norm in front of them can then
+        # ride in that product's prologue (decode steps: fewer dependent launches)
+        defer_mix = {"defer": True} if (getattr(self.mixer_norm, "can_defer", False)
+                                         and all(getattr(m, "takes_normed_rows", False) for m in self.mixers)) else {}
+        defer_ff = {"defer": True} if (getattr(self.ff_norm, "can_defer", False)
+                                       and getattr(self.feed_forward, "takes_normed_rows", False)) else {}
+        ins, residual = self.mixer_norm.forward(x, residual, out_scales=tuple(m.in_scale for m in slots), **defer_mix)
         side = ctx.extras.get("side_stream") if len(self.mixers) == 2 else None
         if side is None:
             outs = [mixer.forward(inp, ctx, cache_layer, writes_cache) for mixer, inp in zip(self.mixers, ins)]
@@ -77,10 +83,10 @@ class PreNormParallelBlock(Part):
             outs = [first, second]
         if len(outs) == 2:
             (h,), residual = self.ff_norm.forward(outs[0], residual, other=outs[1],
-                                                  in_scales=(slots[0].out_scale, slots[1].out_scale))
+                                                  in_scales=(slots[0].out_scale, slots[1].out_scale), **defer_ff)
         else:
             if slots[0].out_scale != 1.0:
                 from ..ops import kernels as K
                 outs[0] = K.scale(outs[0], slots[0].out_scale)
-            (h,), residual = self.ff_norm.forward(outs[0], residual)
+            (h,), residual = self.ff_norm.forward(outs[0], residual, **defer_ff)
         return self.feed_forward.forward(h), residual

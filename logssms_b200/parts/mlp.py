@@ -12,6 +12,7 @@ from .base import MATRIX, ParamSpec, Part
 class GatedMLP(Part):
     """down(silu(gate * s0) * up) * s1.  `gate_proj` and `up_proj` are concatenated at bind time
     (python/logssms/models/weight.py:32-33); flow python/logssms/layers/mlp.py:50-61."""
+    takes_normed_rows = True      # forward() passes its input straight into a product
     kernels = ("norm", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):

@@ -13,7 +13,8 @@ class RMSNorm(Part):
     """`forward(x, residual, other=..., in_scales=..., out_scales=...)`:
     residual <- (x [scaled, + other scaled]) + residual ; outputs = rmsnorm(residual) * out_scale_k.
     (python/logssms/layers/norm.py:56-97, python/logssms/kernel/norm.py:8-52.)"""
-    kernels = ("norm",)
+    kernels = ("norm", "linear_skinny")
+    can_defer = True          # forward() takes `defer=`: see there
 
     def __init__(self, spec, perturb_init: bool = False):
         self.size, self.eps = spec.size, spec.eps
@@ -23,6 +24,14 @@ class RMSNorm(Part):
     def param_specs(self):
         return {"weight": ParamSpec((self.size,), VECTOR, ones_init(self._jitter))}
 
-    def forward(self, x, residual=None, *, other=None, in_scales=(1.0, 1.0), out_scales=(1.0,), want_residual=True):
+    def forward(self, x, residual=None, *, other=None, in_scales=(1.0, 1.0), out_scales=(1.0,), want_residual=True,
+                defer=False):
+        """With `defer` (the caller's consumers all take `NormedRows`: their first step is a product), and
+        few enough rows, nothing is launched here: the outputs are `NormedRows` that the consumers' products
+        normalise in their prologue, and the new residual is a fresh tensor that the first of them writes."""
+        if defer and K.deferred_norm_ok(x):
+            shared = {"residual_out": torch.empty_like(x) if want_residual else None, "written": False}
+            outs = tuple(K.NormedRows(x, other, residual, self.weight, self.eps, in_scales, s, shared) for s in out_scales)
+            return outs, shared["residual_out"]
         return K.add_rmsnorm(x, self.weight, self.eps, residual, other=other, in_scales=in_scales,
                              out_scales=out_scales, want_residual=want_residual)

@@ -74,6 +74,33 @@ def test_eos_and_max_tokens_end_requests(tmp_path):
     assert len(out.token_ids) == 4 and out.finish_reason == "length"
 
 
+def test_overlapped_decoding_gives_the_same_tokens_and_notices_eos_one_step_late(tmp_path):
+    """With the next step launched before the previous ids are read, outputs are the same as without, for
+    requests that end by length, by an end-of-sequence id (noticed a step late, the extra step discarded)
+    and at different times."""
+    from logssms_b200.engine import LLM
+    from logssms_b200.sampling import SamplingParams
+    model_dir = make_model_dir(tmp_path / "m", TINY["B"], seed=31)
+    prompts = [[5, 6, 7, 8], [9, 10], [11, 12, 13, 14, 15, 16]]
+    params = [SamplingParams(max_tokens=9, ignore_eos=True), SamplingParams(max_tokens=20), SamplingParams(max_tokens=14)]
+    probe = LLM(model_dir, "float32", max_running_requests=4, max_seq_len_override=128, num_pages=6)
+    free = probe.generate(prompts, [SamplingParams(max_tokens=20, ignore_eos=True)] * 3)
+    eos = free[1].token_ids[6]                              # an id the second request reaches after a few tokens
+    del probe
+    results = {}
+    for overlap in (False, True):
+        llm = LLM(model_dir, "float32", max_running_requests=4, max_seq_len_override=128, num_pages=6, eos_token_ids=[eos])
+        llm.scheduler.overlap = overlap
+        outs = llm.generate(prompts, params)
+        results[overlap] = [(o.token_ids, o.finish_reason) for o in outs]
+        assert llm.scheduler.steps > 0 and not llm.engine.cache.live
+        llm.engine.cache.check_integrity()
+        del llm
+    assert results[True] == results[False]
+    assert results[True][0][1] == "length" and len(results[True][0][0]) == 9
+    assert results[True][1][1] == "stop" and results[True][1][0][-1] == eos
+
+
 def test_temperature_sampling_is_seeded_per_request_and_independent_of_the_batch(tmp_path):
     from logssms_b200.engine import LLM
     from logssms_b200.sampling import SamplingParams

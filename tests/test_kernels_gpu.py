@@ -573,6 +573,37 @@ def test_linear_skinny_swiglu_matches_the_unfused_chain(M, I, Kd):
     close(k.linear_swiglu(dev(x), dev(w), 0.9), want, torch.bfloat16, tol=1e-2)
 
 
+@pytest.mark.parametrize("M", [1, 8, 13, 16])
+@pytest.mark.parametrize("N,Kd", [(16, 64), (1030, 1000), (768, 2048)])
+@pytest.mark.parametrize("two_inputs", [False, True])
+def test_linear_skinny_with_the_norm_in_its_prologue(M, N, Kd, two_inputs):
+    """Residual add + RMSNorm inside the product against the norm kernel followed by the product."""
+    g = torch.Generator().manual_seed(M * 3 + N)
+    x, other, res = (randn(g, M, Kd, dtype=torch.bfloat16) for _ in range(3))
+    nw = (1 + 0.1 * torch.randn(Kd, generator=g)).cuda()
+    w = randn(g, N, Kd, dtype=torch.bfloat16, scale=0.05).cuda()
+    w2 = randn(g, 2 * N, Kd, dtype=torch.bfloat16, scale=0.05).cuda()
+    b = randn(g, N, dtype=torch.bfloat16).cuda()
+    k = K()
+    oth = dev(other) if two_inputs else None
+    (a0, a1), want_res = k.add_rmsnorm(dev(x), nw, 1e-5, dev(res), other=oth, in_scales=(0.8, 0.7), out_scales=(1.5, 1.2), in_place=False)
+    shared = {"residual_out": torch.empty_like(dev(x)), "written": False}
+    n0 = k.NormedRows(dev(x), oth, dev(res), nw, 1e-5, (0.8, 0.7), 1.5, shared)
+    n1 = k.NormedRows(dev(x), oth, dev(res), nw, 1e-5, (0.8, 0.7), 1.2, shared)
+    close(k.linear(n0, w, b, out_scale=0.7), k.linear_skinny(a0, w, b, out_scale=0.7), torch.bfloat16, tol=8e-3)
+    assert shared["written"]
+    close(shared["residual_out"], want_res, torch.bfloat16, tol=1e-6)
+    shared["residual_out"].fill_(7.0)                      # the second consumer must leave the residual alone
+    close(k.linear_swiglu(n1, w2, 0.9), k.linear_skinny(a1, w2, swiglu_scale=0.9), torch.bfloat16, tol=1.6e-2)
+    assert bool((shared["residual_out"] == 7.0).all())
+    # no residual wanted, float32 out (the output head)
+    lone = k.NormedRows(dev(x), None, None, nw, 1e-6, (1.0, 1.0), 1.0, {"residual_out": None, "written": False})
+    (h,), _ = k.add_rmsnorm(dev(x), nw, 1e-6, None, want_residual=False)
+    close(k.linear(lone, w, out_scale=0.25, out_f32=True), k.linear_skinny(h, w, out_scale=0.25, out_f32=True), torch.bfloat16, tol=8e-3)
+    # any other use falls back to the norm kernel
+    close(n1.tensor(), a1, torch.bfloat16, tol=1e-6)
+
+
 def test_linear_many_rows_goes_to_the_library_with_the_same_epilogues():
     g = torch.Generator().manual_seed(4)
     x = randn(g, 130, 256, dtype=torch.bfloat16)
