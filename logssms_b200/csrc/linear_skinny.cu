@@ -42,6 +42,15 @@ struct SkinnyArgs {
     //   x = round(round(v * rsqrt(mean(v^2) + eps) * nweight) * nscale)
     const __nv_bfloat16* nx; const __nv_bfloat16* nother; const __nv_bfloat16* nres; __nv_bfloat16* nres_out;
     const float* nweight; float neps, nin0, nin1, nscale;
+    // optional epilogue for output features [conv_c0, conv_c1): a depthwise causal conv step per row, each row
+    // being the single new token of its own request (a decode step).  For channel c = n - conv_c0:
+    //   u = round(y * region scale) ; c_out = round(sum_j w[c][j] * window_j + bias[c]) with window = state | u ;
+    //   y <- round(silu(c_out)) ; state <- window without its oldest entry
+    // (python/logssms/kernel/linear_attention/conv_decode.py:112-278; the thread that owns (row, feature) is the
+    // only reader and writer of that row's state for the channel.)
+    const float* conv_w; const float* conv_b; __nv_bfloat16* conv_state;     // [C, Kc] float32, [C] or null, [slots, C, Kc-1]
+    const int* conv_slots; const int* conv_start;                             // per row: state slot, tokens before this one
+    int conv_c0, conv_c1, conv_k, conv_e0, conv_e1; float conv_s0, conv_s1, conv_s2;
 };
 
 __device__ __forceinline__ uint4 load_stream(const void* p) {
@@ -231,6 +240,24 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
             float v = s[0];
             if (a.bias != nullptr) v += __bfloat162float(a.bias[n]);
             v = round_to<__nv_bfloat16>(v);
+            if (EPI == kPlain && a.conv_w != nullptr && n >= a.conv_c0 && n < a.conv_c1) {
+                const int c = n - a.conv_c0, C = a.conv_c1 - a.conv_c0, taps = a.conv_k;
+                const float scale = c < a.conv_e0 ? a.conv_s0 : (c < a.conv_e1 ? a.conv_s1 : a.conv_s2);
+                const float u = round_to<__nv_bfloat16>(v * scale);
+                __nv_bfloat16* st = a.conv_state + ((size_t)a.conv_slots[m] * C + c) * (taps - 1);
+                const bool history = a.conv_start[m] > 0;
+                const float* w = a.conv_w + (size_t)c * taps;
+                float acc2 = w[taps - 1] * u;
+                for (int j = 0; j < taps - 1; ++j) {
+                    const float win = history ? __bfloat162float(st[j]) : 0.f;
+                    acc2 += w[j] * win;
+                    if (j > 0) st[j - 1] = __float2bfloat16_rn(win);          // shift: entry j moves to j - 1
+                }
+                st[taps - 2] = __float2bfloat16_rn(u);
+                if (a.conv_b != nullptr) acc2 += a.conv_b[c];
+                acc2 = round_to<__nv_bfloat16>(acc2);
+                v = round_to<__nv_bfloat16>(silu_f(acc2));
+            }
             if (EPI == kOutF32) ((float*)a.out)[(size_t)m * a.ldo + n] = v * a.out_scale;
             else ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n] =
                 a.out_scale == 1.f ? __float2bfloat16_rn(v) : __float2bfloat16_rn(v * a.out_scale);
@@ -282,7 +309,8 @@ extern "C" int lb_linear_skinny(const void* x, long ldx, const void* w, const vo
     if (M > 64) return kTooLarge;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return kBadSize;
     SkinnyArgs a{(const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, out, ldo,
-                 M, N, K, out_scale, act_scale, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, 1.f, 1.f, 1.f};
+                 M, N, K, out_scale, act_scale, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, 1.f, 1.f, 1.f,
+                 nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 1.f, 1.f, 1.f};
     return launch_epi<false>(a, epilogue, (cudaStream_t)stream);
 }
 
@@ -301,6 +329,31 @@ extern "C" int lb_linear_skinny_normed(const void* nx, const void* nother, const
     if (res_out != nullptr && res_out == nres) return kBadSize;
     SkinnyArgs a{nullptr, 0, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, out, ldo, M, N, K, out_scale, act_scale,
                  (const __nv_bfloat16*)nx, (const __nv_bfloat16*)nother, (const __nv_bfloat16*)nres, (__nv_bfloat16*)res_out,
-                 norm_weight, eps, in0, in1, norm_scale};
+                 norm_weight, eps, in0, in1, norm_scale,
+                 nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 1.f, 1.f, 1.f};
     return launch_epi<true>(a, epilogue, (cudaStream_t)stream);
+}
+
+// The plain product (x given, or made by the norm prologue when `nx` is not null) with the conv step of a
+// decode batch on the output features [c0, c1): see SkinnyArgs.  conv_w: float32 [c1 - c0, taps]; conv_b: float32
+// [c1 - c0] or null; conv_state: bfloat16 [slots, c1 - c0, taps - 1], updated in place; slots / start: int32 per row;
+// e0, e1: channel indices (relative to c0) where the second and third input scale begin.
+extern "C" int lb_linear_skinny_conv(const void* x, long ldx, const void* nx, const void* nother, const void* nres,
+                                     void* res_out, const float* norm_weight, float eps, float in0, float in1,
+                                     float norm_scale, const void* w, const void* bias, void* out, long ldo, int M, int N,
+                                     int K, const float* conv_w, const float* conv_b, void* conv_state,
+                                     const int* slots, const int* start, int c0, int c1, int taps, int e0, int e1,
+                                     float s0, float s1, float s2, void* stream) {
+    if (M <= 0 || N <= 0) return kOk;
+    if (K <= 0 || K % 8 || taps < 2 || taps > 8 || c0 < 0 || c1 > N || c0 > c1) return kBadSize;
+    const bool normed = nx != nullptr;
+    if (normed ? (M > 16 || K > 2048) : (M > 64)) return kTooLarge;
+    if (!normed && (ldx % 8 || ((uintptr_t)x & 15))) return kBadSize;
+    if (((uintptr_t)nx | (uintptr_t)w | (uintptr_t)nother | (uintptr_t)nres | (uintptr_t)res_out | (uintptr_t)norm_weight) & 15) return kBadSize;
+    if (res_out != nullptr && res_out == nres) return kBadSize;
+    SkinnyArgs a{(const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, out, ldo, M, N, K, 1.f, 1.f,
+                 (const __nv_bfloat16*)nx, (const __nv_bfloat16*)nother, (const __nv_bfloat16*)nres, (__nv_bfloat16*)res_out,
+                 norm_weight, eps, in0, in1, norm_scale,
+                 conv_w, conv_b, (__nv_bfloat16*)conv_state, slots, start, c0, c1, taps, e0, e1, s0, s1, s2};
+    return normed ? launch_epi<true>(a, kPlain, (cudaStream_t)stream) : launch_epi<false>(a, kPlain, (cudaStream_t)stream);
 }

@@ -22,7 +22,7 @@ constexpr int kPTile = 16;
 constexpr int kLanesN = 8;
 
 struct SsmArgs {
-    const void* conv; int C;                     // [tokens, C]: x | B | C after the conv
+    const void* conv; int C; long conv_stride;   // [tokens, C] (row stride in elements): x | B | C after the conv
     const void* dt; long dt_stride;              // [tokens, nh] view
     const float* A_log; const float* dt_bias; const float* D;
     float* state;                                // [slots, nh, P, N]
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
 #pragma unroll 2
     for (int t = 0; t < len; ++t) {
         const size_t tok = (size_t)(begin + t);
-        const T* row = conv + tok * a.C;
+        const T* row = conv + tok * a.conv_stride;
         float dt = round_to<T>(to_f32(dtp[tok * a.dt_stride + h]) * a.dt_scale) + dt_bias;
         dt = dt > 20.f ? dt : log1pf(expf(dt));
         const float decay = expf(negA * dt);
@@ -139,7 +139,7 @@ void launch_npt(const SsmArgs& a, int B, bool aligned, cudaStream_t s) {
 template <typename T>
 int launch(const SsmArgs& a, int B, cudaStream_t s) {
     const int inner = a.nh * a.P;
-    const bool aligned = (inner % 4 == 0) && (a.C % 4 == 0) && (a.N % 4 == 0) &&
+    const bool aligned = (inner % 4 == 0) && (a.C % 4 == 0) && (a.conv_stride % 4 == 0) && (((uintptr_t)a.conv & 15) == 0) && (a.N % 4 == 0) &&
                          (sizeof(T) == 4 || (inner % 4 == 0));
     if (a.N <= 32) launch_npt<T, 4>(a, B, aligned, s);
     else if (a.N <= 64) launch_npt<T, 8>(a, B, aligned, s);
@@ -150,7 +150,7 @@ int launch(const SsmArgs& a, int B, cudaStream_t s) {
 }
 }  // namespace
 
-extern "C" int lb_ssm_scan(const void* conv, int C, const void* dt, long dt_stride, const float* A_log,
+extern "C" int lb_ssm_scan(const void* conv, int C, long conv_stride, const void* dt, long dt_stride, const float* A_log,
                            const float* dt_bias, const float* D, float* state, void* y, const int* cu_seqlens,
                            const int* start_pos, const int* slots, int B, int nh, int P, int N, int G,
                            float dt_scale, const void* gate, long gate_stride, float gate_scale,
@@ -158,7 +158,7 @@ extern "C" int lb_ssm_scan(const void* conv, int C, const void* dt, long dt_stri
     if (B <= 0) return kOk;
     if (nh <= 0 || P <= 0 || N <= 0 || G <= 0 || nh % G || N % 4) return kBadSize;
     if (C != nh * P + 2 * G * N) return kBadSize;
-    SsmArgs a{conv, C, dt, dt_stride, A_log, dt_bias, D, state, y, cu_seqlens, start_pos, slots, nh, P, N, G, dt_scale,
+    SsmArgs a{conv, C, conv_stride, dt, dt_stride, A_log, dt_bias, D, state, y, cu_seqlens, start_pos, slots, nh, P, N, G, dt_scale,
               gate, gate_stride, gate_scale, req_list};
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, B, (cudaStream_t)stream));
     return kOk;

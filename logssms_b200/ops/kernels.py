@@ -459,7 +459,7 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
              dt_scale: float, gate: torch.Tensor | None = None, gate_scale: float = 1.0, *,
              request_list: torch.Tensor | None = None, num_listed: int = 0,
              out: torch.Tensor | None = None) -> torch.Tensor:
-    """conv: [tokens, nh*P + 2*G*N] contiguous (x | B | C); dt: [tokens, nh] view; state: float32
+    """conv: [tokens, nh*P + 2*G*N] (x | B | C; a column view is fine); dt: [tokens, nh] view; state: float32
     [slots, nh, P, N], updated in place.  Returns y [tokens, nh*P]; with `gate` ([tokens, nh*P] view)
     the result is y * silu(gate * gate_scale), the gate of a mixer that has no norm.  `request_list`
     (int32 indices into the batch, `num_listed` of them) restricts the call to those requests; the rows
@@ -473,7 +473,7 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
         _need(gate.shape == (conv.shape[0], num_heads * head_dim) and gate.stride(1) == 1 and gate.dtype == conv.dtype,
               "gate must be a [tokens, heads * head_dim] view of the activation dtype")
     tokens, C = conv.shape
-    _need(conv.is_contiguous(), "conv output must be contiguous")
+    _need(conv.stride(1) == 1, "conv output needs unit column stride")
     _need(dt.shape == (tokens, num_heads) and dt.stride(1) == 1 and dt.dtype == conv.dtype, "dt must be a [tokens, heads] view")
     for t, n in ((A_log, "A_log"), (dt_bias, "dt_bias"), (D, "D")):
         _need(t.dtype == torch.float32 and t.shape == (num_heads,) and t.is_contiguous(), f"{n} must be float32 [heads]")
@@ -484,12 +484,12 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
         _i32(t, n)
     y = out if out is not None else torch.empty((tokens, num_heads * head_dim), dtype=conv.dtype, device=conv.device)
     _need(y.shape == (tokens, num_heads * head_dim) and y.dtype == conv.dtype and y.is_contiguous(), "out must be [tokens, heads * head_dim]")
-    f = _fn("ssm", "lb_ssm_scan", [c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    f = _fn("ssm", "lb_ssm_scan", [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                    c_long, c_float, c_void_p, c_int, c_void_p])
-    _check(f(_ptr(conv), C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(state), _ptr(y),
-             _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), num_requests, num_heads, head_dim, state_dim,
-             num_groups, dt_scale, _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale,
+    _check(f(_ptr(conv), C, conv.stride(0) if tokens > 1 else C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D),
+             _ptr(state), _ptr(y), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), num_requests, num_heads, head_dim,
+             state_dim, num_groups, dt_scale, _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale,
              _ptr(request_list), _code(conv), _stream()), "ssm_scan")
     return y
 
@@ -711,6 +711,56 @@ def check_gemm_errors(device=None) -> None:
             err.zero_()
             raise KernelError(f"gemm_tcgen05: a wait inside the kernel gave up (role {(code >> 24) & 0x3F}, "
                               f"block {(code >> 12) & 0xFFF}, k-block {code & 0xFFF})")
+
+
+def linear_conv_step_ok(x, w: torch.Tensor, bias, conv_state: torch.Tensor) -> bool:
+    """Can `linear_conv_step` take these operands (else: `linear`, then `causal_conv1d`)?"""
+    if conv_state.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or w.data_ptr() % 16:
+        return False
+    if bias is not None and not (bias.dtype == torch.bfloat16 and bias.is_contiguous()):
+        return False
+    if isinstance(x, NormedRows):
+        return w.shape[1] == x.shape[1]
+    return _skinny_ok(x, w, bias)
+
+
+def linear_conv_step(x, w: torch.Tensor, bias, conv_weight: torch.Tensor, conv_bias, conv_state: torch.Tensor,
+                     slots: torch.Tensor, start_pos: torch.Tensor, first: int, last: int,
+                     region_ends: tuple[int, int], region_scales: tuple[float, float, float]) -> torch.Tensor:
+    """x @ w^T (+ bias) for a decode batch (every row the single new token of its own request), with the
+    depthwise conv step done on the output columns [first, last) before they are stored: those columns come
+    back as silu(conv(...)) and `conv_state` ([slots, last - first, taps - 1]) is shifted in place.  `x` may be
+    `NormedRows`.  `region_ends` are column indices relative to `first`."""
+    normed = isinstance(x, NormedRows)
+    _need(linear_conv_step_ok(x, w, bias, conv_state), "linear_conv_step takes few bfloat16 rows (see linear_skinny)")
+    C = last - first
+    taps = conv_weight.shape[1]
+    _need(conv_weight.dtype == torch.float32 and conv_weight.shape == (C, taps) and conv_weight.is_contiguous(), "conv weight must be float32 [C, K]")
+    _need(conv_bias is None or (conv_bias.dtype == torch.float32 and conv_bias.shape == (C,) and conv_bias.is_contiguous()), "conv bias must be float32 [C]")
+    _need(conv_state.is_contiguous() and conv_state.shape[1:] == (C, taps - 1), "conv state must be contiguous [slots, C, K-1]")
+    _i32(slots, "slots")
+    _i32(start_pos, "start_pos")
+    M, Kdim = x.shape
+    N = w.shape[0]
+    _need(slots.numel() >= M and start_pos.numel() >= M and 0 <= first <= last <= N, "one slot and start per row; columns within the output")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)
+    write = normed and x.shared["residual_out"] is not None and not x.shared["written"]
+    f = _fn("linear_skinny", "lb_linear_skinny_conv",
+            [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_float, c_void_p,
+             c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    if normed:
+        head = (None, 0, _ptr(x.x), _ptr(x.other), _ptr(x.residual), _ptr(x.shared["residual_out"]) if write else None,
+                _ptr(x.weight), x.eps, x.in_scales[0], x.in_scales[1], x.scale)
+    else:
+        _cuda(x)
+        head = (_ptr(x), x.stride(0), None, None, None, None, None, 0.0, 1.0, 1.0, 1.0)
+    _check(f(*head, _ptr(w), _ptr(bias), _ptr(out), N, M, N, Kdim, _ptr(conv_weight), _ptr(conv_bias), _ptr(conv_state),
+             _ptr(slots), _ptr(start_pos), first, last, taps, region_ends[0], region_ends[1], region_scales[0],
+             region_scales[1], region_scales[2], _stream()), "linear_conv_step")
+    if write:
+        x.shared["written"] = True
+    return out
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out_scale: float = 1.0,

@@ -92,12 +92,18 @@ class Mamba2(Part):
         s = self.spec
         m = s.multipliers
         inner, C = s.inner_size, s.conv_dim
-        proj = K.linear(x, self.in_w, self.in_b)
-        z, xbc, dt = proj[:, :inner], proj[:, inner:inner + C], proj[:, inner + C:]
         states = ctx.cache.states[cache_layer]
-        conv = K.causal_conv1d(xbc, self.conv_w, self.conv_b, states["conv"], ctx.cu_seqlens, ctx.start_pos,
-                               ctx.slots, ctx.num_requests, ctx.max_len,
-                               (inner, inner + s.num_groups * s.state_dim), (m[1], m[2], m[3]))
+        regions = ((inner, inner + s.num_groups * s.state_dim), (m[1], m[2], m[3]))
+        if ctx.max_len == 1 and K.linear_conv_step_ok(x, self.in_w, self.in_b, states["conv"]):
+            # a decode step: the conv step rides in the projection's epilogue (its columns come back convolved)
+            proj = K.linear_conv_step(x, self.in_w, self.in_b, self.conv_w, self.conv_b, states["conv"], ctx.slots,
+                                      ctx.start_pos, inner, inner + C, *regions)
+            z, conv, dt = proj[:, :inner], proj[:, inner:inner + C], proj[:, inner + C:]
+        else:
+            proj = K.linear(x, self.in_w, self.in_b)
+            z, xbc, dt = proj[:, :inner], proj[:, inner:inner + C], proj[:, inner + C:]
+            conv = K.causal_conv1d(xbc, self.conv_w, self.conv_b, states["conv"], ctx.cu_seqlens, ctx.start_pos,
+                                   ctx.slots, ctx.num_requests, ctx.max_len, *regions)
         gate = None if s.gated_norm else z          # the bare gate rides in the scan's epilogue
         head = (conv, dt, self.A_log, self.dt_bias, self.D, states["ssm"], ctx.cu_seqlens, ctx.start_pos, ctx.slots)
         sizes = (s.num_heads, s.head_dim, s.state_dim, s.num_groups, m[4])

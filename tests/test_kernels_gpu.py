@@ -604,6 +604,47 @@ def test_linear_skinny_with_the_norm_in_its_prologue(M, N, Kd, two_inputs):
     close(n1.tensor(), a1, torch.bfloat16, tol=1e-6)
 
 
+@pytest.mark.parametrize("M", [1, 5, 16, 40])
+@pytest.mark.parametrize("taps", [2, 4])
+@pytest.mark.parametrize("normed", [False, True])
+def test_linear_with_the_conv_step_in_its_epilogue(M, taps, normed):
+    """Projection + conv step of a decode batch in one launch against projection, then the conv kernel."""
+    if normed and M > 16:
+        pytest.skip("the norm prologue takes at most 16 rows")
+    g = torch.Generator().manual_seed(M * 5 + taps)
+    Kd, first, C, tail = 96, 24, 56, 10                     # output: 24 plain columns | 56 conv channels | 10 plain
+    N = first + C + tail
+    k = K()
+    x = randn(g, M, Kd, dtype=torch.bfloat16).cuda()
+    w = randn(g, N, Kd, dtype=torch.bfloat16, scale=0.2).cuda()
+    b = randn(g, N, dtype=torch.bfloat16).cuda()
+    cw, cb = randn(g, C, taps, scale=0.4).cuda(), randn(g, C, scale=0.1).cuda()
+    slots = torch.randperm(M + 3, generator=g)[:M].to(torch.int32).cuda()
+    start = torch.tensor([0 if i % 3 == 0 else 5 + i for i in range(M)], dtype=torch.int32).cuda()     # some requests are new
+    state0 = randn(g, M + 3, C, taps - 1, dtype=torch.bfloat16).cuda()
+    ends, scales = (24, 40), (1.1, 0.9, 1.3)
+    if normed:
+        nw = (1 + 0.1 * torch.randn(Kd, generator=g)).cuda()
+        res = randn(g, M, Kd, dtype=torch.bfloat16).cuda()
+        (xin,), _ = k.add_rmsnorm(x, nw, 1e-5, res, out_scales=(1.2,), in_place=False)
+        arg = k.NormedRows(x, None, res, nw, 1e-5, (1.0, 1.0), 1.2, {"residual_out": torch.empty_like(x), "written": False})
+    else:
+        xin = arg = x
+    proj = k.linear_skinny(xin, w, b)
+    st_want = state0.clone()
+    cu = torch.arange(M + 1, dtype=torch.int32).cuda()
+    conv = k.causal_conv1d(proj[:, first:first + C], cw, cb, st_want, cu, start, slots, M, 1, ends, scales)
+    st_got = state0.clone()
+    got = k.linear_conv_step(arg, w, b, cw, cb, st_got, slots, start, first, first + C, ends, scales)
+    assert torch.equal(got[:, :first], proj[:, :first]) and torch.equal(got[:, first + C:], proj[:, first + C:])
+    close(got[:, first:first + C], conv, torch.bfloat16, tol=8e-3)
+    used = slots.long()
+    close(st_got[used], st_want[used], torch.bfloat16, tol=8e-3)
+    others = torch.ones(M + 3, dtype=torch.bool)
+    others[used.cpu()] = False
+    assert torch.equal(st_got[others.cuda()], state0[others.cuda()])
+
+
 def test_linear_many_rows_goes_to_the_library_with_the_same_epilogues():
     g = torch.Generator().manual_seed(4)
     x = randn(g, 130, 256, dtype=torch.bfloat16)
