@@ -199,7 +199,10 @@ def run_ours(args) -> dict:
 
         def decode_run(batch: int, through_host: bool) -> dict:
             """Prefill `batch` prompts (untimed), then W + K decode steps; the K are timed."""
-            sp = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True)
+            # requests whose prompts finish first decode beside the others' portions: room for those tokens too,
+            # so that none ends (and the batch shrinks) inside the timed steps
+            prompt_steps = -(-batch * CONTEXT // args.prefill_budget) + batch
+            sp = SamplingParams(temperature=0.0, max_tokens=new_tokens + prompt_steps, ignore_eos=True)
             reqs = [llm.add_request(p, sp) for p in prompts(batch)]
             while not all(r.prompt_done for r in reqs):
                 llm.step(device_loop=not through_host)
@@ -220,6 +223,8 @@ def run_ours(args) -> dict:
             ms = start.elapsed_time(stop)
             launches = K.launch_count
             hi = clocks.mark()
+            if any(r.state != "running" for r in reqs):
+                raise RuntimeError("a request ended inside the timed decode steps")
             out = {"ms_per_step": ms / args.steps, "tok_s": batch * args.steps / (ms / 1e3), "launches": launches,
                    "wall_tok_s": batch * args.steps / wall, "clock_span": (lo, hi),
                    "h2d": (llm.engine.h2d_bytes - h2d0) / args.steps, "d2h": (llm.d2h_bytes - d2h0) / args.steps}

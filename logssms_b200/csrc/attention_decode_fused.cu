@@ -329,7 +329,7 @@ int launch_chp(const FusedArgs& a, int tokens, cudaStream_t s) {
 // The same step on tensor cores (bfloat16, head_dim <= 128, at most 16 query heads per key/value head).
 // The query heads that share a key/value head are the 16 rows of an mma.sync m16n8k16 tile; every warp
 // walks its own 32-key tiles of the CTA's range: K and V rows arrive by 16-byte cp.async into the warp's
-// own double buffer (the next tile is in flight while this one is used), S = Q K^T and O += P V are
+// own ring of buffers (4 for head sizes up to 64, else 2) (the next tiles are in flight while this one is used), S = Q K^T and O += P V are
 // tensor-core products, the softmax statistics stay float32.  Per 32 keys this costs ~200 instructions
 // where the kernel above needs ~2000, and the copies keep the memory system busy with few warps.
 typedef __nv_bfloat16 bf16;
@@ -361,15 +361,15 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 // HDT: head_dim / 16 rounded up to the instantiated size (4 or 8).
-template <int HDT>
+template <int HDT, int NS>
 __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int hd = a.hd, ld = hd + 8;                    // row stride: an odd number of 16-byte pieces
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [16][ld]   rotated queries (rows beyond the group: zeros)
     bf16* kn_s = q_s + 16 * ld;                          // [ld]       the token's own key (rotated)
     bf16* vn_s = kn_s + ld;                              // [ld]       the token's own value
-    bf16* tiles = vn_s + ld;                             // [kWarps][2 stages][K, V][kKT][ld]
-    float* mrg = reinterpret_cast<float*>(tiles + (size_t)kWarps * 4 * kKT * ld);   // [kWarps][16][hd + 2]
+    bf16* tiles = vn_s + ld;                             // [kWarps][NS stages][K, V][kKT][ld]
+    float* mrg = reinterpret_cast<float*>(tiles);        // [kWarps][16][hd + 2], over the tiles once the keys are done
     __shared__ int last_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;
     const size_t t = blockIdx.x;
@@ -379,7 +379,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     const int pos = a.positions[t];
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int n = pos - lo + 1;
-    const int chunk = (max((n + a.splits - 1) / a.splits, kWarps * kKT) + kKT - 1) / kKT * kKT;
+    // a range is at least two tiles per warp: shorter ranges only add partial results to merge
+    const int chunk = (max((n + a.splits - 1) / a.splits, 2 * kWarps * kKT) + kKT - 1) / kKT * kKT;
     const int used = (n + chunk - 1) / chunk;
     if (split >= used) return;
     const int begin = lo + split * chunk;
@@ -391,27 +392,40 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     const float* cs = a.cos_sin + (size_t)min(max(pos, 0), a.table_rows - 1) * a.rotary_dim;
     const int pieces = hd / 8;
 
-    bf16* my_tiles = tiles + (size_t)warp * 4 * kKT * ld;
+    bf16* my_tiles = tiles + (size_t)warp * NS * 2 * kKT * ld;
     const bf16* kc = (const bf16*)a.k_cache;
     const bf16* vc = (const bf16*)a.v_cache;
     // Lane l looks up the cache row of key j0 + l once; the copies then run with consecutive lanes on
     // consecutive 16-byte pieces of the same row, so that one instruction covers whole 128-byte lines.
-    auto fetch = [&](int j0, int stage) {
+    // The block-table entry of a tile is read one iteration before its copies are issued, so that the warp
+    // never waits on that load with tensor-core work behind it.
+    auto lookup = [&](int j0) -> long long {
         const int j = j0 + lane;
-        const bool mine = j < end && !(use_new && j == pos);
-        long long off = -1;
-        if (mine) {
-            const int page = j / a.page_size;
-            off = (((long long)bt[page] * a.page_size + (j - page * a.page_size)) * a.Hkv + kvh) * hd;
-        }
+        if (j >= end || (use_new && j == pos)) return -1;
+        const int page = j / a.page_size;
+        return (((long long)__ldg(bt + page) * a.page_size + (j - page * a.page_size)) * a.Hkv + kvh) * hd;
+    };
+    auto fetch = [&](long long off, int stage) {
         bf16* kd = my_tiles + (size_t)(stage * 2) * kKT * ld;
         bf16* vd = kd + kKT * ld;
-        for (int i = lane; i < kKT * pieces; i += 32) {
-            const int r = i / pieces, c = i - r * pieces;
-            const long long roff = __shfl_sync(0xffffffffu, off, r);
-            const bool valid = roff >= 0;
-            cp_async16(kd + r * ld + c * 8, kc + (valid ? roff : 0) + c * 8, valid);
-            cp_async16(vd + r * ld + c * 8, vc + (valid ? roff : 0) + c * 8, valid);
+        if (hd == HDT * 16) {                             // the usual case: shifts for the divisions, copies unrolled
+            constexpr int kPieces = HDT * 2;
+#pragma unroll
+            for (int it = 0; it < kKT * kPieces / 32; ++it) {
+                const int i = it * 32 + lane, r = i / kPieces, c = i % kPieces;
+                const long long roff = __shfl_sync(0xffffffffu, off, r);
+                const bool valid = roff >= 0;
+                cp_async16(kd + r * ld + c * 8, kc + (valid ? roff : 0) + c * 8, valid);
+                cp_async16(vd + r * ld + c * 8, vc + (valid ? roff : 0) + c * 8, valid);
+            }
+        } else {
+            for (int i = lane; i < kKT * pieces; i += 32) {
+                const int r = i / pieces, c = i - r * pieces;
+                const long long roff = __shfl_sync(0xffffffffu, off, r);
+                const bool valid = roff >= 0;
+                cp_async16(kd + r * ld + c * 8, kc + (valid ? roff : 0) + c * 8, valid);
+                cp_async16(vd + r * ld + c * 8, vc + (valid ? roff : 0) + c * 8, valid);
+            }
         }
     };
     float o[HDT * 2][4];
@@ -419,9 +433,19 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     for (int i = 0; i < HDT * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;     // rows lg and lg + 8 (query heads)
     const float scale_log2 = a.scale * 1.4426950408889634f;
+    // NS - 1 tiles are on their way before the first one is used (and while the queries are prepared): a warp's
+    // share of the memory system is what it keeps in flight, and a tile takes well over a microsecond to arrive
     const int first = begin + warp * kKT;
-    if (first < end) fetch(first, 0);                    // the first tile is on its way while the queries are prepared
-    cp_async_commit();
+    constexpr int kStride = kWarps * kKT;
+#pragma unroll
+    for (int p = 0; p < NS - 1; ++p) {
+        if (first + p * kStride < end) fetch(lookup(first + p * kStride), p);
+        cp_async_commit();
+    }
+    long long off_next = lookup(first + (NS - 1) * kStride);
+    // Up to here only step tables and keys and values of earlier tokens were read: that may run under the tail of
+    // the q|k|v projection before this kernel.  Its output is read from here on.
+    pdl_wait();
     for (int i = threadIdx.x; i < 16 * hd; i += kThreads) {
         const int g = i / hd, c = i % hd;
         q_s[g * ld + c] = __float2bfloat16_rn(g < G ? rotated<bf16>(row + (size_t)(h0 + g) * hd, c, a.rotary_dim, cs, 1.f, false) : 0.f);
@@ -441,12 +465,17 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     }
     __syncthreads();
 
+    unsigned qa[HDT][4];                                 // the queries' fragments stay in registers
+#pragma unroll
+    for (int kk = 0; kk < HDT; ++kk)
+        if (kk * 16 < hd) ldsm_x4(qa[kk], q_s + (lane & 15) * ld + kk * 16 + (lane >> 4) * 8);
     int stage = 0;
-    for (int j0 = first; j0 < end; j0 += kWarps * kKT, stage ^= 1) {
-        const int next = j0 + kWarps * kKT;
-        if (next < end) fetch(next, stage ^ 1);
+    for (int j0 = first; j0 < end; j0 += kStride, stage = (stage + 1 == NS ? 0 : stage + 1)) {
+        const int ahead = j0 + (NS - 1) * kStride;
+        if (ahead < end) fetch(off_next, (stage + NS - 1) % NS);       // into the stage that was used last iteration
         cp_async_commit();
-        cp_async_wait<1>();
+        off_next = lookup(ahead + kStride);
+        cp_async_wait<NS - 1>();
         __syncwarp();
         bf16* kb = my_tiles + (size_t)(stage * 2) * kKT * ld;
         bf16* vb = kb + kKT * ld;
@@ -460,25 +489,25 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
 #pragma unroll
         for (int kk = 0; kk < HDT; ++kk) {
             if (kk * 16 < hd) {
-                unsigned qa[4];
-                ldsm_x4(qa, q_s + (lane & 15) * ld + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
                 for (int n2 = 0; n2 < 2; ++n2) {
                     unsigned kf[4];
                     ldsm_x4(kf, kb + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * ld + kk * 16 + (mi & 1) * 8);
-                    mma_bf16(s[2 * n2], qa, kf[0], kf[1]);
-                    mma_bf16(s[2 * n2 + 1], qa, kf[2], kf[3]);
+                    mma_bf16(s[2 * n2], qa[kk], kf[0], kf[1]);
+                    mma_bf16(s[2 * n2 + 1], qa[kk], kf[2], kf[3]);
                 }
             }
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        if (j0 + kKT > end) {                            // only a range's last tile has keys beyond its end
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (j0 + nn * 8 + 2 * lt + (e & 1) >= end) s[nn][e] = -INFINITY;
+        }
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = j0 + nn * 8 + 2 * lt + (e & 1);
-                if (j >= end) s[nn][e] = -INFINITY;
-            }
             mx0 = fmaxf(mx0, fmaxf(s[nn][0], s[nn][1]));
             mx1 = fmaxf(mx1, fmaxf(s[nn][2], s[nn][3]));
         }
@@ -518,7 +547,9 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
         }
         __syncwarp();
     }
+    pdl_trigger();                                       // the output projection may fetch its weights under the merge
     cp_async_wait<0>();
+    __syncthreads();                                     // every warp is done with its tiles: the partial results go there
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     // per warp: rows (query heads) x columns -> shared memory, in natural-exponent units for the merge
@@ -586,14 +617,14 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     }
 }
 
-template <int HDT>
+template <int HDT, int NS>
 int launch_mma(const FusedArgs& a, int tokens, cudaStream_t s) {
     const int ld = a.hd + 8;
-    const size_t smem = (size_t)(16 + 2 + kWarps * 4 * kKT) * ld * sizeof(bf16) + (size_t)kWarps * 16 * (a.hd + 2) * sizeof(float);
+    // the per-warp partial results (kWarps * 16 * (hd + 2) floats) lie over the tiles, which are larger
+    const size_t smem = (size_t)(16 + 2 + kWarps * NS * 2 * kKT) * ld * sizeof(bf16);
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(attn_decode_mma_kernel<HDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attn_decode_mma_kernel<HDT><<<dim3(tokens, a.Hkv, a.splits), kThreads, smem, s>>>(a);
-    return launch_status();
+        cudaFuncSetAttribute(attn_decode_mma_kernel<HDT, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl_if(tokens <= pdl_max_rows(), attn_decode_mma_kernel<HDT, NS>, dim3(tokens, a.Hkv, a.splits), dim3(kThreads), smem, s, a);
 }
 
 template <typename T>
@@ -637,7 +668,7 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
                 cos_sin, table_rows, rotary_dim, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
                 write_kv, scale, key_scale};
     if (dtype == kBF16 && hd <= 128 && Hq / Hkv <= 16)
-        return hd <= 64 ? launch_mma<4>(a, tokens, (cudaStream_t)stream) : launch_mma<8>(a, tokens, (cudaStream_t)stream);
+        return hd <= 64 ? launch_mma<4, 2>(a, tokens, (cudaStream_t)stream) : launch_mma<8, 2>(a, tokens, (cudaStream_t)stream);
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, tokens, (cudaStream_t)stream));
     return kOk;
 }

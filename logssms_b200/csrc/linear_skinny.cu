@@ -125,7 +125,6 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     };
     // The weights do not depend on the kernel before this one: their first batch is on its way while
     // that kernel still runs; x (its output) is touched only after the wait.
-    pdl_trigger();
     load_w(c_begin);
     pdl_wait();
     if (NORM) {
@@ -211,6 +210,10 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
             }
         }
     }
+    // The next kernel may start once every CTA here has streamed its weights: it fetches its own under this
+    // kernel's reduction and stores.  (A trigger at the start lets a whole chain of waiting kernels pile up
+    // on the SMs; measured slower.)
+    pdl_trigger();
     // accumulator element e of tile m: feature g + 8*(e/2), batch row m*8 + 2t + (e&1)
 #pragma unroll
     for (int h = 0; h < HALVES; ++h)
@@ -276,7 +279,7 @@ int launch_mt(const SkinnyArgs& a, cudaStream_t s) {
         if (NORM) smem += (size_t)MT * 8 * (a.K + 8) * sizeof(__nv_bfloat16);                               \
         if (smem > 48 * 1024)                                                                               \
             cudaFuncSetAttribute(skinny_linear_kernel<MT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        rc = launch_pdl(skinny_linear_kernel<MT, EPI, NORM>, grid, dim3(kThreads), smem, s, a);             \
+        rc = launch_pdl_if(a.M <= pdl_max_rows(), skinny_linear_kernel<MT, EPI, NORM>, grid, dim3(kThreads), smem, s, a); \
     }
     int rc = 0;
     if (mt <= 1) LB_SKINNY(1)

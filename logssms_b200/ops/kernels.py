@@ -328,16 +328,15 @@ def _counters_for(device: torch.device, n: int) -> torch.Tensor:
 
 
 def decode_step_splits(num_tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
-    """Most key ranges per token for `attention_decode_step`: enough CTAs to fill every SM several times
-    over, never more ranges than 128-key pieces of the longest context (the kernel itself uses fewer
-    ranges for a short context)."""
+    """Most key ranges per token for `attention_decode_step`: about two CTAs per SM, never more ranges than
+    256-key pieces of the longest context (the kernel itself uses fewer ranges for a short context)."""
     G = num_heads // num_kv_heads
     tile = 8 if G >= 8 else (4 if G > 2 else G)
     items = max(1, num_tokens * num_kv_heads * (-(-G // tile)))
-    return max(1, min(_STEP_TARGET_CTAS // items, -(-max_context // 128), 256))
+    return max(1, min(_STEP_TARGET_CTAS // items, -(-max_context // 256), 256))
 
 
-_STEP_TARGET_CTAS = 296         # one round of two CTAs on each of the 148 SMs: long ranges keep the copies streaming
+_STEP_TARGET_CTAS = 296         # two CTAs per SM (three fit): measured best at 1, 8 and 64 tokens of 2,048 and 8,000 keys
 
 
 def attention_decode_step(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,
