@@ -1,6 +1,10 @@
 // Causal grouped-query attention for prompt portions over the paged cache, on tensor cores (bfloat16).
 //
-// One CTA per (tile of 64 query tokens of one request, query head), 4 warps x 16 query rows.  The
+// One CTA per (tile of 64 query tokens of one request, query head).  A group of 4 warps holds the 64 query
+// rows (16 each); a CTA has up to 4 such groups, which take the key tiles in turn (group g: tiles g, g + NG,
+// ...) with buffers and barriers of their own and merge their partial results through shared memory at the
+// end: a tile's walk over the keys is a chain of dependent steps, and the longest chain (the last tile of a
+// long prompt) sets the kernel's time, so it is cut into NG chains that run side by side.  The
 // keys a tile may see (everything the request has in the cache up to the tile's last token, which
 // includes earlier portions and the keys this step stored) are walked in tiles of 64: K and V rows
 // are gathered page by page into shared memory with 16-byte cp.async (double buffered), S = Q K^T and
@@ -16,7 +20,7 @@
 using namespace lb200;
 
 namespace {
-constexpr int kQTile = 64, kKTile = 64, kWarps = 4, kThreads = kWarps * 32;
+constexpr int kQTile = 64, kKTile = 64, kWarps = 4, kGroupThreads = kWarps * 32;
 typedef __nv_bfloat16 bf16;
 
 struct PrefillArgs {
@@ -56,15 +60,34 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 // HDT: head_dim / 16, rounded up to the instantiated size (4, 8 or 16); loops are cut at the real hd.
-template <int HDT>
-__global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
+// A barrier of one group's 128 threads (ids 1..4; a run-time id would make the compiler reserve all sixteen).
+__device__ __forceinline__ void group_barrier(int group) {
+    switch (group) {
+        case 0: asm volatile("bar.sync 1, %0;" ::"n"(kGroupThreads) : "memory"); break;
+        case 1: asm volatile("bar.sync 2, %0;" ::"n"(kGroupThreads) : "memory"); break;
+        case 2: asm volatile("bar.sync 3, %0;" ::"n"(kGroupThreads) : "memory"); break;
+        default: asm volatile("bar.sync 4, %0;" ::"n"(kGroupThreads) : "memory"); break;
+    }
+}
+// Elements of shared memory per group: its two key and two value buffers, and room for its partial result
+// (HDT * 2 + 1 float4 per thread) where small heads make the buffers smaller than that.
+__host__ __device__ inline size_t group_elems(int hd, int hdt) {
+    const size_t buffers = (size_t)4 * kKTile * (hd + 8), partial = (size_t)(hdt * 2 + 1) * kGroupThreads * 8;
+    return buffers > partial ? buffers : partial;
+}
+
+// NG: groups of 4 warps that share the keys of the tile among them.
+template <int HDT, int NG>
+__global__ void __launch_bounds__(kGroupThreads * NG) attn_prefill_kernel(PrefillArgs a) {
+    constexpr int kThreads = kGroupThreads * NG;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int hd = a.hd;
     const int ld = hd + 8;                               // row stride in elements: an odd number of 16-byte pieces
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [64][ld]
-    bf16* k_s = q_s + kQTile * ld;                       // [2][64][ld]
-    bf16* v_s = k_s + 2 * kKTile * ld;                   // [2][64][ld]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int grp = threadIdx.x / kGroupThreads, tid_g = threadIdx.x % kGroupThreads;
+    bf16* k_s = q_s + kQTile * ld + (size_t)grp * group_elems(hd, HDT);   // this group's [2][64][ld]
+    bf16* v_s = k_s + 2 * kKTile * ld;                               // and [2][64][ld]
+    const int warp = tid_g >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     // The host lists the tiles heaviest first.  CTAs are handed to the SMs in rounds of one per SM; every
     // second round takes its items in reverse, so that the SM that got the heaviest item of one round
     // gets the lightest of the next (causal tiles differ by up to the whole context in cost).
@@ -89,7 +112,7 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
     }
     const int kt_begin = lo / kKTile, kt_end = last_pos / kKTile + 1;
     // two threads per key row: one page lookup per row and tile, then 16-byte pieces side by side
-    const int ld_row = threadIdx.x >> 1, ld_half = threadIdx.x & 1;
+    const int ld_row = tid_g >> 1, ld_half = tid_g & 1;
     const int ld_c0 = ld_half * ((pieces + 1) / 2), ld_c1 = ld_half ? pieces : (pieces + 1) / 2;
     auto load_kv = [&](int kt, int buf) {
         const int j = kt * kKTile + ld_row;
@@ -107,8 +130,13 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
             cp_async16(vd + c * 8, a.v_cache + off + c * 8, valid);
         }
     };
-    load_kv(kt_begin, 0);
+    cp_async_commit();                                   // the queries
+    if (kt_begin + grp < kt_end) load_kv(kt_begin + grp, 0);
     cp_async_commit();
+    if (NG > 1) {                                        // the queries came through every group's threads
+        cp_async_wait<1>();
+        __syncthreads();
+    }
 
     float o[HDT * 2][4];
 #pragma unroll
@@ -118,12 +146,11 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
     const int p0 = pos0 + row0, p1 = pos0 + row1;                  // absolute positions (rows beyond `rows` are never stored)
     const int lo0 = a.window > 0 ? p0 - a.window + 1 : 0, lo1 = a.window > 0 ? p1 - a.window + 1 : 0;
 
-    for (int kt = kt_begin; kt < kt_end; ++kt) {
-        const int buf = (kt - kt_begin) & 1;
-        if (kt + 1 < kt_end) load_kv(kt + 1, buf ^ 1);
+    for (int kt = kt_begin + grp, buf = 0; kt < kt_end; kt += NG, buf ^= 1) {
+        if (kt + NG < kt_end) load_kv(kt + NG, buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
-        __syncthreads();
+        group_barrier(grp);
         const bf16* kb = k_s + buf * kKTile * ld;
         const bf16* vb = v_s + buf * kKTile * ld;
         if (warp * 16 < rows) {
@@ -206,9 +233,38 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
                 }
             }
         }
-        __syncthreads();
+        group_barrier(grp);
     }
     cp_async_wait<0>();
+    if (NG > 1) {
+        // groups 1.. leave their partial results (in the threads' own fragment order) in their key buffers;
+        // group 0 folds them into its own
+        float4* part = reinterpret_cast<float4*>(k_s);   // [HDT * 2 + 1][128] per group
+        if (grp > 0) {
+#pragma unroll
+            for (int i = 0; i < HDT * 2; ++i) part[i * kGroupThreads + tid_g] = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
+            part[HDT * 2 * kGroupThreads + tid_g] = make_float4(m0, m1, l0, l1);
+        }
+        __syncthreads();
+        if (grp > 0) return;
+#pragma unroll
+        for (int other = 1; other < NG; ++other) {
+            const float4* theirs = reinterpret_cast<const float4*>(k_s + (size_t)other * group_elems(hd, HDT));
+            const float4 ml = theirs[HDT * 2 * kGroupThreads + tid_g];
+            const float n0 = fmaxf(m0, ml.x), n1 = fmaxf(m1, ml.y);
+            const float r0 = n0 == -INFINITY ? 0.f : n0, r1 = n1 == -INFINITY ? 0.f : n1;
+            const float fa0 = exp2f(m0 - r0), fb0 = exp2f(ml.x - r0), fa1 = exp2f(m1 - r1), fb1 = exp2f(ml.y - r1);
+            m0 = n0; m1 = n1;
+            l0 = l0 * fa0 + ml.z * fb0;
+            l1 = l1 * fa1 + ml.w * fb1;
+#pragma unroll
+            for (int i = 0; i < HDT * 2; ++i) {
+                const float4 v = theirs[i * kGroupThreads + tid_g];
+                o[i][0] = o[i][0] * fa0 + v.x * fb0; o[i][1] = o[i][1] * fa0 + v.y * fb0;
+                o[i][2] = o[i][2] * fa1 + v.z * fb1; o[i][3] = o[i][3] * fa1 + v.w * fb1;
+            }
+        }
+    }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float inv0 = 1.f / l0, inv1 = 1.f / l1;
@@ -226,12 +282,12 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(PrefillArgs a) {
     }
 }
 
-template <int HDT>
+template <int HDT, int NG>
 int launch_hdt(const PrefillArgs& a, int n_tiles, cudaStream_t s) {
-    const size_t smem = (size_t)(kQTile + 4 * kKTile) * (a.hd + 8) * sizeof(bf16);
+    const size_t smem = ((size_t)kQTile * (a.hd + 8) + NG * group_elems(a.hd, HDT)) * sizeof(bf16);
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(attn_prefill_kernel<HDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attn_prefill_kernel<HDT><<<dim3(a.n_items), kThreads, smem, s>>>(a);
+        cudaFuncSetAttribute(attn_prefill_kernel<HDT, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_prefill_kernel<HDT, NG><<<dim3(a.n_items), kGroupThreads * NG, smem, s>>>(a);
     return launch_status();
 }
 }  // namespace
@@ -257,7 +313,15 @@ extern "C" int lb_attention_prefill(const void* q, const void* k_cache, const vo
                   cu_seqlens, start_pos, tiles, Hq, Hkv, hd, page_size, window, scale * 1.4426950408889634f,
                   n_tiles * Hq, num_sms, -1};
     for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
-    if (hd <= 64) return launch_hdt<4>(a, n_tiles, (cudaStream_t)stream);
-    if (hd <= 128) return launch_hdt<8>(a, n_tiles, (cudaStream_t)stream);
-    return launch_hdt<16>(a, n_tiles, (cudaStream_t)stream);
+    // Groups per CTA.  Measured on a 2,048-token prompt of 8 heads of 64: 57 us with one group, 42 with two (two
+    // CTAs per SM), 44 with four (one CTA per SM).  LOGSSMS_B200_PREFILL_GROUPS=1|2|4 overrides it for head
+    // sizes up to 64, =1 for those up to 128; 256-wide heads fill the shared memory with one group.
+    static const int ng_env = [] { const char* e = getenv("LOGSSMS_B200_PREFILL_GROUPS"); return e ? atoi(e) : 0; }();
+    if (hd <= 64) {
+        if (ng_env == 1) return launch_hdt<4, 1>(a, n_tiles, (cudaStream_t)stream);
+        if (ng_env == 4) return launch_hdt<4, 4>(a, n_tiles, (cudaStream_t)stream);
+        return launch_hdt<4, 2>(a, n_tiles, (cudaStream_t)stream);
+    }
+    if (hd <= 128) return ng_env == 1 ? launch_hdt<8, 1>(a, n_tiles, (cudaStream_t)stream) : launch_hdt<8, 2>(a, n_tiles, (cudaStream_t)stream);
+    return launch_hdt<16, 1>(a, n_tiles, (cudaStream_t)stream);
 }

@@ -119,12 +119,27 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
     const bool has_history = a.start_pos[b] > 0;
     const T* x = (const T*)a.x;
     T* st = (T*)a.state + ((size_t)a.slots[b] * a.C + c) * (K - 1);
+    // The rows of the chunk, the thread's taps (8 * K consecutive floats) and its biases are fetched as 16-byte
+    // pieces up front, so that all of them are in flight together: one after the other, each waited for,
+    // they were most of the kernel's time.
+    uint4 rows[kVecChunk];
+#pragma unroll
+    for (int i = 0; i < kVecChunk; ++i)
+        if (i < n) rows[i] = *reinterpret_cast<const uint4*>(x + (size_t)(begin + t0 + i) * a.x_stride + c);
     float w[8][K], win[8][K], bias[8];
+    {
+        float4 raw[2 * K];
+        const float4* wp = reinterpret_cast<const float4*>(a.weight + (size_t)c * K);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        bias[e] = a.bias ? a.bias[c + e] : 0.f;
+        for (int i = 0; i < 2 * K; ++i) raw[i] = __ldg(wp + i);
+        float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+        if (a.bias) { b0 = __ldg(reinterpret_cast<const float4*>(a.bias + c)); b1 = __ldg(reinterpret_cast<const float4*>(a.bias + c) + 1); }
+        bias[0] = b0.x; bias[1] = b0.y; bias[2] = b0.z; bias[3] = b0.w; bias[4] = b1.x; bias[5] = b1.y; bias[6] = b1.z; bias[7] = b1.w;
+        const float* flat = reinterpret_cast<const float*>(raw);
 #pragma unroll
-        for (int j = 0; j < K; ++j) w[e][j] = a.weight[(size_t)(c + e) * K + j];
+        for (int e = 0; e < 8; ++e)
+#pragma unroll
+            for (int j = 0; j < K; ++j) w[e][j] = flat[e * K + j];
     }
 #pragma unroll
     for (int j = 0; j < K - 1; ++j) {
@@ -139,10 +154,6 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
             for (int e = 0; e < 8; ++e) win[e][j] = has_history ? to_f32(st[e * (K - 1) + K - 1 + idx]) : 0.f;
         }
     }
-    uint4 rows[kVecChunk];
-#pragma unroll
-    for (int i = 0; i < kVecChunk; ++i)
-        if (i < n) rows[i] = *reinterpret_cast<const uint4*>(x + (size_t)(begin + t0 + i) * a.x_stride + c);
 #pragma unroll
     for (int i = 0; i < kVecChunk; ++i) {
         if (i < n) {
@@ -187,7 +198,8 @@ void launch_vec(const ConvArgs& a, int B, int max_len, cudaStream_t s) {
 
 inline bool vec_ok(const ConvArgs& a, int dtype) {
     return dtype == kBF16 && a.C % 8 == 0 && a.end0 % 8 == 0 && a.end1 % 8 == 0 && a.x_stride % 8 == 0 &&
-           ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0;
+           ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0 && ((uintptr_t)a.weight & 15) == 0 &&
+           (a.bias == nullptr || ((uintptr_t)a.bias & 15) == 0);
 }
 
 template <typename T>

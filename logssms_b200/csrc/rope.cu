@@ -77,12 +77,96 @@ __global__ void rope_kv_store_kernel(const T* __restrict__ q, const T* __restric
     }
 }
 
+// The same for bfloat16 with 16-byte accesses: a thread owns 8 consecutive columns of one head of one token
+// and reads its partner's 8 columns beside them.  Needs hd and rotary_dim / 2 in multiples of 8 and
+// 16-byte-aligned rows; the launcher falls back to the kernel above otherwise.
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 p = __bfloat1622float2(h[i]); f[2 * i] = p.x; f[2 * i + 1] = p.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+    uint4 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+
+__global__ void __launch_bounds__(256) rope_kv_store_vec_kernel(
+        const __nv_bfloat16* __restrict__ qkv, long row_stride, const int* __restrict__ positions,
+        const int* __restrict__ slot_mapping, const float* __restrict__ cos_sin, int table_rows,
+        __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+        int tokens, int Hq, int Hkv, int hd, int rotary_dim, float key_scale, int write_kv) {
+    const int pieces = hd >> 3, heads = Hq + 2 * Hkv;
+    const long item = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= (long)tokens * heads * pieces) return;
+    const int piece = (int)(item % pieces);
+    const int head = (int)((item / pieces) % heads);
+    const size_t t = (size_t)(item / ((long)pieces * heads));
+    const int c = piece * 8, half = rotary_dim >> 1;
+    const __nv_bfloat16* src = qkv + t * row_stride + (size_t)head * hd;
+    __nv_bfloat16* dst;
+    bool rotate = c < rotary_dim;
+    float scale = 1.f;
+    if (head < Hq) {
+        dst = q_out + (t * Hq + head) * hd;
+    } else {
+        if (!write_kv) return;
+        const long slot = slot_mapping[t];
+        if (slot < 0) return;
+        if (head < Hq + Hkv) {
+            dst = k_cache + ((size_t)slot * Hkv + (head - Hq)) * hd;
+            scale = key_scale;
+        } else {
+            dst = v_cache + ((size_t)slot * Hkv + (head - Hq - Hkv)) * hd;
+            rotate = false;
+        }
+    }
+    const uint4 own = *reinterpret_cast<const uint4*>(src + c);
+    if (!rotate && scale == 1.f) { *reinterpret_cast<uint4*>(dst + c) = own; return; }
+    float x[8];
+    unpack8(own, x);
+    if (scale != 1.f) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = round_to<__nv_bfloat16>(x[i] * scale);       // keys: scaled and rounded first
+    }
+    if (rotate) {
+        const bool low = c < half;
+        float y[8];
+        unpack8(*reinterpret_cast<const uint4*>(src + (low ? c + half : c - half)), y);
+        if (scale != 1.f) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = round_to<__nv_bfloat16>(y[i] * scale);
+        }
+        const int pos = min(max(positions[t], 0), table_rows - 1);
+        const float* cs = cos_sin + (size_t)pos * rotary_dim + (low ? c : c - half);
+        const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(cs + half), s1 = *reinterpret_cast<const float4*>(cs + half + 4);
+        const float co[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float si[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = x[i] * co[i] + (low ? -y[i] : y[i]) * si[i];
+    }
+    *reinterpret_cast<uint4*>(dst + c) = pack8(x);
+}
+
 extern "C" int lb_rope_kv_store(const void* q, const void* k, const void* v, long row_stride, const int* positions,
                                 const int* slot_mapping, const float* cos_sin, int table_rows, void* q_out,
                                 void* k_cache, void* v_cache, int tokens, int Hq, int Hkv, int hd, int rotary_dim,
                                 float key_scale, int write_kv, int dtype, void* stream) {
     if (tokens <= 0) return kOk;
     if (hd <= 0 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1) || Hq <= 0 || Hkv <= 0) return kBadSize;
+    if (dtype == kBF16 && q == (const char*)k - (size_t)Hq * hd * 2 && v == (const char*)k + (size_t)Hkv * hd * 2 &&
+        hd % 8 == 0 && rotary_dim % 16 == 0 && row_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 &&
+        ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 &&
+        ((uintptr_t)cos_sin & 15) == 0) {
+        const long items = (long)tokens * (Hq + 2 * Hkv) * (hd / 8);
+        rope_kv_store_vec_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)q, row_stride, positions, slot_mapping, cos_sin, table_rows, (__nv_bfloat16*)q_out,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, Hq, Hkv, hd, rotary_dim, key_scale, write_kv);
+        return launch_status();
+    }
     dim3 grid(tokens, Hq + 2 * Hkv);
     const int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
     LB_DISPATCH_DTYPE(dtype, rope_kv_store_kernel<T><<<grid, threads, 0, (cudaStream_t)stream>>>(

@@ -126,7 +126,7 @@ def test_swiglu_and_scale(dtype, I):
 
 # --------------------------------------------------------------------------- rotation + cache store
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hd,rotary", [(16, 16), (48, 24), (80, 80), (128, 64)])
+@pytest.mark.parametrize("hd,rotary", [(16, 16), (48, 24), (64, 32), (80, 80), (128, 64)])
 def test_rope_kv_store(dtype, hd, rotary):
     g = torch.Generator().manual_seed(hd)
     k = K()
