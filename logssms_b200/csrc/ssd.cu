@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(MAXT) ssd_chunk_scan_kernel(SsdArgs a) {
     bf16* b_s = c_s + Lpad * ldn;                               // [Lpad][ldn]
     bf16* u_s = b_s + Lpad * ldn;                               // [Lpad][ldp]   x (dt rides in the masked scores)
     bf16* s_s = u_s + Lpad * ldp;                               // [Ppad][ldn]   S_in
-    chunk_decay(a, tok0, Lc, Lpad, h, dt_s, a_s, tot);
+    bf16* z_s = s_s + Ppad * ldn;                               // [Lpad][ldp]   the gate's rows (when there is one)
     const int g = h / (a.nh / a.G), inner = a.nh * P;
     const int threads = blockDim.x;
     // all four tiles come in 16-byte cp.async pieces (zeros outside the chunk and the real sizes)
@@ -253,6 +253,24 @@ __global__ void __launch_bounds__(MAXT) ssd_chunk_scan_kernel(SsdArgs a) {
         const bool ok = p < P && n < N;
         cp_async16(s_s + p * ldn + n, sin + (ok ? (size_t)p * N + n : 0), ok);
     }
+    if (a.gate != nullptr) {
+        // the gate is a view of a wider projection: 16-byte copies where its rows start on such boundaries
+        const bool gate16 = ((uintptr_t)a.gate & 15) == 0 && a.gate_stride % 8 == 0;
+        for (int i = threadIdx.x; i < Lpad * ppieces; i += threads) {
+            const int s = i / ppieces, p = (i % ppieces) * 8;
+            const bool ok = s < Lc && p < P;
+            const bf16* src = a.gate + (size_t)(tok0 + (ok ? s : 0)) * a.gate_stride + h * P + (ok ? p : 0);
+            if (gate16) {
+                cp_async16(z_s + s * ldp + p, src, ok);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) z_s[s * ldp + p + e] = ok ? src[e] : __float2bfloat16_rn(0.f);
+            }
+        }
+    }
+    // the tiles are on their way while the decay factors are computed (that is a chain of its own: dt from
+    // global memory, softplus, a prefix sum over the chunk)
+    chunk_decay(a, tok0, Lc, Lpad, h, dt_s, a_s, tot);
     cp_async_wait_all();
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;
@@ -334,11 +352,11 @@ __global__ void __launch_bounds__(MAXT) ssd_chunk_scan_kernel(SsdArgs a) {
                 const int trow = r0 + lg + 8 * half;
                 if (trow < Lc) {
                     const size_t tok = (size_t)(tok0 + trow);
-                    const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(a.conv + tok * a.C + h * P + p);
+                    const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(u_s + trow * ldp + p);
                     float y0 = acc[j][2 * half] + Dh * __bfloat162float(xv.x);
                     float y1 = acc[j][2 * half + 1] + Dh * __bfloat162float(xv.y);
                     if (a.gate != nullptr) {
-                        const __nv_bfloat162 zv = *reinterpret_cast<const __nv_bfloat162*>(a.gate + tok * a.gate_stride + h * P + p);
+                        const __nv_bfloat162 zv = *reinterpret_cast<const __nv_bfloat162*>(z_s + trow * ldp + p);
                         const float z0 = round_to<bf16>(__bfloat162float(zv.x) * a.gate_scale);
                         const float z1 = round_to<bf16>(__bfloat162float(zv.y) * a.gate_scale);
                         y0 = round_to<bf16>(y0) * round_to<bf16>(silu_f(z0));
@@ -357,7 +375,7 @@ size_t state_smem(int L, int P, int N) {
 }
 size_t scan_smem(int L, int P, int N) {
     const int Lpad = round_up(L, 16), Ppad = round_up(P, 16), Npad = round_up(N, 16);
-    return (size_t)(2 * Lpad + 32) * 4 + ((size_t)2 * Lpad * (Npad + 8) + (size_t)Lpad * (Ppad + 8) + (size_t)Ppad * (Npad + 8)) * 2;
+    return (size_t)(2 * Lpad + 32) * 4 + ((size_t)2 * Lpad * (Npad + 8) + (size_t)2 * Lpad * (Ppad + 8) + (size_t)Ppad * (Npad + 8)) * 2;
 }
 constexpr size_t kSmemLimit = 200 * 1024;
 

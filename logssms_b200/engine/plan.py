@@ -74,8 +74,10 @@ class StepPlanner:
 
     def plan(self, entries: Sequence[StepEntry], static: StaticTables | None = None) -> StepContext:
         """Host side of a step: checks, room in the cache, and every per-step integer packed into one
-        pinned buffer and copied to the device at once.  With `static` (a decode graph's slot) the
-        tables keep a fixed width and a fixed place on the device, so that a captured graph finds them."""
+        pinned buffer and copied to the device at once.  With `static` (a captured step's slot) the
+        tables keep a fixed width and a fixed place on the device, so that a captured graph finds them;
+        every later step planned into the same slot must bring the same numbers of tokens and wanted
+        places, request by request."""
         B = len(entries)
         seen = set()
         for e in entries:
@@ -152,8 +154,11 @@ class StepPlanner:
             num_tokens=T, num_requests=B, max_len=int(lens.max()), token_ids=view(0), positions=view(1),
             token_req=view(2), cu_seqlens=view(3), start_pos=view(4), slots=view(5),
             block_tables=block_tables, slot_mappings=slot_mappings, logit_rows=view(6), cache=self.cache,
+            # a captured step is replayed for other requests of the same lengths: the most keys any of them may
+            # have, and work lists that depend on the lengths only (their order, a matter of speed, is that of
+            # the step they were built for)
             max_context=max_context if static is None else self.max_seq_len,
-            host_lens=None if static is not None else lens, host_starts=None if static is not None else starts,
+            host_lens=lens, host_starts=starts,
         )
         if static is not None:
             static.ctx = ctx

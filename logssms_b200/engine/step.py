@@ -37,7 +37,7 @@ class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", *, max_requests: int = 64, max_seq_len: int = 8192,
                  page_size: int = 64, num_pages: int | None = None, memory_ratio: float = 0.9,
                  device: str = "cuda:0", poison_on_free: bool = False, max_step_tokens: int = 1 << 30,
-                 use_graphs: bool = True, max_graphs: int = 16):
+                 use_graphs: bool = True, max_graphs: int = 16, max_shape_graphs: int = 8, max_graph_tokens: int = 4096):
         if not torch.cuda.is_available():
             raise RuntimeError("logssms_b200 needs a CUDA device (built for sm_100a); there is no CPU path")
         try:
@@ -63,7 +63,10 @@ class Engine:
         self.planner = StepPlanner(self.cache, self.device, self.vocab_size)
         self.use_graphs = use_graphs
         self.max_graphs = max_graphs
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self.max_shape_graphs = max_shape_graphs
+        self.max_graph_tokens = max_graph_tokens
+        self._graphs: dict[int, _StepGraph] = {}             # decode steps, by batch size
+        self._shape_graphs: dict[tuple, _StepGraph] = {}      # other steps, by (tokens of every entry, wanted places)
         self._side_stream: torch.cuda.Stream | None = None
         self.steps_run = 0
 
@@ -101,14 +104,23 @@ class Engine:
         `device_tokens` (int32 on the device, one per entry; decode steps only) replaces the entries' token
         ids: the ids sampled by the step before need not visit the host before they are fed back.
 
-        A step of single decoded tokens that all want their logits is replayed from a CUDA graph
-        (one per batch size, captured the second time that size is seen); the returned tensor is then
-        the graph's own output buffer, valid until the next step of the same size."""
+        Steps are replayed from CUDA graphs where their shape comes again.  A step of single decoded
+        tokens that all want their logits has one graph per batch size, captured the second time that size
+        is seen.  Any other step of at most `max_graph_tokens` tokens has one per shape (the number of tokens
+        of every entry in order, and the number of wanted places), captured the third time the shape is seen:
+        a long prompt cut into equal portions, or the same prompt length again.  The host then does nothing
+        per kernel; a step whose shape is new runs kernel by kernel.  A replayed step returns the graph's own
+        output buffer, valid until the next step of the same shape."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return self._decode_step(entries, device_tokens)
+        if self.use_graphs:
+            lens = tuple(len(e.tokens) for e in entries)
+            if all(n == 1 for n in lens) and all(list(e.want) == [0] for e in entries):
+                return self._graph_step(self._graphs, len(entries), self.max_graphs, 2, entries, device_tokens)
+            if device_tokens is None and sum(lens) <= self.max_graph_tokens:
+                key = (lens, sum(len(e.want) for e in entries))
+                return self._graph_step(self._shape_graphs, key, self.max_shape_graphs, 3, entries, None)
         ctx = self.planner.plan(entries)
         if device_tokens is not None:
             if ctx.num_tokens != len(entries) or device_tokens.numel() != ctx.num_tokens:
@@ -120,20 +132,26 @@ class Engine:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.logits(x, residual, ctx.logit_rows)
 
-    def _decode_step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
-        B = len(entries)
-        slot = self._graphs.get(B)
+    def _graph_step(self, graphs: dict, key, most: int, capture_at: int, entries: Sequence[StepEntry],
+                    device_tokens: torch.Tensor | None) -> torch.Tensor:
+        """A step through the graph of its shape.  First sight: kernel by kernel with tables of its own (this
+        also builds and loads every kernel).  From the second on its tables lie in the slot's fixed buffer;
+        until `capture_at` it still runs kernel by kernel (which builds the work lists that long portions need,
+        outside of any capture), then it is captured once and replayed."""
+        slot = graphs.get(key)
         if slot is None:
-            if len(self._graphs) >= self.max_graphs:
-                self._graphs.pop(next(iter(self._graphs)))
-            slot = self._graphs[B] = _DecodeGraph()
+            if len(graphs) >= most:
+                graphs.pop(next(iter(graphs)))
+            slot = graphs[key] = _StepGraph()
         slot.seen += 1
-        if slot.graph is None and slot.seen < 2:
-            ctx = self.planner.plan(entries)              # first time: eager (this also builds and loads every kernel)
+        if slot.graph is None and slot.seen < capture_at:
+            ctx = self.planner.plan(entries, slot if slot.seen > 1 else None)
             if device_tokens is not None:
                 ctx.token_ids.copy_(device_tokens)
             x, residual = self.model.forward(ctx)
             self.steps_run += 1
+            if ctx.logit_rows.numel() == 0:
+                return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
             return self.model.logits(x, residual, ctx.logit_rows)
         ctx = self.planner.plan(entries, slot)
         if device_tokens is not None:
@@ -144,11 +162,14 @@ class Engine:
             before = K.launch_count
             if self._side_stream is None:
                 self._side_stream = torch.cuda.Stream(self.device)
-            if os.environ.get("LOGSSMS_B200_FORK_MIXERS", "1") != "0":
+            if ctx.max_len == 1 and os.environ.get("LOGSSMS_B200_FORK_MIXERS", "1") != "0":
                 ctx.extras["side_stream"] = self._side_stream  # blocks may fork their mixers onto it while capturing
             with torch.cuda.graph(graph):
                 x, residual = self.model.forward(ctx)
-                slot.logits = self.model.logits(x, residual, ctx.logit_rows)
+                if ctx.logit_rows.numel() == 0:
+                    slot.logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+                else:
+                    slot.logits = self.model.logits(x, residual, ctx.logit_rows)
             ctx.extras.pop("side_stream", None)
             slot.launches = K.launch_count - before
             K.launch_count = before
@@ -158,9 +179,9 @@ class Engine:
         self.steps_run += 1
         return slot.logits
 
-class _DecodeGraph(StaticTables):
-    """A captured decode step for one batch size: its table buffer on the device, the step context
-    whose tensors are views of that buffer, the graph, and the logits it writes."""
+class _StepGraph(StaticTables):
+    """A captured step of one shape: its table buffer on the device, the step context whose tensors are
+    views of that buffer, the graph, and the logits it writes."""
 
     def __init__(self):
         super().__init__()

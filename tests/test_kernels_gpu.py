@@ -488,10 +488,15 @@ def test_ssd_prefill_in_chunks_resumes_from_state_and_matches_the_recurrence(sha
         common = (dev(A_log), dev(dt_bias), dev(D))
         conv_d, dt_d, z_d = torch.cat(cs).cuda(), torch.cat(ds).cuda(), torch.cat(zz).cuda()
         lists = (dev(cu), dev(sp), dev(slots), dev(chunks), chunks.shape[0], dev(per_request), per_request.shape[0], L)
-        st_before = state.clone()
+        st_before, st_before2 = state.clone(), state.clone()
         y = k.ssd_prefill(conv_d, dt_d, *common, state, *lists, nh, Pd, N, G, 0.8)
         yg = k.ssd_prefill(conv_d, dt_d, *common, st_before, *lists, nh, Pd, N, G, 0.8, z_d, 0.6)
         assert torch.equal(yg, k.gated_rmsnorm(y, z_d, None, 1e-5, 1, 0.6, k.GATE_ONLY))
+        # the gate as a view whose rows start on no 16-byte boundary (the kernel copies it piece by piece then)
+        z_wide = torch.zeros(z_d.shape[0], inner + 12, dtype=dtype, device="cuda")
+        z_view = z_wide[:, 4:4 + inner]
+        z_view.copy_(z_d)
+        assert torch.equal(k.ssd_prefill(conv_d, dt_d, *common, st_before2, *lists, nh, Pd, N, G, 0.8, z_view, 0.6), yg)
         k.ssm_scan(conv_d, dt_d, *common, state_seq, dev(cu), dev(sp), dev(slots), 3, nh, Pd, N, G, 0.8)
         for r in range(3):
             got[r].append(y[int(cu[r]):int(cu[r + 1])].cpu())

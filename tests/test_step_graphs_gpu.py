@@ -1,0 +1,79 @@
+"""Steps whose shape comes again are replayed from CUDA graphs: the logits must be those of the same steps
+run kernel by kernel, for other requests, other tokens, other pages and other places in the sequence than
+the ones the graph was captured with."""
+import pytest
+import torch
+
+from tiny import TINY, TOL, make_model_dir
+
+pytestmark = pytest.mark.gpu
+
+
+def run_steps(engine, plan, prompts):
+    """`plan`: a list of steps, each a list of (request name, number of tokens, wanted places); the tokens are
+    taken from the request's prompt in order.  Returns the logits of every step (on the host)."""
+    from logssms_b200.engine import StepEntry
+    live, done, out = {}, {}, []
+    for step in plan:
+        entries = []
+        for name, n, want in step:
+            if name not in live:
+                live[name], done[name] = engine.new_request(), 0
+            ids = prompts[name][done[name]:done[name] + n]
+            assert len(ids) == n
+            done[name] += n
+            entries.append(StepEntry(live[name], ids, want))
+        out.append(engine.step(entries).float().cpu().clone())
+        for name in [nm for nm, _, _ in step if done[nm] == len(prompts[nm])]:
+            engine.release(live.pop(name))
+    for r in live.values():
+        engine.release(r)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_steps_of_a_repeated_shape_replay_from_a_graph_with_the_same_logits(tmp_path, name, dtype):
+    from logssms_b200.engine import Engine
+    raw = TINY[name]
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=41, dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+    g = torch.Generator().manual_seed(9)
+    prompts = {k: torch.randint(0, raw["vocab_size"], (n,), generator=g).tolist()
+               for k, n in (("a", 120), ("b", 80), ("c", 80), ("d", 47), ("e", 47), ("f", 47), ("g", 47))}
+    plan = []
+    # one prompt in equal portions of 40 (the same shape at other places of the sequence)
+    plan += [[("a", 40, [39])] for _ in range(3)]
+    # the same prompt length again and again, for other requests
+    plan += [[(k, 47, [46])] for k in ("d", "e", "f", "g")]
+    # a mixed shape again and again: a portion of 20 beside a portion of 3 and a single token
+    plan += [[("b", 20, [19]), ("c", 3, []), ("d2", 1, [0])] for _ in range(4)]
+    prompts["d2"] = torch.randint(0, raw["vocab_size"], (4,), generator=g).tolist()
+    results = {}
+    for graphs in (False, True):
+        engine = Engine(model_dir, dtype, max_requests=4, max_seq_len=128, num_pages=8, use_graphs=graphs, poison_on_free=True)
+        results[graphs] = run_steps(engine, plan, prompts)
+        engine.cache.check_integrity()
+        if graphs:
+            captured = {k for k, slot in engine._shape_graphs.items() if slot.graph is not None}
+            assert ((40,), 1) in captured and ((47,), 1) in captured and ((20, 3, 1), 2) in captured
+        del engine
+    # the same kernels; a replayed step may cut the keys of single tokens into other ranges than the step run
+    # kernel by kernel (it is planned for the longest context), which moves float32 sums by a rounding
+    tol = 1e-5 if dtype == "float32" else TOL[dtype]
+    for i, (a, b) in enumerate(zip(results[False], results[True])):
+        assert a.shape == b.shape, f"step {i}"
+        scale = float(a.abs().max()) or 1.0
+        assert float((a - b).abs().max()) <= tol * scale, f"step {i}: graph replay differs from the kernel-by-kernel run"
+
+
+def test_step_graphs_are_bounded_in_number_and_in_tokens(tmp_path):
+    from logssms_b200.engine import Engine, StepEntry
+    raw = TINY["A"]
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=42)
+    engine = Engine(model_dir, "float32", max_requests=2, max_seq_len=128, num_pages=4, max_shape_graphs=2, max_graph_tokens=16)
+    for n in (10, 11, 12, 20):
+        for _ in range(3):
+            r = engine.new_request()
+            engine.step([StepEntry(r, list(range(n)), [n - 1])])
+            engine.release(r)
+    assert len(engine._shape_graphs) == 2 and all(k[0][0] <= 16 for k in engine._shape_graphs)
