@@ -64,7 +64,7 @@ def test_embed_gather_and_gather_rows(dtype):
 
 # --------------------------------------------------------------------------- norms
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H", [40, 1000, 3000])
+@pytest.mark.parametrize("H", [40, 100, 1000, 3000, 4104])
 @pytest.mark.parametrize("two_inputs", [False, True])
 def test_add_rmsnorm(dtype, H, two_inputs):
     g = torch.Generator().manual_seed(H)
