@@ -51,6 +51,17 @@ struct SkinnyArgs {
     const float* conv_w; const float* conv_b; __nv_bfloat16* conv_state;     // [C, Kc] float32, [C] or null, [slots, C, Kc-1]
     const int* conv_slots; const int* conv_start;                             // per row: state slot, tokens before this one
     int conv_c0, conv_c1, conv_k, conv_e0, conv_e1; float conv_s0, conv_s1, conv_s2;
+    // optional: the product joins the residual stream in its epilogue (plain epilogue, j_vsum given).  With y the
+    // bfloat16 output the unfused chain would store,
+    //   v = [round(round(y * j_in0) + round(j_other * j_in1))  or  y] + j_res          (float32)
+    //   j_vsum = v ; j_res_out = round(v) ; j_partial[this CTA][row] = sum of v^2 over the CTA's 16 features
+    // which is everything the next RMSNorm needs (python/logssms/kernel/norm.py:16-35): a consumer in mode
+    // NORM == 2 takes s_vsum = j_vsum and the s_nparts partial sums per row, finds each row's factor with
+    // s_nparts / 4 loads per thread, and norms its own columns where it loads them - no pass over whole rows and
+    // no barrier before its main loop, with the rounding points of the norm kernel.
+    const __nv_bfloat16* j_other; const __nv_bfloat16* j_res; float j_in0, j_in1;
+    float* j_vsum; __nv_bfloat16* j_res_out; float* j_partial;
+    const float* s_vsum; const float* s_partial; int s_nparts;
 };
 
 __device__ __forceinline__ uint4 load_stream(const void* p) {
@@ -70,8 +81,9 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 enum Epilogue : int { kPlain = 0, kOutF32 = 1, kSwiglu = 2 };
 
 // MT: tiles of 8 batch rows.  HALVES: 1, or 2 for swiglu (gate and up rows of the same feature).
-// NORM: x is produced in shared memory by the fused residual-add + RMSNorm prologue (K <= 2048, M <= 16).
-template <int MT, int EPI, bool NORM>
+// NORM 1: x is produced in shared memory by the fused residual-add + RMSNorm prologue (K <= 2048, M <= 16).
+// NORM 2: x is the RMSNorm of rows already summed by the product before (see SkinnyArgs), made where it is loaded.
+template <int MT, int EPI, int NORM>
 __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     constexpr int HALVES = EPI == kSwiglu ? 2 : 1;
     constexpr int MP = MT * 8 + 1;
@@ -98,7 +110,7 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     const __nv_bfloat16* xrow[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
-        xrow[m] = NORM ? xs + (size_t)(m * 8 + g) * ldxs : a.x + (size_t)min(m * 8 + g, a.M - 1) * a.ldx;
+        xrow[m] = NORM == 1 ? xs + (size_t)(m * 8 + g) * ldxs : (NORM == 2 ? nullptr : a.x + (size_t)min(m * 8 + g, a.M - 1) * a.ldx);
 
     float acc[HALVES][MT][4];
 #pragma unroll
@@ -127,7 +139,7 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     // that kernel still runs; x (its output) is touched only after the wait.
     load_w(c_begin);
     pdl_wait();
-    if (NORM) {
+    if (NORM == 1) {
         // one warp per row; a lane keeps its 8-element pieces of the row in registers between the two passes
         constexpr int kMaxPieces = 8;                     // K <= 32 lanes * 8 pieces * 8 elements = 2048
         const int pieces = K / 8;
@@ -192,6 +204,50 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
         }
         __syncthreads();
     }
+    // a joining product: the values of the residual and of the other branch that this thread's outputs meet in the
+    // epilogue are fetched now, under the weight stream (thread i of the epilogue loop owns row i / 16, feature i % 16)
+    constexpr int kJoinPer = (MT * 8 * kFeat + kThreads - 1) / kThreads;
+    float j_res_v[kJoinPer], j_other_v[kJoinPer];
+    if (EPI == kPlain && a.j_vsum != nullptr) {
+#pragma unroll
+        for (int q = 0; q < kJoinPer; ++q) {
+            const int i = threadIdx.x + q * kThreads, m = i / kFeat, n = n0 + i % kFeat;
+            const bool in = m < a.M && n < a.N;
+            j_res_v[q] = (in && a.j_res != nullptr) ? __bfloat162float(a.j_res[(size_t)m * a.N + n]) : 0.f;
+            j_other_v[q] = (in && a.j_other != nullptr) ? __bfloat162float(a.j_other[(size_t)m * a.N + n]) : 0.f;
+        }
+    }
+    float inv_row[MT];
+    if (NORM == 2) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const int row = min(m * 8 + g, a.M - 1);
+            float ss = 0.f;
+            for (int p = t; p < a.s_nparts; p += 4) ss += __ldg(a.s_partial + (size_t)p * a.M + row);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            inv_row[m] = rsqrtf(ss / (float)K + a.neps);
+        }
+    }
+    auto summed = [&](int m, int k) -> uint4 {
+        const int row = m * 8 + g;
+        if (row >= a.M) return zero;
+        const float4* vp = reinterpret_cast<const float4*>(a.s_vsum + (size_t)row * K + k);
+        const float4 v0 = __ldg(vp), v1 = __ldg(vp + 1);
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.nweight + k));
+        const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.nweight + k) + 1);
+        const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const float gw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        uint4 outv;
+        __nv_bfloat162* out2 = reinterpret_cast<__nv_bfloat162*>(&outv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float n0 = round_to<__nv_bfloat16>(v[2 * e] * inv_row[m] * gw[2 * e]);
+            const float n1 = round_to<__nv_bfloat16>(v[2 * e + 1] * inv_row[m] * gw[2 * e + 1]);
+            out2[e] = __floats2bfloat162_rn(n0 * a.nscale, n1 * a.nscale);
+        }
+        return outv;
+    };
     for (int c0 = c_begin; c0 < c_end; c0 += kUnroll) {
         if (c0 != c_begin) load_w(c0);
 #pragma unroll
@@ -200,8 +256,8 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
             const bool ok = (c0 + u) < c_end && k < K;
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-                const uint4 xv = ok ? (NORM ? *reinterpret_cast<const uint4*>(xrow[m] + k)
-                                            : __ldg(reinterpret_cast<const uint4*>(xrow[m] + k))) : zero;
+                const uint4 xv = !ok ? zero : (NORM == 2 ? summed(m, k) : (NORM == 1 ? *reinterpret_cast<const uint4*>(xrow[m] + k)
+                                                                                       : __ldg(reinterpret_cast<const uint4*>(xrow[m] + k))));
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
                     mma_bf16(acc[h][m], wv[u][h][0].x, wv[u][h][1].x, wv[u][h][0].y, wv[u][h][1].y, xv.x, xv.y);
@@ -222,10 +278,16 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) red[warp][h][g + 8 * (e >> 1)][m * 8 + 2 * t + (e & 1)] = acc[h][m][e];
     __syncthreads();
-    for (int i = threadIdx.x; i < a.M * kFeat; i += kThreads) {
+    const bool joins = EPI == kPlain && a.j_vsum != nullptr;      // then N is a multiple of 16 (the launcher checks)
+    const int bound = joins ? (a.M * kFeat + 31) / 32 * 32 : a.M * kFeat;
+#pragma unroll
+    for (int q = 0; q < kJoinPer; ++q) {
+        const int i = threadIdx.x + q * kThreads;
+        if (i >= bound) break;
         const int m = i / kFeat, f = i % kFeat;
         const int n = n0 + f;
-        if (n >= a.N) continue;
+        float joined_sq = 0.f;
+        if (m < a.M && n < a.N) {
         float s[HALVES];
 #pragma unroll
         for (int h = 0; h < HALVES; ++h) {
@@ -262,13 +324,31 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
                 v = round_to<__nv_bfloat16>(silu_f(acc2));
             }
             if (EPI == kOutF32) ((float*)a.out)[(size_t)m * a.ldo + n] = v * a.out_scale;
-            else ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n] =
+            else if (!joins) ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n] =
                 a.out_scale == 1.f ? __float2bfloat16_rn(v) : __float2bfloat16_rn(v * a.out_scale);
+            else {
+                float y = a.out_scale == 1.f ? v : round_to<__nv_bfloat16>(v * a.out_scale);
+                const size_t at = (size_t)m * a.N + n;
+                if (a.j_other != nullptr)
+                    y = round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(y * a.j_in0) + round_to<__nv_bfloat16>(j_other_v[q] * a.j_in1));
+                if (a.j_res != nullptr) y += j_res_v[q];
+                a.j_vsum[at] = y;
+                a.j_res_out[at] = __float2bfloat16_rn(y);
+                joined_sq = y * y;
+            }
+        }
+        }
+        if (joins) {                                              // 16 consecutive lanes hold one row's 16 features
+            joined_sq += __shfl_xor_sync(0xffffffffu, joined_sq, 8);
+            joined_sq += __shfl_xor_sync(0xffffffffu, joined_sq, 4);
+            joined_sq += __shfl_xor_sync(0xffffffffu, joined_sq, 2);
+            joined_sq += __shfl_xor_sync(0xffffffffu, joined_sq, 1);
+            if (f == 0 && m < a.M) a.j_partial[(size_t)blockIdx.x * a.M + m] = joined_sq;
         }
     }
 }
 
-template <int EPI, bool NORM>
+template <int EPI, int NORM>
 int launch_mt(const SkinnyArgs& a, cudaStream_t s) {
     const dim3 grid((a.N + kFeat - 1) / kFeat);
     const int mt = (a.M + 7) / 8;
@@ -276,7 +356,7 @@ int launch_mt(const SkinnyArgs& a, cudaStream_t s) {
 #define LB_SKINNY(MT)                                                                                       \
     {                                                                                                       \
         size_t smem = sizeof(float) * ((kWarps * halves * kFeat * (MT * 8 + 1) + 3) / 4 * 4);               \
-        if (NORM) smem += (size_t)MT * 8 * (a.K + 8) * sizeof(__nv_bfloat16);                               \
+        if (NORM == 1) smem += (size_t)MT * 8 * (a.K + 8) * sizeof(__nv_bfloat16);                          \
         if (smem > 48 * 1024)                                                                               \
             cudaFuncSetAttribute(skinny_linear_kernel<MT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         rc = launch_pdl_if(a.M <= pdl_max_rows(), skinny_linear_kernel<MT, EPI, NORM>, grid, dim3(kThreads), smem, s, a); \
@@ -284,14 +364,14 @@ int launch_mt(const SkinnyArgs& a, cudaStream_t s) {
     int rc = 0;
     if (mt <= 1) LB_SKINNY(1)
     else if (mt <= 2) LB_SKINNY(2)
-    else if (NORM) return kTooLarge;
+    else if constexpr (NORM != 0) return kTooLarge;
     else if (mt <= 4) LB_SKINNY(4)
     else LB_SKINNY(8)
 #undef LB_SKINNY
     return rc != 0 ? rc : launch_status();
 }
 
-template <bool NORM>
+template <int NORM>
 int launch_epi(const SkinnyArgs& a, int epilogue, cudaStream_t s) {
     switch (epilogue) {
         case kPlain: return launch_mt<kPlain, NORM>(a, s);
@@ -314,7 +394,7 @@ extern "C" int lb_linear_skinny(const void* x, long ldx, const void* w, const vo
     SkinnyArgs a{(const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, out, ldo,
                  M, N, K, out_scale, act_scale, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, 1.f, 1.f, 1.f,
                  nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 1.f, 1.f, 1.f};
-    return launch_epi<false>(a, epilogue, (cudaStream_t)stream);
+    return launch_epi<0>(a, epilogue, (cudaStream_t)stream);
 }
 
 // The same product with x made on the fly: x = round(rmsnorm(v; norm_weight, eps) * norm_scale) with
@@ -334,7 +414,7 @@ extern "C" int lb_linear_skinny_normed(const void* nx, const void* nother, const
                  (const __nv_bfloat16*)nx, (const __nv_bfloat16*)nother, (const __nv_bfloat16*)nres, (__nv_bfloat16*)res_out,
                  norm_weight, eps, in0, in1, norm_scale,
                  nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 1.f, 1.f, 1.f};
-    return launch_epi<true>(a, epilogue, (cudaStream_t)stream);
+    return launch_epi<1>(a, epilogue, (cudaStream_t)stream);
 }
 
 // The plain product (x given, or made by the norm prologue when `nx` is not null) with the conv step of a
@@ -358,5 +438,51 @@ extern "C" int lb_linear_skinny_conv(const void* x, long ldx, const void* nx, co
                  (const __nv_bfloat16*)nx, (const __nv_bfloat16*)nother, (const __nv_bfloat16*)nres, (__nv_bfloat16*)res_out,
                  norm_weight, eps, in0, in1, norm_scale,
                  conv_w, conv_b, (__nv_bfloat16*)conv_state, slots, start, c0, c1, taps, e0, e1, s0, s1, s2};
-    return normed ? launch_epi<true>(a, kPlain, (cudaStream_t)stream) : launch_epi<false>(a, kPlain, (cudaStream_t)stream);
+    return normed ? launch_epi<1>(a, kPlain, (cudaStream_t)stream) : launch_epi<0>(a, kPlain, (cudaStream_t)stream);
+}
+
+// The plain product whose epilogue joins the residual stream (see SkinnyArgs): instead of its bfloat16 output y it
+// leaves v = [round(round(y * in0) + round(other * in1)) or y] + res as float32 in vsum [M, N], round(v) in res_out
+// [M, N] and per CTA and row the sum of v^2 over its 16 features in partial [N / 16, M].  other, res: contiguous
+// [M, N] bfloat16 or null; N a multiple of 16; M <= 64.
+extern "C" int lb_linear_skinny_join(const void* x, long ldx, const void* w, const void* bias, int M, int N, int K,
+                                     float out_scale, const void* other, const void* res, float in0, float in1,
+                                     float* vsum, void* res_out, float* partial, void* stream) {
+    if (M <= 0 || N <= 0) return kOk;
+    if (K <= 0 || K % 8 || ldx % 8 || N % kFeat || vsum == nullptr || res_out == nullptr || partial == nullptr) return kBadSize;
+    if (M > 64) return kTooLarge;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return kBadSize;
+    SkinnyArgs a{};
+    a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.w = (const __nv_bfloat16*)w; a.bias = (const __nv_bfloat16*)bias;
+    a.out = nullptr; a.ldo = N; a.M = M; a.N = N; a.K = K; a.out_scale = out_scale; a.act_scale = 1.f;
+    a.j_other = (const __nv_bfloat16*)other; a.j_res = (const __nv_bfloat16*)res; a.j_in0 = in0; a.j_in1 = in1;
+    a.j_vsum = vsum; a.j_res_out = (__nv_bfloat16*)res_out; a.j_partial = partial;
+    return launch_epi<0>(a, kPlain, (cudaStream_t)stream);
+}
+
+// A product (any epilogue; with conv_w given, the conv step on the features [c0, c1) as in lb_linear_skinny_conv)
+// whose x is the RMSNorm of rows that lb_linear_skinny_join left: x = round(round(v * rsqrt(mean(v^2) + eps) *
+// norm_weight) * norm_scale), v = vsum [M, K] float32, mean(v^2) from the nparts partial sums per row.  M <= 16.
+extern "C" int lb_linear_skinny_summed(const float* vsum, const float* partial, int nparts, const float* norm_weight,
+                                       float eps, float norm_scale, const void* w, const void* bias, void* out, long ldo,
+                                       int M, int N, int K, float out_scale, float act_scale, int epilogue,
+                                       const float* conv_w, const float* conv_b, void* conv_state, const int* slots,
+                                       const int* start, int c0, int c1, int taps, int e0, int e1, float s0, float s1,
+                                       float s2, void* stream) {
+    if (M <= 0 || N <= 0) return kOk;
+    if (K <= 0 || K % 8 || nparts <= 0 || vsum == nullptr || partial == nullptr || norm_weight == nullptr) return kBadSize;
+    if (M > 16) return kTooLarge;
+    if (((uintptr_t)vsum | (uintptr_t)w | (uintptr_t)norm_weight) & 15) return kBadSize;
+    if (conv_w != nullptr && (epilogue != kPlain || taps < 2 || taps > 8 || c0 < 0 || c1 > N || c0 > c1)) return kBadSize;
+    SkinnyArgs a{};
+    a.w = (const __nv_bfloat16*)w; a.bias = (const __nv_bfloat16*)bias; a.out = out; a.ldo = ldo;
+    a.M = M; a.N = N; a.K = K; a.out_scale = out_scale; a.act_scale = act_scale;
+    a.nweight = norm_weight; a.neps = eps; a.nin0 = 1.f; a.nin1 = 1.f; a.nscale = norm_scale;
+    a.s_vsum = vsum; a.s_partial = partial; a.s_nparts = nparts;
+    if (conv_w != nullptr) {
+        a.conv_w = conv_w; a.conv_b = conv_b; a.conv_state = (__nv_bfloat16*)conv_state; a.conv_slots = slots; a.conv_start = start;
+        a.conv_c0 = c0; a.conv_c1 = c1; a.conv_k = taps; a.conv_e0 = e0; a.conv_e1 = e1;
+        a.conv_s0 = s0; a.conv_s1 = s1; a.conv_s2 = s2;
+    }
+    return launch_epi<2>(a, epilogue, (cudaStream_t)stream);
 }

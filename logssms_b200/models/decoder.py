@@ -73,8 +73,13 @@ class DecoderModel(Part):
         """Residual stream after all scheduled layers, as the pair (x, residual) whose sum it is."""
         x = self.embedding.forward(ctx.token_ids)
         residual = None
-        for e in self.schedule:
+        for i, e in enumerate(self.schedule):
+            # a block may hand its output on already joined with the residual (`SummedRows`) where the norm that
+            # comes next takes it: the next block's first norm (the rows before the head are gathered first)
+            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+            ctx.extras["next_norm_takes_summed"] = getattr(getattr(nxt, "mixer_norm", None), "takes_summed_rows", False)
             x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
+        ctx.extras.pop("next_norm_takes_summed", None)
         return x, residual
 
     def logits(self, x: torch.Tensor, residual, rows: torch.Tensor) -> torch.Tensor:

@@ -557,6 +557,75 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
+class ResidualJoin:
+    """A request to a part: let your last product join the residual stream in its epilogue, i.e. leave
+    v = [round(round(y * in_scales[0]) + round(other * in_scales[1])) or y] + residual instead of its output y.
+    `other` may be a callable that returns the tensor (and first waits for whatever produces it)."""
+    __slots__ = ("residual", "other", "in_scales")
+
+    def __init__(self, residual, other=None, in_scales=(1.0, 1.0)):
+        self.residual, self.other, self.in_scales = residual, other, in_scales
+
+    def other_tensor(self):
+        return self.other() if callable(self.other) else self.other
+
+
+class SummedRows:
+    """What a product with a residual join leaves (`linear_join`): the float32 sums `vsum` [M, N], their rounded
+    copy `residual` (the new residual), and `partial` [N / 16, M], the sums of squares over blocks of 16 columns:
+    everything the next RMSNorm needs, so that its consumers can norm their own columns where they load them."""
+    __slots__ = ("vsum", "residual", "partial")
+
+    def __init__(self, vsum, residual, partial):
+        self.vsum, self.residual, self.partial = vsum, residual, partial
+
+    @property
+    def shape(self):
+        return self.vsum.shape
+
+    @property
+    def dtype(self):
+        return self.residual.dtype
+
+
+def linear_join_ok(x, w: torch.Tensor, bias, join: ResidualJoin | None) -> bool:
+    """Can `linear_join` take this product?  Few bfloat16 rows (the consumers norm at most 16), whole blocks of 16
+    output columns, a residual of the output's shape."""
+    if join is None or isinstance(x, NormedRows) or not _skinny_ok(x, w, bias, 16) or w.shape[0] % 16:
+        return False
+    r = join.residual
+    return r is None or (r.dtype == torch.bfloat16 and r.shape == (x.shape[0], w.shape[0]) and r.is_contiguous())
+
+
+def linear_join(x: torch.Tensor, w: torch.Tensor, bias, join: ResidualJoin, *, out_scale: float = 1.0) -> SummedRows:
+    """x @ w^T (+ bias, * out_scale) whose epilogue joins the residual stream: see `ResidualJoin`, `SummedRows`."""
+    _need(linear_join_ok(x, w, bias, join), "linear_join takes at most 16 bfloat16 rows and N a multiple of 16")
+    M, Kdim = x.shape
+    N = w.shape[0]
+    other = join.other_tensor()
+    _need(other is None or (other.dtype == torch.bfloat16 and other.shape == (M, N) and other.is_contiguous()),
+          "the other branch must be contiguous bfloat16 [M, N]")
+    _cuda(x, w, bias, other, join.residual)
+    vsum = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    partial = torch.empty((N // 16, M), dtype=torch.float32, device=x.device)
+    res_out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    f = _fn("linear_skinny", "lb_linear_skinny_join",
+            [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_float, c_float,
+             c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(bias), M, N, Kdim, out_scale, _ptr(other), _ptr(join.residual),
+             join.in_scales[0], join.in_scales[1], _ptr(vsum), _ptr(res_out), _ptr(partial), _stream()), "linear_skinny_join")
+    return SummedRows(vsum, res_out, partial)
+
+
+def summed_rmsnorm(rows: SummedRows, weight: torch.Tensor, eps: float, out_scales) -> tuple:
+    """The RMSNorm of summed rows with plain tensor operations: only for a consumer that cannot norm them itself
+    (the built-in ones can), same rounding points as the norm kernel."""
+    v = rows.vsum
+    inv = torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+    n = (v * inv * weight).to(rows.residual.dtype).float()
+    return tuple((n * s).to(rows.residual.dtype) for s in out_scales)
+
+
 class NormedRows:
     """Rows that are still to be normalised: what `add_rmsnorm` would compute, handed to the product that
     consumes them so that the few-row kernel can do the norm in its prologue (a decode step is bound by the
@@ -565,9 +634,14 @@ class NormedRows:
     __slots__ = ("x", "other", "residual", "weight", "eps", "in_scales", "scale", "shared", "_tensor")
 
     def __init__(self, x, other, residual, weight, eps, in_scales, scale, shared):
+        # x may be `SummedRows` (the product before has joined the residual already): other and residual are None then
         self.x, self.other, self.residual, self.weight, self.eps = x, other, residual, weight, eps
         self.in_scales, self.scale, self.shared = in_scales, scale, shared
         self._tensor = None
+
+    @property
+    def summed(self) -> bool:
+        return isinstance(self.x, SummedRows)
 
     @property
     def shape(self):
@@ -578,6 +652,8 @@ class NormedRows:
         return self.x.dtype
 
     def tensor(self) -> torch.Tensor:
+        if self._tensor is None and self.summed:
+            (self._tensor,) = summed_rmsnorm(self.x, self.weight, self.eps, (self.scale,))
         if self._tensor is None:
             write = self.shared["residual_out"] is not None and not self.shared["written"]
             (self._tensor,), res = add_rmsnorm(self.x, self.weight, self.eps, self.residual, other=self.other,
@@ -588,8 +664,10 @@ class NormedRows:
         return self._tensor
 
 
-def deferred_norm_ok(x: torch.Tensor) -> bool:
+def deferred_norm_ok(x) -> bool:
     """Can a norm over these rows ride in the prologue of the products that consume it?"""
+    if isinstance(x, SummedRows):
+        return 0 < x.shape[0] <= 16 and x.shape[1] % 8 == 0
     return (x.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= 16 and x.shape[1] % 8 == 0
             and x.shape[1] <= 2048 and x.is_contiguous())
 
@@ -604,6 +682,12 @@ def _skinny_normed(nr: NormedRows, w: torch.Tensor, bias, out_scale: float, out_
     elif out_f32:
         mode = _OUT_F32
     out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=w.device)
+    if nr.summed:
+        _check(_summed_fn()(_ptr(nr.x.vsum), _ptr(nr.x.partial), nr.x.partial.shape[0], _ptr(nr.weight), nr.eps, nr.scale,
+                            _ptr(w), _ptr(bias), _ptr(out), N, M, N, Kdim, out_scale,
+                            swiglu_scale if swiglu_scale is not None else 1.0, mode,
+                            None, None, None, None, None, 0, 0, 0, 0, 0, 1.0, 1.0, 1.0, _stream()), "linear_skinny_summed")
+        return out
     write = nr.shared["residual_out"] is not None and not nr.shared["written"]
     f = _fn("linear_skinny", "lb_linear_skinny_normed",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_float, c_void_p, c_void_p,
@@ -614,6 +698,13 @@ def _skinny_normed(nr: NormedRows, w: torch.Tensor, bias, out_scale: float, out_
     if write:
         nr.shared["written"] = True
     return out
+
+
+def _summed_fn():
+    return _fn("linear_skinny", "lb_linear_skinny_summed",
+               [c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int,
+                c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                c_float, c_float, c_float, c_void_p])
 
 
 SKINNY_MAX_ROWS = 64       # at or below this many rows a bfloat16 product goes to the weight-streaming kernel
@@ -743,6 +834,13 @@ def linear_conv_step(x, w: torch.Tensor, bias, conv_weight: torch.Tensor, conv_b
     N = w.shape[0]
     _need(slots.numel() >= M and start_pos.numel() >= M and 0 <= first <= last <= N, "one slot and start per row; columns within the output")
     out = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)
+    if normed and x.summed:
+        _check(_summed_fn()(_ptr(x.x.vsum), _ptr(x.x.partial), x.x.partial.shape[0], _ptr(x.weight), x.eps, x.scale,
+                            _ptr(w), _ptr(bias), _ptr(out), N, M, N, Kdim, 1.0, 1.0, _PLAIN,
+                            _ptr(conv_weight), _ptr(conv_bias), _ptr(conv_state), _ptr(slots), _ptr(start_pos), first, last, taps,
+                            region_ends[0], region_ends[1], region_scales[0], region_scales[1], region_scales[2], _stream()),
+               "linear_conv_step")
+        return out
     write = normed and x.shared["residual_out"] is not None and not x.shared["written"]
     f = _fn("linear_skinny", "lb_linear_skinny_conv",
             [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_float, c_void_p,

@@ -19,6 +19,7 @@ class Attention(Part):
     bind time, as the reference merges them at load (python/logssms/models/weight.py:27-31);
     the flow is python/logssms/layers/attention.py:115-167."""
     takes_normed_rows = True      # forward() passes its input straight into a product
+    joins_residual = True         # forward() takes `join=`: its last product may add the residual in its epilogue
     kernels = ("rope", "attention_decode", "attention_decode_fused", "attention_prefill", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
@@ -57,7 +58,7 @@ class Attention(Part):
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(kv=KVNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window))
 
-    def forward(self, x: torch.Tensor, ctx, cache_layer: int, writes_cache: bool = True) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, cache_layer: int, writes_cache: bool = True, join=None):
         s = self.spec
         T = x.shape[0]
         qkv = K.linear(x, self.qkv_weight)
@@ -69,7 +70,11 @@ class Attention(Part):
                                         ctx.slot_mappings[group], self.position.table, k_cache, v_cache,
                                         ctx.block_tables[group], ctx.token_req, self.scale, s.key_scale, s.window or 0,
                                         writes_cache, splits=splits)
-            return K.linear(o.view(T, self.q_size), self.o_weight)
+            o = o.view(T, self.q_size)
+            if K.linear_join_ok(o, self.o_weight, None, join):
+                # the output projection adds the other mixer's output and the residual in its epilogue
+                return K.linear_join(o, self.o_weight, None, join)
+            return K.linear(o, self.o_weight)
         q = K.rope_kv_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions, ctx.slot_mappings[group],
                             self.position.table, k_cache, v_cache, s.key_scale, writes_cache)
         tables = ctx.block_tables[group]

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import kernels as K
 from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from .base import Part
 
@@ -64,9 +65,22 @@ class PreNormParallelBlock(Part):
         defer_ff = {"defer": True} if (getattr(self.ff_norm, "can_defer", False)
                                        and getattr(self.feed_forward, "takes_normed_rows", False)) else {}
         ins, residual = self.mixer_norm.forward(x, residual, out_scales=tuple(m.in_scale for m in slots), **defer_mix)
+        # Where the norm in front of the feed-forward is deferred anyway, the first mixer's last product may join the
+        # residual stream in its epilogue (`joins_residual`): it then returns `SummedRows`, the norm has nothing left to
+        # read but those, and the feed-forward's product norms its own columns without a pass over whole rows.
+        join_mix = bool(defer_ff) and getattr(self.mixers[0], "joins_residual", False) \
+            and getattr(self.ff_norm, "takes_summed_rows", False) and isinstance(ins[0], K.NormedRows) \
+            and (len(slots) == 2 or slots[0].out_scale == 1.0)
+        in_scales = (slots[0].out_scale, slots[1].out_scale) if len(slots) == 2 else (slots[0].out_scale, 1.0)
         side = ctx.extras.get("side_stream") if len(self.mixers) == 2 else None
         if side is None:
-            outs = [mixer.forward(inp, ctx, cache_layer, writes_cache) for mixer, inp in zip(self.mixers, ins)]
+            if join_mix:
+                rest = [mixer.forward(inp, ctx, cache_layer, writes_cache) for mixer, inp in zip(self.mixers[1:], ins[1:])]
+                first = self.mixers[0].forward(ins[0], ctx, cache_layer, writes_cache,
+                                               join=K.ResidualJoin(residual, rest[0] if rest else None, in_scales))
+                outs = [first, *rest]
+            else:
+                outs = [mixer.forward(inp, ctx, cache_layer, writes_cache) for mixer, inp in zip(self.mixers, ins)]
         else:
             # Inside a graph capture the two mixers go to two streams, so that the graph may run their
             # kernels side by side (each alone leaves most of the 148 SMs idle at small batch).
@@ -78,15 +92,30 @@ class PreNormParallelBlock(Part):
                 second = self.mixers[1].forward(ins[1], ctx, cache_layer, writes_cache)
                 join = torch.cuda.Event()
                 join.record(side)
-            first = self.mixers[0].forward(ins[0], ctx, cache_layer, writes_cache)
-            main.wait_event(join)
+            if join_mix:
+                def other_branch():
+                    main.wait_event(join)                     # called by the first mixer right before its last product
+                    return second
+                first = self.mixers[0].forward(ins[0], ctx, cache_layer, writes_cache,
+                                               join=K.ResidualJoin(residual, other_branch, in_scales))
+                if not isinstance(first, K.SummedRows):
+                    main.wait_event(join)
+            else:
+                first = self.mixers[0].forward(ins[0], ctx, cache_layer, writes_cache)
+                main.wait_event(join)
             outs = [first, second]
-        if len(outs) == 2:
+        next_join = bool(ctx.extras.get("next_norm_takes_summed")) and getattr(self.feed_forward, "joins_residual", False)
+        if isinstance(outs[0], K.SummedRows):
+            (h,), residual = self.ff_norm.forward(outs[0], None, **defer_ff)
+        elif len(outs) == 2:
             (h,), residual = self.ff_norm.forward(outs[0], residual, other=outs[1],
                                                   in_scales=(slots[0].out_scale, slots[1].out_scale), **defer_ff)
         else:
             if slots[0].out_scale != 1.0:
-                from ..ops import kernels as K
                 outs[0] = K.scale(outs[0], slots[0].out_scale)
             (h,), residual = self.ff_norm.forward(outs[0], residual, **defer_ff)
+        if next_join and isinstance(h, K.NormedRows):
+            # the same at the feed-forward's last product, for the norm of the next layer
+            out = self.feed_forward.forward(h, join=K.ResidualJoin(residual))
+            return (out, None) if isinstance(out, K.SummedRows) else (out, residual)
         return self.feed_forward.forward(h), residual

@@ -13,6 +13,7 @@ class GatedMLP(Part):
     """down(silu(gate * s0) * up) * s1.  `gate_proj` and `up_proj` are concatenated at bind time
     (python/logssms/models/weight.py:32-33); flow python/logssms/layers/mlp.py:50-61."""
     takes_normed_rows = True      # forward() passes its input straight into a product
+    joins_residual = True         # forward() takes `join=`: its last product may add the residual in its epilogue
     kernels = ("norm", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
@@ -34,7 +35,11 @@ class GatedMLP(Part):
     def setup(self, rt) -> None:
         pass
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, join=None):
+        """With `join` (a `K.ResidualJoin`) and few rows the down projection adds the residual in its epilogue and
+        `K.SummedRows` come back instead of a tensor."""
         s = self.spec
         h = K.linear_swiglu(x, self.gate_up, s.activation_scale)
+        if K.linear_join_ok(h, self.down, None, join):
+            return K.linear_join(h, self.down, None, join, out_scale=s.output_scale)
         return K.linear(h, self.down, out_scale=s.output_scale)

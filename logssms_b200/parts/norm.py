@@ -15,6 +15,7 @@ class RMSNorm(Part):
     (python/logssms/layers/norm.py:56-97, python/logssms/kernel/norm.py:8-52.)"""
     kernels = ("norm", "linear_skinny")
     can_defer = True          # forward() takes `defer=`: see there
+    takes_summed_rows = True  # forward() takes `K.SummedRows` as x: the product before has joined the residual already
 
     def __init__(self, spec, perturb_init: bool = False):
         self.size, self.eps = spec.size, spec.eps
@@ -29,6 +30,14 @@ class RMSNorm(Part):
         """With `defer` (the caller's consumers all take `NormedRows`: their first step is a product), and
         few enough rows, nothing is launched here: the outputs are `NormedRows` that the consumers' products
         normalise in their prologue, and the new residual is a fresh tensor that the first of them writes."""
+        if isinstance(x, K.SummedRows):
+            # x is already the residual sum (float32), with its rounded copy and the rows' sums of squares
+            if residual is not None or other is not None:
+                raise ValueError("summed rows have joined their residual already")
+            if defer and K.deferred_norm_ok(x):
+                shared = {"residual_out": None, "written": True}
+                return tuple(K.NormedRows(x, None, None, self.weight, self.eps, (1.0, 1.0), s, shared) for s in out_scales), x.residual
+            return K.summed_rmsnorm(x, self.weight, self.eps, out_scales), x.residual
         if defer and K.deferred_norm_ok(x):
             shared = {"residual_out": torch.empty_like(x) if want_residual else None, "written": False}
             outs = tuple(K.NormedRows(x, other, residual, self.weight, self.eps, in_scales, s, shared) for s in out_scales)

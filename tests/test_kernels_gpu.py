@@ -609,6 +609,68 @@ def test_linear_skinny_with_the_norm_in_its_prologue(M, N, Kd, two_inputs):
     close(n1.tensor(), a1, torch.bfloat16, tol=1e-6)
 
 
+@pytest.mark.parametrize("M", [1, 8, 13, 16])
+@pytest.mark.parametrize("N,Kd", [(16, 64), (1024, 512), (1008, 2048)])
+@pytest.mark.parametrize("two_inputs", [False, True])
+def test_linear_join_leaves_summed_rows_that_later_products_norm_themselves(M, N, Kd, two_inputs):
+    """A product that joins the residual stream in its epilogue, then products that take the summed rows and norm
+    their own columns, against product -> norm kernel -> product."""
+    g = torch.Generator().manual_seed(M * 11 + N)
+    k = K()
+    x = randn(g, M, Kd, dtype=torch.bfloat16).cuda()
+    w = randn(g, N, Kd, dtype=torch.bfloat16, scale=0.05).cuda()
+    b = randn(g, N, dtype=torch.bfloat16).cuda()
+    other, res = (randn(g, M, N, dtype=torch.bfloat16).cuda() for _ in range(2))
+    nw = (1 + 0.1 * torch.randn(N, generator=g)).cuda()
+    N2 = 48
+    w2 = randn(g, N2, N, dtype=torch.bfloat16, scale=0.05).cuda()
+    w3 = randn(g, 2 * N2, N, dtype=torch.bfloat16, scale=0.05).cuda()
+    b2 = randn(g, N2, dtype=torch.bfloat16).cuda()
+    oth = other if two_inputs else None
+    join = k.ResidualJoin(res, (lambda: oth) if two_inputs else None, (0.8, 0.7))
+    assert k.linear_join_ok(x, w, b, join)
+    rows = k.linear_join(x, w, b, join, out_scale=1.1)
+    y = k.linear_skinny(x, w, b, out_scale=1.1)
+    if not two_inputs:            # a lone input is not scaled by the norm kernel either
+        (n0, n1), want_res = k.add_rmsnorm(y, nw, 1e-5, res, out_scales=(1.5, 1.2), in_place=False)
+    else:
+        (n0, n1), want_res = k.add_rmsnorm(y, nw, 1e-5, res, other=oth, in_scales=(0.8, 0.7), out_scales=(1.5, 1.2), in_place=False)
+    assert torch.equal(rows.residual, want_res)
+    assert torch.equal(rows.vsum.to(torch.bfloat16), want_res)
+    close(rows.partial.sum(0), (rows.vsum.double() ** 2).sum(-1), torch.float32, tol=1e-5)
+    shared = {"residual_out": None, "written": True}
+    a0 = k.NormedRows(rows, None, None, nw, 1e-5, (1.0, 1.0), 1.5, shared)
+    a1 = k.NormedRows(rows, None, None, nw, 1e-5, (1.0, 1.0), 1.2, shared)
+    assert k.deferred_norm_ok(rows)
+    # the rows' factors come from sums in another order than the norm kernel's: a value may round the other way
+    close(k.linear(a0, w2, b2, out_scale=0.7), k.linear_skinny(n0, w2, b2, out_scale=0.7), torch.bfloat16, tol=8e-3)
+    close(k.linear_swiglu(a1, w3, 0.9), k.linear_skinny(n1, w3, swiglu_scale=0.9), torch.bfloat16, tol=1e-2)
+    close(k.linear(a0, w2, out_scale=0.25, out_f32=True), k.linear_skinny(n0, w2, out_scale=0.25, out_f32=True), torch.bfloat16, tol=4e-3)
+    close(a1.tensor(), n1, torch.bfloat16, tol=4e-3)
+    # with the conv step in the epilogue of the consumer
+    taps, C, first = 4, 32, 8
+    cw, cb = randn(g, C, taps, scale=0.4).cuda(), randn(g, C, scale=0.1).cuda()
+    slots = torch.randperm(M + 2, generator=g)[:M].to(torch.int32).cuda()
+    start = torch.tensor([0 if i % 3 == 0 else 5 + i for i in range(M)], dtype=torch.int32).cuda()
+    state0 = randn(g, M + 2, C, taps - 1, dtype=torch.bfloat16).cuda()
+    st_a, st_b = state0.clone(), state0.clone()
+    got = k.linear_conv_step(a0, w2, b2, cw, cb, st_a, slots, start, first, first + C, (8, 20), (1.1, 0.9, 1.3))
+    want = k.linear_conv_step(n0, w2, b2, cw, cb, st_b, slots, start, first, first + C, (8, 20), (1.1, 0.9, 1.3))
+    close(got, want, torch.bfloat16, tol=8e-3)
+    close(st_a, st_b, torch.bfloat16, tol=8e-3)
+
+
+def test_linear_join_is_refused_where_it_does_not_fit():
+    k = K()
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
+    res = torch.zeros(4, 24, dtype=torch.bfloat16, device="cuda")
+    assert not k.linear_join_ok(x, torch.zeros(24, 64, dtype=torch.bfloat16, device="cuda"), None, k.ResidualJoin(res))      # 24 columns
+    x17 = torch.zeros(17, 64, dtype=torch.bfloat16, device="cuda")
+    assert not k.linear_join_ok(x17, torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda"), None,
+                                k.ResidualJoin(torch.zeros(17, 32, dtype=torch.bfloat16, device="cuda")))                  # 17 rows
+    assert not k.linear_join_ok(x, torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda"), None, None)
+
+
 @pytest.mark.parametrize("M", [1, 5, 16, 40])
 @pytest.mark.parametrize("taps", [2, 4])
 @pytest.mark.parametrize("normed", [False, True])
