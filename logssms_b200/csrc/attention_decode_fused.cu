@@ -360,8 +360,27 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+// Distributed shared memory: the address of one's own shared variable in the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ unsigned cluster_map(const void* p, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_cluster(unsigned addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+// every thread of every CTA of the cluster (a hardware barrier: the CTAs of a cluster run together)
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // HDT: head_dim / 16 rounded up to the instantiated size (4 or 8).
-template <int HDT, int NS>
+// CL: the key ranges of a token and key/value head are the CTAs of one thread-block cluster (2 to 8 of them): their
+// partial results meet through distributed shared memory and two cluster barriers instead of global memory, a
+// fence, an atomic counter and the loads of the last CTA - about 2 us off a kernel of 13.
+template <int HDT, int NS, bool CL>
 __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int hd = a.hd, ld = hd + 8;                    // row stride: an odd number of 16-byte pieces
@@ -370,6 +389,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     bf16* vn_s = kn_s + ld;                              // [ld]       the token's own value
     bf16* tiles = vn_s + ld;                             // [kWarps][NS stages][K, V][kKT][ld]
     float* mrg = reinterpret_cast<float*>(tiles);        // [kWarps][16][hd + 2], over the tiles once the keys are done
+    float* cta_part = mrg + kWarps * 16 * (hd + 2);      // [16][hd + 2]: the CTA's own partial result (cluster form)
     __shared__ int last_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;
     const size_t t = blockIdx.x;
@@ -382,9 +402,10 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     // a range is at least two tiles per warp: shorter ranges only add partial results to merge
     const int chunk = (max((n + a.splits - 1) / a.splits, 2 * kWarps * kKT) + kKT - 1) / kKT * kKT;
     const int used = (n + chunk - 1) / chunk;
-    if (split >= used) return;
-    const int begin = lo + split * chunk;
-    const int end = min(begin + chunk, pos + 1);
+    const bool idle = split >= used;                     // a range without keys
+    if (idle && (!CL || used == 1)) return;              // in a cluster it still meets the others at the barriers
+    const int begin = idle ? pos + 1 : lo + split * chunk;
+    const int end = idle ? pos + 1 : min(begin + chunk, pos + 1);
     const bool use_new = a.write_kv != 0;
     const bool owns_new = use_new && begin <= pos && pos < end;
     const int* bt = a.block_table + (size_t)a.token_req[t] * a.bt_stride;
@@ -585,6 +606,9 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
         const int h = h0 + g;
         if (used == 1) {
             ((bf16*)a.out)[(t * a.Hq + h) * hd + d] = __float2bfloat16_rn(osum / lsum);
+        } else if (CL) {
+            cta_part[g * stride + d] = osum;
+            if (d == 0) { cta_part[g * stride + hd] = mt; cta_part[g * stride + hd + 1] = lsum; }
         } else {
             const size_t slot = ((size_t)t * a.Hq + h) * a.splits + split;
             a.part_o[slot * hd + d] = osum;
@@ -592,6 +616,25 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
         }
     }
     if (used == 1) return;
+    if (CL) {
+        cluster_barrier();                                // every range's partial result stands in its CTA's shared memory
+        if (split == 0) {
+            for (int i = threadIdx.x; i < G * hd; i += kThreads) {
+                const int g = i / hd, d = i % hd;
+                float mt = -INFINITY;
+                for (int s2 = 0; s2 < used; ++s2) mt = fmaxf(mt, ld_cluster(cluster_map(cta_part + g * stride + hd, s2)));
+                float lsum = 0.f, osum = 0.f;
+                for (int s2 = 0; s2 < used; ++s2) {
+                    const float f = expf(ld_cluster(cluster_map(cta_part + g * stride + hd, s2)) - mt);
+                    lsum += ld_cluster(cluster_map(cta_part + g * stride + hd + 1, s2)) * f;
+                    osum += ld_cluster(cluster_map(cta_part + g * stride + d, s2)) * f;
+                }
+                ((bf16*)a.out)[(t * a.Hq + h0 + g) * hd + d] = __float2bfloat16_rn(osum / lsum);
+            }
+        }
+        cluster_barrier();                                // nobody leaves while its shared memory may still be read
+        return;
+    }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -622,9 +665,25 @@ int launch_mma(const FusedArgs& a, int tokens, cudaStream_t s) {
     const int ld = a.hd + 8;
     // the per-warp partial results (kWarps * 16 * (hd + 2) floats) lie over the tiles, which are larger
     const size_t smem = (size_t)(16 + 2 + kWarps * NS * 2 * kKT) * ld * sizeof(bf16);
+    static const bool clusters = [] { const char* e = getenv("LOGSSMS_B200_ATTN_CLUSTER"); return e == nullptr || e[0] != '0'; }();
+    if (clusters && a.splits >= 2 && a.splits <= 8) {
+        // the ranges of one (token, head) as one cluster along z
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(attn_decode_mma_kernel<HDT, NS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(tokens, a.Hkv, a.splits); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)a.splits;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        static const bool pdl = [] { const char* e = getenv("LOGSSMS_B200_PDL"); return e == nullptr || e[0] != '0'; }();
+        cfg.attrs = attr; cfg.numAttrs = (pdl && tokens <= pdl_max_rows()) ? 2 : 1;
+        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HDT, NS, true>, a);
+    }
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(attn_decode_mma_kernel<HDT, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_pdl_if(tokens <= pdl_max_rows(), attn_decode_mma_kernel<HDT, NS>, dim3(tokens, a.Hkv, a.splits), dim3(kThreads), smem, s, a);
+        cudaFuncSetAttribute(attn_decode_mma_kernel<HDT, NS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl_if(tokens <= pdl_max_rows(), attn_decode_mma_kernel<HDT, NS, false>, dim3(tokens, a.Hkv, a.splits), dim3(kThreads), smem, s, a);
 }
 
 template <typename T>

@@ -333,7 +333,10 @@ def decode_step_splits(num_tokens: int, num_heads: int, num_kv_heads: int, max_c
     G = num_heads // num_kv_heads
     tile = 8 if G >= 8 else (4 if G > 2 else G)
     items = max(1, num_tokens * num_kv_heads * (-(-G // tile)))
-    return max(1, min(_STEP_TARGET_CTAS // items, -(-max_context // 256), 256))
+    splits = max(1, min(_STEP_TARGET_CTAS // items, -(-max_context // 256), 256))
+    # up to 8 ranges are the CTAs of one cluster and merge through distributed shared memory (about 2 us off the
+    # kernel); with a dozen (token, head) items that many ranges fill the GPU, so more would only cost that path
+    return min(splits, 8) if items >= 12 else splits
 
 
 _STEP_TARGET_CTAS = 296         # two CTAs per SM (three fit): measured best at 1, 8 and 64 tokens of 2,048 and 8,000 keys
