@@ -710,7 +710,10 @@ def _summed_fn():
                 c_float, c_float, c_float, c_void_p])
 
 
-SKINNY_MAX_ROWS = 64       # at or below this many rows a bfloat16 product goes to the weight-streaming kernel
+# At or below this many rows a bfloat16 product goes to the weight-streaming kernel (which takes up to 64).  Measured
+# on 36-layer decode steps: with the library above 32 rows a step of 48 rows takes 2.48 instead of 2.72 ms and one of
+# 64 rows 2.77 instead of 3.07 ms; with the library above 16 rows a step of 24 rows 2.62 instead of 2.18 ms.
+SKINNY_MAX_ROWS = int(os.environ.get("LOGSSMS_B200_SKINNY_MAX", "32"))
 
 
 def _skinny_ok(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, max_rows: int | None = None) -> bool:
@@ -750,11 +753,12 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = 
 
 
 _gemm_error: dict[torch.device, torch.Tensor] = {}
-# Which kernel takes bfloat16 products of more than 64 rows.  "auto": the engine's tcgen05 kernel where its
-# fused epilogue pays (gate|up with SwiGLU: 31 us against 18 + 9 us for the library product plus the SwiGLU
-# kernel at 2048 x 4096 x 1024, one 16 MB round trip less), the library (cuBLAS through torch) for plain
-# products, where it is still about twice as fast as the tcgen05 kernel.  "tcgen05": everything on the
-# engine's kernel.  "library": everything on cuBLAS.
+# Which kernel takes bfloat16 products of more rows than the weight streamer.  "auto" and "library": cuBLAS through
+# torch, the SwiGLU as a kernel of its own behind it.  "tcgen05": the engine's own tcgen05 kernel with its fused
+# epilogues.  Measured at 2048 x 4096 x 1024 (gate|up of a 2,048-token prompt): the library product 16.3 us + SwiGLU
+# kernel 7.1 us = 23.4 us against 33.4 us for the fused tcgen05 kernel, whose 128 x 128 one-CTA tiles are bound by
+# L2 -> SM traffic (64 FLOP per byte; the library runs 256 x 256 two-CTA tiles); at 64 rows its 128-row tile is
+# half empty.  It stays selectable and tested, and is not the default until it wins.
 GEMM_MODE = os.environ.get("LOGSSMS_B200_GEMM", "auto")
 
 
@@ -806,15 +810,16 @@ def check_gemm_errors(device=None) -> None:
                               f"block {(code >> 12) & 0xFFF}, k-block {code & 0xFFF})")
 
 
-def linear_conv_step_ok(x, w: torch.Tensor, bias, conv_state: torch.Tensor) -> bool:
-    """Can `linear_conv_step` take these operands (else: `linear`, then `causal_conv1d`)?"""
+def linear_conv_step_ok(x, w: torch.Tensor, bias, conv_state: torch.Tensor, max_rows: int | None = None) -> bool:
+    """Should `linear_conv_step` take these operands (else: `linear`, then `causal_conv1d`)?  `max_rows`: the most
+    rows (default: as many as go to the weight streamer at all; the kernel itself takes 64)."""
     if conv_state.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or w.data_ptr() % 16:
         return False
     if bias is not None and not (bias.dtype == torch.bfloat16 and bias.is_contiguous()):
         return False
     if isinstance(x, NormedRows):
         return w.shape[1] == x.shape[1]
-    return _skinny_ok(x, w, bias)
+    return _skinny_ok(x, w, bias, max_rows)
 
 
 def linear_conv_step(x, w: torch.Tensor, bias, conv_weight: torch.Tensor, conv_bias, conv_state: torch.Tensor,
@@ -825,7 +830,7 @@ def linear_conv_step(x, w: torch.Tensor, bias, conv_weight: torch.Tensor, conv_b
     back as silu(conv(...)) and `conv_state` ([slots, last - first, taps - 1]) is shifted in place.  `x` may be
     `NormedRows`.  `region_ends` are column indices relative to `first`."""
     normed = isinstance(x, NormedRows)
-    _need(linear_conv_step_ok(x, w, bias, conv_state), "linear_conv_step takes few bfloat16 rows (see linear_skinny)")
+    _need(linear_conv_step_ok(x, w, bias, conv_state, 64), "linear_conv_step takes few bfloat16 rows (see linear_skinny)")
     C = last - first
     taps = conv_weight.shape[1]
     _need(conv_weight.dtype == torch.float32 and conv_weight.shape == (C, taps) and conv_weight.is_contiguous(), "conv weight must be float32 [C, K]")
@@ -902,6 +907,6 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_scale: float) ->
         x = x.tensor()
     if _skinny_ok(x, w_gate_up, None):
         return linear_skinny(x, w_gate_up, swiglu_scale=act_scale)
-    if GEMM_MODE in ("auto", "tcgen05") and _tcgen05_ok(x, w_gate_up, None):
+    if GEMM_MODE == "tcgen05" and _tcgen05_ok(x, w_gate_up, None):
         return gemm_tcgen05(x, w_gate_up, swiglu_scale=act_scale)
     return swiglu(linear(x, w_gate_up), act_scale)
