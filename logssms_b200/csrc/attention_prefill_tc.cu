@@ -1,0 +1,380 @@
+// Causal grouped-query attention for prompt portions over the paged cache on the 5th-generation tensor cores
+// (tcgen05, accumulators in tensor memory, operands brought by TMA).  bfloat16, head size 64, pages of a
+// multiple of 64 tokens; every other shape stays on the mma.sync kernel (attention_prefill.cu).
+//
+// One CTA per (128 query tokens of one request's portion, query head), 6 warps:
+//   warp 0    one thread: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the Q tile once, then of the
+//             K and V tiles (64 keys each: one box per tile, since a tile never crosses a page) into a ring of
+//             stages, each with a "full" and an "empty" mbarrier; the page of a tile comes from the block table
+//   warp 1    allocates 128 columns of tensor memory; one thread issues the products
+//                 S  = Q K^T   (M 128 queries, N 64 keys, K 64 dims: 4 x tcgen05.mma, both operands K-major)
+//                 PV = P V     (M 128, N 64 dims, K 64 keys: 4 x tcgen05.mma, V as an MN-major operand: the rows of
+//                               the cache are keys, which is the K dimension of this product)
+//             S of the next tile is issued right behind PV of this one, so it runs while the rows are rescaled
+//   warps 2-5 one thread per query row: read the row of S from tensor memory (tcgen05.ld), mask by absolute
+//             position (causal, optional window), online softmax in float32 (running maximum and sum), round P to
+//             bfloat16 into shared memory in the swizzled K-major layout the tensor core reads, then read the row
+//             of PV and fold it into the float32 output row kept in registers: O = O * alpha + PV
+// Keys of the last tile beyond the newest token are rows of the page that nobody has written for this request:
+// their scores are masked by selection, and their V rows are overwritten with zeros in shared memory before PV
+// (0 x stale-NaN would poison the row).
+//
+// Every wait on an mbarrier is bounded: after about a second of polling the thread records where it gave up in
+// `error`, all roles stop, tensor memory is freed and the kernel returns.
+//
+// Formula: python/logssms/layers/attention_backend/fi.py:175-190 (causal, scale head_dim^-1/2); chunked prompts:
+// the query at absolute position p sees keys 0..p.
+#include <cuda.h>
+
+#include "lb200/common.cuh"
+using namespace lb200;
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int kQ = 128, kKV = 64, kHD = 64;               // queries per CTA, keys per tile, head size
+constexpr int kStages = 3;
+constexpr int kThreads = 192;
+constexpr uint32_t kQBytes = kQ * kHD * 2, kTileBytes = kKV * kHD * 2, kPBytes = kQ * kKV * 2;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kTmemCols = 128;                       // S: columns 0..63, PV: columns 64..127
+
+struct TcArgs {
+    bf16* out;                                            // [tokens, Hq, 64]
+    const int* block_table; int bt_stride;
+    const int* cu_seqlens; const int* start_pos;
+    const int* tiles;                                     // [n_tiles][2]: request index, first token of the tile in its portion
+    int Hq, Hkv, page_size, window;
+    float scale_log2;
+    int n_items;                                          // tiles * query heads
+    int* error;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// An operand tile in shared memory made of rows of 128 bytes with the 128-byte swizzle, 8-row groups 1024 bytes apart.
+// Read K-major (the rows are M or N, a row holds 64 k) or MN-major (the rows are k, a row holds 64 m or n): the
+// descriptor is the same, the instruction descriptor says which.
+__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
+    uint64_t d = (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                               // leading byte offset: unused (one 64-wide block)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                               // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void report(int* error, int role, int tile) {
+    if (error != nullptr) atomicCAS(error, 0, (role << 24) | ((blockIdx.x & 0xFFF) << 12) | (tile & 0xFFF) | 0x40000000);
+}
+
+__global__ void __launch_bounds__(kThreads)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = base;                                  // [128][128 B]
+    uint8_t* p_s = q_s + kQBytes;                         // [128][128 B]
+    uint8_t* kv_s = p_s + kPBytes;                        // stages of K [64][128 B] | V [64][128 B]
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv_s + kStages * 2 * kTileBytes);
+    uint64_t* kv_empty = kv_full + kStages;
+    uint64_t* q_full = kv_empty + kStages;
+    uint64_t* s_ready = q_full + 1;                       // S of the tile is in tensor memory
+    uint64_t* p_ready = s_ready + 1;                      // P of the tile is in shared memory (128 arrivals)
+    uint64_t* o_ready = p_ready + 1;                      // PV of the tile is in tensor memory
+    uint64_t* pv_free = o_ready + 1;                      // the rows have read PV (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_free + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // heaviest tiles first (the host lists them so); the query heads of a tile follow one another
+    const int item = blockIdx.x;
+    const int tile = item / a.Hq, h = item % a.Hq, kvh = h / (a.Hq / a.Hkv);
+    const int b = a.tiles[2 * tile], q0 = a.tiles[2 * tile + 1];
+    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
+    const int rows = min(kQ, len - q0);
+    const int pos0 = a.start_pos[b] + q0, last_pos = pos0 + rows - 1;
+    const int lo = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int kt_begin = lo / kKV, kt_end = last_pos / kKV + 1, n_kt = kt_end - kt_begin;
+    const int* bt = a.block_table + (size_t)b * a.bt_stride;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
+        mbar_init(q_full, 1); mbar_init(s_ready, 1); mbar_init(o_ready, 1);
+        mbar_init(p_ready, 128); mbar_init(pv_free, 128);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, kQBytes);
+            tma_load_2d(q_s, &map_q, q_full, h * kHD, begin + q0);
+            int issued = 0;
+            for (int i = 0; i < n_kt && !*failed; ++i, ++issued) {
+                const int s = i % kStages;
+                if (i >= kStages && !mbar_wait(kv_empty + s, ((i / kStages) - 1) & 1)) { report(a.error, 1, i); *failed = 1; break; }
+                const int j0 = (kt_begin + i) * kKV;
+                const int page = j0 / a.page_size;
+                const int row = bt[page] * a.page_size + (j0 - page * a.page_size);
+                uint8_t* k_tile = kv_s + (size_t)s * 2 * kTileBytes;
+                mbar_expect_tx(kv_full + s, 2 * kTileBytes);
+                tma_load_2d(k_tile, &map_k, kv_full + s, kvh * kHD, row);
+                tma_load_2d(k_tile + kTileBytes, &map_v, kv_full + s, kvh * kHD, row);
+            }
+            if (*failed) {                                 // let the copies already under way land before the CTA leaves
+                mbar_wait(q_full, 0);
+                for (int i = max(0, issued - kStages); i < issued; ++i) mbar_wait(kv_full + i % kStages, (i / kStages) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // float32 accumulator, bfloat16 operands, N 64, M 128; bit 16: the B operand is MN-major (V)
+            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kKV >> 3) << 17) | ((uint32_t)(kQ >> 4) << 24);
+            const uint32_t idesc_o = idesc_s | (1u << 16);
+            const uint64_t qdesc = umma_desc(q_s), pdesc = umma_desc(p_s);
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) { report(a.error, 2, 0xFFF); *failed = 1; }
+            auto issue_s = [&](int i) -> bool {            // S of tile i
+                const int s = i % kStages;
+                if (!mbar_wait(kv_full + s, (i / kStages) & 1)) { report(a.error, 2, i); *failed = 1; return false; }
+                tc_fence_after();
+                const uint64_t kdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kHD / 16; ++k) umma_bf16(tmem, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k != 0);
+                umma_commit(s_ready);
+                return true;
+            };
+            if (ok && n_kt > 0) ok = issue_s(0);
+            for (int i = 0; i < n_kt && ok && !*failed; ++i) {
+                const int s = i % kStages;
+                // P of tile i is written, and the rows are done with S of tile i and with PV of tile i - 1
+                if (!mbar_wait(p_ready, i & 1)) { report(a.error, 3, i); *failed = 1; break; }
+                if (i > 0 && !mbar_wait(pv_free, (i - 1) & 1)) { report(a.error, 4, i); *failed = 1; break; }
+                tc_fence_after();
+                const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kKV / 16; ++k)         // 16 keys: two 8-row groups of V = 2048 bytes; 32 bytes along a row of P
+                    umma_bf16(tmem + 64, pdesc + 2 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, k != 0);
+                umma_commit(o_ready);
+                umma_commit(kv_empty + s);                 // both products have read the stage
+                if (i + 1 < n_kt) ok = issue_s(i + 1);
+            }
+        }
+    } else {
+        const int r = (warp & 3) * 32 + lane;              // the row of the tile this thread owns (its lane of tensor memory)
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const int p = pos0 + r;                            // absolute position of the row's query
+        const int lo_r = a.window > 0 ? p - a.window + 1 : 0;
+        float o[kHD];
+#pragma unroll
+        for (int d = 0; d < kHD; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        uint8_t* p_row = p_s + (size_t)r * 128;
+        bool ok = true;
+        for (int i = 0; i < n_kt; ++i) {
+            const int j0 = (kt_begin + i) * kKV;
+            ok = mbar_wait(s_ready, i & 1);
+            if (!ok && lane == 0) { report(a.error, 5, i); *failed = 1; }
+            if (!__all_sync(0xffffffffu, ok && !*failed)) { ok = false; break; }
+            tc_fence_after();
+            // keys of this tile beyond the newest token: zero their V rows (the rows share the work)
+            if (j0 + kKV - 1 > last_pos) {
+                uint8_t* v_tile = kv_s + (size_t)(i % kStages) * 2 * kTileBytes + kTileBytes;
+                const int first_bad = last_pos + 1 - j0;   // >= 1: the tile holds at least one key
+                for (int x = (warp & 3) * 32 + lane; x < (kKV - first_bad) * 8; x += 128)
+                    *reinterpret_cast<uint4*>(v_tile + (size_t)(first_bad + x / 8) * 128 + (x % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            const bool whole = j0 + kKV - 1 <= pos0 && (a.window <= 0 || j0 >= pos0 + kQ - a.window);
+            float alpha;
+            {
+                uint32_t s0[32], s1[32];
+                tmem_ld32(lane_addr, s0);
+                tmem_ld32(lane_addr + 32, s1);
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float v0 = __uint_as_float(s0[c]), v1 = __uint_as_float(s1[c]);
+                    if (!whole) {
+                        const int ka = j0 + c, kb = j0 + 32 + c;
+                        if (ka > p || ka < lo_r) v0 = -INFINITY;
+                        if (kb > p || kb < lo_r) v1 = -INFINITY;
+                        s0[c] = __float_as_uint(v0); s1[c] = __float_as_uint(v1);
+                    }
+                    mx = fmaxf(mx, fmaxf(v0, v1));
+                }
+                const float m_new = fmaxf(m, mx * a.scale_log2);
+                const float ref = m_new == -INFINITY ? 0.f : m_new;     // a row that has seen no key yet
+                alpha = exp2f(m - ref);
+                m = m_new;
+                float sum = 0.f;
+#pragma unroll
+                for (int c8 = 0; c8 < 8; ++c8) {           // 8 keys = one 16-byte piece of the row of P
+                    uint4 piece;
+                    uint32_t* pw = reinterpret_cast<uint32_t*>(&piece);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = c8 * 8 + 2 * e;
+                        const float x0 = __uint_as_float(c < 32 ? s0[c] : s1[c - 32]);
+                        const float x1 = __uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]);
+                        const float e0 = exp2f(fmaf(x0, a.scale_log2, -ref)), e1 = exp2f(fmaf(x1, a.scale_log2, -ref));
+                        sum += e0 + e1;
+                        __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+                        pw[e] = *reinterpret_cast<uint32_t*>(&pr);
+                    }
+                    *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) * 16)) = piece;
+                }
+                l = l * alpha + sum;
+            }
+            fence_async_smem();                            // P (and the zeroed V rows) are for the tensor core's reads
+            tc_fence_before();
+            mbar_arrive(p_ready);
+            ok = mbar_wait(o_ready, i & 1);
+            if (!ok && lane == 0) { report(a.error, 6, i); *failed = 1; }
+            if (!__all_sync(0xffffffffu, ok && !*failed)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t pv[32];
+                tmem_ld32(lane_addr + 64 + half * 32, pv);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[half * 32 + c] = fmaf(o[half * 32 + c], alpha, __uint_as_float(pv[c]));
+            }
+            tc_fence_before();
+            mbar_arrive(pv_free);
+        }
+        if (ok && r < rows) {
+            const float inv = 1.f / l;
+            bf16* dst = a.out + ((size_t)(begin + q0 + r) * a.Hq + h) * kHD;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+                uint4 piece;
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&piece);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(o[c8 * 8 + 2 * e] * inv, o[c8 * 8 + 2 * e + 1] * inv);
+                    pw[e] = *reinterpret_cast<uint32_t*>(&pr);
+                }
+                *reinterpret_cast<uint4*>(dst + c8 * 8) = piece;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// rows x width bfloat16 matrix (contiguous rows); box = box_rows x 64 elements, 128-byte swizzle, zero fill
+int make_map(CUtensorMap* map, const void* ptr, long rows, long width, int box_rows) {
+    EncodeTiled enc = encoder();
+    if (enc == nullptr) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+// Does the tensor-core kernel take these sizes?  (Else: lb_attention_prefill.)
+extern "C" int lb_attention_prefill_tc_ok(int Hq, int Hkv, int hd, int page_size) {
+    return hd == kHD && page_size > 0 && page_size % kKV == 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 ? 1 : 0;
+}
+
+// q, out: [tokens, Hq, 64] bfloat16 contiguous; caches [pages, page_size, Hkv, 64] contiguous; tiles: int32
+// [n_tiles, 2] (request index, first token of the tile within the request's portion; 128 tokens per tile).
+// `error`: a device int that is 0 before the call; non-zero afterwards: a wait inside the kernel gave up.
+extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, long tokens,
+                                       long pages, const int* block_table, int bt_stride, const int* cu_seqlens,
+                                       const int* start_pos, const int* tiles, int n_tiles, int Hq, int Hkv, int hd,
+                                       int page_size, float scale, int window, int* error, void* stream) {
+    if (n_tiles <= 0) return kOk;
+    if (!lb_attention_prefill_tc_ok(Hq, Hkv, hd, page_size)) return kBadSize;
+    if ((long)n_tiles * Hq > 0x7fffffffL) return kTooLarge;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return kBadSize;
+    CUtensorMap map_q, map_k, map_v;
+    int rc = make_map(&map_q, q, tokens, (long)Hq * hd, kQ);
+    if (rc == 0) rc = make_map(&map_k, k_cache, pages * page_size, (long)Hkv * hd, kKV);
+    if (rc == 0) rc = make_map(&map_v, v_cache, pages * page_size, (long)Hkv * hd, kKV);
+    if (rc != 0) return rc;
+    TcArgs a{(bf16*)out, block_table, bt_stride, cu_seqlens, start_pos, tiles, Hq, Hkv, page_size, window,
+             scale * 1.4426950408889634f, n_tiles * Hq, error};
+    const size_t smem = kQBytes + kPBytes + (size_t)kStages * 2 * kTileBytes + 256 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured = true;
+    }
+    attn_prefill_tc_kernel<<<(unsigned)a.n_items, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_k, map_v, a);
+    return launch_status();
+}

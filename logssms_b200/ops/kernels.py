@@ -425,6 +425,48 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 ATTENTION_TILE = 64        # query tokens per CTA of the prefill kernel
+ATTENTION_TC_TILE = 128    # and of its tcgen05 form
+ATTENTION_TC = os.environ.get("LOGSSMS_B200_ATTN_TC", "1") != "0"
+
+
+def attention_prefill_tc_ok(q: torch.Tensor, k_cache: torch.Tensor) -> bool:
+    """Does the tcgen05 prompt-attention kernel take these operands (bfloat16, head size 64, pages of a multiple of
+    64 tokens)?  Else `attention_prefill`."""
+    return (ATTENTION_TC and q.dtype == torch.bfloat16 and q.dim() == 3 and q.shape[2] == 64 and k_cache.dim() == 4
+            and k_cache.shape[1] % 64 == 0 and k_cache.shape[3] == 64 and q.shape[1] % k_cache.shape[2] == 0
+            and q.is_contiguous() and k_cache.is_contiguous())
+
+
+def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                         cu_seqlens: torch.Tensor, start_pos: torch.Tensor, tiles: torch.Tensor, num_tiles: int,
+                         scale: float, window: int = 0, *, out: torch.Tensor | None = None) -> torch.Tensor:
+    """`attention_prefill` on the tcgen05 tensor cores: the same arguments, but `tiles` lists 128-token tiles.
+    `check_gemm_errors()` reports a kernel whose internal wait gave up."""
+    _cuda(q, k_cache, v_cache, block_table, cu_seqlens, start_pos, tiles)
+    _need(attention_prefill_tc_ok(q, k_cache), "attention_prefill_tc takes bfloat16, head size 64 and pages of a multiple of 64 tokens")
+    tokens, Hq, hd = q.shape
+    _need(v_cache.shape == k_cache.shape and v_cache.is_contiguous() and v_cache.dtype == k_cache.dtype == q.dtype,
+          "caches must be contiguous [pages, page_size, kv_heads, head_dim] of q's dtype")
+    pages, page_size, Hkv = k_cache.shape[0], k_cache.shape[1], k_cache.shape[2]
+    _need(block_table.dim() == 2 and block_table.dtype == torch.int32 and block_table.stride(1) == 1,
+          "block table must be a row-major int32 matrix")
+    _i32(cu_seqlens, "cu_seqlens")
+    _i32(start_pos, "start_pos")
+    _i32(tiles, "tiles")
+    _need(tiles.numel() >= 2 * num_tiles, "tiles holds fewer pairs than num_tiles")
+    if out is None:
+        out = torch.empty_like(q)
+    _need(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+    err = _gemm_error.get(q.device)
+    if err is None:
+        err = _gemm_error[q.device] = torch.zeros(1, dtype=torch.int32, device=q.device)
+    f = _fn("attention_prefill_tc", "lb_attention_prefill_tc",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_long, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), tokens, pages, _ptr(block_table), block_table.stride(0),
+             _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), num_tiles, Hq, Hkv, hd, page_size, scale, int(window or 0),
+             _ptr(err), _stream()), "attention_prefill_tc")
+    return out
 
 
 # --------------------------------------------------------------------------- Mamba2
@@ -806,7 +848,7 @@ def check_gemm_errors(device=None) -> None:
         code = int(err.item())
         if code:
             err.zero_()
-            raise KernelError(f"gemm_tcgen05: a wait inside the kernel gave up (role {(code >> 24) & 0x3F}, "
+            raise KernelError(f"a tcgen05 kernel: a wait inside the kernel gave up (role {(code >> 24) & 0x3F}, "
                               f"block {(code >> 12) & 0xFFF}, k-block {code & 0xFFF})")
 
 

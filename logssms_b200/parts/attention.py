@@ -20,7 +20,7 @@ class Attention(Part):
     the flow is python/logssms/layers/attention.py:115-167."""
     takes_normed_rows = True      # forward() passes its input straight into a product
     joins_residual = True         # forward() takes `join=`: its last product may add the residual in its epilogue
-    kernels = ("rope", "attention_decode", "attention_decode_fused", "attention_prefill", "linear_skinny", "gemm_tcgen05")
+    kernels = ("rope", "attention_decode", "attention_decode_fused", "attention_prefill", "attention_prefill_tc", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
         self.spec = spec
@@ -83,9 +83,14 @@ class Attention(Part):
         token_list, n_short = None, T
         if q.dtype == torch.bfloat16 and ctx.has_long_portions:
             # long portions on the tensor-core kernel; what is left (decoded tokens, short portions) token by token
-            tiles, n_tiles = ctx.long_portion_tiles(K.ATTENTION_TILE)
-            o = K.attention_prefill(q, k_cache, v_cache, tables, ctx.cu_seqlens, ctx.start_pos, tiles, n_tiles,
-                                    self.scale, window)
+            if K.attention_prefill_tc_ok(q, k_cache):
+                tiles, n_tiles = ctx.long_portion_tiles(K.ATTENTION_TC_TILE)
+                o = K.attention_prefill_tc(q, k_cache, v_cache, tables, ctx.cu_seqlens, ctx.start_pos, tiles, n_tiles,
+                                           self.scale, window)
+            else:
+                tiles, n_tiles = ctx.long_portion_tiles(K.ATTENTION_TILE)
+                o = K.attention_prefill(q, k_cache, v_cache, tables, ctx.cu_seqlens, ctx.start_pos, tiles, n_tiles,
+                                        self.scale, window)
             token_list, n_short = ctx.short_portion_tokens()
         if n_short > 0:
             splits = ctx.attention_splits or K.attention_splits(n_short, s.num_heads, s.num_kv_heads, ctx.max_context)

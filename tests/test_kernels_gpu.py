@@ -309,10 +309,10 @@ def test_attention_decode_step_rotates_stores_attends_and_merges(dtype, shape, s
     assert int(k._counters_for(torch.device("cuda", torch.cuda.current_device()), 1).abs().sum()) == 0
 
 
-def prefill_inputs(case, lengths, new):
+def prefill_inputs(case, lengths, new, tile=64):
     cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32)
     start = torch.tensor([n - m for n, m in zip(lengths, new)], dtype=torch.int32)
-    tiles = torch.tensor([(b, t0) for b, m in enumerate(new) for t0 in range(0, m, 64)], dtype=torch.int32)
+    tiles = torch.tensor([(b, t0) for b, m in enumerate(new) for t0 in range(0, m, tile)], dtype=torch.int32)
     return cu, start, tiles
 
 
@@ -356,6 +356,55 @@ def test_attention_prefill_finds_a_far_key_honours_a_window_and_leaves_other_row
     lo, hi = int(cu[1]), int(cu[2])
     close(out[lo:hi], rnd_of(dtype)(want)[lo:hi], dtype)
     assert bool((out[:lo] == 7.0).all()) and bool((out[hi:] == 7.0).all())
+
+
+@pytest.mark.parametrize("shape", [(8, 2, 64, 64), (3, 3, 64, 128), (4, 1, 64, 64)])
+def test_attention_prefill_on_tcgen05_over_pages_and_earlier_portions(shape):
+    """The tcgen05 form (head size 64, pages of a multiple of 64 tokens): whole prompts and later portions, tiles
+    that end inside a page whose other rows hold NaN (what a reused page holds in the replay tests), a planted far
+    key, windows."""
+    Hq, Hkv, hd, page = shape
+    dtype = torch.bfloat16
+    k = K()
+    g = torch.Generator().manual_seed(hd * 3 + Hq)
+    lengths, new = [70, 333, 64, 129, 700, 9, 300], [70, 100, 64, 65, 130, 9, 300]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new, plant=True)
+    assert k.attention_prefill_tc_ok(dev(case["q"]), dev(case["kc"]))
+    cu, start, tiles = prefill_inputs(case, lengths, new, 128)
+    scale = hd ** -0.5
+    kc, vc = dev(case["kc"]).clone(), dev(case["vc"]).clone()
+    # rows of the requests' last pages beyond their lengths: stale memory
+    for r, n in enumerate(lengths):
+        last_page = int(case["bt"][r, (n - 1) // page])
+        if n % page:
+            kc[last_page, n % page:] = float("nan")
+            vc[last_page, n % page:] = float("nan")
+    args = (dev(case["q"]), kc, vc, dev(case["bt"]), dev(cu), dev(start))
+    rd = ref_dtype(dtype)
+    want = attention_reference(case, scale, 0, rd)
+    got = k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale)
+    k.check_gemm_errors()
+    close(got, rnd_of(dtype)(want), dtype)
+    for window in (1, 64, 65, 300):
+        want_w = rnd_of(dtype)(attention_reference(case, scale, window, rd))
+        close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale, window), want_w, dtype)
+    k.check_gemm_errors()
+    # only one request's tiles: the other rows stay as they were
+    out = torch.full_like(dev(case["q"]), 7.0)
+    only = torch.tensor([[1, 0]], dtype=torch.int32)
+    k.attention_prefill_tc(*args, dev(only), 1, scale, out=out)
+    lo, hi = int(cu[1]), int(cu[2])
+    close(out[lo:hi], rnd_of(dtype)(want)[lo:hi], dtype)
+    assert bool((out[:lo] == 7.0).all()) and bool((out[hi:] == 7.0).all())
+
+
+def test_attention_prefill_on_tcgen05_refuses_other_shapes():
+    k = K()
+    q = torch.zeros(4, 2, 48, dtype=torch.bfloat16, device="cuda")
+    assert not k.attention_prefill_tc_ok(q, torch.zeros(2, 64, 2, 48, dtype=torch.bfloat16, device="cuda"))       # head size 48
+    q = torch.zeros(4, 2, 64, dtype=torch.bfloat16, device="cuda")
+    assert not k.attention_prefill_tc_ok(q, torch.zeros(2, 16, 2, 64, dtype=torch.bfloat16, device="cuda"))       # pages of 16
+    assert not k.attention_prefill_tc_ok(q.float(), torch.zeros(2, 64, 2, 64, device="cuda"))                     # float32
 
 
 # --------------------------------------------------------------------------- Mamba2: conv and scan
