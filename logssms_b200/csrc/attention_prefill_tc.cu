@@ -11,7 +11,10 @@
 //                 PV = P V     (M 128, N 64 dims, K 64 keys: 4 x tcgen05.mma, V as an MN-major operand: the rows of
 //                               the cache are keys, which is the K dimension of this product)
 //             S of the next tile is issued right behind PV of this one, so it runs while the rows are rescaled
-//   warps 2-5 one thread per query row: read the row of S from tensor memory (tcgen05.ld), mask by absolute
+//   warps 2-9 two groups of 128 threads, one thread per query row in each; group g owns the key tiles g, g + 2, ...
+//             with its own S, PV, P and running (maximum, sum, output), so that one group's chain of
+//             product -> softmax -> product -> rescale runs while the other waits for the tensor core; the two
+//             partial results meet in shared memory at the end.  A thread: read the row of S from tensor memory (tcgen05.ld), mask by absolute
 //             position (causal, optional window), online softmax in float32 (running maximum and sum), round P to
 //             bfloat16 into shared memory in the swizzled K-major layout the tensor core reads, then read the row
 //             of PV and fold it into the float32 output row kept in registers: O = O * alpha + PV
@@ -32,11 +35,13 @@ using namespace lb200;
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int kQ = 128, kKV = 64, kHD = 64;               // queries per CTA, keys per tile, head size
-constexpr int kStages = 3;
-constexpr int kThreads = 192;
+constexpr int kStages = 4;
+constexpr int kGroups = 2;                               // softmax groups of 128 threads
+constexpr int kThreads = 64 + kGroups * 128;
 constexpr uint32_t kQBytes = kQ * kHD * 2, kTileBytes = kKV * kHD * 2, kPBytes = kQ * kKV * 2;
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr uint32_t kTmemCols = 128;                       // S: columns 0..63, PV: columns 64..127
+constexpr uint32_t kTmemCols = 128 * kGroups;             // per group: S in columns 0..63, PV in columns 64..127
+constexpr uint32_t kMergeBytes = (kHD + 2) * kQ * 4;      // group 1's partial result, [column][row] float32
 
 struct TcArgs {
     bf16* out;                                            // [tokens, Hq, 64]
@@ -117,16 +122,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = base;                                  // [128][128 B]
-    uint8_t* p_s = q_s + kQBytes;                         // [128][128 B]
-    uint8_t* kv_s = p_s + kPBytes;                        // stages of K [64][128 B] | V [64][128 B]
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv_s + kStages * 2 * kTileBytes);
+    uint8_t* p_s = q_s + kQBytes;                         // per group [128][128 B]
+    uint8_t* kv_s = p_s + kGroups * kPBytes;              // stages of K [64][128 B] | V [64][128 B]
+    float* merge = reinterpret_cast<float*>(kv_s + kStages * 2 * kTileBytes);       // [66][128]
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(merge) + kMergeBytes);
     uint64_t* kv_empty = kv_full + kStages;
     uint64_t* q_full = kv_empty + kStages;
-    uint64_t* s_ready = q_full + 1;                       // S of the tile is in tensor memory
-    uint64_t* p_ready = s_ready + 1;                      // P of the tile is in shared memory (128 arrivals)
-    uint64_t* o_ready = p_ready + 1;                      // PV of the tile is in tensor memory
-    uint64_t* pv_free = o_ready + 1;                      // the rows have read PV (128 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_free + 1);
+    uint64_t* s_ready = q_full + 1;                       // per group: S of its tile is in tensor memory
+    uint64_t* p_ready = s_ready + kGroups;                // per group: P of its tile is in shared memory (128 arrivals)
+    uint64_t* o_ready = p_ready + kGroups;                // per group: PV of its tile is in tensor memory
+    uint64_t* pv_free = o_ready + kGroups;                // per group: its rows have read PV (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_free + kGroups);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -143,8 +149,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
-        mbar_init(q_full, 1); mbar_init(s_ready, 1); mbar_init(o_ready, 1);
-        mbar_init(p_ready, 128); mbar_init(pv_free, 128);
+        mbar_init(q_full, 1);
+        for (int g = 0; g < kGroups; ++g) {
+            mbar_init(s_ready + g, 1); mbar_init(o_ready + g, 1);
+            mbar_init(p_ready + g, 128); mbar_init(pv_free + g, 128);
+        }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -183,49 +192,51 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // float32 accumulator, bfloat16 operands, N 64, M 128; bit 16: the B operand is MN-major (V)
             const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kKV >> 3) << 17) | ((uint32_t)(kQ >> 4) << 24);
             const uint32_t idesc_o = idesc_s | (1u << 16);
-            const uint64_t qdesc = umma_desc(q_s), pdesc = umma_desc(p_s);
+            const uint64_t qdesc = umma_desc(q_s);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) { report(a.error, 2, 0xFFF); *failed = 1; }
-            auto issue_s = [&](int i) -> bool {            // S of tile i
-                const int s = i % kStages;
+            auto issue_s = [&](int i) -> bool {            // S of tile i, into its group's columns
+                const int s = i % kStages, g = i % kGroups;
                 if (!mbar_wait(kv_full + s, (i / kStages) & 1)) { report(a.error, 2, i); *failed = 1; return false; }
                 tc_fence_after();
                 const uint64_t kdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes);
 #pragma unroll
-                for (int k = 0; k < kHD / 16; ++k) umma_bf16(tmem, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k != 0);
-                umma_commit(s_ready);
+                for (int k = 0; k < kHD / 16; ++k) umma_bf16(tmem + g * 128, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k != 0);
+                umma_commit(s_ready + g);
                 return true;
             };
-            if (ok && n_kt > 0) ok = issue_s(0);
+            for (int i = 0; i < kGroups && i < n_kt && ok; ++i) ok = issue_s(i);
             for (int i = 0; i < n_kt && ok && !*failed; ++i) {
-                const int s = i % kStages;
-                // P of tile i is written, and the rows are done with S of tile i and with PV of tile i - 1
-                if (!mbar_wait(p_ready, i & 1)) { report(a.error, 3, i); *failed = 1; break; }
-                if (i > 0 && !mbar_wait(pv_free, (i - 1) & 1)) { report(a.error, 4, i); *failed = 1; break; }
+                const int s = i % kStages, g = i % kGroups, t = i / kGroups;
+                // P of tile i is written, and the group's rows are done with S of tile i and with PV of its tile before
+                if (!mbar_wait(p_ready + g, t & 1)) { report(a.error, 3, i); *failed = 1; break; }
+                if (t > 0 && !mbar_wait(pv_free + g, (t - 1) & 1)) { report(a.error, 4, i); *failed = 1; break; }
                 tc_fence_after();
+                const uint64_t pdesc = umma_desc(p_s + (size_t)g * kPBytes);
                 const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes);
 #pragma unroll
                 for (int k = 0; k < kKV / 16; ++k)         // 16 keys: two 8-row groups of V = 2048 bytes; 32 bytes along a row of P
-                    umma_bf16(tmem + 64, pdesc + 2 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, k != 0);
-                umma_commit(o_ready);
+                    umma_bf16(tmem + g * 128 + 64, pdesc + 2 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, k != 0);
+                umma_commit(o_ready + g);
                 umma_commit(kv_empty + s);                 // both products have read the stage
-                if (i + 1 < n_kt) ok = issue_s(i + 1);
+                if (i + kGroups < n_kt) ok = issue_s(i + kGroups);
             }
         }
     } else {
+        const int grp = (warp - 2) / 4;                    // which tiles: grp, grp + kGroups, ...
         const int r = (warp & 3) * 32 + lane;              // the row of the tile this thread owns (its lane of tensor memory)
-        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * 128;
         const int p = pos0 + r;                            // absolute position of the row's query
         const int lo_r = a.window > 0 ? p - a.window + 1 : 0;
         float o[kHD];
 #pragma unroll
         for (int d = 0; d < kHD; ++d) o[d] = 0.f;
         float m = -INFINITY, l = 0.f;
-        uint8_t* p_row = p_s + (size_t)r * 128;
+        uint8_t* p_row = p_s + (size_t)grp * kPBytes + (size_t)r * 128;
         bool ok = true;
-        for (int i = 0; i < n_kt; ++i) {
+        for (int i = grp, t = 0; i < n_kt; i += kGroups, ++t) {
             const int j0 = (kt_begin + i) * kKV;
-            ok = mbar_wait(s_ready, i & 1);
+            ok = mbar_wait(s_ready + grp, t & 1);
             if (!ok && lane == 0) { report(a.error, 5, i); *failed = 1; }
             if (!__all_sync(0xffffffffu, ok && !*failed)) { ok = false; break; }
             tc_fence_after();
@@ -279,8 +290,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             fence_async_smem();                            // P (and the zeroed V rows) are for the tensor core's reads
             tc_fence_before();
-            mbar_arrive(p_ready);
-            ok = mbar_wait(o_ready, i & 1);
+            mbar_arrive(p_ready + grp);
+            ok = mbar_wait(o_ready + grp, t & 1);
             if (!ok && lane == 0) { report(a.error, 6, i); *failed = 1; }
             if (!__all_sync(0xffffffffu, ok && !*failed)) { ok = false; break; }
             tc_fence_after();
@@ -292,9 +303,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int c = 0; c < 32; ++c) o[half * 32 + c] = fmaf(o[half * 32 + c], alpha, __uint_as_float(pv[c]));
             }
             tc_fence_before();
-            mbar_arrive(pv_free);
+            mbar_arrive(pv_free + grp);
         }
-        if (ok && r < rows) {
+        // the groups' partial results meet: group 1 leaves its row in shared memory ([column][row]: a warp's rows lie
+        // side by side), group 0 folds it into its own
+        if (grp == 1) {
+#pragma unroll
+            for (int d = 0; d < kHD; ++d) merge[d * kQ + r] = o[d];
+            merge[kHD * kQ + r] = m;
+            merge[(kHD + 1) * kQ + r] = l;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");        // the 256 softmax threads
+        if (grp == 0) {
+            const float m1 = merge[kHD * kQ + r], l1 = merge[(kHD + 1) * kQ + r];
+            const float mn = fmaxf(m, m1), ref = mn == -INFINITY ? 0.f : mn;
+            const float f0 = exp2f(m - ref), f1 = exp2f(m1 - ref);
+            l = l * f0 + l1 * f1;
+#pragma unroll
+            for (int d = 0; d < kHD; ++d) o[d] = o[d] * f0 + merge[d * kQ + r] * f1;
+        }
+        if (ok && grp == 0 && r < rows) {
             const float inv = 1.f / l;
             bf16* dst = a.out + ((size_t)(begin + q0 + r) * a.Hq + h) * kHD;
 #pragma unroll
@@ -369,7 +397,7 @@ extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const
     if (rc != 0) return rc;
     TcArgs a{(bf16*)out, block_table, bt_stride, cu_seqlens, start_pos, tiles, Hq, Hkv, page_size, window,
              scale * 1.4426950408889634f, n_tiles * Hq, error};
-    const size_t smem = kQBytes + kPBytes + (size_t)kStages * 2 * kTileBytes + 256 + 1024;
+    const size_t smem = kQBytes + kGroups * kPBytes + (size_t)kStages * 2 * kTileBytes + kMergeBytes + 256 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
