@@ -162,7 +162,9 @@ class Engine:
             before = K.launch_count
             if self._side_stream is None:
                 self._side_stream = torch.cuda.Stream(self.device)
-            if ctx.max_len == 1 and os.environ.get("LOGSSMS_B200_FORK_MIXERS", "1") != "0":
+            # "all": every captured step; "decode": steps of single tokens only; "0": never
+            fork = os.environ.get("LOGSSMS_B200_FORK_MIXERS", "all")
+            if fork != "0" and (ctx.max_len == 1 or fork == "all"):
                 ctx.extras["side_stream"] = self._side_stream  # blocks may fork their mixers onto it while capturing
             with torch.cuda.graph(graph):
                 x, residual = self.model.forward(ctx)
