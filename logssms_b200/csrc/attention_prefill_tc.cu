@@ -27,10 +27,10 @@
 //
 // Formula: python/logssms/layers/attention_backend/fi.py:175-190 (causal, scale head_dim^-1/2); chunked prompts:
 // the query at absolute position p sees keys 0..p.
-#include <cuda.h>
-
 #include "lb200/common.cuh"
+#include "lb200/tcgen05.cuh"
 using namespace lb200;
+using namespace lb200::tc;
 
 namespace {
 typedef __nv_bfloat16 bf16;
@@ -39,7 +39,6 @@ constexpr int kStages = 4;
 constexpr int kGroups = 2;                               // softmax groups of 128 threads
 constexpr int kThreads = 64 + kGroups * 128;
 constexpr uint32_t kQBytes = kQ * kHD * 2, kTileBytes = kKV * kHD * 2, kPBytes = kQ * kKV * 2;
-constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr uint32_t kTmemCols = 128 * kGroups;             // per group: S in columns 0..63, PV in columns 64..127
 constexpr uint32_t kMergeBytes = (kHD + 2) * kQ * 4;      // group 1's partial result, [column][row] float32
 
@@ -53,64 +52,6 @@ struct TcArgs {
     int n_items;                                          // tiles * query heads
     int* error;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-// An operand tile in shared memory made of rows of 128 bytes with the 128-byte swizzle, 8-row groups 1024 bytes apart.
-// Read K-major (the rows are M or N, a row holds 64 k) or MN-major (the rows are k, a row holds 64 m or n): the
-// descriptor is the same, the instruction descriptor says which.
-__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
-    uint64_t d = (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;                               // leading byte offset: unused (one 64-wide block)
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                               // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
-    return d;
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void report(int* error, int role, int tile) {
     if (error != nullptr) atomicCAS(error, 0, (role << 24) | ((blockIdx.x & 0xFFF) << 12) | (tile & 0xFFF) | 0x40000000);
@@ -155,15 +96,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(p_ready + g, 128); mbar_init(pv_free + g, 128);
         }
         *failed = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tmem_alloc<kTmemCols>(tmem_slot);
     }
-    tc_fence_before();
+    fence_before_sync();
     __syncthreads();
-    tc_fence_after();
+    fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
@@ -190,15 +130,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     } else if (warp == 1) {
         if (lane == 0) {
             // float32 accumulator, bfloat16 operands, N 64, M 128; bit 16: the B operand is MN-major (V)
-            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kKV >> 3) << 17) | ((uint32_t)(kQ >> 4) << 24);
-            const uint32_t idesc_o = idesc_s | (1u << 16);
+            const uint32_t idesc_s = umma_idesc(kQ, kKV);
+            const uint32_t idesc_o = idesc_s | kBMnMajor;
             const uint64_t qdesc = umma_desc(q_s);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) { report(a.error, 2, 0xFFF); *failed = 1; }
             auto issue_s = [&](int i) -> bool {            // S of tile i, into its group's columns
                 const int s = i % kStages, g = i % kGroups;
                 if (!mbar_wait(kv_full + s, (i / kStages) & 1)) { report(a.error, 2, i); *failed = 1; return false; }
-                tc_fence_after();
+                fence_after_sync();
                 const uint64_t kdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes);
 #pragma unroll
                 for (int k = 0; k < kHD / 16; ++k) umma_bf16(tmem + g * 128, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k != 0);
@@ -211,7 +151,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // P of tile i is written, and the group's rows are done with S of tile i and with PV of its tile before
                 if (!mbar_wait(p_ready + g, t & 1)) { report(a.error, 3, i); *failed = 1; break; }
                 if (t > 0 && !mbar_wait(pv_free + g, (t - 1) & 1)) { report(a.error, 4, i); *failed = 1; break; }
-                tc_fence_after();
+                fence_after_sync();
                 const uint64_t pdesc = umma_desc(p_s + (size_t)g * kPBytes);
                 const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes);
 #pragma unroll
@@ -239,7 +179,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = mbar_wait(s_ready + grp, t & 1);
             if (!ok && lane == 0) { report(a.error, 5, i); *failed = 1; }
             if (!__all_sync(0xffffffffu, ok && !*failed)) { ok = false; break; }
-            tc_fence_after();
+            fence_after_sync();
             // keys of this tile beyond the newest token: zero their V rows (the rows share the work)
             if (j0 + kKV - 1 > last_pos) {
                 uint8_t* v_tile = kv_s + (size_t)(i % kStages) * 2 * kTileBytes + kTileBytes;
@@ -289,12 +229,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 l = l * alpha + sum;
             }
             fence_async_smem();                            // P (and the zeroed V rows) are for the tensor core's reads
-            tc_fence_before();
+            fence_before_sync();
             mbar_arrive(p_ready + grp);
             ok = mbar_wait(o_ready + grp, t & 1);
             if (!ok && lane == 0) { report(a.error, 6, i); *failed = 1; }
             if (!__all_sync(0xffffffffu, ok && !*failed)) { ok = false; break; }
-            tc_fence_after();
+            fence_after_sync();
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t pv[32];
@@ -302,7 +242,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int c = 0; c < 32; ++c) o[half * 32 + c] = fmaf(o[half * 32 + c], alpha, __uint_as_float(pv[c]));
             }
-            tc_fence_before();
+            fence_before_sync();
             mbar_arrive(pv_free + grp);
         }
         // the groups' partial results meet: group 1 leaves its row in shared memory ([column][row]: a warp's rows lie
@@ -338,40 +278,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
         }
     }
-    tc_fence_before();
+    fence_before_sync();
     __syncthreads();
     __syncwarp();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    if (warp == 1) tmem_free<kTmemCols>(tmem);
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encoder() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
-// rows x width bfloat16 matrix (contiguous rows); box = box_rows x 64 elements, 128-byte swizzle, zero fill
-int make_map(CUtensorMap* map, const void* ptr, long rows, long width, int box_rows) {
-    EncodeTiled enc = encoder();
-    if (enc == nullptr) return (int)cudaErrorNotSupported;
-    const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)width * 2};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return rc == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
-}
 }  // namespace
 
 // Does the tensor-core kernel take these sizes?  (Else: lb_attention_prefill.)
@@ -391,9 +303,9 @@ extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const
     if ((long)n_tiles * Hq > 0x7fffffffL) return kTooLarge;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return kBadSize;
     CUtensorMap map_q, map_k, map_v;
-    int rc = make_map(&map_q, q, tokens, (long)Hq * hd, kQ);
-    if (rc == 0) rc = make_map(&map_k, k_cache, pages * page_size, (long)Hkv * hd, kKV);
-    if (rc == 0) rc = make_map(&map_v, v_cache, pages * page_size, (long)Hkv * hd, kKV);
+    int rc = make_tile_map(&map_q, q, tokens, (long)Hq * hd, (long)Hq * hd, kQ);
+    if (rc == 0) rc = make_tile_map(&map_k, k_cache, pages * page_size, (long)Hkv * hd, (long)Hkv * hd, kKV);
+    if (rc == 0) rc = make_tile_map(&map_v, v_cache, pages * page_size, (long)Hkv * hd, (long)Hkv * hd, kKV);
     if (rc != 0) return rc;
     TcArgs a{(bf16*)out, block_table, bt_stride, cu_seqlens, start_pos, tiles, Hq, Hkv, page_size, window,
              scale * 1.4426950408889634f, n_tiles * Hq, error};

@@ -411,13 +411,13 @@ extern "C" int lb_ssd_prefill(const void* conv, int C, const void* dt, long dt_s
                               const int* start_pos, const int* slots, const int* chunks, int n_chunks,
                               const int* req_chunks, int n_long, float* scratch, void* s_in, float* chunk_a, int nh, int P, int N,
                               int G, int L, float dt_scale, const void* gate, long gate_stride, float gate_scale,
-                              int dtype, void* stream) {
+                              int run_scan, int dtype, void* stream) {
     if (n_chunks <= 0 || n_long <= 0) return kOk;
     if (dtype != kBF16) return kBadDType;
     if (nh <= 0 || G <= 0 || nh % G || P <= 0 || N <= 0 || P % 8 || N % 8 || L <= 0) return kBadSize;
     if (C != nh * P + 2 * G * N) return kBadSize;
     if (P > 128 || N > 256 || L > 256 || nh > 65535) return kTooLarge;
-    if (scan_smem(L, P, N) > kSmemLimit || state_smem(L, P, N) > kSmemLimit) return kTooLarge;
+    if ((run_scan && scan_smem(L, P, N) > kSmemLimit) || state_smem(L, P, N) > kSmemLimit) return kTooLarge;
     SsdArgs a{(const bf16*)conv, C, (const bf16*)dt, dt_stride, A_log, dt_bias, D, state, (bf16*)y, cu_seqlens,
               start_pos, slots, chunks, req_chunks, scratch, (bf16*)s_in, chunk_a, nh, P, N, G, L, dt_scale,
               (const bf16*)gate, gate_stride, gate_scale};
@@ -431,7 +431,7 @@ extern "C" int lb_ssd_prefill(const void* conv, int C, const void* dt, long dt_s
     const int pieces = (int)(((size_t)P * N / 4 + 255) / 256);
     ssd_state_pass_kernel<<<dim3(n_long, nh, pieces), 256, 0, s>>>(a);
     rc = launch_status();
-    if (rc != 0) return rc;
+    if (rc != 0 || !run_scan) return rc;                 // run_scan 0: the caller runs lb_ssd_chunk_scan_tc behind this
     if (!wide(P, N)) return launch_scan<8, 8, 512>(a, n_chunks, s);
     return launch_scan<16, 16, 256>(a, n_chunks, s);
 }

@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared",
 ]
-ALL_LIBRARIES = ("embed", "norm", "rope", "attention", "attention_decode", "attention_decode_fused", "attention_prefill", "attention_prefill_tc", "conv", "ssm", "ssd", "gemm_f32", "gemm_tcgen05", "linear_skinny", "sample")
+ALL_LIBRARIES = ("embed", "norm", "rope", "attention", "attention_decode", "attention_decode_fused", "attention_prefill", "attention_prefill_tc", "conv", "ssm", "ssd", "ssd_tc", "gemm_f32", "gemm_tcgen05", "linear_skinny", "sample")
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.RLock()

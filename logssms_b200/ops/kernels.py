@@ -538,9 +538,21 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
     return y
 
 
+SSD_TC = os.environ.get("LOGSSMS_B200_SSD_TC", "1") != "0"
+SSD_TC_CHUNK = 128
+
+
+def ssd_chunk_scan_tc_ok(head_dim: int, state_dim: int, chunk_len: int) -> bool:
+    """Does the tcgen05 chunk-scan kernel take these sizes (head size 64, state size 64..256 in steps of 64,
+    chunks of 128 tokens)?"""
+    return SSD_TC and head_dim == 64 and state_dim % 64 == 0 and 64 <= state_dim <= 256 and chunk_len == SSD_TC_CHUNK
+
+
 def ssd_chunk_len(chunk_size: int, head_dim: int, state_dim: int) -> int:
     """Chunk length the tensor-core SSD kernels will use for these sizes (at most `chunk_size`), or 0
     when they do not take them (then the token-by-token scan runs everything)."""
+    if chunk_size >= SSD_TC_CHUNK and ssd_chunk_scan_tc_ok(head_dim, state_dim, SSD_TC_CHUNK):
+        return SSD_TC_CHUNK                   # the tcgen05 chunk scan wants its 128 rows
     lib = build.load("ssd")
     f = lib.lb_ssd_chunk_len
     f.argtypes, f.restype = [c_int, c_int, c_int], c_int
@@ -575,14 +587,28 @@ def ssd_prefill(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bi
     scratch = torch.empty((max(num_chunks, 1), num_heads, head_dim, state_dim), dtype=torch.float32, device=conv.device)
     chunk_a = torch.empty((max(num_chunks, 1), num_heads), dtype=torch.float32, device=conv.device)
     s_in = torch.empty(scratch.shape, dtype=torch.bfloat16, device=conv.device)
+    gate_stride = gate.stride(0) if gate is not None else 0
+    # the chunk scan on the tcgen05 kernel where it takes the sizes
+    tc = ssd_chunk_scan_tc_ok(head_dim, state_dim, chunk_len) and conv.data_ptr() % 16 == 0 and y.data_ptr() % 16 == 0
     f = _fn("ssd", "lb_ssd_prefill", [c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                      c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_float, c_int, c_void_p])
+                                      c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_float, c_int, c_int, c_void_p])
     _check(f(_ptr(conv), C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(state), _ptr(y),
              _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(req_chunks), num_long,
              _ptr(scratch), _ptr(s_in), _ptr(chunk_a), num_heads, head_dim, state_dim, num_groups, chunk_len, dt_scale,
-             _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale, _code(conv), _stream()),
-           "ssd_prefill", f"(head_dim {head_dim}, state_dim {state_dim}, chunk {chunk_len})", launches=3)
+             _ptr(gate), gate_stride, gate_scale, 0 if tc else 1, _code(conv), _stream()),
+           "ssd_prefill", f"(head_dim {head_dim}, state_dim {state_dim}, chunk {chunk_len})", launches=2 if tc else 3)
+    if tc:
+        err = _gemm_error.get(conv.device)
+        if err is None:
+            err = _gemm_error[conv.device] = torch.zeros(1, dtype=torch.int32, device=conv.device)
+        g = _fn("ssd_tc", "lb_ssd_chunk_scan_tc",
+                [c_void_p, c_long, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_float, c_void_p, c_void_p])
+        _check(g(_ptr(conv), tokens, C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(y),
+                 _ptr(cu_seqlens), _ptr(chunks), num_chunks, _ptr(s_in), num_heads, head_dim, state_dim, num_groups,
+                 chunk_len, dt_scale, _ptr(gate), gate_stride, gate_scale, _ptr(err), _stream()),
+               "ssd_chunk_scan_tc", f"(head_dim {head_dim}, state_dim {state_dim}, chunk {chunk_len})")
     return y
 
 

@@ -32,7 +32,7 @@ class Mamba2(Part):
     python/logssms/kernel/linear_attention/mamba2.py:27-36 and :261-292,
     python/logssms/kernel/norm.py:55-86."""
     takes_normed_rows = True      # forward() passes its input straight into a product
-    kernels = ("conv", "ssm", "ssd", "norm", "linear_skinny", "gemm_tcgen05")
+    kernels = ("conv", "ssm", "ssd", "ssd_tc", "norm", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
         self.spec = spec

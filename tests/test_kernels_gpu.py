@@ -501,7 +501,9 @@ def chunk_lists(lens, L):
 
 
 @pytest.mark.parametrize("shape", [(4, 16, 16, 1, 8), (6, 24, 32, 2, 16), (3, 64, 128, 1, 128), (2, 40, 256, 2, 64),
-                                   (2, 128, 64, 1, 32), (5, 8, 24, 5, 256)])
+                                   (2, 128, 64, 1, 32), (5, 8, 24, 5, 256),
+                                   # head size 64 with chunks of 128: the tcgen05 chunk scan, state sizes 64 to 256
+                                   (4, 64, 64, 2, 128), (2, 64, 192, 1, 128), (2, 64, 256, 2, 256), (3, 64, 128, 1, 64)])
 def test_ssd_prefill_in_chunks_resumes_from_state_and_matches_the_recurrence(shape):
     nh, Pd, N, G, chunk = shape
     dtype = torch.bfloat16
@@ -545,7 +547,8 @@ def test_ssd_prefill_in_chunks_resumes_from_state_and_matches_the_recurrence(sha
         z_wide = torch.zeros(z_d.shape[0], inner + 12, dtype=dtype, device="cuda")
         z_view = z_wide[:, 4:4 + inner]
         z_view.copy_(z_d)
-        assert torch.equal(k.ssd_prefill(conv_d, dt_d, *common, st_before2, *lists, nh, Pd, N, G, 0.8, z_view, 0.6), yg)
+        y_view = k.ssd_prefill(conv_d, dt_d, *common, st_before2, *lists, nh, Pd, N, G, 0.8, z_view, 0.6)
+        assert torch.equal(y_view, yg)
         k.ssm_scan(conv_d, dt_d, *common, state_seq, dev(cu), dev(sp), dev(slots), 3, nh, Pd, N, G, 0.8)
         for r in range(3):
             got[r].append(y[int(cu[r]):int(cu[r + 1])].cpu())

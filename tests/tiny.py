@@ -50,7 +50,17 @@ TINY_C = {
     "num_attention_heads": 4, "num_key_value_heads": 4, "head_dim": 48, "vocab_size": 300,
 }
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# a fourth one with the head sizes of the released models (attention heads of 64, SSM heads of 64 with 128-token
+# chunks): in bfloat16 its prompt portions run on the tcgen05 attention and chunk-scan kernels
+TINY_D = {
+    **copy.deepcopy(TINY_B),
+    "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "intermediate_size": 176, "vocab_size": 389, "rms_norm_eps": 1e-5,
+    "mamba_d_ssm": 192, "mamba_n_heads": 3, "mamba_d_head": 64, "mamba_d_state": 64, "mamba_n_groups": 1,
+    "mamba_d_conv": 4, "mamba_chunk_size": 128, "mamba_rms_norm": False,
+}
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_model_dir(path: str, raw: dict, seed: int = 0, dtype=torch.float32, perturb: bool = True) -> str:
