@@ -183,6 +183,115 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
     }
 }
 
+// Long portions (bfloat16, the same alignment rules): a CTA of 256 threads stages kTileTokens + K - 1 rows of 256
+// channels in shared memory, already scaled and rounded, each row fetched once with 16-byte loads that are all in
+// flight together; a thread then walks 4 consecutive tokens of 8 channels.  One thread per 32 outputs instead of
+// per 64 with the rows shared through shared memory: four times the warps of the register form above, which at
+// 2,048 tokens left the SMs a dozen warps each.
+constexpr int kTileTokens = 32, kTileGroups = 32, kTileThreads = 256;
+
+template <int K>
+__global__ void __launch_bounds__(kTileThreads, 3) conv_forward_tile_kernel(ConvArgs a) {
+    typedef __nv_bfloat16 T;
+    constexpr int kRows = kTileTokens + K - 1;
+    __shared__ __align__(16) T tile[kRows][kTileGroups * 8];
+    const int b = blockIdx.z;
+    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
+    const int t0 = blockIdx.y * kTileTokens;
+    if (t0 >= len) return;
+    const int c0 = blockIdx.x * kTileGroups * 8;
+    const bool has_history = a.start_pos[b] > 0;
+    const T* x = (const T*)a.x;
+    const T* st = (const T*)a.state + (size_t)a.slots[b] * a.C * (K - 1);
+    const int g = threadIdx.x % kTileGroups, ts = threadIdx.x / kTileGroups;
+    const int c = c0 + g * 8;
+    const bool live = c < a.C;
+    // The CTA's taps and biases go through shared memory: its 256 channels are one contiguous run of K * 256 floats,
+    // fetched coalesced.  (A thread fetching its own 8 * K floats makes every load instruction of a warp touch 32
+    // different lines; that was most of this kernel's time.)  A thread's 8 channels lie 8 * K + 4 floats from the
+    // next thread's, so that the 16-byte reads below spread over all banks.
+    constexpr int kWPitch = 8 * K + 4;
+    __shared__ __align__(16) float w_s[kTileGroups * kWPitch];
+    __shared__ __align__(16) float bias_s[kTileGroups * 8];
+    for (int f = threadIdx.x; f < kTileGroups * 8 * K; f += kTileThreads) {
+        const int ch = f / K, j = f - ch * K;
+        w_s[(ch >> 3) * kWPitch + (ch & 7) * K + j] = c0 + ch < a.C ? __ldg(a.weight + (size_t)c0 * K + f) : 0.f;
+    }
+    bias_s[threadIdx.x] = (a.bias != nullptr && c0 + (int)threadIdx.x < a.C) ? __ldg(a.bias + c0 + threadIdx.x) : 0.f;
+    // rows t0 - (K - 1) .. t0 + kTileTokens - 1 of the portion; row rr of the tile, channel group g
+    constexpr int kPer = (kRows + kTileThreads / kTileGroups - 1) / (kTileThreads / kTileGroups);
+    const float scale = c < a.end0 ? a.s0 : (c < a.end1 ? a.s1 : a.s2);
+    uint4 fetched[kPer];
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int rr = ts + i * (kTileThreads / kTileGroups), idx = t0 - (K - 1) + rr;
+        if (live && rr < kRows && idx >= 0 && idx < len)
+            fetched[i] = *reinterpret_cast<const uint4*>(x + (size_t)(begin + idx) * a.x_stride + c);
+    }
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int rr = ts + i * (kTileThreads / kTileGroups), idx = t0 - (K - 1) + rr;
+        if (!live || rr >= kRows) continue;
+        __nv_bfloat162 o[4];
+        if (idx >= 0 && idx < len) {
+            float f[8];
+            unpack8(fetched[i], f);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(f[2 * e] * scale, f[2 * e + 1] * scale);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {                 // before the portion: the saved inputs, or zeros
+                const T v = (idx < 0 && has_history) ? st[(size_t)(c + e) * (K - 1) + K - 1 + idx] : __float2bfloat16_rn(0.f);
+                if (e & 1) o[e >> 1].y = v; else o[e >> 1].x = v;
+            }
+        }
+        *reinterpret_cast<uint4*>(&tile[rr][g * 8]) = *reinterpret_cast<uint4*>(o);
+    }
+    __syncthreads();
+    if (!live) return;
+    float w[8][K], bias[8];
+    {
+        const float* flat = w_s + g * kWPitch;            // K * 8 floats: 16-byte reads when K is even, else single ones
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+#pragma unroll
+            for (int j = 0; j < K; ++j) w[e][j] = flat[e * K + j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) bias[e] = bias_s[g * 8 + e];
+    }
+    constexpr int kWalk = kTileTokens / (kTileThreads / kTileGroups);      // 4 consecutive tokens per thread
+    const int first = ts * kWalk;
+    float win[8][K];
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(&tile[first + j][g * 8]), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[e][j] = f[e];
+    }
+#pragma unroll
+    for (int i = 0; i < kWalk; ++i) {
+        const int t = t0 + first + i;
+        if (t >= len) break;
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(&tile[first + i + K - 1][g * 8]), f);
+        __nv_bfloat162 o[4];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            win[e][K - 1] = f[e];
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < K; ++j) acc += win[e][j] * w[e][j];
+            acc = round_to<T>(acc + bias[e]);
+            acc = __fdividef(acc, 1.f + __expf(-acc));      // SiLU; the result is rounded to bfloat16 next
+            if (e & 1) o[e >> 1].y = __float2bfloat16_rn(acc); else o[e >> 1].x = __float2bfloat16_rn(acc);
+#pragma unroll
+            for (int j = 0; j < K - 1; ++j) win[e][j] = win[e][j + 1];
+        }
+        *reinterpret_cast<uint4*>((T*)a.out + (size_t)(begin + t) * a.C + c) = *reinterpret_cast<uint4*>(o);
+    }
+}
+
 template <int K>
 void launch_vec(const ConvArgs& a, int B, int max_len, cudaStream_t s) {
     const int threads = 128, groups = a.C / 8;
@@ -191,7 +300,10 @@ void launch_vec(const ConvArgs& a, int B, int max_len, cudaStream_t s) {
         conv_forward_vec_kernel<K, true><<<grid_f, threads, 0, s>>>(a);
     } else {
         dim3 grid_u((a.C + threads - 1) / threads, B);
-        conv_forward_vec_kernel<K, false><<<grid_f, threads, 0, s>>>(a);
+        dim3 grid_t((groups + kTileGroups - 1) / kTileGroups, (max_len + kTileTokens - 1) / kTileTokens, B);
+        static const bool tiled = [] { const char* e = getenv("LOGSSMS_B200_CONV_TILE"); return e == nullptr || e[0] != '0'; }();
+        if (tiled) conv_forward_tile_kernel<K><<<grid_t, kTileThreads, 0, s>>>(a);
+        else conv_forward_vec_kernel<K, false><<<grid_f, threads, 0, s>>>(a);
         conv_state_update_kernel<__nv_bfloat16, K><<<grid_u, threads, 0, s>>>(a);
     }
 }
