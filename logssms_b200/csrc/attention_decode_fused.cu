@@ -467,9 +467,45 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     // Up to here only step tables and keys and values of earlier tokens were read: that may run under the tail of
     // the q|k|v projection before this kernel.  Its output is read from here on.
     pdl_wait();
-    for (int i = threadIdx.x; i < 16 * hd; i += kThreads) {
-        const int g = i / hd, c = i % hd;
-        q_s[g * ld + c] = __float2bfloat16_rn(g < G ? rotated<bf16>(row + (size_t)(h0 + g) * hd, c, a.rotary_dim, cs, 1.f, false) : 0.f);
+    const int half = a.rotary_dim >> 1;
+    if ((half & 7) == 0 && (a.row_stride & 7) == 0 && ((uintptr_t)a.qkv & 15) == 0) {
+        // eight columns per thread: the piece, its partner half a rotation away, cos and sin come as 16-byte loads
+        // that are all in flight together (element by element this was a chain of 2- and 4-byte loads per column)
+        for (int i = threadIdx.x; i < 16 * pieces; i += kThreads) {
+            const int g = i / pieces, c0 = (i - g * pieces) * 8;
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (g < G) {
+                const bf16* src = row + (size_t)(h0 + g) * hd;
+                packed = *reinterpret_cast<const uint4*>(src + c0);
+                if (c0 < a.rotary_dim) {
+                    const bool low = c0 < half;
+                    const int f0 = low ? c0 : c0 - half;
+                    const uint4 other = *reinterpret_cast<const uint4*>(src + (low ? c0 + half : c0 - half));
+                    const float4 cA = *reinterpret_cast<const float4*>(cs + f0), cB = *reinterpret_cast<const float4*>(cs + f0 + 4);
+                    const float4 sA = *reinterpret_cast<const float4*>(cs + half + f0), sB = *reinterpret_cast<const float4*>(cs + half + f0 + 4);
+                    const float cosv[8] = {cA.x, cA.y, cA.z, cA.w, cB.x, cB.y, cB.z, cB.w};
+                    const float sinv[8] = {sA.x, sA.y, sA.z, sA.w, sB.x, sB.y, sB.z, sB.w};
+                    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&packed);
+                    const __nv_bfloat162* yh = reinterpret_cast<const __nv_bfloat162*>(&other);
+                    uint4 res;
+                    unsigned* rw = reinterpret_cast<unsigned*>(&res);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 x = __bfloat1622float2(xh[e]), y = __bfloat1622float2(yh[e]);
+                        const float v0 = x.x * cosv[2 * e] + (low ? -y.x : y.x) * sinv[2 * e];
+                        const float v1 = x.y * cosv[2 * e + 1] + (low ? -y.y : y.y) * sinv[2 * e + 1];
+                        rw[e] = pack_bf16(v0, v1);
+                    }
+                    packed = res;
+                }
+            }
+            *reinterpret_cast<uint4*>(q_s + g * ld + c0) = packed;
+        }
+    } else {
+        for (int i = threadIdx.x; i < 16 * hd; i += kThreads) {
+            const int g = i / hd, c = i % hd;
+            q_s[g * ld + c] = __float2bfloat16_rn(g < G ? rotated<bf16>(row + (size_t)(h0 + g) * hd, c, a.rotary_dim, cs, 1.f, false) : 0.f);
+        }
     }
     if (owns_new) {
         const bf16* ksrc = row + (size_t)(a.Hq + kvh) * hd;
@@ -618,16 +654,30 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     if (used == 1) return;
     if (CL) {
         cluster_barrier();                                // every range's partial result stands in its CTA's shared memory
-        if (split == 0) {
-            for (int i = threadIdx.x; i < G * hd; i += kThreads) {
+        // Every CTA of the cluster merges a contiguous share of the G * hd outputs, one output per thread, and
+        // asks for all ranges' values at once: the loads from the other CTAs' shared memory take hundreds of
+        // cycles each, so one CTA walking the ranges one after the other was a quarter of the kernel's time.
+        {
+            const int n_out = G * hd, per = (n_out + a.splits - 1) / a.splits;
+            for (int i = split * per + threadIdx.x; i < min(n_out, (split + 1) * per); i += kThreads) {
                 const int g = i / hd, d = i % hd;
+                float mv[8], lv[8], ov[8];
+#pragma unroll
+                for (int s2 = 0; s2 < 8; ++s2) {
+                    const bool on = s2 < used;
+                    mv[s2] = on ? ld_cluster(cluster_map(cta_part + g * stride + hd, s2)) : -INFINITY;
+                    lv[s2] = on ? ld_cluster(cluster_map(cta_part + g * stride + hd + 1, s2)) : 0.f;
+                    ov[s2] = on ? ld_cluster(cluster_map(cta_part + g * stride + d, s2)) : 0.f;
+                }
                 float mt = -INFINITY;
-                for (int s2 = 0; s2 < used; ++s2) mt = fmaxf(mt, ld_cluster(cluster_map(cta_part + g * stride + hd, s2)));
+#pragma unroll
+                for (int s2 = 0; s2 < 8; ++s2) mt = fmaxf(mt, mv[s2]);
                 float lsum = 0.f, osum = 0.f;
-                for (int s2 = 0; s2 < used; ++s2) {
-                    const float f = expf(ld_cluster(cluster_map(cta_part + g * stride + hd, s2)) - mt);
-                    lsum += ld_cluster(cluster_map(cta_part + g * stride + hd + 1, s2)) * f;
-                    osum += ld_cluster(cluster_map(cta_part + g * stride + d, s2)) * f;
+#pragma unroll
+                for (int s2 = 0; s2 < 8; ++s2) {
+                    const float f = s2 < used ? expf(mv[s2] - mt) : 0.f;
+                    lsum += lv[s2] * f;
+                    osum += ov[s2] * f;
                 }
                 ((bf16*)a.out)[(t * a.Hq + h0 + g) * hd + d] = __float2bfloat16_rn(osum / lsum);
             }
