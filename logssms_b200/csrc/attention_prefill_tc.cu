@@ -219,7 +219,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         const int c = c8 * 8 + 2 * e;
                         const float x0 = __uint_as_float(c < 32 ? s0[c] : s1[c - 32]);
                         const float x1 = __uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]);
-                        const float e0 = exp2f(fmaf(x0, a.scale_log2, -ref)), e1 = exp2f(fmaf(x1, a.scale_log2, -ref));
+                        const float e0 = ex2_approx(fmaf(x0, a.scale_log2, -ref)), e1 = ex2_approx(fmaf(x1, a.scale_log2, -ref));
                         sum += e0 + e1;
                         __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
                         pw[e] = *reinterpret_cast<uint32_t*>(&pr);

@@ -92,6 +92,14 @@ __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence
 // writes of this thread to shared memory become visible to the tensor core's and TMA's reads
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// 2^x in one special-function instruction (relative error 2^-22, results below 2^-126 flushed to zero): for softmax
+// weights and decay factors, which lie in [0, 1] and are rounded to bfloat16 operands next
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

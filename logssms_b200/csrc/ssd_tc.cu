@@ -226,8 +226,8 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
                         for (int e = 0; e < 4; ++e) {
                             const int c = j * 8 + 2 * e, s0 = cb * 32 + c;
                             const float4 ad = *reinterpret_cast<const float4*>(ad_s + s0);      // (a, dt) of s0 and s0 + 1
-                            const float w0 = s0 <= last ? __uint_as_float(gv[c]) * exp2f(at - ad.x) * ad.y : 0.f;
-                            const float w1 = s0 + 1 <= last ? __uint_as_float(gv[c + 1]) * exp2f(at - ad.z) * ad.w : 0.f;
+                            const float w0 = s0 <= last ? __uint_as_float(gv[c]) * ex2_approx(at - ad.x) * ad.y : 0.f;
+                            const float w1 = s0 + 1 <= last ? __uint_as_float(gv[c + 1]) * ex2_approx(at - ad.z) * ad.w : 0.f;
                             pw[e] = pack2(w0, w1);
                         }
                         *reinterpret_cast<uint4*>(w_row + (((hf * 4 + j) ^ (r & 7)) * 16)) = piece;
@@ -266,8 +266,9 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
                         if (gated) {
                             const float2 zf = __bfloat1622float2(zh[e]);
                             const float z0 = round_to<bf16>(zf.x * a.gate_scale), z1 = round_to<bf16>(zf.y * a.gate_scale);
-                            v0 = round_to<bf16>(v0) * round_to<bf16>(silu_f(z0));
-                            v1 = round_to<bf16>(v1) * round_to<bf16>(silu_f(z1));
+                            // SiLU by the fast exponential and division: its result is rounded to bfloat16 next
+                            v0 = round_to<bf16>(v0) * round_to<bf16>(__fdividef(z0, 1.f + __expf(-z0)));
+                            v1 = round_to<bf16>(v1) * round_to<bf16>(__fdividef(z1, 1.f + __expf(-z1)));
                         }
                         pw[e] = pack2(v0, v1);
                     }

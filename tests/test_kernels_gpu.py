@@ -542,7 +542,11 @@ def test_ssd_prefill_in_chunks_resumes_from_state_and_matches_the_recurrence(sha
         st_before, st_before2 = state.clone(), state.clone()
         y = k.ssd_prefill(conv_d, dt_d, *common, state, *lists, nh, Pd, N, G, 0.8)
         yg = k.ssd_prefill(conv_d, dt_d, *common, st_before, *lists, nh, Pd, N, G, 0.8, z_d, 0.6)
-        assert torch.equal(yg, k.gated_rmsnorm(y, z_d, None, 1e-5, 1, 0.6, k.GATE_ONLY))
+        y_then_gate = k.gated_rmsnorm(y, z_d, None, 1e-5, 1, 0.6, k.GATE_ONLY)
+        if k.ssd_chunk_scan_tc_ok(Pd, N, L):             # that kernel's SiLU is the fast one: a last bit may differ
+            close(yg, y_then_gate, dtype, tol=1e-2)
+        else:
+            assert torch.equal(yg, y_then_gate)
         # the gate as a view whose rows start on no 16-byte boundary (the kernel copies it piece by piece then)
         z_wide = torch.zeros(z_d.shape[0], inner + 12, dtype=dtype, device="cuda")
         z_view = z_wide[:, 4:4 + inner]
