@@ -2,11 +2,12 @@
 // (tcgen05, accumulators in tensor memory, operands brought by TMA).  bfloat16, head size 64, pages of a
 // multiple of 64 tokens; every other shape stays on the mma.sync kernel (attention_prefill.cu).
 //
-// One CTA per (128 query tokens of one request's portion, query head), 6 warps:
+// One CTA per (128 query tokens of one request's portion, query head), 11 warps:
 //   warp 0    one thread: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the Q tile once, then of the
 //             K and V tiles (64 keys each: one box per tile, since a tile never crosses a page) into a ring of
 //             stages, each with a "full" and an "empty" mbarrier; the page of a tile comes from the block table
-//   warp 1    allocates 128 columns of tensor memory; one thread issues the products
+//   warp 1    allocates 256 columns of tensor memory; one thread issues the first softmax group's products,
+//   warp 10   one thread those of the second group:
 //                 S  = Q K^T   (M 128 queries, N 64 keys, K 64 dims: 4 x tcgen05.mma, both operands K-major)
 //                 PV = P V     (M 128, N 64 dims, K 64 keys: 4 x tcgen05.mma, V as an MN-major operand: the rows of
 //                               the cache are keys, which is the K dimension of this product)
@@ -14,8 +15,8 @@
 //   warps 2-9 two groups of 128 threads, one thread per query row in each; group g owns the key tiles g, g + 2, ...
 //             with its own S, PV, P and running (maximum, sum, output), so that one group's chain of
 //             product -> softmax -> product -> rescale runs while the other waits for the tensor core; the two
-//             partial results meet in shared memory at the end.  A thread: read the row of S from tensor memory (tcgen05.ld), mask by absolute
-//             position (causal, optional window), online softmax in float32 (running maximum and sum), round P to
+//             partial results meet in shared memory at the end.  A thread: read the row of S from tensor memory
+//             (tcgen05.ld), mask by absolute position (causal, optional window), online softmax in float32 (running maximum and sum), round P to
 //             bfloat16 into shared memory in the swizzled K-major layout the tensor core reads, then read the row
 //             of PV and fold it into the float32 output row kept in registers: O = O * alpha + PV
 // Keys of the last tile beyond the newest token are rows of the page that nobody has written for this request:
@@ -37,7 +38,8 @@ typedef __nv_bfloat16 bf16;
 constexpr int kQ = 128, kKV = 64, kHD = 64;               // queries per CTA, keys per tile, head size
 constexpr int kStages = 4;
 constexpr int kGroups = 2;                               // softmax groups of 128 threads
-constexpr int kThreads = 64 + kGroups * 128;
+constexpr int kIssuer1 = 2 + kGroups * 4;                 // the warp whose first thread issues the second group's products
+constexpr int kThreads = 64 + kGroups * 128 + 32;
 constexpr uint32_t kQBytes = kQ * kHD * 2, kTileBytes = kKV * kHD * 2, kPBytes = kQ * kKV * 2;
 constexpr uint32_t kTmemCols = 128 * kGroups;             // per group: S in columns 0..63, PV in columns 64..127
 constexpr uint32_t kMergeBytes = (kHD + 2) * kQ * 4;      // group 1's partial result, [column][row] float32
@@ -72,8 +74,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* s_ready = q_full + 1;                       // per group: S of its tile is in tensor memory
     uint64_t* p_ready = s_ready + kGroups;                // per group: P of its tile is in shared memory (128 arrivals)
     uint64_t* o_ready = p_ready + kGroups;                // per group: PV of its tile is in tensor memory
-    uint64_t* pv_free = o_ready + kGroups;                // per group: its rows have read PV (128 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_free + kGroups);
+    uint64_t* s_free = o_ready + kGroups;                 // per group: its rows hold S in registers (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + kGroups);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -93,7 +95,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_init(q_full, 1);
         for (int g = 0; g < kGroups; ++g) {
             mbar_init(s_ready + g, 1); mbar_init(o_ready + g, 1);
-            mbar_init(p_ready + g, 128); mbar_init(pv_free + g, 128);
+            mbar_init(p_ready + g, 128); mbar_init(s_free + g, 128);
         }
         *failed = 0;
         mbar_fence_init();
@@ -127,16 +129,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int i = max(0, issued - kStages); i < issued; ++i) mbar_wait(kv_full + i % kStages, (i / kStages) & 1);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == kIssuer1) {
         if (lane == 0) {
-            // float32 accumulator, bfloat16 operands, N 64, M 128; bit 16: the B operand is MN-major (V)
+            // One issuing thread per softmax group (its tiles g, g + 2, ...): a thread that serves both waits for one
+            // group's P while the other group's is ready.
+            const int g = warp == 1 ? 0 : 1;
+            // float32 accumulator, bfloat16 operands, N 64, M 128; the B operand of PV is MN-major (V)
             const uint32_t idesc_s = umma_idesc(kQ, kKV);
             const uint32_t idesc_o = idesc_s | kBMnMajor;
             const uint64_t qdesc = umma_desc(q_s);
+            const uint64_t pdesc = umma_desc(p_s + (size_t)g * kPBytes);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) { report(a.error, 2, 0xFFF); *failed = 1; }
-            auto issue_s = [&](int i) -> bool {            // S of tile i, into its group's columns
-                const int s = i % kStages, g = i % kGroups;
+            auto issue_s = [&](int i) -> bool {            // S of tile i, into the group's columns
+                const int s = i % kStages;
                 if (!mbar_wait(kv_full + s, (i / kStages) & 1)) { report(a.error, 2, i); *failed = 1; return false; }
                 fence_after_sync();
                 const uint64_t kdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes);
@@ -145,21 +151,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 umma_commit(s_ready + g);
                 return true;
             };
-            for (int i = 0; i < kGroups && i < n_kt && ok; ++i) ok = issue_s(i);
-            for (int i = 0; i < n_kt && ok && !*failed; ++i) {
-                const int s = i % kStages, g = i % kGroups, t = i / kGroups;
-                // P of tile i is written, and the group's rows are done with S of tile i and with PV of its tile before
+            if (ok && g < n_kt) ok = issue_s(g);
+            for (int i = g, t = 0; i < n_kt && ok && !*failed; i += kGroups, ++t) {
+                const int s = i % kStages;
+                // the rows hold S of tile i in registers: S of the group's next tile may go over it, and runs under
+                // this tile's softmax
+                if (!mbar_wait(s_free + g, t & 1)) { report(a.error, 4, i); *failed = 1; break; }
+                if (i + kGroups < n_kt && !(ok = issue_s(i + kGroups))) break;
+                // P of tile i is written, and the rows have read PV of the group's tile before
                 if (!mbar_wait(p_ready + g, t & 1)) { report(a.error, 3, i); *failed = 1; break; }
-                if (t > 0 && !mbar_wait(pv_free + g, (t - 1) & 1)) { report(a.error, 4, i); *failed = 1; break; }
                 fence_after_sync();
-                const uint64_t pdesc = umma_desc(p_s + (size_t)g * kPBytes);
                 const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes);
 #pragma unroll
                 for (int k = 0; k < kKV / 16; ++k)         // 16 keys: two 8-row groups of V = 2048 bytes; 32 bytes along a row of P
                     umma_bf16(tmem + g * 128 + 64, pdesc + 2 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, k != 0);
                 umma_commit(o_ready + g);
                 umma_commit(kv_empty + s);                 // both products have read the stage
-                if (i + kGroups < n_kt) ok = issue_s(i + kGroups);
             }
         }
     } else {
@@ -174,6 +181,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         float m = -INFINITY, l = 0.f;
         uint8_t* p_row = p_s + (size_t)grp * kPBytes + (size_t)r * 128;
         bool ok = true;
+        float alpha_prev = 1.f;                            // the factor O takes before the product of the tile before is added
+        int done = 0;                                      // tiles of this group whose P has been handed over
+        // O <- O * alpha_prev + PV of the group's tile before: asked for only after the next tile's softmax, so that
+        // the product runs under that arithmetic instead of being waited for
+        auto fold = [&](int t_of, int tile) -> bool {
+            bool good = mbar_wait(o_ready + grp, t_of & 1);
+            if (!good && lane == 0) { report(a.error, 6, tile); *failed = 1; }
+            if (!__all_sync(0xffffffffu, good && !*failed)) return false;
+            fence_after_sync();
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t pv[32];
+                tmem_ld32(lane_addr + 64 + half * 32, pv);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[half * 32 + c] = fmaf(o[half * 32 + c], alpha_prev, __uint_as_float(pv[c]));
+            }
+            return true;
+        };
         for (int i = grp, t = 0; i < n_kt; i += kGroups, ++t) {
             const int j0 = (kt_begin + i) * kKV;
             ok = mbar_wait(s_ready + grp, t & 1);
@@ -188,22 +213,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     *reinterpret_cast<uint4*>(v_tile + (size_t)(first_bad + x / 8) * 128 + (x % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
             }
             const bool whole = j0 + kKV - 1 <= pos0 && (a.window <= 0 || j0 >= pos0 + kQ - a.window);
+            uint32_t pk[32];                               // the row of P, two bfloat16 per word
             float alpha;
             {
                 uint32_t s0[32], s1[32];
                 tmem_ld32(lane_addr, s0);
                 tmem_ld32(lane_addr + 32, s1);
+                // the row of S is in registers: the tensor core may write the group's next S over it
+                fence_before_sync();
+                mbar_arrive(s_free + grp);
                 float mx = -INFINITY;
+                if (whole) {                               // no key of the tile is masked for any row: the common case
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float v0 = __uint_as_float(s0[c]), v1 = __uint_as_float(s1[c]);
-                    if (!whole) {
+                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        float v0 = __uint_as_float(s0[c]), v1 = __uint_as_float(s1[c]);
                         const int ka = j0 + c, kb = j0 + 32 + c;
                         if (ka > p || ka < lo_r) v0 = -INFINITY;
                         if (kb > p || kb < lo_r) v1 = -INFINITY;
                         s0[c] = __float_as_uint(v0); s1[c] = __float_as_uint(v1);
+                        mx = fmaxf(mx, fmaxf(v0, v1));
                     }
-                    mx = fmaxf(mx, fmaxf(v0, v1));
                 }
                 const float m_new = fmaxf(m, mx * a.scale_log2);
                 const float ref = m_new == -INFINITY ? 0.f : m_new;     // a row that has seen no key yet
@@ -211,40 +243,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 m = m_new;
                 float sum = 0.f;
 #pragma unroll
-                for (int c8 = 0; c8 < 8; ++c8) {           // 8 keys = one 16-byte piece of the row of P
-                    uint4 piece;
-                    uint32_t* pw = reinterpret_cast<uint32_t*>(&piece);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = c8 * 8 + 2 * e;
-                        const float x0 = __uint_as_float(c < 32 ? s0[c] : s1[c - 32]);
-                        const float x1 = __uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]);
-                        const float e0 = ex2_approx(fmaf(x0, a.scale_log2, -ref)), e1 = ex2_approx(fmaf(x1, a.scale_log2, -ref));
-                        sum += e0 + e1;
-                        __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-                        pw[e] = *reinterpret_cast<uint32_t*>(&pr);
-                    }
-                    *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) * 16)) = piece;
+                for (int c = 0; c < 64; c += 2) {
+                    const float x0 = __uint_as_float(c < 32 ? s0[c] : s1[c - 32]);
+                    const float x1 = __uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]);
+                    const float e0 = ex2_approx(fmaf(x0, a.scale_log2, -ref)), e1 = ex2_approx(fmaf(x1, a.scale_log2, -ref));
+                    sum += e0 + e1;
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+                    pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pr);
                 }
                 l = l * alpha + sum;
             }
+            // the product of the tile before has had this tile's softmax to finish; it has read P, and once its result
+            // is folded in, the next one may write over it
+            if (t > 0 && !fold(t - 1, i - kGroups)) { ok = false; break; }
+            alpha_prev = alpha;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8)                 // 8 keys = one 16-byte piece of the row of P
+                *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) * 16)) = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
             fence_async_smem();                            // P (and the zeroed V rows) are for the tensor core's reads
             fence_before_sync();
             mbar_arrive(p_ready + grp);
-            ok = mbar_wait(o_ready + grp, t & 1);
-            if (!ok && lane == 0) { report(a.error, 6, i); *failed = 1; }
-            if (!__all_sync(0xffffffffu, ok && !*failed)) { ok = false; break; }
-            fence_after_sync();
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t pv[32];
-                tmem_ld32(lane_addr + 64 + half * 32, pv);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) o[half * 32 + c] = fmaf(o[half * 32 + c], alpha, __uint_as_float(pv[c]));
-            }
-            fence_before_sync();
-            mbar_arrive(pv_free + grp);
+            done = t + 1;
         }
+        if (ok && done > 0) ok = fold(done - 1, grp + (done - 1) * kGroups);
         // the groups' partial results meet: group 1 leaves its row in shared memory ([column][row]: a warp's rows lie
         // side by side), group 0 folds it into its own
         if (grp == 1) {
