@@ -217,20 +217,35 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
                 } else {
                     uint32_t gv[32];
                     tmem_ld32(lane_addr + cb * 32, gv);
-                    const int last = cb < wq ? kL : r;     // the last token s this row takes
+                    if (cb < wq) {                         // below the diagonal block: every token s counts
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint4 piece;
-                        uint32_t* pw = reinterpret_cast<uint32_t*>(&piece);
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 piece;
+                            uint32_t* pw = reinterpret_cast<uint32_t*>(&piece);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int c = j * 8 + 2 * e, s0 = cb * 32 + c;
-                            const float4 ad = *reinterpret_cast<const float4*>(ad_s + s0);      // (a, dt) of s0 and s0 + 1
-                            const float w0 = s0 <= last ? __uint_as_float(gv[c]) * ex2_approx(at - ad.x) * ad.y : 0.f;
-                            const float w1 = s0 + 1 <= last ? __uint_as_float(gv[c + 1]) * ex2_approx(at - ad.z) * ad.w : 0.f;
-                            pw[e] = pack2(w0, w1);
+                            for (int e = 0; e < 4; ++e) {
+                                const int c = j * 8 + 2 * e;
+                                const float4 ad = *reinterpret_cast<const float4*>(ad_s + cb * 32 + c);     // (a, dt) of two tokens
+                                pw[e] = pack2(__uint_as_float(gv[c]) * ex2_approx(at - ad.x) * ad.y,
+                                              __uint_as_float(gv[c + 1]) * ex2_approx(at - ad.z) * ad.w);
+                            }
+                            *reinterpret_cast<uint4*>(w_row + (((hf * 4 + j) ^ (r & 7)) * 16)) = piece;
                         }
-                        *reinterpret_cast<uint4*>(w_row + (((hf * 4 + j) ^ (r & 7)) * 16)) = piece;
+                    } else {                               // the diagonal block: tokens s <= r
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 piece;
+                            uint32_t* pw = reinterpret_cast<uint32_t*>(&piece);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int c = j * 8 + 2 * e, s0 = cb * 32 + c;
+                                const float4 ad = *reinterpret_cast<const float4*>(ad_s + s0);
+                                const float w0 = s0 <= r ? __uint_as_float(gv[c]) * ex2_approx(at - ad.x) * ad.y : 0.f;
+                                const float w1 = s0 + 1 <= r ? __uint_as_float(gv[c + 1]) * ex2_approx(at - ad.z) * ad.w : 0.f;
+                                pw[e] = pack2(w0, w1);
+                            }
+                            *reinterpret_cast<uint4*>(w_row + (((hf * 4 + j) ^ (r & 7)) * 16)) = piece;
+                        }
                     }
                 }
             }
