@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
 #pragma unroll
                 for (int j = 0; j < K; ++j) acc += win[e][j] * w[e][j];
                 acc = round_to<T>(acc + bias[e]);
-                acc = __fdividef(acc, 1.f + __expf(-acc));      // SiLU; the result is rounded to bfloat16 next
+                acc = silu_fast(acc);                            // the result is rounded to bfloat16 next
                 if (e & 1) o[e >> 1].y = __float2bfloat16_rn(acc); else o[e >> 1].x = __float2bfloat16_rn(acc);
 #pragma unroll
                 for (int j = 0; j < K - 1; ++j) win[e][j] = win[e][j + 1];
@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(kTileThreads, 3) conv_forward_tile_kernel(Conv
 #pragma unroll
             for (int j = 0; j < K; ++j) acc += win[e][j] * w[e][j];
             acc = round_to<T>(acc + bias[e]);
-            acc = __fdividef(acc, 1.f + __expf(-acc));      // SiLU; the result is rounded to bfloat16 next
+            acc = silu_fast(acc);                            // the result is rounded to bfloat16 next
             if (e & 1) o[e >> 1].y = __float2bfloat16_rn(acc); else o[e >> 1].x = __float2bfloat16_rn(acc);
 #pragma unroll
             for (int j = 0; j < K - 1; ++j) win[e][j] = win[e][j + 1];

@@ -63,6 +63,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+// the same by the fast exponential and division (a few units in the last place of float32): for bfloat16 kernels that
+// round the result to bfloat16 next and whose time the accurate form would set
+__device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.f + __expf(-v)); }
 
 // Programmatic dependent launch.  A kernel that is launched with `launch_pdl` may start while the kernel
 // before it on the stream still runs; everything it does before `pdl_wait()` must not depend on that

@@ -222,8 +222,8 @@ __global__ void swiglu_vec_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfl
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
         const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-        const float a0 = round_to<T>(silu_f(round_to<T>(g.x * act_scale)));
-        const float a1 = round_to<T>(silu_f(round_to<T>(g.y * act_scale)));
+        const float a0 = round_to<T>(silu_fast(round_to<T>(g.x * act_scale)));
+        const float a1 = round_to<T>(silu_fast(round_to<T>(g.y * act_scale)));
         o2[e] = __floats2bfloat162_rn(a0 * u.x, a1 * u.y);
     }
     *reinterpret_cast<uint4*>(out + r * I + c) = ov;

@@ -282,8 +282,8 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
                             const float2 zf = __bfloat1622float2(zh[e]);
                             const float z0 = round_to<bf16>(zf.x * a.gate_scale), z1 = round_to<bf16>(zf.y * a.gate_scale);
                             // SiLU by the fast exponential and division: its result is rounded to bfloat16 next
-                            v0 = round_to<bf16>(v0) * round_to<bf16>(__fdividef(z0, 1.f + __expf(-z0)));
-                            v1 = round_to<bf16>(v1) * round_to<bf16>(__fdividef(z1, 1.f + __expf(-z1)));
+                            v0 = round_to<bf16>(v0) * round_to<bf16>(silu_fast(z0));
+                            v1 = round_to<bf16>(v1) * round_to<bf16>(silu_fast(z1));
                         }
                         pw[e] = pack2(v0, v1);
                     }
