@@ -777,7 +777,18 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
                 cos_sin, table_rows, rotary_dim, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
                 write_kv, scale, key_scale};
     if (dtype == kBF16 && hd <= 128 && Hq / Hkv <= 16)
-        return hd <= 64 ? launch_mma<4, 2>(a, tokens, (cudaStream_t)stream) : launch_mma<8, 2>(a, tokens, (cudaStream_t)stream);
+    {
+        // Stages of a warp's tile ring: 3 for a small grid (two tiles on their way before the first is used), 2 for a
+        // large one, which then keeps three CTAs per SM.  Measured on 8-layer decode steps at batch 1 / 8 / 64:
+        // 2 stages 0.304 / 0.366 / 0.674 ms, 3 stages 0.305 / 0.361 / 0.676 ms, 4 stages 0.301 / 0.406 / 0.749 ms (their
+        // 147 KB per CTA delay the start of a cluster under the kernel before).  LOGSSMS_B200_ATTN_STAGES overrides it.
+        static const int forced = [] { const char* e = getenv("LOGSSMS_B200_ATTN_STAGES"); return e ? atoi(e) : 0; }();
+        const bool small = (long)tokens * Hkv * splits <= 2 * 148;
+        const int ns = forced >= 2 && forced <= 4 ? forced : (small ? 3 : 2);
+        cudaStream_t st = (cudaStream_t)stream;
+        if (hd <= 64) return ns >= 4 ? launch_mma<4, 4>(a, tokens, st) : (ns == 3 ? launch_mma<4, 3>(a, tokens, st) : launch_mma<4, 2>(a, tokens, st));
+        return ns >= 3 ? launch_mma<8, 3>(a, tokens, st) : launch_mma<8, 2>(a, tokens, st);
+    }
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, tokens, (cudaStream_t)stream));
     return kOk;
 }
