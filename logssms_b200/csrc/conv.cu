@@ -107,6 +107,7 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
 template <int K, bool UPDATE>
 __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
     typedef __nv_bfloat16 T;
+    static_assert(K - 1 <= kVecChunk, "only a portion's first chunk may reach back into the saved inputs");
     const int cg = blockIdx.x * blockDim.x + threadIdx.x;
     const int c = cg * 8;
     if (c >= a.C) return;
@@ -141,6 +142,13 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
 #pragma unroll
             for (int j = 0; j < K; ++j) w[e][j] = flat[e * K + j];
     }
+    // the thread's 8 channels' saved inputs are 8 * (K - 1) consecutive values: K - 1 pieces of 16 bytes, asked for
+    // together (one 2-byte load per value made a decode step's conv a chain of dependent loads)
+    __align__(16) T hist[8 * (K - 1)];
+    if (has_history && t0 == 0) {
+#pragma unroll
+        for (int j = 0; j < K - 1; ++j) reinterpret_cast<uint4*>(hist)[j] = reinterpret_cast<const uint4*>(st)[j];
+    }
 #pragma unroll
     for (int j = 0; j < K - 1; ++j) {
         const int idx = t0 - (K - 1) + j;
@@ -151,7 +159,8 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
             for (int e = 0; e < 8; ++e) win[e][j] = round_to<T>(f[e] * scale);
         } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) win[e][j] = has_history ? to_f32(st[e * (K - 1) + K - 1 + idx]) : 0.f;
+            for (int e = 0; e < 8; ++e)                  // idx < 0 only in the portion's first chunk: idx = j - (K - 1)
+                win[e][j] = has_history ? __bfloat162float(hist[e * (K - 1) + j]) : 0.f;
         }
     }
 #pragma unroll
@@ -176,10 +185,13 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
         }
     }
     if (UPDATE) {
+        __align__(16) T next[8 * (K - 1)];
 #pragma unroll
         for (int e = 0; e < 8; ++e)
 #pragma unroll
-            for (int j = 0; j < K - 1; ++j) st[e * (K - 1) + j] = __float2bfloat16_rn(win[e][j]);
+            for (int j = 0; j < K - 1; ++j) next[e * (K - 1) + j] = __float2bfloat16_rn(win[e][j]);
+#pragma unroll
+        for (int j = 0; j < K - 1; ++j) reinterpret_cast<uint4*>(st)[j] = reinterpret_cast<const uint4*>(next)[j];
     }
 }
 
@@ -311,6 +323,7 @@ void launch_vec(const ConvArgs& a, int B, int max_len, cudaStream_t s) {
 inline bool vec_ok(const ConvArgs& a, int dtype) {
     return dtype == kBF16 && a.C % 8 == 0 && a.end0 % 8 == 0 && a.end1 % 8 == 0 && a.x_stride % 8 == 0 &&
            ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.out & 15) == 0 && ((uintptr_t)a.weight & 15) == 0 &&
+           ((uintptr_t)a.state & 15) == 0 &&
            (a.bias == nullptr || ((uintptr_t)a.bias & 15) == 0);
 }
 
