@@ -38,7 +38,7 @@ struct SkinnyArgs {
     int M, N, K;
     float out_scale, act_scale;
     // optional prologue: x is not given but made here, as the RMSNorm of a residual sum
-    //   v = [round(round(nx * in0) + round(nother * in1))  or  nx] + nres ; residual_out = round(v) (one CTA writes it)
+    //   v = [round(round(nx * in0) + round(nother * in1))  or  round(nx * in0)] + nres ; residual_out = round(v) (one CTA writes it)
     //   x = round(round(v * rsqrt(mean(v^2) + eps) * nweight) * nscale)
     const __nv_bfloat16* nx; const __nv_bfloat16* nother; const __nv_bfloat16* nres; __nv_bfloat16* nres_out;
     const float* nweight; float neps, nin0, nin1, nscale;
@@ -172,6 +172,8 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
                             const float2 fo = __bfloat1622float2(o2[e]);
                             f.x = round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(f.x * a.nin0) + round_to<__nv_bfloat16>(fo.x * a.nin1));
                             f.y = round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(f.y * a.nin0) + round_to<__nv_bfloat16>(fo.y * a.nin1));
+                        } else if (a.nin0 != 1.f) {
+                            f.x = round_to<__nv_bfloat16>(f.x * a.nin0); f.y = round_to<__nv_bfloat16>(f.y * a.nin0);
                         }
                         if (a.nres != nullptr) { const float2 fr = __bfloat1622float2(r2[e]); f.x += fr.x; f.y += fr.y; }
                         v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y;
@@ -398,7 +400,7 @@ extern "C" int lb_linear_skinny(const void* x, long ldx, const void* w, const vo
 }
 
 // The same product with x made on the fly: x = round(rmsnorm(v; norm_weight, eps) * norm_scale) with
-// v = [round(round(nx * in0) + round(nother * in1)) or nx] + nres.  nx / nother / nres / res_out: contiguous
+// v = [round(round(nx * in0) + round(nother * in1)) or round(nx * in0)] + nres.  nx / nother / nres / res_out: contiguous
 // [M, K] bfloat16 (nother, nres, res_out may be null); res_out (the new residual, round(v)) must not alias
 // nres: other CTAs still read it.  M <= 16, K a multiple of 8 up to 2048, norm_weight float32 [K].
 extern "C" int lb_linear_skinny_normed(const void* nx, const void* nother, const void* nres, void* res_out,

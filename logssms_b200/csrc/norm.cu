@@ -10,7 +10,7 @@
 #include "lb200/common.cuh"
 using namespace lb200;
 
-// r = round(round(x*in0) + round(other*in1))  (only when `other` is given; else r = x)
+// r = round(round(x*in0) + round(other*in1)) when `other` is given; else r = round(x*in0) (in0 = 1: r = x)
 // r += residual ; residual_out = round(r) ; n = round(r * rsqrt(mean(r^2)+eps) * w)
 // out0 = round(n*s0) ; out1 = round(n*s1)
 template <typename T>
@@ -26,6 +26,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict_
         float v = to_f32(x[base + c]);
         if (other != nullptr) {
             v = round_to<T>(round_to<T>(v * in0) + round_to<T>(to_f32(other[base + c]) * in1));
+        } else if (in0 != 1.f) {
+            v = round_to<T>(v * in0);                 // the output multiplier of the product that made x, applied here
         }
         if (residual_in != nullptr) v += to_f32(residual_in[base + c]);
         row[c] = v;
@@ -84,6 +86,8 @@ __global__ void __launch_bounds__(kVecThreads) add_rmsnorm_vec_kernel(
                     const float2 o = __bfloat1622float2(o2[e]);
                     f.x = round_to<T>(round_to<T>(f.x * in0) + round_to<T>(o.x * in1));
                     f.y = round_to<T>(round_to<T>(f.y * in0) + round_to<T>(o.y * in1));
+                } else if (in0 != 1.f) {
+                    f.x = round_to<T>(f.x * in0); f.y = round_to<T>(f.y * in0);
                 }
                 if (residual_in != nullptr) { const float2 r = __bfloat1622float2(r2[e]); f.x += r.x; f.y += r.y; }
                 v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y;

@@ -78,13 +78,18 @@ class DecoderModel(Part):
             # comes next takes it: the next block's first norm (the rows before the head are gathered first)
             nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             ctx.extras["next_norm_takes_summed"] = getattr(getattr(nxt, "mixer_norm", None), "takes_summed_rows", False)
+            # ... or with its output multiplier still to be applied (`ScaledRows`); after the last block that norm is
+            # the one before the head
+            ctx.extras["next_norm_takes_scaled"] = getattr(getattr(nxt, "mixer_norm", None) if nxt is not None else self.final_norm,
+                                                           "takes_scaled_rows", False)
             x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
         ctx.extras.pop("next_norm_takes_summed", None)
+        ctx.extras.pop("next_norm_takes_scaled", None)
         return x, residual
 
     def logits(self, x: torch.Tensor, residual, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] at the token rows that were asked for."""
-        x = K.gather_rows(x, rows)
+        x = K.ScaledRows(K.gather_rows(x.rows, rows), x.scale) if isinstance(x, K.ScaledRows) else K.gather_rows(x, rows)
         if residual is not None:
             residual = K.gather_rows(residual, rows)
         defer = {"defer": True} if getattr(self.final_norm, "can_defer", False) else {}

@@ -697,6 +697,28 @@ def summed_rmsnorm(rows: SummedRows, weight: torch.Tensor, eps: float, out_scale
     return tuple((n * s).to(rows.residual.dtype) for s in out_scales)
 
 
+class ScaledRows:
+    """Rows whose output multiplier is still to be applied: round(rows * scale).  The product that made them ran in
+    the library, which has no such epilogue; the norm that reads them next applies the multiplier while it loads
+    them (`add_rmsnorm` with `in_scales[0]`: the same rounding), which saves a pass over the rows.  `tensor()` is
+    the scaled tensor for any other use."""
+    __slots__ = ("rows", "scale")
+
+    def __init__(self, rows: torch.Tensor, scale: float):
+        self.rows, self.scale = rows, float(scale)
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+    def tensor(self) -> torch.Tensor:
+        return scale(self.rows, self.scale)
+
+
 class NormedRows:
     """Rows that are still to be normalised: what `add_rmsnorm` would compute, handed to the product that
     consumes them so that the few-row kernel can do the norm in its prologue (a decode step is bound by the
@@ -937,8 +959,10 @@ def linear_conv_step(x, w: torch.Tensor, bias, conv_weight: torch.Tensor, conv_b
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out_scale: float = 1.0,
-           out_f32: bool = False) -> torch.Tensor:
+           out_f32: bool = False, lazy_scale: bool = False):
     """round(round(x [M, K] @ w[N, K]^T + bias) * out_scale) in x's dtype, or as float32 with `out_f32`.
+    With `lazy_scale` (the caller's consumer takes `ScaledRows`) a product whose kernel has no epilogue for the
+    multiplier comes back as `ScaledRows` instead of going through the scale kernel.
 
     float32 activations: the engine's own 32-bit kernel.  bfloat16: at most 64 rows go to the
     weight-streaming kernel (a decode step is bound by reading the weights once); more rows go to
@@ -960,6 +984,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
         return gemm_tcgen05(x, w, bias, out_scale=out_scale, out_f32=out_f32)
     else:
         y = F.linear(x, w, None if bias is None else bias.to(x.dtype))
+    if lazy_scale and not out_f32 and out_scale != 1.0:
+        return ScaledRows(y, out_scale)
     if out_f32 or out_scale != 1.0:
         y = scale(y, out_scale, to_f32=out_f32)
     return y

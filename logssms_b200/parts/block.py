@@ -118,4 +118,7 @@ class PreNormParallelBlock(Part):
             # the same at the feed-forward's last product, for the norm of the next layer
             out = self.feed_forward.forward(h, join=K.ResidualJoin(residual))
             return (out, None) if isinstance(out, K.SummedRows) else (out, residual)
+        if ctx.extras.get("next_norm_takes_scaled") and getattr(self.feed_forward, "can_lazy_scale", False):
+            # the norm that reads the output next applies the feed-forward's output multiplier while it loads it
+            return self.feed_forward.forward(h, lazy_scale=True), residual
         return self.feed_forward.forward(h), residual

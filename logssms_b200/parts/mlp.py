@@ -35,11 +35,14 @@ class GatedMLP(Part):
     def setup(self, rt) -> None:
         pass
 
-    def forward(self, x: torch.Tensor, join=None):
+    can_lazy_scale = True     # forward() takes `lazy_scale=`: see there
+
+    def forward(self, x: torch.Tensor, join=None, lazy_scale: bool = False):
         """With `join` (a `K.ResidualJoin`) and few rows the down projection adds the residual in its epilogue and
-        `K.SummedRows` come back instead of a tensor."""
+        `K.SummedRows` come back instead of a tensor.  With `lazy_scale` (the norm that reads the output next takes
+        `K.ScaledRows`) the output multiplier may be left to that norm."""
         s = self.spec
         h = K.linear_swiglu(x, self.gate_up, s.activation_scale)
         if K.linear_join_ok(h, self.down, None, join):
             return K.linear_join(h, self.down, None, join, out_scale=s.output_scale)
-        return K.linear(h, self.down, out_scale=s.output_scale)
+        return K.linear(h, self.down, out_scale=s.output_scale, lazy_scale=lazy_scale)

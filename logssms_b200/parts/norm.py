@@ -16,6 +16,7 @@ class RMSNorm(Part):
     kernels = ("norm", "linear_skinny")
     can_defer = True          # forward() takes `defer=`: see there
     takes_summed_rows = True  # forward() takes `K.SummedRows` as x: the product before has joined the residual already
+    takes_scaled_rows = True  # forward() takes `K.ScaledRows` as x: it applies the pending multiplier while it loads x
 
     def __init__(self, spec, perturb_init: bool = False):
         self.size, self.eps = spec.size, spec.eps
@@ -30,6 +31,12 @@ class RMSNorm(Part):
         """With `defer` (the caller's consumers all take `NormedRows`: their first step is a product), and
         few enough rows, nothing is launched here: the outputs are `NormedRows` that the consumers' products
         normalise in their prologue, and the new residual is a fresh tensor that the first of them writes."""
+        if isinstance(x, K.ScaledRows):
+            # the multiplier of the product that made x rides in this norm's load of x (as in_scales[0])
+            if other is None and in_scales[0] == 1.0:
+                x, in_scales = x.rows, (x.scale, in_scales[1])
+            else:
+                x = x.tensor()
         if isinstance(x, K.SummedRows):
             # x is already the residual sum (float32), with its rounded copy and the rows' sums of squares
             if residual is not None or other is not None:

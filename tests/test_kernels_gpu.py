@@ -74,7 +74,9 @@ def test_add_rmsnorm(dtype, H, two_inputs):
     rd = ref_dtype(dtype)
     outs, new_res = K().add_rmsnorm(dev(x), dev(w), 1e-5, dev(res.clone()), other=dev(other) if two_inputs else None,
                                     in_scales=(0.8, 0.7), out_scales=(1.5, 1.2))
-    want_outs, want_res = P.rms_norm_branches(x.to(rd), w.to(rd), 1e-5, res.to(rd), other.to(rd) if two_inputs else None,
+    # one input: its multiplier is the output multiplier of the product before, applied (and rounded) while x is read
+    x_in = x.to(rd) if two_inputs else rnd_of(dtype)(x.to(rd) * 0.8)
+    want_outs, want_res = P.rms_norm_branches(x_in, w.to(rd), 1e-5, res.to(rd), other.to(rd) if two_inputs else None,
                                               (0.8, 0.7), (1.5, 1.2), rnd_of(dtype))
     close(new_res, want_res, dtype)
     for a, b in zip(outs, want_outs):
