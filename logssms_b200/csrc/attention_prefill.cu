@@ -285,8 +285,8 @@ __global__ void __launch_bounds__(kGroupThreads * NG) attn_prefill_kernel(Prefil
 template <int HDT, int NG>
 int launch_hdt(const PrefillArgs& a, int n_tiles, cudaStream_t s) {
     const size_t smem = ((size_t)kQTile * (a.hd + 8) + NG * group_elems(a.hd, HDT)) * sizeof(bf16);
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(attn_prefill_kernel<HDT, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t have = 0;
+    ensure_dynamic_smem(attn_prefill_kernel<HDT, NG>, smem, have);
     attn_prefill_kernel<HDT, NG><<<dim3(a.n_items), kGroupThreads * NG, smem, s>>>(a);
     return launch_status();
 }

@@ -76,6 +76,17 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 inline int launch_status() { return (int)cudaGetLastError(); }
 
+// Raise a kernel's dynamic shared-memory limit, once per size: the attribute call costs the host tens of microseconds,
+// which a step that is launched kernel by kernel pays at every launch otherwise.  `have` is a static of the calling
+// launcher (one per kernel instantiation; the engine drives one device per process).
+template <typename Kernel>
+inline void ensure_dynamic_smem(Kernel kernel, size_t smem, size_t& have) {
+    if (smem > 48 * 1024 && smem > have) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        have = smem;
+    }
+}
+
 // `allow` false: plain stream order for this launch.  LOGSSMS_B200_PDL=0 switches it off everywhere (to
 // measure what it buys).
 template <typename... KArgs, typename... Args>

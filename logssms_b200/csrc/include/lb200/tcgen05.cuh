@@ -116,6 +116,19 @@ inline EncodeTiled tensor_map_encoder() {
 // A rows x width bfloat16 matrix whose rows lie `row_stride` elements apart (a multiple of 8; base on a 16-byte
 // boundary); box = box_rows x 64 elements, 128-byte swizzle, zeros outside.  0 or a cudaError.
 inline int make_tile_map(CUtensorMap* map, const void* ptr, long rows, long width, long row_stride, int box_rows) {
+    // The same few tensors come back step after step (caches; activations that the allocator hands out at the same
+    // address): the last maps are kept, an encoding costs the host a few microseconds.
+    struct Entry { const void* ptr; long rows, width, stride; int box_rows; CUtensorMap map; };
+    constexpr int kEntries = 16;
+    thread_local Entry cache[kEntries] = {};
+    thread_local int next = 0;
+    for (int i = 0; i < kEntries; ++i) {
+        const Entry& e = cache[i];
+        if (e.ptr == ptr && e.rows == rows && e.width == width && e.stride == row_stride && e.box_rows == box_rows) {
+            *map = e.map;
+            return 0;
+        }
+    }
     EncodeTiled enc = tensor_map_encoder();
     if (enc == nullptr) return (int)cudaErrorNotSupported;
     const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
@@ -125,7 +138,10 @@ inline int make_tile_map(CUtensorMap* map, const void* ptr, long rows, long widt
     const CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return rc == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+    if (rc != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    cache[next] = Entry{ptr, rows, width, row_stride, box_rows, *map};
+    next = (next + 1) % kEntries;
+    return 0;
 }
 
 }  // namespace tc

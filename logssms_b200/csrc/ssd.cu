@@ -383,8 +383,8 @@ template <int NKT, int PT, int MAXT>
 int launch_scan(const SsdArgs& a, int n_chunks, cudaStream_t s) {
     const size_t smem = scan_smem(a.L, a.P, a.N);
     if (round_up(a.L, 16) * 2 > MAXT) return kTooLarge;
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(ssd_chunk_scan_kernel<NKT, PT, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t have = 0;
+    ensure_dynamic_smem(ssd_chunk_scan_kernel<NKT, PT, MAXT>, smem, have);
     ssd_chunk_scan_kernel<NKT, PT, MAXT><<<dim3(n_chunks, a.nh), round_up(a.L, 16) * 2, smem, s>>>(a);
     return launch_status();
 }
@@ -423,8 +423,8 @@ extern "C" int lb_ssd_prefill(const void* conv, int C, const void* dt, long dt_s
               (const bf16*)gate, gate_stride, gate_scale};
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem1 = state_smem(L, P, N);
-    if (smem1 > 48 * 1024)
-        cudaFuncSetAttribute(ssd_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    static size_t have1 = 0;
+    ensure_dynamic_smem(ssd_chunk_state_kernel, smem1, have1);
     ssd_chunk_state_kernel<<<dim3(n_chunks, nh), kStateThreads, smem1, s>>>(a);
     int rc = launch_status();
     if (rc != 0) return rc;
