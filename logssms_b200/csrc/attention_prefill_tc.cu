@@ -11,14 +11,17 @@
 //                 S  = Q K^T   (M 128 queries, N 64 keys, K 64 dims: 4 x tcgen05.mma, both operands K-major)
 //                 PV = P V     (M 128, N 64 dims, K 64 keys: 4 x tcgen05.mma, V as an MN-major operand: the rows of
 //                               the cache are keys, which is the K dimension of this product)
-//             S of the next tile is issued right behind PV of this one, so it runs while the rows are rescaled
+//             S of a group's next tile is issued as soon as its rows hold the present S in registers, so it runs
+//             under their softmax
 //   warps 2-9 two groups of 128 threads, one thread per query row in each; group g owns the key tiles g, g + 2, ...
 //             with its own S, PV, P and running (maximum, sum, output), so that one group's chain of
 //             product -> softmax -> product -> rescale runs while the other waits for the tensor core; the two
 //             partial results meet in shared memory at the end.  A thread: read the row of S from tensor memory
-//             (tcgen05.ld), mask by absolute position (causal, optional window), online softmax in float32 (running maximum and sum), round P to
-//             bfloat16 into shared memory in the swizzled K-major layout the tensor core reads, then read the row
-//             of PV and fold it into the float32 output row kept in registers: O = O * alpha + PV
+//             (tcgen05.ld), mask by absolute position (causal, optional window; tiles that need no mask take a
+//             loop without it), online softmax in float32 (running maximum and sum), round P to bfloat16; then
+//             fold the PV of the tile BEFORE into the float32 output row kept in registers (O = O * alpha + PV:
+//             that product has had this tile's softmax to finish), and only then write P into shared memory in
+//             the swizzled K-major layout the tensor core reads
 // Keys of the last tile beyond the newest token are rows of the page that nobody has written for this request:
 // their scores are masked by selection, and their V rows are overwritten with zeros in shared memory before PV
 // (0 x stale-NaN would poison the row).

@@ -13,10 +13,11 @@
 //                 Y2 = C S_in^T   M 128, N 64 head dims, K = state size              -> columns 128..191
 //                 Y1 = W x        M 128, N 64, K 128 tokens s (x as an MN-major operand) -> columns 192..255
 //   warps 2-9 two threads per token t (a warp reads its own quarter of tensor memory's lanes, so warps w and w + 4
-//             share 32 tokens and split the columns): dt (softplus) and the running sum of dA over the chunk (float32, a prefix sum
-//             over the 128 threads) while the loads are under way; then its row of G from tensor memory, times the
-//             decay and dt_s, zero above the diagonal, rounded to bfloat16 into shared memory as W (over the tile of
-//             B, which G has consumed by then); at the end y_t = e^{a_t} Y2 + Y1 + D x_t, the gate, the store.
+//             share 32 tokens and split the columns): dt (softplus) and the running sum of dA over the chunk
+//             (float32, a prefix sum over the chunk) while the loads are under way; then their halves of the row of
+//             G from tensor memory, times the decay and dt_s, zero above the diagonal, rounded to bfloat16 into
+//             shared memory as W (over the tile of B, which G has consumed by then); at the end
+//             y_t = e^{a_t} Y2 + Y1 + D x_t, the gate, the store.
 // Rows of a last, shorter chunk: the loads bring whatever follows in the step (other requests' rows, zeros beyond
 // the end), all finite; dt_s = 0 for them, so they add nothing, and their own rows are not stored.
 //
