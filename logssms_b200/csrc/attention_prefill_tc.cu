@@ -3,25 +3,27 @@
 // multiple of 64 tokens; every other shape stays on the mma.sync kernel (attention_prefill.cu).
 //
 // One CTA per (128 query tokens of one request's portion, query head), 11 warps:
-//   warp 0    one thread: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the Q tile once, then of the
-//             K and V tiles (64 keys each: one box per tile, since a tile never crosses a page) into a ring of
-//             stages, each with a "full" and an "empty" mbarrier; the page of a tile comes from the block table
-//   warp 1    allocates 256 columns of tensor memory; one thread issues the first softmax group's products,
-//   warp 10   one thread those of the second group:
-//                 S  = Q K^T   (M 128 queries, N 64 keys, K 64 dims: 4 x tcgen05.mma, both operands K-major)
-//                 PV = P V     (M 128, N 64 dims, K 64 keys: 4 x tcgen05.mma, V as an MN-major operand: the rows of
-//                               the cache are keys, which is the K dimension of this product)
-//             S of a group's next tile is issued as soon as its rows hold the present S in registers, so it runs
-//             under their softmax
-//   warps 2-9 two groups of 128 threads, one thread per query row in each; group g owns the key tiles g, g + 2, ...
-//             with its own S, PV, P and running (maximum, sum, output), so that one group's chain of
-//             product -> softmax -> product -> rescale runs while the other waits for the tensor core; the two
-//             partial results meet in shared memory at the end.  A thread: read the row of S from tensor memory
-//             (tcgen05.ld), mask by absolute position (causal, optional window; tiles that need no mask take a
-//             loop without it), online softmax in float32 (running maximum and sum), round P to bfloat16; then
-//             fold the PV of the tile BEFORE into the float32 output row kept in registers (O = O * alpha + PV:
-//             that product has had this tile's softmax to finish), and only then write P into shared memory in
-//             the swizzled K-major layout the tensor core reads
+//   warp 0     one thread: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the Q tile once, then of the
+//              K and V tiles (64 keys each: one box per tile, since a tile never crosses a page) into a ring of 8
+//              stages, each with a "full" and an "empty" mbarrier; the page of a tile comes from the block table
+//   warp 1     allocates the tensor memory; one thread issues the first softmax group's products,
+//   warp 2     one thread those of the second group:
+//                  S  = Q K^T    (M 128 queries, N 64 keys, K 64 dims: 4 x tcgen05.mma, both operands K-major), into
+//                                one of the group's two S buffers in turn
+//                  O += P V      (M 128, N 64 dims, K 64 keys: 4 x tcgen05.mma, V as an MN-major operand: the rows of
+//                                the cache are keys, which is the K dimension of this product); O stays in tensor
+//                                memory for the whole CTA
+//              S of a group's first two tiles is issued up front, S of tile t + 2 right behind PV of tile t, so a
+//              row never waits for its next S
+//   warps 3-10 two groups of 128 threads, one thread per query row in each; group g owns the key tiles g, g + 2, ...
+//              with its own S buffers, P buffers, O and running (maximum, sum), so that one group's chain of
+//              product -> softmax -> product runs while the other's is in another phase; the two partial results
+//              meet in shared memory at the end.  A thread: read the row of S from tensor memory (tcgen05.ld), mask
+//              by absolute position (causal, optional window; tiles that need no mask take a loop without it),
+//              softmax weights in float32 relative to a maximum that follows the row's true maximum lazily (O is
+//              fetched, scaled and put back only when the maximum has grown by more than 2^8; exact, since O and
+//              the row sum carry the same factor), P rounded to bfloat16 into shared memory in the swizzled K-major
+//              layout the tensor core reads
 // Keys of the last tile beyond the newest token are rows of the page that nobody has written for this request:
 // their scores are masked by selection, and their V rows are overwritten with zeros in shared memory before PV
 // (0 x stale-NaN would poison the row).
@@ -39,13 +41,17 @@ using namespace lb200::tc;
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int kQ = 128, kKV = 64, kHD = 64;               // queries per CTA, keys per tile, head size
-constexpr int kStages = 4;
-constexpr int kGroups = 2;                               // softmax groups of 128 threads
-constexpr int kIssuer1 = 2 + kGroups * 4;                 // the warp whose first thread issues the second group's products
-constexpr int kThreads = 64 + kGroups * 128 + 32;
+constexpr int kStages = 8;                                // K|V tiles in shared memory: each group has three in use, the rest are on their way
+constexpr int kGroups = 2;                                // softmax groups of 128 threads
+constexpr int kFirstSoftmaxWarp = 1 + kGroups;            // warp 0: TMA; warps 1..kGroups: one issuing thread per group
+constexpr int kThreads = 32 * (kFirstSoftmaxWarp + 4 * kGroups);
 constexpr uint32_t kQBytes = kQ * kHD * 2, kTileBytes = kKV * kHD * 2, kPBytes = kQ * kKV * 2;
-constexpr uint32_t kTmemCols = 128 * kGroups;             // per group: S in columns 0..63, PV in columns 64..127
-constexpr uint32_t kMergeBytes = (kHD + 2) * kQ * 4;      // group 1's partial result, [column][row] float32
+constexpr uint32_t kGroupCols = 192;                      // per group: S of even tiles 0..63, of odd tiles 64..127, O 128..191
+constexpr uint32_t kTmemCols = 512;
+static_assert(kGroups * kGroupCols <= kTmemCols, "tensor memory");
+constexpr uint32_t kMergeBytes = (kHD + 2) * kQ * 4;      // a group's partial result, [column][row] float32
+constexpr float kTau = 8.f;                               // log2 of the growth of a row's maximum that O is rescaled for
+static_assert((kGroups - 1) * kMergeBytes <= kGroups * 2 * kPBytes, "the partial results lie over the P buffers");
 
 struct TcArgs {
     bf16* out;                                            // [tokens, Hq, 64]
@@ -68,17 +74,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = base;                                  // [128][128 B]
-    uint8_t* p_s = q_s + kQBytes;                         // per group [128][128 B]
-    uint8_t* kv_s = p_s + kGroups * kPBytes;              // stages of K [64][128 B] | V [64][128 B]
-    float* merge = reinterpret_cast<float*>(kv_s + kStages * 2 * kTileBytes);       // [66][128]
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(merge) + kMergeBytes);
+    uint8_t* p_s = q_s + kQBytes;                         // per group two buffers of [128][128 B] (tiles in turn)
+    uint8_t* kv_s = p_s + kGroups * 2 * kPBytes;          // stages of K [64][128 B] | V [64][128 B]
+    float* merge = reinterpret_cast<float*>(p_s);         // at the end, over P: per group beyond the first [66][128]
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv_s + kStages * 2 * kTileBytes);
     uint64_t* kv_empty = kv_full + kStages;
     uint64_t* q_full = kv_empty + kStages;
-    uint64_t* s_ready = q_full + 1;                       // per group: S of its tile is in tensor memory
-    uint64_t* p_ready = s_ready + kGroups;                // per group: P of its tile is in shared memory (128 arrivals)
-    uint64_t* o_ready = p_ready + kGroups;                // per group: PV of its tile is in tensor memory
-    uint64_t* s_free = o_ready + kGroups;                 // per group: its rows hold S in registers (128 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + kGroups);
+    uint64_t* s_ready = q_full + 1;                       // per group and tile parity: S of the tile is in tensor memory
+    uint64_t* p_ready = s_ready + 2 * kGroups;            // per group: P of its tile is in shared memory (128 arrivals)
+    uint64_t* o_ready = p_ready + kGroups;                // per group and tile parity: PV of the tile is added to O
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 2 * kGroups);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -97,15 +102,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int s = 0; s < kStages; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
         mbar_init(q_full, 1);
         for (int g = 0; g < kGroups; ++g) {
-            mbar_init(s_ready + g, 1); mbar_init(o_ready + g, 1);
-            mbar_init(p_ready + g, 128); mbar_init(s_free + g, 128);
+            mbar_init(s_ready + 2 * g, 1); mbar_init(s_ready + 2 * g + 1, 1);
+            mbar_init(o_ready + 2 * g, 1); mbar_init(o_ready + 2 * g + 1, 1);
+            mbar_init(p_ready + g, 128);
         }
         *failed = 0;
         mbar_fence_init();
     }
-    if (warp == 1) {
-        tmem_alloc<kTmemCols>(tmem_slot);
-    }
+    if (warp == 1) tmem_alloc<kTmemCols>(tmem_slot);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -132,79 +136,70 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int i = max(0, issued - kStages); i < issued; ++i) mbar_wait(kv_full + i % kStages, (i / kStages) & 1);
             }
         }
-    } else if (warp == 1 || warp == kIssuer1) {
+    } else if (warp < kFirstSoftmaxWarp) {
         if (lane == 0) {
-            // One issuing thread per softmax group (its tiles g, g + 2, ...): a thread that serves both waits for one
-            // group's P while the other group's is ready.
-            const int g = warp == 1 ? 0 : 1;
+            // One issuing thread per softmax group (its tiles g, g + kGroups, ...): a thread that served all of them
+            // would wait for one group's P while another's is ready.
+            const int g = warp - 1;
             // float32 accumulator, bfloat16 operands, N 64, M 128; the B operand of PV is MN-major (V)
             const uint32_t idesc_s = umma_idesc(kQ, kKV);
             const uint32_t idesc_o = idesc_s | kBMnMajor;
             const uint64_t qdesc = umma_desc(q_s);
-            const uint64_t pdesc = umma_desc(p_s + (size_t)g * kPBytes);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) { report(a.error, 2, 0xFFF); *failed = 1; }
-            auto issue_s = [&](int i) -> bool {            // S of tile i, into the group's columns
+            auto issue_s = [&](int i, int t) -> bool {     // S of tile i, the group's tile number t, into its S buffer t & 1
                 const int s = i % kStages;
                 if (!mbar_wait(kv_full + s, (i / kStages) & 1)) { report(a.error, 2, i); *failed = 1; return false; }
                 fence_after_sync();
                 const uint64_t kdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes);
 #pragma unroll
-                for (int k = 0; k < kHD / 16; ++k) umma_bf16(tmem + g * 128, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k != 0);
-                umma_commit(s_ready + g);
+                for (int k = 0; k < kHD / 16; ++k) umma_bf16(tmem + g * kGroupCols + (t & 1) * 64, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k != 0);
+                umma_commit(s_ready + 2 * g + (t & 1));
                 return true;
             };
-            if (ok && g < n_kt) ok = issue_s(g);
+            // S of the group's first two tiles is on its way before any softmax starts; from then on S of tile t + 2
+            // follows PV of tile t (whose P the rows wrote after they had read S of tile t out of that buffer), so a
+            // row never waits for the tensor core to start on its next S
+            if (ok && g < n_kt) ok = issue_s(g, 0);
+            if (ok && g + kGroups < n_kt) ok = issue_s(g + kGroups, 1);
             for (int i = g, t = 0; i < n_kt && ok && !*failed; i += kGroups, ++t) {
                 const int s = i % kStages;
-                // the rows hold S of tile i in registers: S of the group's next tile may go over it, and runs under
-                // this tile's softmax
-                if (!mbar_wait(s_free + g, t & 1)) { report(a.error, 4, i); *failed = 1; break; }
-                if (i + kGroups < n_kt && !(ok = issue_s(i + kGroups))) break;
-                // P of tile i is written, and the rows have read PV of the group's tile before
+                // P of tile i is written (and O rescaled where a row's maximum grew): O += P V
                 if (!mbar_wait(p_ready + g, t & 1)) { report(a.error, 3, i); *failed = 1; break; }
                 fence_after_sync();
+                const uint64_t pdesc = umma_desc(p_s + (size_t)(2 * g + (t & 1)) * kPBytes);
                 const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes);
 #pragma unroll
                 for (int k = 0; k < kKV / 16; ++k)         // 16 keys: two 8-row groups of V = 2048 bytes; 32 bytes along a row of P
-                    umma_bf16(tmem + g * 128 + 64, pdesc + 2 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, k != 0);
-                umma_commit(o_ready + g);
+                    umma_bf16(tmem + g * kGroupCols + 128, pdesc + 2 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, (t > 0 || k != 0) ? 1u : 0u);
+                umma_commit(o_ready + 2 * g + (t & 1));
                 umma_commit(kv_empty + s);                 // both products have read the stage
+                if (i + 2 * kGroups < n_kt) ok = issue_s(i + 2 * kGroups, t + 2);
             }
         }
     } else {
-        const int grp = (warp - 2) / 4;                    // which tiles: grp, grp + kGroups, ...
+        const int grp = (warp - kFirstSoftmaxWarp) / 4;    // which tiles: grp, grp + kGroups, ...
         const int r = (warp & 3) * 32 + lane;              // the row of the tile this thread owns (its lane of tensor memory)
-        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * 128;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * kGroupCols;
         const int p = pos0 + r;                            // absolute position of the row's query
         const int lo_r = a.window > 0 ? p - a.window + 1 : 0;
-        float o[kHD];
-#pragma unroll
-        for (int d = 0; d < kHD; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;
-        uint8_t* p_row = p_s + (size_t)grp * kPBytes + (size_t)r * 128;
+        // The output row O stays in tensor memory, where the PV products add to it.  It and the row sum l are kept
+        // relative to m_used, a maximum that follows the true one lazily: only when the row's maximum has grown by
+        // more than 2^kTau does the thread fetch O, scale it and put it back (with random scores after a handful of
+        // tiles never again); until then P = 2^(s - m_used) may exceed 1, by at most 2^kTau.  The result is the same:
+        // O and l carry the same factor, and it cancels in O / l.
+        float m_used = -INFINITY, l = 0.f;
+        uint64_t* o_bar = o_ready + 2 * grp;
         bool ok = true;
-        float alpha_prev = 1.f;                            // the factor O takes before the product of the tile before is added
         int done = 0;                                      // tiles of this group whose P has been handed over
-        // O <- O * alpha_prev + PV of the group's tile before: asked for only after the next tile's softmax, so that
-        // the product runs under that arithmetic instead of being waited for
-        auto fold = [&](int t_of, int tile) -> bool {
-            bool good = mbar_wait(o_ready + grp, t_of & 1);
-            if (!good && lane == 0) { report(a.error, 6, tile); *failed = 1; }
-            if (!__all_sync(0xffffffffu, good && !*failed)) return false;
-            fence_after_sync();
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t pv[32];
-                tmem_ld32(lane_addr + 64 + half * 32, pv);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) o[half * 32 + c] = fmaf(o[half * 32 + c], alpha_prev, __uint_as_float(pv[c]));
-            }
-            return true;
+        auto wait_pv = [&](int t_of, int code, int tile) -> bool {      // PV of the group's tile number t_of is in O
+            bool good = mbar_wait(o_bar + (t_of & 1), (t_of >> 1) & 1);
+            if (!good && lane == 0) { report(a.error, code, tile); *failed = 1; }
+            return __all_sync(0xffffffffu, good && !*failed);
         };
         for (int i = grp, t = 0; i < n_kt; i += kGroups, ++t) {
             const int j0 = (kt_begin + i) * kKV;
-            ok = mbar_wait(s_ready + grp, t & 1);
+            ok = mbar_wait(s_ready + 2 * grp + (t & 1), (t >> 1) & 1);
             if (!ok && lane == 0) { report(a.error, 5, i); *failed = 1; }
             if (!__all_sync(0xffffffffu, ok && !*failed)) { ok = false; break; }
             fence_after_sync();
@@ -212,19 +207,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (j0 + kKV - 1 > last_pos) {
                 uint8_t* v_tile = kv_s + (size_t)(i % kStages) * 2 * kTileBytes + kTileBytes;
                 const int first_bad = last_pos + 1 - j0;   // >= 1: the tile holds at least one key
-                for (int x = (warp & 3) * 32 + lane; x < (kKV - first_bad) * 8; x += 128)
+                for (int x = r; x < (kKV - first_bad) * 8; x += 128)
                     *reinterpret_cast<uint4*>(v_tile + (size_t)(first_bad + x / 8) * 128 + (x % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
             }
             const bool whole = j0 + kKV - 1 <= pos0 && (a.window <= 0 || j0 >= pos0 + kQ - a.window);
             uint32_t pk[32];                               // the row of P, two bfloat16 per word
-            float alpha;
             {
                 uint32_t s0[32], s1[32];
-                tmem_ld32(lane_addr, s0);
-                tmem_ld32(lane_addr + 32, s1);
-                // the row of S is in registers: the tensor core may write the group's next S over it
-                fence_before_sync();
-                mbar_arrive(s_free + grp);
+                tmem_ld32(lane_addr + (t & 1) * 64, s0);
+                tmem_ld32(lane_addr + (t & 1) * 64 + 32, s1);
                 float mx = -INFINITY;
                 if (whole) {                               // no key of the tile is masked for any row: the common case
 #pragma unroll
@@ -240,10 +231,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         mx = fmaxf(mx, fmaxf(v0, v1));
                     }
                 }
-                const float m_new = fmaxf(m, mx * a.scale_log2);
-                const float ref = m_new == -INFINITY ? 0.f : m_new;     // a row that has seen no key yet
-                alpha = exp2f(m - ref);
-                m = m_new;
+                mx *= a.scale_log2;
+                const bool grow = mx > m_used + kTau;      // also the first key a row sees (m_used = -inf)
+                float factor = 1.f;
+                if (grow) { factor = exp2f(m_used - mx); m_used = mx; l *= factor; }
+                if (t > 0 && __any_sync(0xffffffffu, grow)) {
+                    // O <- O * factor for the rows of this warp whose maximum grew (factor 1 for the others); the
+                    // product of the tile before must have landed in O first
+                    if (!wait_pv(t - 1, 6, i)) { ok = false; break; }
+                    fence_after_sync();
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t ov[32];
+                        tmem_ld32(lane_addr + 128 + half * 32, ov);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
+                        tmem_st32(lane_addr + 128 + half * 32, ov);
+                    }
+                    tmem_st_wait();
+                }
+                const float ref = m_used == -INFINITY ? 0.f : m_used;  // a row that has seen no key yet
                 float sum = 0.f;
 #pragma unroll
                 for (int c = 0; c < 64; c += 2) {
@@ -254,12 +261,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
                     pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pr);
                 }
-                l = l * alpha + sum;
+                l += sum;
             }
-            // the product of the tile before has had this tile's softmax to finish; it has read P, and once its result
-            // is folded in, the next one may write over it
-            if (t > 0 && !fold(t - 1, i - kGroups)) { ok = false; break; }
-            alpha_prev = alpha;
+            // P goes to the buffer of the tile's parity.  The product of the group's tile before the last has read it:
+            // the issuing thread sent S of this tile behind that product, the arrival that this thread has seen for S
+            // covers everything that thread had issued before, so that product is complete.
+            uint8_t* p_row = p_s + (size_t)(2 * grp + (t & 1)) * kPBytes + (size_t)r * 128;
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8)                 // 8 keys = one 16-byte piece of the row of P
                 *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) * 16)) = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
@@ -268,23 +275,51 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(p_ready + grp);
             done = t + 1;
         }
-        if (ok && done > 0) ok = fold(done - 1, grp + (done - 1) * kGroups);
-        // the groups' partial results meet: group 1 leaves its row in shared memory ([column][row]: a warp's rows lie
-        // side by side), group 0 folds it into its own
-        if (grp == 1) {
+        // the row of O once the group's last product has landed
+        float o[kHD];
 #pragma unroll
-            for (int d = 0; d < kHD; ++d) merge[d * kQ + r] = o[d];
-            merge[kHD * kQ + r] = m;
-            merge[(kHD + 1) * kQ + r] = l;
+        for (int d = 0; d < kHD; ++d) o[d] = 0.f;
+        if (ok && done > 0) {
+            ok = wait_pv(done - 1, 8, grp + (done - 1) * kGroups);
+            if (ok) {
+                fence_after_sync();
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t ov[32];
+                    tmem_ld32(lane_addr + 128 + half * 32, ov);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[half * 32 + c] = __uint_as_float(ov[c]);
+                }
+            }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");        // the 256 softmax threads
-        if (grp == 0) {
-            const float m1 = merge[kHD * kQ + r], l1 = merge[(kHD + 1) * kQ + r];
-            const float mn = fmaxf(m, m1), ref = mn == -INFINITY ? 0.f : mn;
-            const float f0 = exp2f(m - ref), f1 = exp2f(m1 - ref);
-            l = l * f0 + l1 * f1;
+        // The groups' partial results meet in shared memory ([column][row]: a warp's rows lie side by side), over the P
+        // buffers: every group's products have read them by now (each group has waited for its own last one above).
+        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");
+        if (grp > 0) {
+            float* mine = merge + (size_t)(grp - 1) * (kHD + 2) * kQ;
 #pragma unroll
-            for (int d = 0; d < kHD; ++d) o[d] = o[d] * f0 + merge[d * kQ + r] * f1;
+            for (int d = 0; d < kHD; ++d) mine[d * kQ + r] = o[d];
+            mine[kHD * kQ + r] = m_used;
+            mine[(kHD + 1) * kQ + r] = l;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");
+        if (grp == 0) {
+            float mt = m_used;
+#pragma unroll
+            for (int g = 1; g < kGroups; ++g) mt = fmaxf(mt, merge[(size_t)(g - 1) * (kHD + 2) * kQ + kHD * kQ + r]);
+            const float ref = mt == -INFINITY ? 0.f : mt;
+            const float f0 = exp2f(m_used - ref);
+            l *= f0;
+#pragma unroll
+            for (int d = 0; d < kHD; ++d) o[d] *= f0;
+#pragma unroll
+            for (int g = 1; g < kGroups; ++g) {
+                const float* theirs = merge + (size_t)(g - 1) * (kHD + 2) * kQ;
+                const float fg = exp2f(theirs[kHD * kQ + r] - ref);
+                l += theirs[(kHD + 1) * kQ + r] * fg;
+#pragma unroll
+                for (int d = 0; d < kHD; ++d) o[d] += theirs[d * kQ + r] * fg;
+            }
         }
         if (ok && grp == 0 && r < rows) {
             const float inv = 1.f / l;
@@ -307,7 +342,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncwarp();
     if (warp == 1) tmem_free<kTmemCols>(tmem);
 }
-
 }  // namespace
 
 // Does the tensor-core kernel take these sizes?  (Else: lb_attention_prefill.)
@@ -333,7 +367,7 @@ extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const
     if (rc != 0) return rc;
     TcArgs a{(bf16*)out, block_table, bt_stride, cu_seqlens, start_pos, tiles, Hq, Hkv, page_size, window,
              scale * 1.4426950408889634f, n_tiles * Hq, error};
-    const size_t smem = kQBytes + kGroups * kPBytes + (size_t)kStages * 2 * kTileBytes + kMergeBytes + 256 + 1024;
+    const size_t smem = kQBytes + kGroups * 2 * kPBytes + (size_t)kStages * 2 * kTileBytes + 256 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
