@@ -162,7 +162,7 @@ def test_rope_kv_store(dtype, hd, rotary):
 
 
 # --------------------------------------------------------------------------- attention over pages
-def paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new_tokens, plant=False):
+def paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new_tokens, plant=False, key_ramp=0.0):
     """Requests of `lengths` tokens whose last `new_tokens[r]` tokens are this step's queries, keys and
     values scattered over shuffled pages.  Returns device inputs and, per query row, (request, position)."""
     total_pages = sum(-(-n // page) for n in lengths) + 3
@@ -177,6 +177,8 @@ def paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new_tokens, plant=False):
         v = randn(g, n, Hkv, hd, dtype=dtype)
         if plant and n > 40:
             k[3] *= 6.0                                  # one far key that the query below will pick
+        if key_ramp:                                     # scores that rise (or fall) steadily with the key's position
+            k[:, :, 0] = (key_ramp * torch.arange(n) / 64.0)[:, None].to(dtype)
         for p in range(-(-n // page)):
             page_id = perm.pop()
             bt[r, p] = page_id
@@ -187,6 +189,8 @@ def paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new_tokens, plant=False):
         values.append(v)
         rows += [(r, pos) for pos in range(n - new_tokens[r], n)]
     q = randn(g, len(rows), Hq, hd, dtype=dtype)
+    if key_ramp:
+        q[:, :, 0] = 8.0
     if plant:
         for i, (r, pos) in enumerate(rows):
             if lengths[r] > 40 and pos >= 3:
@@ -398,6 +402,30 @@ def test_attention_prefill_on_tcgen05_over_pages_and_earlier_portions(shape):
     lo, hi = int(cu[1]), int(cu[2])
     close(out[lo:hi], rnd_of(dtype)(want)[lo:hi], dtype)
     assert bool((out[:lo] == 7.0).all()) and bool((out[hi:] == 7.0).all())
+
+
+@pytest.mark.parametrize("ramp", [8.3, -8.3, 1.0])
+def test_attention_prefill_on_tcgen05_when_the_row_maximum_keeps_moving(ramp):
+    """Scores that grow by about 2^12 per 64-key tile make every tile rescale the output row that the kernel keeps in
+    tensor memory (with random scores that happens in the first tiles only); falling scores never do after the first
+    tile, and leave later tiles with weights that underflow; a slow rise stays below the kernel's threshold, so the
+    weights exceed 1 for many tiles."""
+    Hq, Hkv, hd, page = 4, 2, 64, 64
+    dtype = torch.bfloat16
+    k = K()
+    g = torch.Generator().manual_seed(7)
+    lengths, new = [700, 333, 130], [700, 200, 2]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new, key_ramp=ramp)
+    cu, start, tiles = prefill_inputs(case, lengths, new, 128)
+    tiles64 = prefill_inputs(case, lengths, new, 64)[2]
+    scale = hd ** -0.5
+    args = (dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(cu), dev(start))
+    rd = ref_dtype(dtype)
+    for window in (0, 200):
+        want = rnd_of(dtype)(attention_reference(case, scale, window, rd))
+        close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale, window), want, dtype)
+        close(k.attention_prefill(*args, dev(tiles64), tiles64.shape[0], scale, window), want, dtype)     # and the mma.sync form
+    k.check_gemm_errors()
 
 
 def test_attention_prefill_on_tcgen05_refuses_other_shapes():
