@@ -10,20 +10,21 @@
 //   warp 2     one thread those of the second group:
 //                  S  = Q K^T    (M 128 queries, N 64 keys, K 64 dims: 4 x tcgen05.mma, both operands K-major), into
 //                                one of the group's two S buffers in turn
-//                  O += P V      (M 128, N 64 dims, K 64 keys: 4 x tcgen05.mma, V as an MN-major operand: the rows of
+//                  O += P V      (M 128, N 64 dims, K 64 keys: 4 x tcgen05.mma, P from tensor memory, V as an MN-major operand: the rows of
 //                                the cache are keys, which is the K dimension of this product); O stays in tensor
 //                                memory for the whole CTA
 //              S of a group's first two tiles is issued up front, S of tile t + 2 right behind PV of tile t, so a
 //              row never waits for its next S
 //   warps 3-10 two groups of 128 threads, one thread per query row in each; group g owns the key tiles g, g + 2, ...
-//              with its own S buffers, P buffers, O and running (maximum, sum), so that one group's chain of
+//              with its own S / P buffers, O and running (maximum, sum), so that one group's chain of
 //              product -> softmax -> product runs while the other's is in another phase; the two partial results
 //              meet in shared memory at the end.  A thread: read the row of S from tensor memory (tcgen05.ld), mask
 //              by absolute position (causal, optional window; tiles that need no mask take a loop without it),
 //              softmax weights in float32 relative to a maximum that follows the row's true maximum lazily (O is
 //              fetched, scaled and put back only when the maximum has grown by more than 2^8; exact, since O and
-//              the row sum carry the same factor), P rounded to bfloat16 into shared memory in the swizzled K-major
-//              layout the tensor core reads
+//              the row sum carry the same factor), P rounded to bfloat16 and stored into tensor memory over the S
+//              it was made from (tcgen05.st): PV takes it from there as its A operand, without a round trip through
+//              shared memory
 // Keys of the last tile beyond the newest token are rows of the page that nobody has written for this request:
 // their scores are masked by selection, and their V rows are overwritten with zeros in shared memory before PV
 // (0 x stale-NaN would poison the row).
@@ -45,13 +46,13 @@ constexpr int kStages = 8;                                // K|V tiles in shared
 constexpr int kGroups = 2;                                // softmax groups of 128 threads
 constexpr int kFirstSoftmaxWarp = 1 + kGroups;            // warp 0: TMA; warps 1..kGroups: one issuing thread per group
 constexpr int kThreads = 32 * (kFirstSoftmaxWarp + 4 * kGroups);
-constexpr uint32_t kQBytes = kQ * kHD * 2, kTileBytes = kKV * kHD * 2, kPBytes = kQ * kKV * 2;
-constexpr uint32_t kGroupCols = 192;                      // per group: S of even tiles 0..63, of odd tiles 64..127, O 128..191
+constexpr uint32_t kQBytes = kQ * kHD * 2, kTileBytes = kKV * kHD * 2;
+constexpr uint32_t kGroupCols = 192;                      // per group: S (then P) of even tiles 0..63, of odd tiles 64..127, O 128..191
 constexpr uint32_t kTmemCols = 512;
 static_assert(kGroups * kGroupCols <= kTmemCols, "tensor memory");
 constexpr uint32_t kMergeBytes = (kHD + 2) * kQ * 4;      // a group's partial result, [column][row] float32
 constexpr float kTau = 8.f;                               // log2 of the growth of a row's maximum that O is rescaled for
-static_assert((kGroups - 1) * kMergeBytes <= kGroups * 2 * kPBytes, "the partial results lie over the P buffers");
+static_assert((kGroups - 1) * kMergeBytes <= kStages * 2 * kTileBytes, "the partial results lie over the K|V ring");
 
 struct TcArgs {
     bf16* out;                                            // [tokens, Hq, 64]
@@ -74,9 +75,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = base;                                  // [128][128 B]
-    uint8_t* p_s = q_s + kQBytes;                         // per group two buffers of [128][128 B] (tiles in turn)
-    uint8_t* kv_s = p_s + kGroups * 2 * kPBytes;          // stages of K [64][128 B] | V [64][128 B]
-    float* merge = reinterpret_cast<float*>(p_s);         // at the end, over P: per group beyond the first [66][128]
+    uint8_t* kv_s = q_s + kQBytes;                        // stages of K [64][128 B] | V [64][128 B]
+    float* merge = reinterpret_cast<float*>(kv_s);        // at the end, over the ring: per group beyond the first [66][128]
     uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv_s + kStages * 2 * kTileBytes);
     uint64_t* kv_empty = kv_full + kStages;
     uint64_t* q_full = kv_empty + kStages;
@@ -167,11 +167,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // P of tile i is written (and O rescaled where a row's maximum grew): O += P V
                 if (!mbar_wait(p_ready + g, t & 1)) { report(a.error, 3, i); *failed = 1; break; }
                 fence_after_sync();
-                const uint64_t pdesc = umma_desc(p_s + (size_t)(2 * g + (t & 1)) * kPBytes);
                 const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes);
+                const uint32_t p_tmem = tmem + g * kGroupCols + (t & 1) * 64;     // P lies over the S it was made from
 #pragma unroll
-                for (int k = 0; k < kKV / 16; ++k)         // 16 keys: two 8-row groups of V = 2048 bytes; 32 bytes along a row of P
-                    umma_bf16(tmem + g * kGroupCols + 128, pdesc + 2 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, (t > 0 || k != 0) ? 1u : 0u);
+                for (int k = 0; k < kKV / 16; ++k)         // 16 keys: 8 columns of P (two bfloat16 each), two 8-row groups of V = 2048 bytes
+                    umma_bf16_tmem_a(tmem + g * kGroupCols + 128, p_tmem + 8 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, (t > 0 || k != 0) ? 1u : 0u);
                 umma_commit(o_ready + 2 * g + (t & 1));
                 umma_commit(kv_empty + s);                 // both products have read the stage
                 if (i + 2 * kGroups < n_kt) ok = issue_s(i + 2 * kGroups, t + 2);
@@ -263,14 +263,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 l += sum;
             }
-            // P goes to the buffer of the tile's parity.  The product of the group's tile before the last has read it:
-            // the issuing thread sent S of this tile behind that product, the arrival that this thread has seen for S
-            // covers everything that thread had issued before, so that product is complete.
-            uint8_t* p_row = p_s + (size_t)(2 * grp + (t & 1)) * kPBytes + (size_t)r * 128;
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8)                 // 8 keys = one 16-byte piece of the row of P
-                *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) * 16)) = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
-            fence_async_smem();                            // P (and the zeroed V rows) are for the tensor core's reads
+            // P goes into tensor memory, over the S it was made from (this thread has that row of S in registers; S of
+            // the group's tile after the next goes there only behind the product that reads this P)
+            tmem_st32(lane_addr + (t & 1) * 64, pk);
+            tmem_st_wait();
+            if (j0 + kKV - 1 > last_pos) fence_async_smem();               // the zeroed V rows are for the tensor core's reads
             fence_before_sync();
             mbar_arrive(p_ready + grp);
             done = t + 1;
@@ -292,8 +289,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
         }
-        // The groups' partial results meet in shared memory ([column][row]: a warp's rows lie side by side), over the P
-        // buffers: every group's products have read them by now (each group has waited for its own last one above).
+        // The groups' partial results meet in shared memory ([column][row]: a warp's rows lie side by side), over the
+        // K|V ring: every group's products have read it by now (each group has waited for its own last one above).
         asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");
         if (grp > 0) {
             float* mine = merge + (size_t)(grp - 1) * (kHD + 2) * kQ;
@@ -367,7 +364,7 @@ extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const
     if (rc != 0) return rc;
     TcArgs a{(bf16*)out, block_table, bt_stride, cu_seqlens, start_pos, tiles, Hq, Hkv, page_size, window,
              scale * 1.4426950408889634f, n_tiles * Hq, error};
-    const size_t smem = kQBytes + kGroups * 2 * kPBytes + (size_t)kStages * 2 * kTileBytes + 256 + 1024;
+    const size_t smem = kQBytes + (size_t)kStages * 2 * kTileBytes + 256 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
