@@ -36,6 +36,10 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-running-requests", type=int, default=64)
     p.add_argument("--max-seq-len-override", type=int, default=None)
     p.add_argument("--max-prefill-tokens", type=int, default=8192, help="token budget of one step")
+    p.add_argument("--scheduling-policy", default="mixed", choices=["mixed", "prefill-first"],
+                   help="mixed: prompt portions beside decoded tokens in one step; prefill-first: prompts before decoding")
+    p.add_argument("--mixed-prefill-tokens", type=int, default=None,
+                   help="most prompt tokens in a step that also decodes (mixed policy; default: the step's budget)")
     p.add_argument("--memory-ratio", type=float, default=0.9)
     p.add_argument("--num-pages", type=int, default=None)
     p.add_argument("--page-size", type=int, default=64)
@@ -170,7 +174,8 @@ def main(argv=None) -> int:
     from .sampling import SamplingParams
     llm = LLM(_model_folder(args), args.dtype, max_running_requests=args.max_running_requests,
               max_seq_len_override=args.max_seq_len_override, page_size=args.page_size, num_pages=args.num_pages,
-              memory_ratio=args.memory_ratio, max_prefill_tokens=args.max_prefill_tokens, seed=args.seed)
+              memory_ratio=args.memory_ratio, max_prefill_tokens=args.max_prefill_tokens, seed=args.seed,
+              scheduling_policy=args.scheduling_policy, mixed_prefill_tokens=args.mixed_prefill_tokens)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             ignore_eos=args.ignore_eos, max_tokens=args.max_tokens)
     if args.prompt_ids is not None:

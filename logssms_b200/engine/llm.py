@@ -28,7 +28,8 @@ class LLM:
                  max_seq_len_override: int | None = None, page_size: int = 64, num_pages: int | None = None,
                  memory_ratio: float = 0.9, max_prefill_tokens: int = 8192, seed: int = 0,
                  device: str = "cuda:0", tokenizer=None, eos_token_ids: Sequence[int] | None = None,
-                 poison_on_free: bool = False, use_graphs: bool = True):
+                 poison_on_free: bool = False, use_graphs: bool = True, scheduling_policy: str = "mixed",
+                 mixed_prefill_tokens: int | None = None):
         from ..config import load_model_config
         config = load_model_config(model_path)
         max_seq_len = max_seq_len_override or min(getattr(config, "max_position_embeddings", 8192), 8192)
@@ -43,7 +44,8 @@ class LLM:
             eos_token_ids = [] if eos is None else [eos]
         self.sampler = Sampler(self.engine.device, seed)
         self.scheduler = Scheduler(self.engine, max_step_tokens=max_prefill_tokens, sampler=self.sampler,
-                                   eos_token_ids=eos_token_ids)
+                                   eos_token_ids=eos_token_ids, policy=scheduling_policy,
+                                   mixed_prefill_tokens=mixed_prefill_tokens)
 
     # ------------------------------------------------------------------ step-wise use
     def add_request(self, prompt_ids: Sequence[int], sampling_params: SamplingParams | None = None):

@@ -1,8 +1,7 @@
 """The scheduler above the step function: admit, cut prompts into portions, decode, finish, free.
 
 Rules (the reference's, python/logssms/scheduler/prefill.py:94-152 and :294-324,
-python/logssms/scheduler/scheduler.py:194-205, python/logssms/scheduler/ar.py:114-117,
-with its "mixed" policy as the only one):
+python/logssms/scheduler/scheduler.py:194-205 and :264-319, python/logssms/scheduler/ar.py:114-117):
 
   * Admission is first-come-first-served and stops at the first request that does not fit; nobody
     overtakes.  A request fits when a request row is free and every page group can set aside the
@@ -12,9 +11,14 @@ with its "mixed" policy as the only one):
     back.  A request that could not fit even into an empty pool, or whose prompt does not leave room
     for one new token within max_seq_len, is finished at once with reason "rejected".
     `max_tokens` is clamped so that prompt + max_tokens <= max_seq_len.
-  * Every step takes one token from each decoding request, then fills what is left of the token
-    budget (`max_step_tokens`) with prompt portions, oldest request first; a prompt that does not
-    fit is cut at the budget, anywhere, and goes on in the next step.
+  * Policy "mixed" (the default here): every step takes one token from each decoding request, then
+    fills what is left of the token budget (`max_step_tokens`) with prompt portions, oldest request
+    first; a prompt that does not fit is cut at the budget, anywhere, and goes on in the next step.
+    `mixed_prefill_tokens` (the reference's `--mixed-prefill-tokens`) caps the prompt tokens of a step
+    that also decodes, so that the decoding requests' step time stays short.
+  * Policy "prefill-first" (the reference's default, `--scheduling-policy`): a step is either prompt
+    portions or decoded tokens, and prompts win: while any prompt portion can run, the decoding
+    requests wait.
   * A request ends after `max_tokens` new tokens or at an end-of-sequence token (unless
     `ignore_eos`); its row, pages and state slot go back at once.
   * Host and device overlap in the steady state of decoding: sampled ids are copied to pinned host memory
@@ -80,9 +84,18 @@ class StepDecision:
 
 
 class Scheduler:
-    def __init__(self, engine, *, max_step_tokens: int = 8192, sampler=None, eos_token_ids: Iterable[int] = ()):
+    POLICIES = ("mixed", "prefill-first")
+
+    def __init__(self, engine, *, max_step_tokens: int = 8192, sampler=None, eos_token_ids: Iterable[int] = (),
+                 policy: str = "mixed", mixed_prefill_tokens: int | None = None):
         if max_step_tokens < 1:
             raise ValueError("max_step_tokens must be at least 1")
+        if policy not in self.POLICIES:
+            raise ValueError(f"unknown scheduling policy {policy!r}: one of {', '.join(self.POLICIES)}")
+        if mixed_prefill_tokens is not None and mixed_prefill_tokens < 1:
+            raise ValueError("mixed_prefill_tokens must be at least 1")
+        self.policy = policy
+        self.mixed_prefill_tokens = mixed_prefill_tokens
         self.engine = engine
         self.cache = engine.cache
         self.max_step_tokens = max_step_tokens
@@ -120,7 +133,12 @@ class Scheduler:
     # ------------------------------------------------------------------ one step
     def schedule(self) -> StepDecision:
         decodes = [r for r in self.running if r.prompt_done]
-        budget = self.max_step_tokens - len(decodes)
+        if self.policy == "prefill-first":
+            budget = self.max_step_tokens               # the whole step for prompts, if there are any
+        else:
+            budget = self.max_step_tokens - len(decodes)
+            if decodes and self.mixed_prefill_tokens is not None:
+                budget = min(budget, self.mixed_prefill_tokens)
         portions: list[tuple[Request, int, int, bool]] = []
 
         def give_portion(r: Request) -> None:
@@ -143,6 +161,8 @@ class Scheduler:
             r.state = RUNNING
             self.running.append(r)
             give_portion(r)
+        if self.policy == "prefill-first":
+            return StepDecision([], portions) if portions else StepDecision(decodes, [])
         return StepDecision(decodes, portions)
 
     def step(self) -> list[Request]:

@@ -45,8 +45,9 @@ class ArgmaxSampler:
 def make(**kw):
     budget = kw.pop("max_step_tokens", 32)
     eos = kw.pop("eos", ())
+    policy = {k: kw.pop(k) for k in ("policy", "mixed_prefill_tokens") if k in kw}
     eng = FakeEngine(**kw)
-    return eng, Scheduler(eng, max_step_tokens=budget, sampler=ArgmaxSampler(), eos_token_ids=eos)
+    return eng, Scheduler(eng, max_step_tokens=budget, sampler=ArgmaxSampler(), eos_token_ids=eos, **policy)
 
 
 def test_prompt_is_cut_at_the_budget_and_decoding_follows():
@@ -140,3 +141,36 @@ def test_abort_frees_everything():
     s.abort(b)
     assert not s.has_work and eng.cache.groups[0].pool.num_free == 8 and eng.cache.rows.num_free == 3
     eng.cache.check_integrity()
+
+
+def test_prefill_first_policy_never_mixes_and_prompts_win():
+    eng, s = make(max_step_tokens=8, policy="prefill-first")
+    a = s.add_request([1, 2, 3], SamplingParams(max_tokens=4))
+    s.step()                                                                 # a's prompt
+    b = s.add_request(list(range(20)), SamplingParams(max_tokens=2))
+    s.run()
+    sizes = [[len(t) for _, _, t, _ in batch] for batch in eng.batches]
+    # b's prompt takes three whole steps (8 + 8 + 4) while a waits; then both decode together
+    assert sizes[:4] == [[3], [8], [8], [4]]
+    assert all(len(set(len(t) > 1 for _, _, t, _ in batch)) == 1 or all(len(t) == 1 for _, _, t, _ in batch)
+               for batch in eng.batches[1:]), "a step held prompt portions beside decoded tokens"
+    assert sizes[4] == [1, 1]
+    assert a.output == [4, 5, 6, 7] and b.output == [20, 21]
+
+
+def test_mixed_prefill_tokens_cap_the_prompt_share_of_a_step_that_decodes():
+    eng, s = make(max_step_tokens=16, mixed_prefill_tokens=5)
+    a = s.add_request([1, 2, 3], SamplingParams(max_tokens=6))
+    b = s.add_request(list(range(30)), SamplingParams(max_tokens=1))
+    s.step()                                    # nobody decodes yet: the whole budget goes to prompts (3 + 13)
+    s.run()
+    sizes = [[len(t) for _, _, t, _ in batch] for batch in eng.batches]
+    assert sizes[0] == [3, 13]
+    assert sizes[1:5] == [[1, 5], [1, 5], [1, 5], [1, 2]]                    # beside a's decoded token: at most 5
+    assert a.output == [4, 5, 6, 7, 8, 9] and b.output == [30]
+
+
+def test_unknown_policy_is_refused():
+    import pytest
+    with pytest.raises(ValueError, match="scheduling policy"):
+        make(policy="decode-first")
