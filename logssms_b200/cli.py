@@ -40,6 +40,7 @@ def build_parser() -> argparse.ArgumentParser:
                    help="mixed: prompt portions beside decoded tokens in one step; prefill-first: prompts before decoding")
     p.add_argument("--mixed-prefill-tokens", type=int, default=None,
                    help="most prompt tokens in a step that also decodes (mixed policy; default: the step's budget)")
+    p.add_argument("--no-graph", action="store_true", help="launch every step kernel by kernel (no CUDA graphs)")
     p.add_argument("--memory-ratio", type=float, default=0.9)
     p.add_argument("--num-pages", type=int, default=None)
     p.add_argument("--page-size", type=int, default=64)
@@ -175,7 +176,8 @@ def main(argv=None) -> int:
     llm = LLM(_model_folder(args), args.dtype, max_running_requests=args.max_running_requests,
               max_seq_len_override=args.max_seq_len_override, page_size=args.page_size, num_pages=args.num_pages,
               memory_ratio=args.memory_ratio, max_prefill_tokens=args.max_prefill_tokens, seed=args.seed,
-              scheduling_policy=args.scheduling_policy, mixed_prefill_tokens=args.mixed_prefill_tokens)
+              scheduling_policy=args.scheduling_policy, mixed_prefill_tokens=args.mixed_prefill_tokens,
+              use_graphs=not args.no_graph)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             ignore_eos=args.ignore_eos, max_tokens=args.max_tokens)
     if args.prompt_ids is not None:
