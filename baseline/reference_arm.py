@@ -40,10 +40,48 @@ def _write_model_folder(model: dict, path: str) -> None:
         json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "eos_token": "<eos>", "unk_token": "t0"}, f)
 
 
+def _named_dlpack_include() -> str | None:
+    """A folder to put FIRST on nvcc's include path: a copy of the installed tvm-ffi `dlpack/dlpack.h`, made here
+    at run time, in which every `typedef struct { ... } Name;` reads `typedef struct Name { ... } Name;`.
+
+    Why: the reference's `csrc/include/logssms/tensor.hpp` holds `std::vector<DLDataType>` in a class with a
+    defaulted destructor and is compiled with `-std=c++20` (python/logssms/tvm/utils.py:20-21).  nvcc 12.9's
+    front end aborts (`lexical.c`, `find_allocated_name_reference`) on `std::destroy_at` of a struct that has a
+    typedef name only, which is how dlpack declares `DLDataType` and `DLDevice`.  Naming the structs changes
+    neither layout nor ABI, and neither the reference nor the installed package is touched: the folder reaches
+    nvcc through the NVCC_PREPEND_FLAGS environment variable of this process only."""
+    import re
+    try:
+        import tvm_ffi
+    except ImportError:
+        return None
+    src = os.path.join(os.path.dirname(tvm_ffi.__file__), "include", "dlpack", "dlpack.h")
+    if not os.path.isfile(src):
+        return None
+    with open(src) as f:
+        text = f.read()
+    pieces, pos = [], 0
+    for m in re.finditer(r"typedef struct \{", text):
+        close = re.compile(r"\n\} (\w+);").search(text, m.end())
+        if close is None:
+            continue
+        pieces += [text[pos:m.start()], f"typedef struct {close.group(1)} {{"]
+        pos = m.end()
+    pieces.append(text[pos:])
+    out = tempfile.mkdtemp(prefix="logssms_ref_dlpack_")
+    os.makedirs(os.path.join(out, "dlpack"))
+    with open(os.path.join(out, "dlpack", "dlpack.h"), "w") as f:
+        f.write("".join(pieces))
+    return out
+
+
 def run(args, model: dict, context: int, max_seq_len: int) -> dict:
     if not os.path.isdir(os.path.join(REF, "logssms")):
         raise RuntimeError("baseline/_ref holds no installed reference (pip install --target baseline/_ref did not run)")
     sys.path.insert(0, REF)
+    shim = _named_dlpack_include()
+    if shim is not None:
+        os.environ["NVCC_PREPEND_FLAGS"] = (os.environ.get("NVCC_PREPEND_FLAGS", "") + f" -I{shim}").strip()
     import numpy as np
     import torch
     from logssms.core import SamplingParams

@@ -198,6 +198,32 @@ class CacheManager:
                     self._claim(gi, rc, want - have)
         rc.length = new_length
 
+    def check_room(self, growth: list[tuple[RequestCache, int]]) -> None:
+        """Raise `OutOfPages` unless `extend(rc, new_length)` will succeed for ALL the given pairs, one after the
+        other; nothing is changed.  A step extends several requests: without this check a later one could run dry
+        after earlier ones had already grown, although none of the step's tokens ever ran."""
+        for gi, g in enumerate(self.groups):
+            available = self.available_pages(gi)
+            for rc, new_length in growth:
+                if new_length < rc.length:
+                    raise ValueError("a request's cache never shrinks")
+                if new_length > self.max_seq_len:
+                    raise OutOfPages(f"request grows to {new_length} tokens, beyond max_seq_len {self.max_seq_len}")
+                have, reserved = int(g.num_pages_of[rc.row]), rc.reserved.get(gi, 0)
+                if g.need.window is not None:
+                    # pages the window has passed go back first; a request with a reservation may claim them again
+                    oldest_needed = max(0, rc.length - g.need.window + 1)
+                    given_back = max(0, min(oldest_needed // g.page_size, have) - int(g.first_page[rc.row]))
+                    if gi in rc.reserved:
+                        reserved += given_back
+                    else:
+                        available += given_back
+                beyond = max(0, g.pages_for(new_length) - have) - reserved
+                if beyond > available:
+                    raise OutOfPages(f"group {gi}: request row {rc.row} needs {beyond} more pages than it reserved, "
+                                     f"{max(available, 0)} are free and unpromised")
+                available -= max(beyond, 0)
+
     def _claim(self, gi: int, rc: RequestCache, n: int) -> None:
         take = min(n, rc.reserved[gi])
         rc.reserved[gi] -= take

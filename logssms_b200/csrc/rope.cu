@@ -37,7 +37,7 @@ __global__ void rope_kv_store_kernel(const T* __restrict__ q, const T* __restric
     int head = blockIdx.y;
     const int half = rotary_dim >> 1;
     int pos = positions[t];
-    pos = min(max(pos, 0), table_rows - 1);          // the host refuses positions beyond the table
+    pos = min(max(pos, 0), table_rows - 1);          // the table has a row for every position the cache manager admits; the clamp only keeps a bad index in bounds
     const float* cs = cos_sin + (size_t)pos * rotary_dim;
     if (head < Hq) {
         const T* src = q + t * row_stride + (size_t)head * hd;

@@ -40,7 +40,10 @@ __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, long row_stride, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
-              int* __restrict__ out) {
+              int* __restrict__ out, const int* __restrict__ status, int rows) {
+    // `status`: a word on the device (the error word of the kernels with bounded waits) that travels to the host
+    // behind the sampled ids, out[rows], in the same copy
+    if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) out[rows] = *status;
     __shared__ float red[32];
     __shared__ int red_i[32];
     __shared__ float scan[kThreads];
@@ -150,10 +153,10 @@ sample_kernel(const float* __restrict__ logits, long row_stride, int V, const fl
 
 extern "C" int lb_sample(const float* logits, long row_stride, int rows, int V, const float* temperature,
                          const int* top_k, const float* top_p, const unsigned long long* seeds,
-                         const unsigned long long* counters, int* out, void* stream) {
+                         const unsigned long long* counters, int* out, const int* status, void* stream) {
     if (rows <= 0) return kOk;
     if (V <= 0) return kBadSize;
     sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, row_stride, V, temperature, top_k, top_p,
-                                                               seeds, counters, out);
+                                                               seeds, counters, out, status, rows);
     return launch_status();
 }

@@ -98,7 +98,9 @@ class StepPlanner:
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"wanted place {w} is outside the entry's {n} tokens")
-        # room in the cache first: this may give back pages a window has passed
+        # room in the cache first, for all entries or for none (a step that cannot run leaves no request grown);
+        # extending may give back pages a window has passed
+        self.cache.check_room([(e.request, int(s + n)) for e, s, n in zip(entries, starts, lens)])
         for e, s, n in zip(entries, starts, lens):
             self.cache.extend(e.request, int(s + n))
         token_req = np.repeat(np.arange(B, dtype=np.int64), lens)

@@ -70,6 +70,7 @@ class _InFlight:
     tokens: torch.Tensor          # int32 on the device, one per request
     pinned: torch.Tensor          # their copy in pinned host memory (valid after `event`)
     event: "torch.cuda.Event | None"      # None: the ids are already on the host (a sampler that runs there)
+    has_status: bool = False      # pinned[len(requests)] holds the device's kernel error word as the step left it
 
 
 @dataclass
@@ -207,18 +208,22 @@ class Scheduler:
 
     def _sample(self, logits: torch.Tensor, reqs: list, pending: int) -> _InFlight:
         """Sample one id per request and start its copy to pinned host memory; nobody waits here."""
-        tokens = self.sampler.sample(logits, [r.params for r in reqs], [r.seed for r in reqs],
-                                     [len(r.output) + pending for r in reqs])
-        n = tokens.numel()
+        # a sampler that `reports_kernel_errors` appends the device's kernel error word to the ids, so that the word
+        # reaches the host in the copy that is made anyway (a kernel whose bounded wait gave up leaves it non-zero)
+        status = bool(getattr(self.sampler, "reports_kernel_errors", False))
+        args = (logits, [r.params for r in reqs], [r.seed for r in reqs], [len(r.output) + pending for r in reqs])
+        tokens = self.sampler.sample(*args, with_status=True) if status else self.sampler.sample(*args)
+        n = len(reqs)
         if not tokens.is_cuda:
             return _InFlight(list(reqs), tokens, tokens, None)
+        m = tokens.numel()
         pinned = self._pinned.pop() if self._pinned else None
-        if pinned is None or pinned.numel() < n:
-            pinned = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
-        pinned[:n].copy_(tokens, non_blocking=True)
+        if pinned is None or pinned.numel() < m:
+            pinned = torch.empty(max(m, 256), dtype=torch.int32, pin_memory=True)
+        pinned[:m].copy_(tokens, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
-        return _InFlight(list(reqs), tokens, pinned, event)
+        return _InFlight(list(reqs), tokens[:n], pinned, event, has_status=status and m == n + 1)
 
     def _goes_on(self, inflight: _InFlight) -> bool:
         """Will the next step be exactly one more token for each of these requests, whatever their pending ids
@@ -242,7 +247,16 @@ class Scheduler:
             inflight.event.synchronize()
             self._pinned.append(inflight.pinned)
         ids = inflight.pinned[:n].tolist()
-        self.d2h_bytes += n * 4
+        self.d2h_bytes += (n + inflight.has_status) * 4
+        if inflight.has_status and int(inflight.pinned[n]) != 0:
+            # a kernel of that step (or of one since) gave up on a wait: its logits, and these ids, mean nothing
+            code = int(inflight.pinned[n])
+            later, self._inflight = self._inflight, None
+            for r in {*inflight.requests, *(later.requests if later is not None else ())}:
+                if r.state != FINISHED:
+                    self._finish(r, "error: a kernel gave up on a wait")
+            from ..ops import kernels as K
+            K.raise_kernel_error(code, self.engine.device)
         done: list[Request] = []
         for r, tok in zip(inflight.requests, ids):
             if r.state == FINISHED:

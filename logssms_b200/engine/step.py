@@ -67,6 +67,7 @@ class Engine:
         self.max_graph_tokens = max_graph_tokens
         self._graphs: dict[int, _StepGraph] = {}             # decode steps, by batch size
         self._shape_graphs: dict[tuple, _StepGraph] = {}      # other steps, by (tokens of every entry, wanted places)
+        self._sightings: dict[tuple, int] = {}               # shapes seen once: (which kind of graph, key) -> count
         self._side_stream: torch.cuda.Stream | None = None
         self.steps_run = 0
 
@@ -121,9 +122,12 @@ class Engine:
             if device_tokens is None and sum(lens) <= self.max_graph_tokens:
                 key = (lens, sum(len(e.want) for e in entries))
                 return self._graph_step(self._shape_graphs, key, self.max_shape_graphs, 3, entries, None)
-        ctx = self.planner.plan(entries)
+        return self._run(self.planner.plan(entries), device_tokens)
+
+    def _run(self, ctx, device_tokens: torch.Tensor | None) -> torch.Tensor:
+        """The planned step, kernel by kernel."""
         if device_tokens is not None:
-            if ctx.num_tokens != len(entries) or device_tokens.numel() != ctx.num_tokens:
+            if ctx.num_tokens != ctx.num_requests or device_tokens.numel() != ctx.num_tokens:
                 raise ValueError("device_tokens feeds steps of one token per entry only")
             ctx.token_ids.copy_(device_tokens)
         x, residual = self.model.forward(ctx)
@@ -140,19 +144,26 @@ class Engine:
         outside of any capture), then it is captured once and replayed."""
         slot = graphs.get(key)
         if slot is None:
+            # A shape takes a slot (fixed tables on the device, later a graph) only when it comes a second time:
+            # until then it is a count in a bounded list, so that shapes that never recur cost no device memory
+            # and push no captured graph out.
+            seen = self._sightings.pop((id(graphs), key), 0) + 1
+            if seen < 2:
+                self._sightings[(id(graphs), key)] = seen
+                while len(self._sightings) > 64:
+                    self._sightings.pop(next(iter(self._sightings)))
+                return self._run(self.planner.plan(entries), device_tokens)
             if len(graphs) >= most:
-                graphs.pop(next(iter(graphs)))
+                # room: a slot that holds no graph yet goes first, then the graph used longest ago
+                victim = next((k for k, g in graphs.items() if g.graph is None), next(iter(graphs)))
+                graphs.pop(victim)
             slot = graphs[key] = _StepGraph()
+            slot.seen = seen - 1
+        else:
+            graphs[key] = graphs.pop(key)                 # most recently used last
         slot.seen += 1
         if slot.graph is None and slot.seen < capture_at:
-            ctx = self.planner.plan(entries, slot if slot.seen > 1 else None)
-            if device_tokens is not None:
-                ctx.token_ids.copy_(device_tokens)
-            x, residual = self.model.forward(ctx)
-            self.steps_run += 1
-            if ctx.logit_rows.numel() == 0:
-                return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-            return self.model.logits(x, residual, ctx.logit_rows)
+            return self._run(self.planner.plan(entries, slot), device_tokens)
         ctx = self.planner.plan(entries, slot)
         if device_tokens is not None:
             ctx.token_ids.copy_(device_tokens)            # before the capture / replay, on the same stream

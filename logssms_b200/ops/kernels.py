@@ -440,7 +440,7 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          cu_seqlens: torch.Tensor, start_pos: torch.Tensor, tiles: torch.Tensor, num_tiles: int,
                          scale: float, window: int = 0, *, out: torch.Tensor | None = None) -> torch.Tensor:
     """`attention_prefill` on the tcgen05 tensor cores: the same arguments, but `tiles` lists 128-token tiles.
-    `check_gemm_errors()` reports a kernel whose internal wait gave up."""
+    `check_kernel_errors()` reports a kernel whose internal wait gave up."""
     _cuda(q, k_cache, v_cache, block_table, cu_seqlens, start_pos, tiles)
     _need(attention_prefill_tc_ok(q, k_cache), "attention_prefill_tc takes bfloat16, head size 64 and pages of a multiple of 64 tokens")
     tokens, Hq, hd = q.shape
@@ -456,9 +456,7 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     if out is None:
         out = torch.empty_like(q)
     _need(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
-    err = _gemm_error.get(q.device)
-    if err is None:
-        err = _gemm_error[q.device] = torch.zeros(1, dtype=torch.int32, device=q.device)
+    err = error_word(q.device)
     f = _fn("attention_prefill_tc", "lb_attention_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_long, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
              c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
@@ -598,9 +596,7 @@ def ssd_prefill(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bi
              _ptr(gate), gate_stride, gate_scale, 0 if tc else 1, _code(conv), _stream()),
            "ssd_prefill", f"(head_dim {head_dim}, state_dim {state_dim}, chunk {chunk_len})", launches=2 if tc else 3)
     if tc:
-        err = _gemm_error.get(conv.device)
-        if err is None:
-            err = _gemm_error[conv.device] = torch.zeros(1, dtype=torch.int32, device=conv.device)
+        err = error_word(conv.device)
         g = _fn("ssd_tc", "lb_ssd_chunk_scan_tc",
                 [c_void_p, c_long, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_float, c_void_p, c_void_p])
@@ -862,7 +858,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = N
                  out_f32: bool = False, swiglu_scale: float | None = None) -> torch.Tensor:
     """x [M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory), with the
     bias, output multiplier, float32 output or SwiGLU (w = [gate rows; up rows]) done on the sums.
-    `check_gemm_errors()` reports a kernel whose internal wait gave up."""
+    `check_kernel_errors()` reports a kernel whose internal wait gave up."""
     _cuda(x, w, bias)
     _need(_tcgen05_ok(x, w, bias), "gemm_tcgen05 takes bfloat16 operands, K a multiple of 8, 16-byte aligned")
     M, Kdim = x.shape
@@ -877,9 +873,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = N
         mode = _OUT_F32
     _need(bias is None or bias.shape == (N,), "bias must be [N]")
     out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
-    err = _gemm_error.get(x.device)
-    if err is None:
-        err = _gemm_error[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    err = error_word(x.device)
     f = _fn("gemm_tcgen05", "lb_gemm_tcgen05", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int,
                                                 c_float, c_float, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(bias), _ptr(out), N, M, N, Kdim, out_scale,
@@ -887,16 +881,41 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = N
     return out
 
 
-def check_gemm_errors(device=None) -> None:
-    """Raise if a tcgen05 product gave up on one of its bounded waits since the last check (synchronises)."""
+def error_word(device) -> torch.Tensor:
+    """The int32 word on `device` into which a kernel whose bounded wait gave up writes where it stopped (0: none
+    did).  One per device, shared by all such kernels; the scheduler reads it with every step's sampled ids, the
+    trace replay after every step."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device(device.type, torch.cuda.current_device())
+    err = _gemm_error.get(device)
+    if err is None:
+        err = _gemm_error[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return err
+
+
+def raise_kernel_error(code: int, device=None) -> None:
+    """Clear the error word of `device` (all devices when None) and raise what `code` says."""
     for dev, err in _gemm_error.items():
-        if device is not None and torch.device(device) != dev:
+        if device is None or _same_device(dev, device):
+            err.zero_()
+    raise KernelError(f"a wait inside a kernel gave up, its results are not valid (role {(code >> 24) & 0x3F}, "
+                      f"block {(code >> 12) & 0xFFF}, step {code & 0xFFF})")
+
+
+def _same_device(a, b) -> bool:
+    a, b = torch.device(a), torch.device(b)
+    return a.type == b.type and (a.index is None or b.index is None or a.index == b.index)
+
+
+def check_kernel_errors(device=None) -> None:
+    """Raise if a kernel gave up on one of its bounded waits since the last check (synchronises)."""
+    for dev, err in _gemm_error.items():
+        if device is not None and not _same_device(dev, device):
             continue
         code = int(err.item())
         if code:
-            err.zero_()
-            raise KernelError(f"a tcgen05 kernel: a wait inside the kernel gave up (role {(code >> 24) & 0x3F}, "
-                              f"block {(code >> 12) & 0xFFF}, k-block {code & 0xFFF})")
+            raise_kernel_error(code, dev)
 
 
 def linear_conv_step_ok(x, w: torch.Tensor, bias, conv_state: torch.Tensor, max_rows: int | None = None) -> bool:

@@ -51,8 +51,10 @@ class RotaryEmbedding(Part):
         self.table: torch.Tensor | None = None
 
     def setup(self, rt) -> None:
-        rows = min(rt.max_seq_len, self.spec.max_position) if self.spec.max_position else rt.max_seq_len
-        rows = max(rows, 1)
+        # one row per position the engine can ever hold: its sequence limit replaces the model's
+        # max_position_embeddings when the two differ (python/logssms/engine/config.py:76-80), and the kernels
+        # index the table by position without a check of their own
+        rows = max(rt.max_seq_len, 1)
         if self.table is None or self.table.shape[0] != rows or self.table.device != rt.device:
             self.table = K.rope_table(inverse_frequencies(self.spec).to(rt.device), rows)
 

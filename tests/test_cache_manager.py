@@ -159,3 +159,54 @@ def test_poison_marks_freed_memory():
     page = int(m.groups[0].block_table[a.row, 0])
     m.release(a)
     assert torch.isnan(m.groups[0].storage[:, :, page]).all() and torch.isnan(m.states[0]["s"][a.row]).all()
+
+
+def test_check_room_refuses_a_step_whose_third_request_runs_dry_and_changes_nothing():
+    m = manager([CacheNeeds(kv=FULL), CacheNeeds(kv=WINDOW)], pages=6)
+    a, b, c = m.admit(), m.admit(), m.admit()
+    for rc in (a, b, c):
+        m.extend(rc, 10)                       # one page each in both groups
+    before = [(rc.length, int(m.groups[0].num_pages_of[rc.row])) for rc in (a, b, c)]
+    growth = [(a, 30), (b, 30), (c, 40)]       # 1 + 1 + 2 more pages of the full group; three are free
+    with pytest.raises(OutOfPages):
+        m.check_room(growth)
+    assert [(rc.length, int(m.groups[0].num_pages_of[rc.row])) for rc in (a, b, c)] == before
+    m.check_integrity()
+    m.check_room(growth[:2])
+    for rc, n in growth[:2]:
+        m.extend(rc, n)
+    m.check_integrity()
+
+
+def test_check_room_agrees_with_what_extend_does():
+    rng = random.Random(5)
+    for trial in range(200):
+        needs = [CacheNeeds(kv=FULL)] + ([CacheNeeds(kv=WINDOW)] if trial % 2 else [])
+        m = manager(needs, pages=rng.randint(3, 10), max_seq=160)
+        reqs = []
+        for _ in range(rng.randint(1, 4)):
+            reserve = rng.choice([0, 0, 40, 90])
+            if m.can_admit(reserve):
+                reqs.append(m.admit(reserve))
+        # a few steps so that requests hold pages and windows have passed some
+        for _ in range(rng.randint(0, 3)):
+            for rc in reqs:
+                try:
+                    m.extend(rc, min(rc.length + rng.randint(1, 50), 160))
+                except OutOfPages:
+                    pass
+        growth = [(rc, min(rc.length + rng.randint(1, 60), 160)) for rc in reqs]
+        try:
+            m.check_room(growth)
+            fits = True
+        except OutOfPages:
+            fits = False
+        ran_dry = False
+        for rc, n in growth:
+            try:
+                m.extend(rc, n)
+            except OutOfPages:
+                ran_dry = True
+                break
+        assert fits != ran_dry, (trial, fits, ran_dry)
+        m.check_integrity()

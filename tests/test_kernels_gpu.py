@@ -389,12 +389,12 @@ def test_attention_prefill_on_tcgen05_over_pages_and_earlier_portions(shape):
     rd = ref_dtype(dtype)
     want = attention_reference(case, scale, 0, rd)
     got = k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale)
-    k.check_gemm_errors()
+    k.check_kernel_errors()
     close(got, rnd_of(dtype)(want), dtype)
     for window in (1, 64, 65, 300):
         want_w = rnd_of(dtype)(attention_reference(case, scale, window, rd))
         close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale, window), want_w, dtype)
-    k.check_gemm_errors()
+    k.check_kernel_errors()
     # only one request's tiles: the other rows stay as they were
     out = torch.full_like(dev(case["q"]), 7.0)
     only = torch.tensor([[1, 0]], dtype=torch.int32)
@@ -425,7 +425,7 @@ def test_attention_prefill_on_tcgen05_when_the_row_maximum_keeps_moving(ramp):
         want = rnd_of(dtype)(attention_reference(case, scale, window, rd))
         close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale, window), want, dtype)
         close(k.attention_prefill(*args, dev(tiles64), tiles64.shape[0], scale, window), want, dtype)     # and the mma.sync form
-    k.check_gemm_errors()
+    k.check_kernel_errors()
 
 
 def test_attention_prefill_on_tcgen05_refuses_other_shapes():
@@ -825,7 +825,7 @@ def test_gemm_tcgen05_plain_bias_scale_and_f32(shape):
     out32 = k.gemm_tcgen05(xd, dev(w), out_scale=0.25, out_f32=True)
     assert out32.dtype == torch.float32
     close(out32, rnd(acc) * 0.25, torch.bfloat16, tol=8e-3)
-    k.check_gemm_errors()
+    k.check_kernel_errors()
     # exact structure: one hot rows of x pick single rows of w, whatever tile and k-block they sit in
     eye = torch.zeros(M, Kd, dtype=torch.bfloat16)
     cols = torch.randint(0, Kd, (M,), generator=g)
@@ -844,7 +844,7 @@ def test_gemm_tcgen05_swiglu_matches_the_unfused_chain(shape):
     gu = rnd(x.float() @ w.float().T)
     want = rnd(rnd(P.silu(rnd(gu[:, :I] * 0.9))) * gu[:, I:])
     close(k.gemm_tcgen05(dev(x), dev(w), swiglu_scale=0.9), want, torch.bfloat16, tol=1.6e-2)
-    k.check_gemm_errors()
+    k.check_kernel_errors()
 
 
 def test_ssm_scan_with_the_gate_in_its_epilogue():

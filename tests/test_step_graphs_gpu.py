@@ -77,3 +77,35 @@ def test_step_graphs_are_bounded_in_number_and_in_tokens(tmp_path):
             engine.step([StepEntry(r, list(range(n)), [n - 1])])
             engine.release(r)
     assert len(engine._shape_graphs) == 2 and all(k[0][0] <= 16 for k in engine._shape_graphs)
+
+
+def test_shapes_that_never_recur_push_no_captured_graph_out(tmp_path):
+    """One-off shapes take no slot and no device tables; a shape that came only twice goes before a captured one;
+    among captured graphs the one used longest ago goes."""
+    from logssms_b200.engine import Engine, StepEntry
+    raw = TINY["A"]
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=43)
+    engine = Engine(model_dir, "float32", max_requests=2, max_seq_len=128, num_pages=4, max_shape_graphs=2, max_graph_tokens=64)
+
+    def prompt(n):
+        r = engine.new_request()
+        engine.step([StepEntry(r, list(range(n)), [n - 1])])
+        engine.release(r)
+
+    def captured():
+        return {k[0][0] for k, slot in engine._shape_graphs.items() if slot.graph is not None}
+
+    for n in (10, 11):
+        for _ in range(3):
+            prompt(n)
+    assert captured() == {10, 11}
+    for n in range(20, 40):            # twenty shapes that come once
+        prompt(n)
+    assert captured() == {10, 11} and len(engine._shape_graphs) == 2
+    prompt(12)
+    prompt(12)                         # a second sight takes a slot: the graph used longest ago (10) makes room
+    assert captured() == {11} and set(k[0][0] for k in engine._shape_graphs) == {11, 12}
+    prompt(13)
+    prompt(13)                         # ... and the slot without a graph (12) goes before the captured one
+    assert captured() == {11} and set(k[0][0] for k in engine._shape_graphs) == {11, 13}
+    assert len(engine._sightings) <= 64
