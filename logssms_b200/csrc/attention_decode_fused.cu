@@ -715,8 +715,7 @@ int launch_mma(const FusedArgs& a, int tokens, cudaStream_t s) {
     const int ld = a.hd + 8;
     // the per-warp partial results (kWarps * 16 * (hd + 2) floats) lie over the tiles, which are larger
     const size_t smem = (size_t)(16 + 2 + kWarps * NS * 2 * kKT) * ld * sizeof(bf16);
-    static const bool clusters = [] { const char* e = getenv("LOGSSMS_B200_ATTN_CLUSTER"); return e == nullptr || e[0] != '0'; }();
-    if (clusters && a.splits >= 2 && a.splits <= 8) {
+    if (a.splits >= 2 && a.splits <= 8) {
         // the ranges of one (token, head) as one cluster along z
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(attn_decode_mma_kernel<HDT, NS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -727,13 +726,12 @@ int launch_mma(const FusedArgs& a, int tokens, cudaStream_t s) {
         attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)a.splits;
         attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[1].val.programmaticStreamSerializationAllowed = 1;
-        static const bool pdl = [] { const char* e = getenv("LOGSSMS_B200_PDL"); return e == nullptr || e[0] != '0'; }();
-        cfg.attrs = attr; cfg.numAttrs = (pdl && tokens <= pdl_max_rows()) ? 2 : 1;
+        cfg.attrs = attr; cfg.numAttrs = tokens <= kPdlMaxRows ? 2 : 1;
         return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HDT, NS, true>, a);
     }
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(attn_decode_mma_kernel<HDT, NS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_pdl_if(tokens <= pdl_max_rows(), attn_decode_mma_kernel<HDT, NS, false>, dim3(tokens, a.Hkv, a.splits), dim3(kThreads), smem, s, a);
+    return launch_pdl_if(tokens <= kPdlMaxRows, attn_decode_mma_kernel<HDT, NS, false>, dim3(tokens, a.Hkv, a.splits), dim3(kThreads), smem, s, a);
 }
 
 template <typename T>
@@ -781,13 +779,11 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
         // Stages of a warp's tile ring: 3 for a small grid (two tiles on their way before the first is used), 2 for a
         // large one, which then keeps three CTAs per SM.  Measured on 8-layer decode steps at batch 1 / 8 / 64:
         // 2 stages 0.304 / 0.366 / 0.674 ms, 3 stages 0.305 / 0.361 / 0.676 ms, 4 stages 0.301 / 0.406 / 0.749 ms (their
-        // 147 KB per CTA delay the start of a cluster under the kernel before).  LOGSSMS_B200_ATTN_STAGES overrides it.
-        static const int forced = [] { const char* e = getenv("LOGSSMS_B200_ATTN_STAGES"); return e ? atoi(e) : 0; }();
+        // 147 KB per CTA delay the start of a cluster under the kernel before).
         const bool small = (long)tokens * Hkv * splits <= 2 * 148;
-        const int ns = forced >= 2 && forced <= 4 ? forced : (small ? 3 : 2);
         cudaStream_t st = (cudaStream_t)stream;
-        if (hd <= 64) return ns >= 4 ? launch_mma<4, 4>(a, tokens, st) : (ns == 3 ? launch_mma<4, 3>(a, tokens, st) : launch_mma<4, 2>(a, tokens, st));
-        return ns >= 3 ? launch_mma<8, 3>(a, tokens, st) : launch_mma<8, 2>(a, tokens, st);
+        if (hd <= 64) return small ? launch_mma<4, 3>(a, tokens, st) : launch_mma<4, 2>(a, tokens, st);
+        return small ? launch_mma<8, 3>(a, tokens, st) : launch_mma<8, 2>(a, tokens, st);
     }
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, tokens, (cudaStream_t)stream));
     return kOk;

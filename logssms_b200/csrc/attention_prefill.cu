@@ -314,14 +314,8 @@ extern "C" int lb_attention_prefill(const void* q, const void* k_cache, const vo
                   n_tiles * Hq, num_sms, -1};
     for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
     // Groups per CTA.  Measured on a 2,048-token prompt of 8 heads of 64: 57 us with one group, 42 with two (two
-    // CTAs per SM), 44 with four (one CTA per SM).  LOGSSMS_B200_PREFILL_GROUPS=1|2|4 overrides it for head
-    // sizes up to 64, =1 for those up to 128; 256-wide heads fill the shared memory with one group.
-    static const int ng_env = [] { const char* e = getenv("LOGSSMS_B200_PREFILL_GROUPS"); return e ? atoi(e) : 0; }();
-    if (hd <= 64) {
-        if (ng_env == 1) return launch_hdt<4, 1>(a, n_tiles, (cudaStream_t)stream);
-        if (ng_env == 4) return launch_hdt<4, 4>(a, n_tiles, (cudaStream_t)stream);
-        return launch_hdt<4, 2>(a, n_tiles, (cudaStream_t)stream);
-    }
-    if (hd <= 128) return ng_env == 1 ? launch_hdt<8, 1>(a, n_tiles, (cudaStream_t)stream) : launch_hdt<8, 2>(a, n_tiles, (cudaStream_t)stream);
+    // CTAs per SM), 44 with four (one CTA per SM); 256-wide heads fill the shared memory with one group.
+    if (hd <= 64) return launch_hdt<4, 2>(a, n_tiles, (cudaStream_t)stream);
+    if (hd <= 128) return launch_hdt<8, 2>(a, n_tiles, (cudaStream_t)stream);
     return launch_hdt<16, 1>(a, n_tiles, (cudaStream_t)stream);
 }

@@ -313,9 +313,7 @@ void launch_vec(const ConvArgs& a, int B, int max_len, cudaStream_t s) {
     } else {
         dim3 grid_u((a.C + threads - 1) / threads, B);
         dim3 grid_t((groups + kTileGroups - 1) / kTileGroups, (max_len + kTileTokens - 1) / kTileTokens, B);
-        static const bool tiled = [] { const char* e = getenv("LOGSSMS_B200_CONV_TILE"); return e == nullptr || e[0] != '0'; }();
-        if (tiled) conv_forward_tile_kernel<K><<<grid_t, kTileThreads, 0, s>>>(a);
-        else conv_forward_vec_kernel<K, false><<<grid_f, threads, 0, s>>>(a);
+        conv_forward_tile_kernel<K><<<grid_t, kTileThreads, 0, s>>>(a);
         conv_state_update_kernel<__nv_bfloat16, K><<<grid_u, threads, 0, s>>>(a);
     }
 }

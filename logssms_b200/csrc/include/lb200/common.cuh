@@ -87,18 +87,16 @@ inline void ensure_dynamic_smem(Kernel kernel, size_t smem, size_t& have) {
     }
 }
 
-// `allow` false: plain stream order for this launch.  LOGSSMS_B200_PDL=0 switches it off everywhere (to
-// measure what it buys).
+// `allow` false: plain stream order for this launch.
 template <typename... KArgs, typename... Args>
 inline int launch_pdl_if(bool allow, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                          Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-    static const bool enabled = [] { const char* e = getenv("LOGSSMS_B200_PDL"); return e == nullptr || e[0] != '0'; }();
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = (enabled && allow) ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = allow ? 1 : 0;
     return (int)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 template <typename... KArgs, typename... Args>
@@ -107,11 +105,8 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
 }
 // Rows (tokens of a step) up to which a kernel starts under the one before it: with more rows the kernels are
 // long enough to fill the GPU by themselves, and an early start only takes SM space from the one that runs
-// (measured on a 36-layer decode step: 1-4 % faster at 1 and 8 rows, 4-10 % slower at 16, 32 and 64).  LOGSSMS_B200_PDL_ROWS overrides it.
-inline int pdl_max_rows() {
-    static const int rows = [] { const char* e = getenv("LOGSSMS_B200_PDL_ROWS"); return e ? atoi(e) : 8; }();
-    return rows;
-}
+// (measured on a 36-layer decode step: 1-4 % faster at 1 and 8 rows, 4-10 % slower at 16, 32 and 64).
+constexpr int kPdlMaxRows = 8;
 
 }  // namespace lb200
 

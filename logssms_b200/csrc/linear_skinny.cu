@@ -361,7 +361,7 @@ int launch_mt(const SkinnyArgs& a, cudaStream_t s) {
         if (NORM == 1) smem += (size_t)MT * 8 * (a.K + 8) * sizeof(__nv_bfloat16);                          \
         if (smem > 48 * 1024)                                                                               \
             cudaFuncSetAttribute(skinny_linear_kernel<MT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        rc = launch_pdl_if(a.M <= pdl_max_rows(), skinny_linear_kernel<MT, EPI, NORM>, grid, dim3(kThreads), smem, s, a); \
+        rc = launch_pdl_if(a.M <= kPdlMaxRows, skinny_linear_kernel<MT, EPI, NORM>, grid, dim3(kThreads), smem, s, a); \
     }
     int rc = 0;
     if (mt <= 1) LB_SKINNY(1)

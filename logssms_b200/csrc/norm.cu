@@ -148,6 +148,35 @@ extern "C" int lb_add_rmsnorm(const void* x, const void* other, const void* resi
     return launch_status();
 }
 
+// RMSNorm of rows that are already the 32-bit residual sums (left by a product that joined the residual in its
+// epilogue): n = round(v * rsqrt(mean(v^2)+eps) * w); out_k = round(n * s_k).  The rounding points of the kernel above.
+template <typename T>
+__global__ void summed_rmsnorm_kernel(const float* __restrict__ v, const float* __restrict__ weight,
+                                      T* __restrict__ out0, T* __restrict__ out1, int H, float eps, float s0, float s1) {
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) { const float f = v[base + c]; ss += f * f; }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float n = round_to<T>(v[base + c] * inv * weight[c]);
+        out0[base + c] = from_f32<T>(n * s0);
+        if (out1 != nullptr) out1[base + c] = from_f32<T>(n * s1);
+    }
+}
+
+extern "C" int lb_summed_rmsnorm(const float* v, const float* weight, void* out0, void* out1, int rows, int H,
+                                 float eps, float s0, float s1, int dtype, void* stream) {
+    if (rows <= 0) return kOk;
+    if (H <= 0) return kBadSize;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    LB_DISPATCH_DTYPE(dtype, {
+        summed_rmsnorm_kernel<T><<<rows, threads, 0, (cudaStream_t)stream>>>(v, weight, (T*)out0, (T*)out1, H, eps, s0, s1);
+    });
+    return launch_status();
+}
+
 // mode 0: out = y * round(silu(round(gate*s)))               (no norm)
 // mode 1: norm before gate: out = y*rsqrt(mean_g(y^2)+eps)*w * silu(round(gate*s))
 // mode 2: norm after gate : t = y*silu(round(gate*s)); out = t*rsqrt(mean_g(t^2)+eps)*w

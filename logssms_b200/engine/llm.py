@@ -53,9 +53,11 @@ class LLM:
         `step()` is called."""
         return self.scheduler.add_request(prompt_ids, sampling_params)
 
-    def step(self, device_loop: bool = True):
+    def step(self):
         """Run one scheduled step (prompt portions and one token of every decoding request); returns
-        the requests that finished in it."""
+        the requests that finished in it.  In the steady state of decoding the sampled ids are fed back on the
+        device and read by the host one step late (`scheduler.overlap`; switch it off to have every step's ids
+        visit the host before the next step is launched from them)."""
         return self.scheduler.step()
 
     def abort(self, request) -> None:

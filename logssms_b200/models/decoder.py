@@ -37,6 +37,13 @@ class DecoderModel(Part):
             kids[block_spec.prefix] = block
         return kids
 
+    def duplicate_names(self) -> dict[str, str]:
+        """Checkpoint names that may be stored although the model shares the tensor with another name: with tied
+        embeddings some writers still store the output head."""
+        if not self.spec.tie_word_embeddings:
+            return {}
+        return {self.spec.lm_head_name + "weight": self.spec.embedding_name + "weight"}
+
     def cache_needs(self):
         from ..cache import CacheNeeds
         needs = [None] * self.num_cache_layers

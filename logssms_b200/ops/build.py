@@ -6,6 +6,12 @@ per-user temporary folder when the package folder cannot be written).  The
 library's file name carries a hash of its sources and flags, so an edit never
 loads a stale binary.  There is no fallback: without nvcc or without the source
 the call raises.
+
+A library is named by the bare name of a source in the package's `csrc/`, or by
+the path of a `.cu` file anywhere else: a part that lives outside the package
+lists the path of its own kernels in its `kernels` attribute and they are built
+and loaded the same way (with the package's `include/` and the file's own
+folder on the include path).
 """
 from __future__ import annotations
 
@@ -26,7 +32,35 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared",
 ]
-ALL_LIBRARIES = ("embed", "norm", "rope", "attention", "attention_decode", "attention_decode_fused", "attention_prefill", "attention_prefill_tc", "conv", "ssm", "ssd", "ssd_tc", "gemm_f32", "gemm_tcgen05", "linear_skinny", "sample")
+
+
+def package_libraries() -> tuple[str, ...]:
+    """Names of all kernel sources of the package itself."""
+    return tuple(sorted(f[:-3] for f in os.listdir(CSRC) if f.endswith(".cu")))
+
+
+def all_libraries() -> tuple[str, ...]:
+    """Every library anything registered may ask for: the package's own sources and what the parts in the
+    registries name in their `kernels` (a part outside the package may name `.cu` files of its own)."""
+    from .. import registry
+    names = list(package_libraries())
+    for reg in (registry.MIXERS, registry.FEED_FORWARDS, registry.NORMS, registry.POSITION_ENCODINGS, registry.BLOCKS):
+        for key in reg.names():
+            names.extend(getattr(reg.get(key), "kernels", ()))
+    return tuple(dict.fromkeys(names))
+
+
+def source_path(name: str) -> str:
+    """The `.cu` file behind a library name: `name` itself if it is a path, else `csrc/<name>.cu`."""
+    src = name if (os.sep in name or name.endswith(".cu")) else os.path.join(CSRC, f"{name}.cu")
+    if not os.path.isfile(src):
+        raise KernelBuildError(f"kernel source {src} is missing")
+    return os.path.abspath(src)
+
+
+def _stem(name: str) -> str:
+    return os.path.splitext(os.path.basename(name))[0]
+
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.RLock()
@@ -81,30 +115,30 @@ def _find_build_dir() -> str:
 def _digest(name: str) -> str:
     h = hashlib.sha1()
     h.update(" ".join(NVCC_FLAGS).encode())
-    paths = [os.path.join(CSRC, f"{name}.cu")]
+    src = source_path(name)
+    paths = [src]
     for root, _, files in sorted(os.walk(INCLUDE)):
         paths += [os.path.join(root, f) for f in sorted(files)]
     for p in paths:
         with open(p, "rb") as f:
-            h.update(p[len(CSRC):].encode())
+            h.update((p[len(CSRC):] if p.startswith(CSRC) else p).encode())
             h.update(f.read())
     return h.hexdigest()[:12]
 
 
 def library_path(name: str) -> str:
-    return os.path.join(_build_dir(), f"lb200_{name}-{_digest(name)}.so")
+    return os.path.join(_build_dir(), f"lb200_{_stem(name)}-{_digest(name)}.so")
 
 
 def build(name: str, verbose: bool = True) -> str:
-    """Compile `csrc/<name>.cu` if its library is not there yet; return the path."""
-    src = os.path.join(CSRC, f"{name}.cu")
-    if not os.path.isfile(src):
-        raise KernelBuildError(f"kernel source {src} is missing")
+    """Compile the library's source if its library is not there yet; return the path."""
+    src = source_path(name)
     out = library_path(name)
     if os.path.isfile(out):
         return out
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", INCLUDE, "-o", tmp, src]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", INCLUDE, "-I", os.path.dirname(src), "-o", tmp, src]
+    name = _stem(name)
     if verbose:
         _log(f"compiling {name}.cu for sm_100a ...")
     start = time.time()
@@ -122,6 +156,14 @@ def build(name: str, verbose: bool = True) -> str:
             os.remove(tmp)
         raise KernelBuildError(f"nvcc failed on {name}.cu:\n{output}")
     os.replace(tmp, out)
+    # builds of earlier versions of this source are of no use any more
+    prefix = f"lb200_{name}-"
+    for f in os.listdir(os.path.dirname(out)):
+        if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(out):
+            try:
+                os.remove(os.path.join(os.path.dirname(out), f))
+            except OSError:
+                pass
     if verbose:
         _log(f"built {os.path.basename(out)} in {time.time() - start:.1f} s")
     return out
@@ -138,7 +180,7 @@ def build_many(names, verbose: bool = True) -> None:
 
 
 def load(name: str) -> ctypes.CDLL:
-    """The loaded library of `csrc/<name>.cu`, building it first if needed."""
+    """The loaded library of a kernel source (a name in `csrc/`, or a path), building it first if needed."""
     lib = _loaded.get(name)
     if lib is not None:
         return lib

@@ -230,33 +230,6 @@ def rope_kv_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim
 
 
 # --------------------------------------------------------------------------- attention
-def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
-                    token_req: torch.Tensor, positions: torch.Tensor, scale: float, window: int = 0) -> torch.Tensor:
-    """q: [tokens, Hq, hd]; caches: [pages, page_size, Hkv, hd]; block_table: [requests, max_pages] int32;
-    token_req / positions: per token its request row and absolute position.  Returns [tokens, Hq, hd]."""
-    _cuda(q, k_cache, v_cache, block_table, token_req, positions)
-    tokens, Hq, hd = q.shape
-    _need(q.is_contiguous(), "q must be contiguous")
-    _need(k_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
-          and k_cache.dtype == q.dtype == v_cache.dtype and k_cache.shape[3] == hd,
-          "caches must be contiguous [pages, page_size, kv_heads, head_dim] of q's dtype")
-    page_size, Hkv = k_cache.shape[1], k_cache.shape[2]
-    _need(hd % 16 == 0 and hd <= 256, f"attention takes head sizes in steps of 16 up to 256, got {hd}")
-    _need(Hq % Hkv == 0, f"query heads ({Hq}) must be a multiple of key/value heads ({Hkv})")
-    _need(block_table.dim() == 2 and block_table.dtype == torch.int32 and block_table.stride(1) == 1,
-          "block table must be a row-major int32 matrix")
-    _i32(token_req, "token_req")
-    _i32(positions, "positions")
-    out = torch.empty_like(q)
-    f = _fn("attention", "lb_paged_attention", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                                c_void_p])
-    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
-             _ptr(token_req), _ptr(positions), tokens, Hq, Hkv, hd, page_size, scale, int(window or 0), _code(q),
-             _stream()), "paged_attention")
-    return out
-
-
 def attention_splits(num_tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
     """How many ranges each context is cut into so that the grid covers the SMs a few times over."""
     G = num_heads // num_kv_heads
@@ -272,8 +245,9 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      token_req: torch.Tensor, positions: torch.Tensor, scale: float, window: int = 0, *,
                      splits: int = 1, token_list: torch.Tensor | None = None, out: torch.Tensor | None = None,
                      scratch: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
-    """Split-KV attention, each token on its own over its request's pages (see `paged_attention` for
-    the arguments).  `token_list` (int32) restricts the call to those tokens; the other rows of `out`
+    """Split-KV attention, each token on its own over its request's pages.  q: [tokens, Hq, hd]; caches:
+    [pages, page_size, Hkv, hd]; block_table: [requests, max_pages] int32; token_req / positions: per token its
+    request row and absolute position.  Returns [tokens, Hq, hd].  `token_list` (int32) restricts the call to those tokens; the other rows of `out`
     are left as they are.  `scratch`: float32 buffers (>= tokens*Hq*splits*hd and >= tokens*Hq*splits*2
     elements) for the ranges' partial results; allocated here when missing."""
     _cuda(q, k_cache, v_cache, block_table, token_req, positions, token_list)
@@ -394,7 +368,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       scale: float, window: int = 0, *, out: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core attention for prompt portions (bfloat16).  `tiles`: int32 [n, 2] = (request index,
     first token of a 64-token tile within that request's portion).  Rows of `out` that no tile covers
-    are left as they are.  Other arguments as for `paged_attention`."""
+    are left as they are.  Other arguments as for `attention_decode`."""
     _cuda(q, k_cache, v_cache, block_table, cu_seqlens, start_pos, tiles)
     tokens, Hq, hd = q.shape
     _need(q.dtype == torch.bfloat16, "attention_prefill is the bfloat16 kernel; float32 runs the general kernel")
@@ -684,12 +658,23 @@ def linear_join(x: torch.Tensor, w: torch.Tensor, bias, join: ResidualJoin, *, o
 
 
 def summed_rmsnorm(rows: SummedRows, weight: torch.Tensor, eps: float, out_scales) -> tuple:
-    """The RMSNorm of summed rows with plain tensor operations: only for a consumer that cannot norm them itself
-    (the built-in ones can), same rounding points as the norm kernel."""
+    """The RMSNorm of summed rows as a kernel of its own: for a consumer that cannot norm them itself (the built-in
+    products can), same rounding points as `add_rmsnorm`."""
     v = rows.vsum
-    inv = torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
-    n = (v * inv * weight).to(rows.residual.dtype).float()
-    return tuple((n * s).to(rows.residual.dtype) for s in out_scales)
+    _cuda(v, weight)
+    M, H = v.shape
+    _need(v.dtype == torch.float32 and v.is_contiguous(), "summed rows are contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.shape == (H,) and weight.is_contiguous(),
+          "norm weight must be a contiguous float32 vector of the row width")
+    _need(1 <= len(out_scales) <= 2, "one or two outputs")
+    act = rows.residual.dtype
+    out0 = torch.empty((M, H), dtype=act, device=v.device)
+    out1 = torch.empty((M, H), dtype=act, device=v.device) if len(out_scales) == 2 else None
+    f = _fn("norm", "lb_summed_rmsnorm", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float,
+                                          c_int, c_void_p])
+    _check(f(_ptr(v), _ptr(weight), _ptr(out0), _ptr(out1), M, H, eps, out_scales[0], out_scales[-1],
+             _DTYPE_CODE[act], _stream()), "summed_rmsnorm")
+    return (out0,) if out1 is None else (out0, out1)
 
 
 class ScaledRows:
@@ -798,7 +783,7 @@ def _summed_fn():
 # At or below this many rows a bfloat16 product goes to the weight-streaming kernel (which takes up to 64).  Measured
 # on 36-layer decode steps: with the library above 32 rows a step of 48 rows takes 2.48 instead of 2.72 ms and one of
 # 64 rows 2.77 instead of 3.07 ms; with the library above 16 rows a step of 24 rows 2.62 instead of 2.18 ms.
-SKINNY_MAX_ROWS = int(os.environ.get("LOGSSMS_B200_SKINNY_MAX", "32"))
+SKINNY_MAX_ROWS = 32
 
 
 def _skinny_ok(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, max_rows: int | None = None) -> bool:

@@ -1,6 +1,5 @@
 from .base import MATRIX, TABLE, VECTOR, ParamSpec, Part
 from .context import Runtime, StepContext
-from .linear import Linear
 from .norm import RMSNorm
 from .rope import RotaryEmbedding, inverse_frequencies
 from .attention import Attention
@@ -9,6 +8,6 @@ from .mlp import GatedMLP
 from .embedding import Embedding, LMHead
 from .block import PreNormParallelBlock
 
-__all__ = ["MATRIX", "TABLE", "VECTOR", "ParamSpec", "Part", "Runtime", "StepContext", "Linear", "RMSNorm",
+__all__ = ["MATRIX", "TABLE", "VECTOR", "ParamSpec", "Part", "Runtime", "StepContext", "RMSNorm",
            "RotaryEmbedding", "inverse_frequencies", "Attention", "Mamba2", "GatedMLP", "Embedding", "LMHead",
            "PreNormParallelBlock"]

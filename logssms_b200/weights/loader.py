@@ -83,7 +83,13 @@ def check_and_place(model: Part, stored: dict[str, torch.Tensor], dtype: torch.d
                     device, source: str = "") -> dict[str, torch.Tensor]:
     expected = dict(model.named_param_specs())
     missing = [n for n in expected if n not in stored]
-    unexpected = [n for n in stored if n not in expected]
+    # a tensor the model shares with another one (a tied output head) may be stored all the same: it is dropped
+    # when it equals the tensor it is tied to (the reference drops it unseen, python/logssms/layers/embedding.py:60-76)
+    # and stays an error when it differs, since the model could not honour it
+    twins = getattr(model, "duplicate_names", dict)()
+    unexpected = [n for n in stored if n not in expected
+                  and not (n in twins and twins[n] in stored and stored[n].shape == stored[twins[n]].shape
+                           and torch.equal(stored[n], stored[twins[n]]))]
     wrong = [(n, stored[n].shape, expected[n].shape) for n in expected
              if n in stored and tuple(stored[n].shape) != tuple(expected[n].shape)]
     if missing or unexpected or wrong:

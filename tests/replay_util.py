@@ -23,6 +23,7 @@ class Trace:
     rows: list[list[tuple[str, int]]] = field(default_factory=list)     # per step: (request id, position) per wanted row
     progress: dict[str, int] = field(default_factory=dict)
     peak_tokens: int = 0
+    page: int = PAGE                     # tokens per page of the engine that will replay this (for `peak_tokens`)
     _live: dict[str, int] = field(default_factory=dict)
 
     def add_step(self, portions: list[tuple[str, list[int]]], end: list[str] = (), want_all: bool = True) -> None:
@@ -34,7 +35,7 @@ class Trace:
             rows += [(rid, start + w) for w in want]
             self.progress[rid] = start + len(tokens)
             self._live[rid] = self.progress[rid]
-        self.peak_tokens = max(self.peak_tokens, sum(-(-n // PAGE) * PAGE for n in self._live.values()))
+        self.peak_tokens = max(self.peak_tokens, sum(-(-n // self.page) * self.page for n in self._live.values()))
         for rid in end:
             self._live.pop(rid, None)
             self.progress.pop(rid, None)
@@ -117,7 +118,7 @@ def run_trace(model_dir: str, dtype: str, trace: Trace, out_dir: str, max_tokens
             line = proc.stdout.readline().strip()
             assert line == f"done {step['step']}", f"trace_run answered {line!r} to step {step['step']}"
         proc.stdin.close()
-        assert proc.wait(timeout=120) == 0
+        assert proc.wait(timeout=300) == 0
     finally:
         if proc.poll() is None:
             proc.kill()

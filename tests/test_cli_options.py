@@ -33,6 +33,73 @@ def test_unknown_policy_and_dtype_are_refused():
             build_parser().parse_args(["--model", "/m", *bad])
 
 
-def test_chat_commands_are_the_reference_clients():
+class FakeLLM:
+    """Stands in for `LLM` under the chat loop: records the prompts and answers with their length."""
+
+    def __init__(self, tokenizer=None, fail_on=None):
+        self.tokenizer, self.fail_on, self.prompts = tokenizer, fail_on, []
+
+    def generate(self, prompts, params):
+        from logssms_b200.engine.llm import Output
+        self.prompts.append(list(prompts[0]))
+        if self.fail_on is not None and len(self.prompts) == self.fail_on:
+            raise RuntimeError("out of pages")
+        ids = [len(prompts[0]), 1]
+        text = self.tokenizer.decode(ids) if self.tokenizer is not None else None
+        return [Output(ids, "length", text, list(prompts[0]))]
+
+
+class FakeTokenizer:
+    """Words of the form t<number>; no chat template: the turns are joined by newlines."""
+    chat_template = None
+
+    def encode(self, text):
+        return [int(w[1:]) for w in text.split() if w[0] == "t"]
+
+    def decode(self, ids):
+        return " ".join(f"t{i}" for i in ids)
+
+
+def chat(lines, **kw):
+    import io
+    out = io.StringIO()
+    llm = FakeLLM(**kw)
+    c = Chat(llm, params=None, system=None, out=out)
+    c.loop(iter(lines))
+    return c, llm, out.getvalue().splitlines()
+
+
+def test_chat_loop_runs_every_command_of_the_reference_client_on_token_ids():
+    """examples/chat.py:120-124: /help /new /list /switch /rename /delete /clear /system /history /exit."""
     assert set(Chat.COMMANDS) == {"/help", "/new", "/list", "/switch", "/rename", "/delete", "/clear", "/system",
                                   "/history", "/exit"}
+    c, llm, said = chat([
+        "/help", "5 6 7", "8, 9", "/history", "/new work", "1 2", "/list", "/switch chat-1", "3", "/rename first",
+        "/list", "/switch nowhere", "/delete work", "/delete first", "/clear", "/history", "4", "/system be brief",
+        "/frobnicate", "not ids", "", "/exit", "99"])
+    # the history of a conversation is fed back: second turn = first prompt + its answer + the new ids
+    assert llm.prompts[0] == [5, 6, 7] and llm.prompts[1] == [5, 6, 7, 3, 1, 8, 9]
+    assert llm.prompts[2] == [1, 2]                                  # a new conversation starts empty
+    assert llm.prompts[3] == [5, 6, 7, 3, 1, 8, 9, 7, 1, 3]          # back in chat-1
+    assert llm.prompts[4] == [4]                                     # after /clear
+    assert len(llm.prompts) == 5                                     # nothing ran after /exit, nor for "not ids"
+    assert said[0].startswith("commands:") and sum(line.lstrip().startswith("/") for line in said) >= 10
+    assert "3 1   [length]" in said and "7 1   [length]" in said
+    assert "[user] [5, 6, 7]" in said and "[assistant] [3, 1]" in said
+    assert "now in work" in said and "* work (2 turns)" in said and "  chat-1 (4 turns)" in said
+    assert "* first (6 turns)" in said                               # after /rename
+    assert "no conversation 'nowhere'" in said
+    assert "cannot delete that" in said                              # the last conversation stays
+    assert any("unknown command /frobnicate" in line for line in said)
+    assert any("type token ids" in line for line in said)
+    assert said[-1] == "bye" and c.system == "be brief" and list(c.conversations) == ["first"]
+
+
+def test_chat_loop_with_a_tokenizer_builds_the_prompt_from_system_and_turns_and_survives_an_error():
+    c, llm, said = chat(["/system t1 t2", "t5 t6", "t7", "t8", "/history", "/exit"], tokenizer=FakeTokenizer(), fail_on=3)
+    assert llm.prompts[0] == [1, 2, 5, 6]                            # system prompt, then the user's words
+    assert llm.prompts[1] == [1, 2, 5, 6, 4, 1, 7]                   # ... the answer (t4 t1) and the next turn
+    assert "t4 t1" in said and "t7 t1" in said
+    assert any(line.startswith("Error: out of pages") for line in said)
+    assert said.count("[user] t8") == 0                              # the failed turn left no history
+    assert said[-1] == "bye"

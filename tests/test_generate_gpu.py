@@ -134,5 +134,83 @@ def test_command_line_generates_from_random_weights(tmp_path):
     assert first.returncode == 0, first.stderr[-2000:]
     ids = [int(t) for t in first.stdout.split()]
     assert len(ids) == 5 and all(0 <= t < TINY["A"]["vocab_size"] for t in ids)
+    # ... and they are the plain implementation's tokens for the weights that seed gives
+    from logssms_b200.config import make_model_config
+    from logssms_b200.weights import write_random_model
+    same_weights = write_random_model(make_model_config(TINY["A"]), str(tmp_path / "same"), seed=3, dtype=torch.float32)
+    check_greedy(same_weights, "float32", [5, 6, 7], ids)
     second = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=300)
     assert second.stdout == first.stdout                         # seeded weights, greedy: the same ids again
+
+
+def word_tokenizer(model_dir, vocab_size):
+    """The smallest tokenizer folder `AutoTokenizer` reads: words t0 .. t<V-2> and an end-of-sequence word."""
+    import json
+    import os
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    vocab = {f"t{i}": i for i in range(vocab_size - 1)}
+    vocab["<eos>"] = vocab_size - 1
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="t0"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok.save(os.path.join(model_dir, "tokenizer.json"))
+    with open(os.path.join(model_dir, "tokenizer_config.json"), "w") as f:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "eos_token": "<eos>", "unk_token": "t0"}, f)
+
+
+def test_text_prompts_go_through_the_folders_tokenizer_and_the_chat_loop(tmp_path):
+    import io
+    from logssms_b200.cli import Chat
+    from logssms_b200.engine import LLM
+    from logssms_b200.sampling import SamplingParams
+    raw = TINY["A"]
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=24)
+    word_tokenizer(model_dir, raw["vocab_size"])
+    llm = LLM(model_dir, "float32", max_running_requests=2, max_seq_len_override=128, num_pages=4)
+    assert llm.tokenizer is not None and llm.scheduler.eos == {raw["vocab_size"] - 1}
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    by_text = llm.generate(["t5 t17 t3 t200"], sp)[0]
+    by_ids = llm.generate([[5, 17, 3, 200]], sp)[0]
+    assert by_text.prompt_token_ids == [5, 17, 3, 200] and by_text.token_ids == by_ids.token_ids
+    assert by_text.text == " ".join(f"t{i}" if i < raw["vocab_size"] - 1 else "<eos>" for i in by_text.token_ids)
+    check_greedy(model_dir, "float32", [5, 17, 3, 200], by_text.token_ids)
+    # the chat loop on the real engine: two turns of one conversation, the second sees the first
+    out = io.StringIO()
+    chat = Chat(llm, sp, system=None, out=out)
+    chat.loop(iter(["t5 t17 t3 t200", "t9", "/history", "/exit"]))
+    said = out.getvalue().splitlines()
+    assert said[0] == by_text.text
+    turns = chat.conversations["chat-1"]
+    assert [r for r, _ in turns] == ["user", "assistant", "user", "assistant"]
+    second_prompt = llm.tokenizer.encode("\n".join(["t5 t17 t3 t200", by_text.text, "t9"]))
+    assert llm.tokenizer.decode(llm.generate([list(second_prompt)], sp)[0].token_ids) == turns[3][1]
+    # without a tokenizer a text prompt is refused with a clear error
+    bare = make_model_dir(tmp_path / "bare", raw, seed=24)
+    with pytest.raises(ValueError, match="tokenizer"):
+        LLM(bare, "float32", max_running_requests=2, max_seq_len_override=64, num_pages=2).generate(["t1"], sp)
+
+
+def test_a_kernel_that_gave_up_ends_the_requests_of_its_step_with_an_error(tmp_path):
+    """The error word that the kernels with bounded waits write is read with every step's sampled ids.  Here the
+    host sets the word itself (no kernel is made to give up): the next step's requests end with an error, the
+    word is cleared, the cache is whole, and the engine goes on."""
+    from logssms_b200.engine import LLM
+    from logssms_b200.ops import kernels as K
+    from logssms_b200.sampling import SamplingParams
+    model_dir = make_model_dir(tmp_path / "m", TINY["A"], seed=25)
+    llm = LLM(model_dir, "float32", max_running_requests=2, max_seq_len_override=64, num_pages=2)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    good = llm.generate([[1, 2, 3]], sp)[0].token_ids
+    word = K.error_word(llm.engine.device)
+    word.fill_((3 << 24) | (17 << 12) | 5)
+    a = llm.add_request([1, 2, 3], sp)
+    b = llm.add_request([4, 5], sp)
+    with pytest.raises(K.KernelError, match="role 3, block 17, step 5"):
+        llm.scheduler.run()
+    assert a.state == b.state == "finished" and a.finish_reason.startswith("error") and b.finish_reason.startswith("error")
+    assert int(word.item()) == 0 and not llm.engine.cache.live and not llm.scheduler.has_work
+    llm.engine.cache.check_integrity()
+    assert llm.generate([[1, 2, 3]], sp)[0].token_ids == good
+    word.fill_(7)
+    with pytest.raises(K.KernelError):
+        K.check_kernel_errors(llm.engine.device)
+    K.check_kernel_errors(llm.engine.device)        # cleared by the report

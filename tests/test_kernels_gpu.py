@@ -220,7 +220,7 @@ ATTN_SHAPES = [  # Hq, Hkv, hd, page
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", ATTN_SHAPES)
-@pytest.mark.parametrize("kernel", ["general", "split1", "split5", "split_auto"])
+@pytest.mark.parametrize("kernel", ["split1", "split5", "split_auto"])
 def test_paged_attention_kernels(dtype, shape, kernel):
     Hq, Hkv, hd, page = shape
     g = torch.Generator().manual_seed(hd + Hq)
@@ -229,11 +229,8 @@ def test_paged_attention_kernels(dtype, shape, kernel):
     k = K()
     scale = hd ** -0.5
     args = (dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(case["token_req"]), dev(case["positions"]), scale)
-    if kernel == "general":
-        out = k.paged_attention(*args)
-    else:
-        splits = {"split1": 1, "split5": 5}.get(kernel) or k.attention_splits(len(case["rows"]), Hq, Hkv, max(lengths))
-        out = k.attention_decode(*args, splits=splits)
+    splits = {"split1": 1, "split5": 5}.get(kernel) or k.attention_splits(len(case["rows"]), Hq, Hkv, max(lengths))
+    out = k.attention_decode(*args, splits=splits)
     close(out, rnd_of(dtype)(attention_reference(case, scale, 0, ref_dtype(dtype))), dtype)
 
 
@@ -252,11 +249,9 @@ def test_attention_finds_a_far_key_and_honours_a_window(dtype, splits):
     v3 = case["values"][0].to(rd)[3].repeat_interleave(Hq // Hkv, 0)
     assert float((want[0] - v3).abs().max()) < 0.05
     close(k.attention_decode(*args, splits=splits), rnd_of(dtype)(want), dtype)
-    close(k.paged_attention(*args), rnd_of(dtype)(want), dtype)
     for window in (1, 64, 65, 300):
         want_w = rnd_of(dtype)(attention_reference(case, scale, window, rd))
         close(k.attention_decode(*args, window, splits=splits), want_w, dtype)
-        close(k.paged_attention(*args, window), want_w, dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -535,6 +530,17 @@ def chunk_lists(lens, L):
                                    # head size 64 with chunks of 128: the tcgen05 chunk scan, state sizes 64 to 256
                                    (4, 64, 64, 2, 128), (2, 64, 192, 1, 128), (2, 64, 256, 2, 256), (3, 64, 128, 1, 64)])
 def test_ssd_prefill_in_chunks_resumes_from_state_and_matches_the_recurrence(shape):
+    ssd_case(shape, [150, 40, 300], [70, 17, 129])
+
+
+@pytest.mark.parametrize("shape", [(3, 64, 128, 1, 128), (2, 128, 256, 1, 128), (2, 64, 256, 2, 128), (2, 48, 64, 1, 64)])
+def test_ssd_prefill_over_dozens_of_chunks(shape):
+    """The state pass over 33 and 32 chunks of one request (and a short neighbour), as a 4,096-token portion and the
+    4,133 tokens that follow it."""
+    ssd_case(shape, [8229, 40, 2300], [4096, 17, 2048])
+
+
+def ssd_case(shape, full, first):
     nh, Pd, N, G, chunk = shape
     dtype = torch.bfloat16
     k = K()
@@ -542,7 +548,6 @@ def test_ssd_prefill_in_chunks_resumes_from_state_and_matches_the_recurrence(sha
     assert 0 < L <= chunk
     g = torch.Generator().manual_seed(nh * 31 + N)
     inner = nh * Pd
-    full, first = [150, 40, 300], [70, 17, 129]
     convs = [randn(g, n, inner + 2 * G * N, dtype=dtype) for n in full]
     dts = [randn(g, n, nh, dtype=dtype) for n in full]
     zs = [randn(g, n, inner, dtype=dtype) for n in full]
@@ -907,3 +912,79 @@ def test_sample_temperature_frequencies_and_reproducibility():
     # temperature -> 0 is greedy
     a4 = sample_tokens(logits, dev(torch.full((rows,), 1e-6)), topk, topp, seeds, counters).cpu()
     assert set(a4.tolist()) == {3}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [40, 1000, 3072])
+def test_summed_rmsnorm_norms_32_bit_residual_sums(dtype, H):
+    """Rows left by a product that joined the residual, for a consumer that cannot norm them itself."""
+    from plain import falcon_h1_plain as P
+    k = K()
+    g = torch.Generator().manual_seed(H)
+    v = randn(g, 5, H, scale=3.0)
+    w = 1.0 + 0.1 * randn(g, H)
+    rows = k.SummedRows(dev(v), dev(v).to(dtype), None)
+    got = k.summed_rmsnorm(rows, dev(w), 1e-5, (1.5, 0.7))
+    rd = ref_dtype(dtype)
+    want, _ = P.rms_norm_branches(v.to(rd), w.to(rd), 1e-5, out_scales=(1.5, 0.7), rnd=rnd_of(dtype))
+    assert got[0].dtype == dtype and len(got) == 2
+    for a, b in zip(got, want):
+        close(a, b, dtype)
+
+
+# --------------------------------------------------------------------------- the attention kernels at long contexts
+LONG_ATTN_SHAPES = [(8, 2, 64, 64), (12, 2, 128, 64), (6, 2, 128, 128), (3, 1, 32, 64)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", LONG_ATTN_SHAPES)
+def test_decode_attention_kernels_over_thousands_of_keys(dtype, shape):
+    """Single new tokens over 8,192, 5,000 and 2,065 keys (block tables of up to 128 pages): the split-KV kernel
+    against the reference, with a planted far key, and the one-launch decode-step kernel (cluster merge of 8 ranges,
+    and more ranges than a cluster holds) against the three-kernel chain."""
+    Hq, Hkv, hd, page = shape
+    g = torch.Generator().manual_seed(hd + 7 * Hq)
+    lengths = [8192, 5000, 2065, 3]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, [1] * len(lengths), plant=True)
+    k = K()
+    scale = hd ** -0.5
+    rd = ref_dtype(dtype)
+    want = attention_reference(case, scale, 0, rd)
+    v3 = case["values"][0].to(rd)[3].repeat_interleave(Hq // Hkv, 0)
+    assert float((want[0] - v3).abs().max()) < 0.05          # key 3 of 8,192 decides the first row
+    args = (dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(case["token_req"]), dev(case["positions"]), scale)
+    for splits in (1, k.attention_splits(len(lengths), Hq, Hkv, max(lengths)), 64):
+        close(k.attention_decode(*args, splits=splits), rnd_of(dtype)(want), dtype)
+    tokens = len(lengths)
+    qkv = randn(g, tokens, (Hq + 2 * Hkv) * hd, dtype=dtype)
+    inv = 1.0 / (1e4 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+    table = k.rope_table(dev(inv), 8192)
+    slots = torch.tensor([int(case["bt"][r, p // page]) * page + p % page for r, p in case["rows"]], dtype=torch.int32)
+    for splits in (k.decode_step_splits(tokens, Hq, Hkv, 8192), 8, 40):
+        kc1, vc1, kc2, vc2 = dev(case["kc"]), dev(case["vc"]), dev(case["kc"]), dev(case["vc"])
+        q = k.rope_kv_store(dev(qkv), Hq, Hkv, hd, dev(case["positions"]), dev(slots), table, kc1, vc1, 0.5)
+        chain = k.attention_decode(q, kc1, vc1, dev(case["bt"]), dev(case["token_req"]), dev(case["positions"]), scale, splits=4)
+        step = k.attention_decode_step(dev(qkv), Hq, Hkv, hd, dev(case["positions"]), dev(slots), table, kc2, vc2,
+                                       dev(case["bt"]), dev(case["token_req"]), scale, 0.5, splits=splits)
+        close(step, chain, dtype)
+
+
+@pytest.mark.parametrize("shape", LONG_ATTN_SHAPES)
+def test_prompt_attention_kernels_over_thousands_of_keys(shape):
+    """A 2,048-token portion behind 2,148 earlier tokens, a whole 2,300-token prompt and a short neighbour: the
+    tensor-core prompt kernels (tcgen05 where it takes the shape) against the reference, a planted far key."""
+    Hq, Hkv, hd, page = shape
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(hd + 11 * Hq)
+    lengths, new = [4196, 2300, 50], [2048, 2300, 50]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new, plant=True)
+    k = K()
+    scale = hd ** -0.5
+    want = rnd_of(dtype)(attention_reference(case, scale, 0, ref_dtype(dtype)))
+    args = (dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]))
+    cu, start, tiles = prefill_inputs(case, lengths, new, 64)
+    close(k.attention_prefill(*args, dev(cu), dev(start), dev(tiles), tiles.shape[0], scale), want, dtype)
+    if k.attention_prefill_tc_ok(args[0], args[1]):
+        cu, start, tiles = prefill_inputs(case, lengths, new, k.ATTENTION_TC_TILE)
+        close(k.attention_prefill_tc(*args, dev(cu), dev(start), dev(tiles), tiles.shape[0], scale), want, dtype)
+        k.check_kernel_errors()

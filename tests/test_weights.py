@@ -102,3 +102,21 @@ def test_sharded_checkpoint_reads_like_a_single_file(tmp_path):
     save_file({n: stored[n] for n in names[1::2]}, os.path.join(d, "model-00002-of-00002.safetensors"))
     again = read_checkpoint(d)
     assert again.keys() == stored.keys() and all(torch.equal(again[k], stored[k]) for k in stored)
+
+
+def test_a_tied_checkpoint_may_store_the_output_head_if_it_equals_the_embedding(tmp_path):
+    d = make_model_dir(tmp_path / "m", TINY_A, seed=4)               # TINY_A ties its embeddings
+    model = build_model(make_model_config(TINY_A))
+    stored = read_checkpoint(d)
+    assert "lm_head.weight" not in stored
+    same = {**stored, "lm_head.weight": stored["model.embed_tokens.weight"].clone()}
+    placed = check_and_place(model, same, torch.float32, "cpu")
+    assert "lm_head.weight" not in placed
+    other = {**stored, "lm_head.weight": stored["model.embed_tokens.weight"] + 1.0}
+    with pytest.raises(WeightError) as err:
+        check_and_place(model, other, torch.float32, "cpu")
+    assert err.value.unexpected == ["lm_head.weight"]
+    # an untied model needs the tensor and never drops it
+    untied = build_model(make_model_config(TINY_B))
+    d2 = make_model_dir(tmp_path / "m2", TINY_B, seed=4)
+    assert "lm_head.weight" in check_and_place(untied, read_checkpoint(d2), torch.float32, "cpu")

@@ -60,7 +60,19 @@ TINY_D = {
     "mamba_d_conv": 4, "mamba_chunk_size": 128, "mamba_rms_norm": False,
 }
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# a fifth one with heads of 128 in both mixers (the larger released models), two KV groups of three query heads
+TINY_E = {
+    **copy.deepcopy(TINY_D),
+    "hidden_size": 192, "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 208,
+    "vocab_size": 301, "mamba_d_ssm": 256, "mamba_n_heads": 2, "mamba_d_head": 128, "mamba_d_state": 128,
+    "max_position_embeddings": 8192,
+}
+
+# the literal second tiny configuration of the benchmark definition (intermediate 192, vocabulary 512); TINY_B above
+# is the same model with sizes that are no multiples of 8 or 16
+TINY_B_LITERAL = {**copy.deepcopy(TINY_B), "intermediate_size": 192, "vocab_size": 512}
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "Bl": TINY_B_LITERAL}
 
 
 def make_model_dir(path: str, raw: dict, seed: int = 0, dtype=torch.float32, perturb: bool = True) -> str:
