@@ -81,8 +81,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* kv_empty = kv_full + kStages;
     uint64_t* q_full = kv_empty + kStages;
     uint64_t* s_ready = q_full + 1;                       // per group and tile parity: S of the tile is in tensor memory
-    uint64_t* p_ready = s_ready + 2 * kGroups;            // per group: P of its tile is in shared memory (128 arrivals)
-    uint64_t* o_ready = p_ready + kGroups;                // per group and tile parity: PV of the tile is added to O
+    // per group and tile parity: P of the tile is in tensor memory (128 arrivals).  Two barriers per group, because a
+    // warp may be a tile ahead of its neighbours (S of the next tile is ready early, and only some warps take the
+    // detour that rescales O): with one barrier its arrival for tile t + 1 would count towards tile t, and the
+    // product would start before a slower warp had stored its rows of P.  Nobody can be two tiles ahead: S of tile
+    // t + 2 is issued behind the product of tile t.
+    uint64_t* p_ready = s_ready + 2 * kGroups;
+    uint64_t* o_ready = p_ready + 2 * kGroups;            // per group and tile parity: PV of the tile is added to O
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 2 * kGroups);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,7 +109,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int g = 0; g < kGroups; ++g) {
             mbar_init(s_ready + 2 * g, 1); mbar_init(s_ready + 2 * g + 1, 1);
             mbar_init(o_ready + 2 * g, 1); mbar_init(o_ready + 2 * g + 1, 1);
-            mbar_init(p_ready + g, 128);
+            mbar_init(p_ready + 2 * g, 128); mbar_init(p_ready + 2 * g + 1, 128);
         }
         *failed = 0;
         mbar_fence_init();
@@ -165,7 +170,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int i = g, t = 0; i < n_kt && ok && !*failed; i += kGroups, ++t) {
                 const int s = i % kStages;
                 // P of tile i is written (and O rescaled where a row's maximum grew): O += P V
-                if (!mbar_wait(p_ready + g, t & 1)) { report(a.error, 3, i); *failed = 1; break; }
+                if (!mbar_wait(p_ready + 2 * g + (t & 1), (t >> 1) & 1)) { report(a.error, 3, i); *failed = 1; break; }
                 fence_after_sync();
                 const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes);
                 const uint32_t p_tmem = tmem + g * kGroupCols + (t & 1) * 64;     // P lies over the S it was made from
@@ -269,7 +274,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tmem_st_wait();
             if (j0 + kKV - 1 > last_pos) fence_async_smem();               // the zeroed V rows are for the tensor core's reads
             fence_before_sync();
-            mbar_arrive(p_ready + grp);
+            mbar_arrive(p_ready + 2 * grp + (t & 1));
             done = t + 1;
         }
         // the row of O once the group's last product has landed

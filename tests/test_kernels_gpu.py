@@ -988,3 +988,25 @@ def test_prompt_attention_kernels_over_thousands_of_keys(shape):
         cu, start, tiles = prefill_inputs(case, lengths, new, k.ATTENTION_TC_TILE)
         close(k.attention_prefill_tc(*args, dev(cu), dev(start), dev(tiles), tiles.shape[0], scale), want, dtype)
         k.check_kernel_errors()
+
+
+def test_attention_prefill_on_tcgen05_when_only_some_warps_keep_rescaling():
+    """Rows 0..31 of every 128-query tile see scores that rise steeply along the keys (their warp fetches, scales and
+    puts back its output rows at every tile), the other rows see random scores (their warps run ahead, up to a tile):
+    the products must still wait for every warp's rows of P.  Several launches, since the order of the warps is a
+    matter of timing."""
+    Hq, Hkv, hd, page = 4, 2, 64, 64
+    dtype = torch.bfloat16
+    k = K()
+    g = torch.Generator().manual_seed(23)
+    lengths, new = [2300, 1500], [2300, 1100]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new, key_ramp=8.3)
+    calm = torch.tensor([(pos - (lengths[r] - new[r])) % 128 >= 32 for r, pos in case["rows"]])
+    case["q"][calm, :, 0] = 0.0
+    cu, start, tiles = prefill_inputs(case, lengths, new, 128)
+    scale = hd ** -0.5
+    args = (dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(cu), dev(start))
+    want = rnd_of(dtype)(attention_reference(case, scale, 0, ref_dtype(dtype)))
+    for _ in range(5):
+        close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale), want, dtype)
+    k.check_kernel_errors()
