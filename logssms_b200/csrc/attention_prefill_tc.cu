@@ -262,9 +262,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     const float x0 = __uint_as_float(c < 32 ? s0[c] : s1[c - 32]);
                     const float x1 = __uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]);
                     const float e0 = ex2_approx(fmaf(x0, a.scale_log2, -ref)), e1 = ex2_approx(fmaf(x1, a.scale_log2, -ref));
-                    sum += e0 + e1;
                     __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
                     pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+                    // the row sum takes the weights as the product will see them (rounded): relative to a lazy maximum
+                    // the largest weight is no power of two, and its rounding would otherwise show in O / l undiminished
+                    const float2 seen = __bfloat1622float2(pr);
+                    sum += seen.x + seen.y;
                 }
                 l += sum;
             }
