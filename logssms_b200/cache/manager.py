@@ -60,9 +60,12 @@ class PageGroup:
         self.pool = FreeList(num_pages, "page")
         self.layer_index = {layer: i for i, layer in enumerate(layers)}
         # [2 (k, v), layers, pages, page_size, kv_heads, head_dim]
-        self.storage = torch.zeros((2, len(layers), max(num_pages, 1), page_size, need.num_kv_heads, need.head_dim),
+        # one page more than the pool hands out: the dummy page (index `num_pages`), where the dummy requests of a
+        # padded step keep their keys and values; its block-table row is the last one
+        self.storage = torch.zeros((2, len(layers), num_pages + 1, page_size, need.num_kv_heads, need.head_dim),
                                    dtype=dtype, device=device)
-        self.block_table = np.full((max_requests, max_pages_per_request), -1, dtype=np.int32)
+        self.block_table = np.full((max_requests + 1, max_pages_per_request), -1, dtype=np.int32)
+        self.block_table[max_requests, :] = num_pages
         self.first_page = np.zeros(max_requests, dtype=np.int64)     # pages below are given back (window)
         self.num_pages_of = np.zeros(max_requests, dtype=np.int64)    # logical pages handed out so far
 
@@ -105,6 +108,9 @@ class CacheManager:
         self.max_pages_per_request = -(-max_seq_len // page_size)
         self.rows = FreeList(max_requests, "request slot")
         self.live: dict[int, RequestCache] = {}
+        # Row, state slot and (per group) page that no request ever gets: a step that is filled up to fixed sizes
+        # (`engine.plan.Bucket`) lets its dummy requests read and write there.
+        self.dummy_row = max_requests
 
         by_need: dict[KVNeed, list[int]] = {}
         for layer, need in enumerate(needs):
@@ -119,7 +125,7 @@ class CacheManager:
         for need in needs:
             per_layer = {}
             for s in need.states:
-                per_layer[s.name] = torch.zeros((max_requests, *s.shape), dtype=s.dtype or dtype, device=self.device)
+                per_layer[s.name] = torch.zeros((max_requests + 1, *s.shape), dtype=s.dtype or dtype, device=self.device)
             self.states.append(per_layer)
 
     # ------------------------------------------------------------------ sizes

@@ -17,6 +17,7 @@ import torch
 
 from ..cache import CacheManager, RequestCache
 from ..parts import StepContext
+from ..parts.context import SHORT_PORTION, Padding
 
 
 @dataclass
@@ -60,6 +61,40 @@ class StaticTables:
         self.ctx: StepContext | None = None
 
 
+@dataclass(frozen=True)
+class Bucket:
+    """Sizes a step is filled up to (see `parts.context.Padding`): requests, tokens, long portions, tokens of short
+    portions.  Wanted places are filled up to `requests`."""
+    requests: int
+    tokens: int
+    long_cap: int
+    short_cap: int
+
+
+def _up(n: int, steps) -> int:
+    for size, grain in steps:
+        if n <= size:
+            return -(-n // grain) * grain
+    size, grain = steps[-1]
+    return -(-n // grain) * grain
+
+
+def bucket_for(lens, wanted: int) -> Bucket | None:
+    """The bucket of a step whose requests bring `lens` tokens and that wants `wanted` places, or None if it has
+    none (more wanted places than requests).  Every bucket leaves room for at least one dummy single token and a
+    dummy portion of more than SHORT_PORTION tokens: the work lists are filled up with those."""
+    B = len(lens)
+    requests = _up(B + 2, ((8, 4), (32, 8), (64, 16), (1 << 30, 32)))
+    if wanted > requests:
+        return None
+    singles = requests - B - 1
+    tokens = _up(int(sum(lens)) + singles + SHORT_PORTION + 1, ((512, 64), (2048, 128), (1 << 30, 256)))
+    n_long = sum(1 for n in lens if n > SHORT_PORTION) + 1
+    n_short = sum(int(n) for n in lens if n <= SHORT_PORTION) + singles
+    return Bucket(requests, tokens, _up(n_long, ((2, 2), (4, 4), (1 << 30, 8))),
+                  _up(n_short, ((8, 8), (32, 8), (64, 16), (1 << 30, 64))))
+
+
 class StepPlanner:
     def __init__(self, cache: CacheManager, device, vocab_size: int | None = None):
         self.cache = cache
@@ -72,12 +107,16 @@ class StepPlanner:
         self._staging_half = 0
         self.h2d_bytes = 0          # bytes of step tables copied host -> device so far
 
-    def plan(self, entries: Sequence[StepEntry], static: StaticTables | None = None) -> StepContext:
+    def plan(self, entries: Sequence[StepEntry], static: StaticTables | None = None,
+             bucket: Bucket | None = None) -> StepContext:
         """Host side of a step: checks, room in the cache, and every per-step integer packed into one
         pinned buffer and copied to the device at once.  With `static` (a captured step's slot) the
         tables keep a fixed width and a fixed place on the device, so that a captured graph finds them;
         every later step planned into the same slot must bring the same numbers of tokens and wanted
-        places, request by request."""
+        places, request by request, or, with `bucket`, fit the same bucket: the step is then filled up
+        with dummy requests (single tokens and one portion, on a state slot and a cache page of their
+        own) to the bucket's numbers of requests, tokens and wanted places, and the context's work lists
+        have the bucket's fixed lengths."""
         B = len(entries)
         seen = set()
         for e in entries:
@@ -103,13 +142,28 @@ class StepPlanner:
         self.cache.check_room([(e.request, int(s + n)) for e, s, n in zip(entries, starts, lens)])
         for e, s, n in zip(entries, starts, lens):
             self.cache.extend(e.request, int(s + n))
-        token_req = np.repeat(np.arange(B, dtype=np.int64), lens)
-        positions = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1], lens) + np.repeat(starts, lens)
         rows = np.fromiter((e.request.row for e in entries), dtype=np.int64, count=B)
         logit_rows = np.asarray([cu[b] + w for b, e in enumerate(entries) for w in e.want], dtype=np.int64)
+        real_entries = B
+        if bucket is not None:
+            # dummy requests behind the real ones: single tokens, then one portion that takes the rest of the tokens
+            singles = bucket.requests - B - 1
+            portion = bucket.tokens - T - singles
+            if singles < 1 or portion <= SHORT_PORTION or len(logit_rows) > bucket.requests:
+                raise ValueError("the step does not fit the bucket it was planned for")
+            lens = np.concatenate([lens, np.ones(singles, dtype=np.int64), [portion]])
+            starts = np.concatenate([starts, np.zeros(singles + 1, dtype=np.int64)])
+            rows = np.concatenate([rows, np.full(singles + 1, self.cache.dummy_row, dtype=np.int64)])
+            tokens = np.concatenate([tokens, np.zeros(singles + portion, dtype=np.int64)])
+            B, T = bucket.requests, bucket.tokens
+            cu = np.zeros(B + 1, dtype=np.int64)
+            np.cumsum(lens, out=cu[1:])
+            logit_rows = np.concatenate([logit_rows, np.full(bucket.requests - len(logit_rows), T - 1, dtype=np.int64)])
+        token_req = np.repeat(np.arange(B, dtype=np.int64), lens)
+        positions = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1], lens) + np.repeat(starts, lens)
         groups = self.cache.groups
         ps = self.page_size
-        max_context = int((starts + lens).max())
+        max_context = int((starts[:real_entries] + lens[:real_entries]).max())
         P = self.cache.max_pages_per_request if static is not None else -(-max_context // ps)
         tables, mappings = [], []
         for g in groups:
@@ -145,7 +199,12 @@ class StepPlanner:
         self.h2d_bytes += total * 4
         self._ring.mark(ring_slot)
         if static is not None and static.ctx is not None:
-            return static.ctx
+            ctx = static.ctx
+            if bucket is not None:
+                ctx.host_lens, ctx.host_starts = lens, starts
+                ctx.padding = Padding(real_entries, bucket.long_cap, bucket.short_cap)
+                ctx.refresh_lists()
+            return ctx
 
         def view(i, shape=None):
             t = dev[int(offsets[i]): int(offsets[i]) + sizes[i]]
@@ -161,7 +220,10 @@ class StepPlanner:
             # the step they were built for)
             max_context=max_context if static is None else self.max_seq_len,
             host_lens=lens, host_starts=starts,
+            padding=None if bucket is None else Padding(real_entries, bucket.long_cap, bucket.short_cap),
         )
+        if bucket is not None:
+            ctx.max_len = T               # an upper bound: the longest real portion differs from step to step
         if static is not None:
             static.ctx = ctx
         return ctx

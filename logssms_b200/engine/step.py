@@ -24,7 +24,7 @@ from ..models import build_model
 from ..ops import kernels as K
 from ..parts import Runtime
 from ..weights import load_weights
-from .plan import StaticTables, StepEntry, StepPlanner
+from .plan import StaticTables, StepEntry, StepPlanner, bucket_for
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -36,7 +36,8 @@ class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", *, max_requests: int = 64, max_seq_len: int = 8192,
                  page_size: int = 64, num_pages: int | None = None, memory_ratio: float = 0.9,
                  device: str = "cuda:0", poison_on_free: bool = False, max_step_tokens: int = 1 << 30,
-                 use_graphs: bool = True, max_graphs: int = 16, max_shape_graphs: int = 8, max_graph_tokens: int = 4096):
+                 use_graphs: bool = True, max_graphs: int = 64, max_shape_graphs: int = 8, max_bucket_graphs: int = 32,
+                 max_graph_tokens: int = 4096):
         if not torch.cuda.is_available():
             raise RuntimeError("logssms_b200 needs a CUDA device (built for sm_100a); there is no CPU path")
         try:
@@ -64,8 +65,10 @@ class Engine:
         self.max_graphs = max_graphs
         self.max_shape_graphs = max_shape_graphs
         self.max_graph_tokens = max_graph_tokens
+        self.max_bucket_graphs = max_bucket_graphs
         self._graphs: dict[int, _StepGraph] = {}             # decode steps, by batch size
         self._shape_graphs: dict[tuple, _StepGraph] = {}      # other steps, by (tokens of every entry, wanted places)
+        self._bucket_graphs: dict[tuple, _StepGraph] = {}     # other steps filled up to a bucket of sizes, by bucket
         self._sightings: dict[tuple, int] = {}               # shapes seen once: (which kind of graph, key) -> count
         self._side_stream: torch.cuda.Stream | None = None
         self.steps_run = 0
@@ -119,7 +122,22 @@ class Engine:
             if all(n == 1 for n in lens) and all(list(e.want) == [0] for e in entries):
                 return self._graph_step(self._graphs, len(entries), self.max_graphs, 2, entries, device_tokens)
             if device_tokens is None and sum(lens) <= self.max_graph_tokens:
-                key = (lens, sum(len(e.want) for e in entries))
+                # The graph of exactly this shape, if the shape has come before (no padding: a prompt length that
+                # recurs, equal portions of a long prompt).  A shape that is new goes through the graph of its bucket:
+                # the step filled up with dummy requests to round numbers of requests, tokens and work-list entries.
+                wanted = sum(len(e.want) for e in entries)
+                key = (lens, wanted)
+                if key in self._shape_graphs or (id(self._shape_graphs), key) in self._sightings:
+                    return self._graph_step(self._shape_graphs, key, self.max_shape_graphs, 3, entries, None)
+                bucket = bucket_for(lens, wanted)
+                # (the dummy portion that fills the bucket is a request like any other: it must fit the sequence limit)
+                if bucket is not None and bucket.tokens <= self.max_graph_tokens + 256 \
+                        and bucket.tokens - sum(lens) <= self.max_seq_len:
+                    self._sightings[(id(self._shape_graphs), key)] = 1
+                    while len(self._sightings) > 64:
+                        self._sightings.pop(next(iter(self._sightings)))
+                    logits = self._graph_step(self._bucket_graphs, bucket, self.max_bucket_graphs, 2, entries, None, bucket)
+                    return logits[:wanted]
                 return self._graph_step(self._shape_graphs, key, self.max_shape_graphs, 3, entries, None)
         return self._run(self.planner.plan(entries), device_tokens)
 
@@ -136,13 +154,20 @@ class Engine:
         return self.model.logits(x, residual, ctx.logit_rows)
 
     def _graph_step(self, graphs: dict, key, most: int, capture_at: int, entries: Sequence[StepEntry],
-                    device_tokens: torch.Tensor | None) -> torch.Tensor:
+                    device_tokens: torch.Tensor | None, bucket=None) -> torch.Tensor:
         """A step through the graph of its shape.  First sight: kernel by kernel with tables of its own (this
         also builds and loads every kernel).  From the second on its tables lie in the slot's fixed buffer;
         until `capture_at` it still runs kernel by kernel (which builds the work lists that long portions need,
         outside of any capture), then it is captured once and replayed."""
         slot = graphs.get(key)
-        if slot is None:
+        if slot is None and bucket is not None:
+            # a bucket serves many shapes: it takes its slot (and its fixed tables) at first sight, and its first
+            # step runs kernel by kernel on them, which also tells which work lists the model asks for
+            if len(graphs) >= most:
+                victim = next((k for k, g in graphs.items() if g.graph is None), next(iter(graphs)))
+                graphs.pop(victim)
+            slot = graphs[key] = _StepGraph()
+        elif slot is None:
             # A shape takes a slot (fixed tables on the device, later a graph) only when it comes a second time:
             # until then it is a count in a bounded list, so that shapes that never recur cost no device memory
             # and push no captured graph out.
@@ -162,8 +187,12 @@ class Engine:
             graphs[key] = graphs.pop(key)                 # most recently used last
         slot.seen += 1
         if slot.graph is None and slot.seen < capture_at:
-            return self._run(self.planner.plan(entries, slot), device_tokens)
-        ctx = self.planner.plan(entries, slot)
+            ctx = self.planner.plan(entries, slot, bucket)
+            logits = self._run(ctx, device_tokens)
+            if bucket is not None:
+                ctx.freeze_lists()
+            return logits
+        ctx = self.planner.plan(entries, slot, bucket)
         if device_tokens is not None:
             ctx.token_ids.copy_(device_tokens)            # before the capture / replay, on the same stream
         if slot.graph is None:

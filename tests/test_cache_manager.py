@@ -35,10 +35,11 @@ def test_groups_are_formed_by_need():
     m = manager(needs)
     assert len(m.groups) == 2
     assert m.groups[0].layers == [0, 2] and m.groups[1].layers == [1]
-    assert m.groups[0].storage.shape == (2, 2, 12, 16, 2, 16)
-    assert m.states[2]["s"].shape == (4, 3, 2) and m.states[3]["only"].dtype == torch.float32
+    assert m.groups[0].storage.shape == (2, 2, 13, 16, 2, 16)        # 12 pages and the dummy page
+    assert m.states[2]["s"].shape == (5, 3, 2) and m.states[3]["only"].dtype == torch.float32
     k, v, gi = m.kv(2)
-    assert gi == 0 and k.shape == (12, 16, 2, 16)
+    assert gi == 0 and k.shape == (13, 16, 2, 16)
+    assert m.dummy_row == 4 and (m.groups[0].block_table[4] == 12).all()     # the dummy request's row names the dummy page
 
 
 def test_pages_follow_length_and_return_at_release():

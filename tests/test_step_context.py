@@ -52,3 +52,52 @@ def test_a_step_of_short_portions_has_no_long_ones():
     assert not ctx.has_long_portions
     tokens, n = ctx.short_portion_tokens()
     assert n == 2 + SHORT_PORTION and tokens.tolist() == list(range(n))
+
+
+def test_buckets_leave_room_for_the_dummy_requests_and_hold_every_list():
+    """Any step fits the bucket chosen for it: at least one dummy single token and a dummy portion of more than
+    SHORT_PORTION tokens behind the real requests, and the fixed list lengths hold the real work plus the dummies'."""
+    from logssms_b200.engine.plan import bucket_for
+    from logssms_b200.parts.context import Padding, chunk_lists, request_lists, short_token_list, tile_list
+    rng = random.Random(11)
+    seen = set()
+    for _ in range(300):
+        B = rng.randint(1, 40)
+        lens = [rng.choice([1, 1, 1, 2, SHORT_PORTION, SHORT_PORTION + 1, 40, 64, 129, 300, 512, 700]) for _ in range(B)]
+        starts = [rng.choice([0, 3, 64, 1000]) for _ in range(B)]
+        wanted = rng.randint(0, B)
+        bk = bucket_for(lens, wanted)
+        assert bk is not None and bk.requests >= B + 2 and bk.requests >= wanted
+        singles = bk.requests - B - 1
+        portion = bk.tokens - sum(lens) - singles
+        assert singles >= 1 and portion > SHORT_PORTION
+        assert bk.tokens % 64 == 0 and bk.requests % 4 == 0
+        seen.add(bk)
+        # the step as the planner pads it
+        plens = np.asarray(lens + [1] * singles + [portion])
+        pstarts = np.asarray(starts + [0] * (singles + 1))
+        pad = Padding(B, bk.long_cap, bk.short_cap)
+        dummy_single_request, dummy_single_token = B, sum(lens)
+        for tile in (64, 128):
+            cap = -(-bk.tokens // tile) + pad.long_cap
+            tiles = tile_list(plens, pstarts, tile, cap)
+            real = sorted((b, t0) for b, m in enumerate(plens) if m > SHORT_PORTION for t0 in range(0, int(m), tile))
+            assert tiles.shape == (cap, 2) and sorted(map(tuple, tiles[:len(real)].tolist())) == real
+            assert all(tuple(t) == (bk.requests - 1, 0) for t in tiles[len(real):].tolist())      # the dummy portion's first tile
+            chunks, per_request = chunk_lists(plens, tile, cap, pad.long_cap)
+            assert chunks.shape == (cap, 2) and per_request.shape == (pad.long_cap, 3)
+            n_long = sum(1 for m in plens if m > SHORT_PORTION)
+            assert all(tuple(r) == tuple(per_request[n_long - 1]) for r in per_request[n_long:].tolist())
+            assert per_request[n_long - 1][0] == bk.requests - 1
+        short = short_token_list(plens, pad.short_cap, dummy_single_token)
+        n_short = sum(int(m) for m in plens if m <= SHORT_PORTION)
+        assert short.shape == (pad.short_cap,) and n_short <= pad.short_cap and set(short[n_short:].tolist()) <= {dummy_single_token}
+        long_r, short_r = request_lists(plens, pad.long_cap, min(pad.short_cap, bk.requests), dummy_single_request)
+        assert long_r.shape == (pad.long_cap,) and long_r[-1] == bk.requests - 1
+        assert set(short_r[sum(1 for m in plens if m <= SHORT_PORTION):].tolist()) <= {dummy_single_request}
+    # the shapes of chunked serving (some decoding requests beside one prompt portion under a budget of 512 tokens):
+    # a thousand different shapes, a few dozen buckets (requests x tokens)
+    shapes = {(d, rng.randint(SHORT_PORTION + 1, 512 - d)) for d in (rng.randint(0, 32) for _ in range(1500))}
+    buckets = {bucket_for([1] * d + [n], d + 1) for d, n in shapes}
+    assert len(shapes) > 1000 and len(buckets) <= 60, (len(shapes), len(buckets))
+    assert bucket_for([5, 5], 3) is not None and bucket_for([5], 9) is None      # more wanted places than the bucket has requests

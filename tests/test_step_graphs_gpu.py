@@ -109,3 +109,45 @@ def test_shapes_that_never_recur_push_no_captured_graph_out(tmp_path):
     prompt(13)                         # ... and the slot without a graph (12) goes before the captured one
     assert captured() == {11} and set(k[0][0] for k in engine._shape_graphs) == {11, 13}
     assert len(engine._sightings) <= 64
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_steps_of_new_shapes_replay_the_graph_of_their_bucket(tmp_path, name, dtype):
+    """Mixed steps none of whose shapes comes twice (decoding requests beside prompt portions of changing length):
+    filled up with dummy requests to the sizes of a bucket, they are captured once per bucket and replayed.  The
+    logits must be those of the same steps run kernel by kernel without any filling, and the plain model's."""
+    from logssms_b200.engine import Engine
+    from tiny import plain_logits, rel_err
+    raw = TINY[name]
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=44, dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+    g = torch.Generator().manual_seed(19)
+    sizes = {"p": 700, "q": 520, "d0": 40, "d1": 23, "d2": 31}
+    prompts = {k: torch.randint(0, raw["vocab_size"], (n,), generator=g).tolist() for k, n in sizes.items()}
+    plan = [[("d0", 12, [11]), ("d1", 9, [8]), ("d2", 10, [9])]]
+    # prompt p in portions of 100 + i beside the three decoding requests; then q beside two of them
+    portions_p = [100, 101, 99, 102, 98, 103, 97]
+    for n in portions_p:
+        plan.append([("d0", 1, [0]), ("d1", 1, [0]), ("d2", 1, [0]), ("p", n, [n - 1])])
+    for n in (150, 133, 129, 108):
+        plan.append([("d0", 1, [0]), ("q", n, [n - 1]), ("d2", 1, [0])])
+    results = {}
+    for graphs in (False, True):
+        engine = Engine(model_dir, dtype, max_requests=6, max_seq_len=1024, num_pages=24, use_graphs=graphs, poison_on_free=True)
+        results[graphs] = run_steps(engine, plan, prompts)
+        engine.cache.check_integrity()
+        if graphs:
+            replayed = sum(max(0, slot.seen - 1) for slot in engine._bucket_graphs.values() if slot.graph is not None)
+            assert replayed >= 7, {k: slot.seen for k, slot in engine._bucket_graphs.items()}
+            assert not engine._shape_graphs                      # no shape came twice
+        del engine
+    tol = 2e-5 if dtype == "float32" else TOL[dtype]
+    for i, (a, b) in enumerate(zip(results[False], results[True])):
+        assert a.shape == b.shape, f"step {i}"
+        scale = float(a.abs().max()) or 1.0
+        assert float((a - b).abs().max()) <= tol * scale, f"step {i}: the bucket's graph differs from the kernel-by-kernel run"
+    # and against the plain model: the last token of every portion of p
+    want = plain_logits(model_dir, prompts["p"], dtype)
+    ends = [sum(portions_p[:i + 1]) - 1 for i in range(len(portions_p))]
+    got = torch.stack([results[True][1 + i][3] for i in range(len(portions_p))])
+    assert rel_err(got, want[ends]) <= TOL[dtype]
