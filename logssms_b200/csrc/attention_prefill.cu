@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(kGroupThreads * NG) attn_prefill_kernel(Prefil
     const int item = (wave & 1) ? wave_begin + (min(a.per_wave, a.n_items - wave_begin) - 1 - wave_pos) : (int)blockIdx.x;
     const int tile = item / a.Hq;
     const int b = a.tiles[2 * tile], q0 = a.tiles[2 * tile + 1];
+    if (b < 0) return;                                  // a list entry without work: the lists of a step that was filled up to fixed sizes end in such entries
     const int h = item % a.Hq, kvh = h / (a.Hq / a.Hkv);
     const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
     const int rows = min(kQTile, len - q0);              // valid query rows of this tile

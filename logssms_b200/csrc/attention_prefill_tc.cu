@@ -96,6 +96,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int item = blockIdx.x;
     const int tile = item / a.Hq, h = item % a.Hq, kvh = h / (a.Hq / a.Hkv);
     const int b = a.tiles[2 * tile], q0 = a.tiles[2 * tile + 1];
+    if (b < 0) return;                                  // a list entry without work: the lists of a step that was filled up to fixed sizes end in such entries
     const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
     const int rows = min(kQ, len - q0);
     const int pos0 = a.start_pos[b] + q0, last_pos = pos0 + rows - 1;

@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(kStateThreads) ssd_chunk_state_kernel(SsdArgs 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int chunk = blockIdx.x, h = blockIdx.y;
     const int b = a.chunks[2 * chunk], t0 = a.chunks[2 * chunk + 1];
+    if (b < 0) return;                                  // a list entry without work: the lists of a step that was filled up to fixed sizes end in such entries
     const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
     const int Lc = min(a.L, len - t0), Lpad = round_up(a.L, 16);
     const int tok0 = begin + t0;
@@ -180,6 +181,7 @@ __global__ void __launch_bounds__(kStateThreads) ssd_chunk_state_kernel(SsdArgs 
 __global__ void __launch_bounds__(256) ssd_state_pass_kernel(SsdArgs a) {
     const int r = blockIdx.x, h = blockIdx.y;
     const int b = a.req_chunks[3 * r], c0 = a.req_chunks[3 * r + 1], nc = a.req_chunks[3 * r + 2];
+    if (b < 0) return;                                  // a list entry without work: the lists of a step that was filled up to fixed sizes end in such entries
     const size_t per_head = (size_t)a.P * a.N;
     const size_t i = ((size_t)blockIdx.z * blockDim.x + threadIdx.x) * 4;
     if (i >= per_head) return;
@@ -218,6 +220,7 @@ __global__ void __launch_bounds__(MAXT) ssd_chunk_scan_kernel(SsdArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int chunk = blockIdx.x, h = blockIdx.y;
     const int b = a.chunks[2 * chunk], t0 = a.chunks[2 * chunk + 1];
+    if (b < 0) return;                                  // a list entry without work: the lists of a step that was filled up to fixed sizes end in such entries
     const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
     const int Lc = min(a.L, len - t0), Lpad = round_up(a.L, 16);
     const int tok0 = begin + t0;

@@ -81,6 +81,7 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
 
     const int chunk = blockIdx.x, h = blockIdx.y;
     const int b = a.chunks[2 * chunk], t0 = a.chunks[2 * chunk + 1];
+    if (b < 0) return;                                  // a list entry without work: the lists of a step that was filled up to fixed sizes end in such entries
     const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
     const int Lc = min(kL, len - t0);
     const int tok0 = begin + t0;

@@ -26,7 +26,10 @@ class Padding:
     Behind the `entries` real requests of the batch lie dummy ones that all use a state slot and a cache page nobody
     else uses: first single tokens, then one portion of more than SHORT_PORTION tokens (the last request of the
     batch).  To the kernels they are requests like any other; nobody reads what they compute.  The work lists below
-    have fixed lengths (`*_cap`) and are filled up with work for the dummy requests."""
+    have fixed lengths (`*_cap`): lists of tiles and chunks end in entries that name request -1 (no work), lists of
+    single tokens and of requests are filled up with a dummy single token.  What the dummy requests compute stays
+    finite like any request's, which matters: a tensor-core kernel that reads a box of rows beyond its own request's
+    end multiplies them by zero weights, and 0 x NaN is NaN."""
     entries: int          # real requests; requests entries .. num_requests - 1 are dummies
     long_cap: int         # most portions of more than SHORT_PORTION tokens, the dummy one included
     short_cap: int        # most tokens of portions of at most SHORT_PORTION tokens, the dummy ones included
@@ -44,11 +47,11 @@ def _fill(rows: list, cap: int | None, filler, width: int) -> np.ndarray:
 def tile_list(lens, starts, tile: int, cap: int | None = None) -> np.ndarray:
     """int32 [n, 2]: (request index in the batch, first token within its portion) for every run of `tile` tokens of
     every portion longer than SHORT_PORTION, the tile that sees the most keys first (a causal tile's cost grows with
-    its position).  With `cap` the list has exactly that many rows; the surplus repeats the last request's first tile
-    (a dummy request's, in a padded step)."""
+    its position).  With `cap` the list has exactly that many rows; the surplus rows name request -1, which the
+    kernels skip."""
     pairs = [(b, t0) for b, n in enumerate(lens) if n > SHORT_PORTION for t0 in range(0, int(n), tile)]
     pairs.sort(key=lambda bt: -(int(starts[bt[0]]) + min(bt[1] + tile, int(lens[bt[0]]))))
-    return _fill(pairs, cap, (len(lens) - 1, 0), 2)
+    return _fill(pairs, cap, (-1, 0), 2)
 
 
 def short_token_list(lens, cap: int | None = None, filler: int = 0) -> np.ndarray:
@@ -61,15 +64,14 @@ def short_token_list(lens, cap: int | None = None, filler: int = 0) -> np.ndarra
 def chunk_lists(lens, chunk: int, cap_chunks: int | None = None, cap_long: int | None = None) -> tuple[np.ndarray, np.ndarray]:
     """Work lists of a chunked scan over the long portions: int32 [n, 2] (request index, first token of the chunk
     within its portion) and int32 [m, 3] (request index, its first chunk, its number of chunks).  With capacities the
-    surplus repeats the last request's chunks (a dummy request's, in a padded step)."""
+    surplus rows name request -1, which the kernels skip."""
     chunks, per_request = [], []
     for b, n in enumerate(lens):
         if n > SHORT_PORTION:
             first = len(chunks)
             chunks += [(b, t0) for t0 in range(0, int(n), chunk)]
             per_request.append((b, first, len(chunks) - first))
-    return (_fill(chunks, cap_chunks, (len(lens) - 1, 0), 2),
-            _fill(per_request, cap_long, per_request[-1] if per_request else (0, 0, 0), 3))
+    return _fill(chunks, cap_chunks, (-1, 0), 2), _fill(per_request, cap_long, (-1, 0, 0), 3)
 
 
 def request_lists(lens, cap_long: int | None = None, cap_short: int | None = None, short_filler: int = 0) -> tuple[np.ndarray, np.ndarray]:

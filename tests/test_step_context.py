@@ -83,12 +83,12 @@ def test_buckets_leave_room_for_the_dummy_requests_and_hold_every_list():
             tiles = tile_list(plens, pstarts, tile, cap)
             real = sorted((b, t0) for b, m in enumerate(plens) if m > SHORT_PORTION for t0 in range(0, int(m), tile))
             assert tiles.shape == (cap, 2) and sorted(map(tuple, tiles[:len(real)].tolist())) == real
-            assert all(tuple(t) == (bk.requests - 1, 0) for t in tiles[len(real):].tolist())      # the dummy portion's first tile
+            assert all(tuple(t) == (-1, 0) for t in tiles[len(real):].tolist())                    # entries without work
             chunks, per_request = chunk_lists(plens, tile, cap, pad.long_cap)
             assert chunks.shape == (cap, 2) and per_request.shape == (pad.long_cap, 3)
             n_long = sum(1 for m in plens if m > SHORT_PORTION)
-            assert all(tuple(r) == tuple(per_request[n_long - 1]) for r in per_request[n_long:].tolist())
-            assert per_request[n_long - 1][0] == bk.requests - 1
+            assert all(tuple(r) == (-1, 0, 0) for r in per_request[n_long:].tolist())
+            assert per_request[n_long - 1][0] == bk.requests - 1 and all(c[0] == -1 for c in chunks[len(real):].tolist())
         short = short_token_list(plens, pad.short_cap, dummy_single_token)
         n_short = sum(int(m) for m in plens if m <= SHORT_PORTION)
         assert short.shape == (pad.short_cap,) and n_short <= pad.short_cap and set(short[n_short:].tolist()) <= {dummy_single_token}

@@ -122,15 +122,19 @@ def test_steps_of_new_shapes_replay_the_graph_of_their_bucket(tmp_path, name, dt
     raw = TINY[name]
     model_dir = make_model_dir(tmp_path / "m", raw, seed=44, dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
     g = torch.Generator().manual_seed(19)
-    sizes = {"p": 700, "q": 520, "d0": 40, "d1": 23, "d2": 31}
+    sizes = {"p": 700, "q": 520, "r": 74 + 81 + 60, "d0": 40, "d1": 23, "d2": 31}
     prompts = {k: torch.randint(0, raw["vocab_size"], (n,), generator=g).tolist() for k, n in sizes.items()}
     plan = [[("d0", 12, [11]), ("d1", 9, [8]), ("d2", 10, [9])]]
     # prompt p in portions of 100 + i beside the three decoding requests; then q beside two of them
     portions_p = [100, 101, 99, 102, 98, 103, 97]
     for n in portions_p:
         plan.append([("d0", 1, [0]), ("d1", 1, [0]), ("d2", 1, [0]), ("p", n, [n - 1])])
-    for n in (150, 133, 129, 108):
+    for n in (150, 133):
         plan.append([("d0", 1, [0]), ("q", n, [n - 1]), ("d2", 1, [0])])
+    # two prompt portions in one step: q goes on while r starts (a new request behind a continuing one) and goes on
+    for n, m in ((129, 74), (108, 81)):
+        plan.append([("d0", 1, [0]), ("q", n, [n - 1]), ("r", m, [m - 1]), ("d2", 1, [0])])
+    plan.append([("r", 60, [59]), ("d0", 1, [0])])
     results = {}
     for graphs in (False, True):
         engine = Engine(model_dir, dtype, max_requests=6, max_seq_len=1024, num_pages=24, use_graphs=graphs, poison_on_free=True)
