@@ -369,7 +369,7 @@ def run_0p5b(args, clocks) -> dict:
         def prefill_run() -> dict:
             ids = rng.integers(0, cfg["vocab_size"], PREFILL_TOKENS).tolist()
             times = []
-            for i in range(3 + 5):
+            for i in range(8 + 5):
                 req = llm.engine.new_request()
                 torch.cuda.synchronize()
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -377,7 +377,7 @@ def run_0p5b(args, clocks) -> dict:
                 llm.engine.step([StepEntry(req, ids, [PREFILL_TOKENS - 1])])
                 stop.record()
                 torch.cuda.synchronize()
-                if i >= 3:
+                if i >= 8:
                     times.append(start.elapsed_time(stop))
                 llm.engine.release(req)
             K.check_kernel_errors(llm.engine.device)
@@ -386,17 +386,37 @@ def run_0p5b(args, clocks) -> dict:
             return {"value": PREFILL_TOKENS / (ms / 1e3), "tokens": PREFILL_TOKENS, "ms": ms,
                     "frac": flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), "tflops": flops / (ms / 1e3) / 1e12}
 
+        def new_length_run() -> float:
+            """Prompts of lengths that have never come before (2,041, 2,039, ...): each runs through the graph of its
+            bucket, filled up with dummy requests to 2,176 tokens.  Median device time of the later ones."""
+            times = []
+            for i, n in enumerate(range(PREFILL_TOKENS - 7, PREFILL_TOKENS - 7 - 2 * 8, -2)):
+                ids = rng.integers(0, cfg["vocab_size"], n).tolist()
+                req = llm.engine.new_request()
+                torch.cuda.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                llm.engine.step([StepEntry(req, ids, [n - 1])])
+                stop.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    times.append(start.elapsed_time(stop))
+                llm.engine.release(req)
+            return statistics.median(times)
+
         def prefill_both() -> dict:
-            """The engine replays a step whose shape it has seen twice from a CUDA graph (`ms`, `value`, `frac`);
-            `first_ms` is the same step launched kernel by kernel, as a prompt of a new length runs."""
+            """A prompt length that keeps coming is replayed from a CUDA graph of its own (`ms`, `value`, `frac`);
+            `first_ms` is a prompt of a length that has never come before, through the graph of its bucket;
+            `eager_ms` the same step launched kernel by kernel (graphs off)."""
             out = prefill_run()
+            out["first_ms"] = new_length_run()
             llm.engine.use_graphs = False
             try:
-                first = prefill_run()
+                out["eager_ms"] = prefill_run()["ms"]
             finally:
                 llm.engine.use_graphs = True
-            out["first_ms"] = first["ms"]
-            out["path"] = "step graph (third and later steps of a shape); first_ms: kernel by kernel"
+            out["path"] = ("graph of the shape (a length that keeps coming); first_ms: a new length through the graph "
+                           "of its bucket; eager_ms: kernel by kernel")
             return out
 
         main = run(args.batch, False)
@@ -425,7 +445,7 @@ def run_0p5b(args, clocks) -> dict:
                     "path": "LLM.add_request / LLM.step, token ids through the host every step",
                     "overlapped_value": main["wall_tok_s"]},
             "gpu_launches": main["launches"],
-            "prefill": {k: prefill[k] for k in ("value", "tokens", "ms", "frac", "first_ms", "path")},
+            "prefill": {k: prefill[k] for k in ("value", "tokens", "ms", "frac", "first_ms", "eager_ms", "path")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / pk["hbm_gbs"], "bytes_per_step": bytes_step, "peaks": pk_src},
             "points": points,
@@ -491,7 +511,8 @@ def run_1p5b_deep(args, clocks, layers: int | None = None) -> dict:
                     "clock_span": (lo, clocks.mark()), "bound_s": sum(step_bound_seconds(num, e, w, pk) for e, w in shapes)}
 
         llm.engine.step = recording_step
-        once(99)                                   # warm-up: builds kernels, captures the graphs of recurring shapes
+        once(99)                                   # warm-up with other prompts and lengths: builds kernels,
+        once(98)                                   # captures the graphs of the buckets that such steps fall into
         run = once(4321)
         ck = clocks.summary(*run["clock_span"])
         gen = requests * new_tokens

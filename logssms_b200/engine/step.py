@@ -70,6 +70,8 @@ class Engine:
         self._shape_graphs: dict[tuple, _StepGraph] = {}      # other steps, by (tokens of every entry, wanted places)
         self._bucket_graphs: dict[tuple, _StepGraph] = {}     # other steps filled up to a bucket of sizes, by bucket
         self._sightings: dict[tuple, int] = {}               # shapes seen once: (which kind of graph, key) -> count
+        self._often: dict[tuple, int] = {}                   # how often a shape has gone through its bucket's graph
+        self.exact_after = 4                                 # ... before it gets a graph of its own
         self._side_stream: torch.cuda.Stream | None = None
         self.steps_run = 0
 
@@ -127,15 +129,19 @@ class Engine:
                 # the step filled up with dummy requests to round numbers of requests, tokens and work-list entries.
                 wanted = sum(len(e.want) for e in entries)
                 key = (lens, wanted)
-                if key in self._shape_graphs or (id(self._shape_graphs), key) in self._sightings:
-                    return self._graph_step(self._shape_graphs, key, self.max_shape_graphs, 3, entries, None)
                 bucket = bucket_for(lens, wanted)
                 # (the dummy portion that fills the bucket is a request like any other: it must fit the sequence limit)
-                if bucket is not None and bucket.tokens <= self.max_graph_tokens + 256 \
-                        and bucket.tokens - sum(lens) <= self.max_seq_len:
-                    self._sightings[(id(self._shape_graphs), key)] = 1
-                    while len(self._sightings) > 64:
-                        self._sightings.pop(next(iter(self._sightings)))
+                if bucket is not None and (bucket.tokens > self.max_graph_tokens + 256
+                                           or bucket.tokens - sum(lens) > self.max_seq_len):
+                    bucket = None
+                often = self._often.get(key, 0) + 1
+                if key not in self._shape_graphs and bucket is not None and often <= self.exact_after:
+                    # (a graph of its own costs a shape two slow steps, one kernel by kernel and one captured: that pays
+                    # only for a shape that keeps coming)
+                    self._often.pop(key, None)
+                    self._often[key] = often
+                    while len(self._often) > 256:
+                        self._often.pop(next(iter(self._often)))
                     logits = self._graph_step(self._bucket_graphs, bucket, self.max_bucket_graphs, 2, entries, None, bucket)
                     return logits[:wanted]
                 return self._graph_step(self._shape_graphs, key, self.max_shape_graphs, 3, entries, None)

@@ -34,7 +34,12 @@ def run_steps(engine, plan, prompts):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_steps_of_a_repeated_shape_replay_from_a_graph_with_the_same_logits(tmp_path, name, dtype):
-    from logssms_b200.engine import Engine
+    from logssms_b200.engine import Engine as _Engine
+
+    def Engine(*a, **kw):
+        e = _Engine(*a, **kw)
+        e.exact_after = 0          # a shape gets a graph of its own at once (by default only after some steps through its bucket's)
+        return e
     raw = TINY[name]
     model_dir = make_model_dir(tmp_path / "m", raw, seed=41, dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
     g = torch.Generator().manual_seed(9)
@@ -71,6 +76,7 @@ def test_step_graphs_are_bounded_in_number_and_in_tokens(tmp_path):
     raw = TINY["A"]
     model_dir = make_model_dir(tmp_path / "m", raw, seed=42)
     engine = Engine(model_dir, "float32", max_requests=2, max_seq_len=128, num_pages=4, max_shape_graphs=2, max_graph_tokens=16)
+    engine.exact_after = 0             # every shape straight to a graph of its own
     for n in (10, 11, 12, 20):
         for _ in range(3):
             r = engine.new_request()
@@ -86,6 +92,7 @@ def test_shapes_that_never_recur_push_no_captured_graph_out(tmp_path):
     raw = TINY["A"]
     model_dir = make_model_dir(tmp_path / "m", raw, seed=43)
     engine = Engine(model_dir, "float32", max_requests=2, max_seq_len=128, num_pages=4, max_shape_graphs=2, max_graph_tokens=64)
+    engine.exact_after = 0             # every shape straight to a graph of its own
 
     def prompt(n):
         r = engine.new_request()
