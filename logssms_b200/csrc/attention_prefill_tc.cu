@@ -1,6 +1,8 @@
 // Causal grouped-query attention for prompt portions over the paged cache on the 5th-generation tensor cores
-// (tcgen05, accumulators in tensor memory, operands brought by TMA).  bfloat16, head size 64, pages of a
-// multiple of 64 tokens; every other shape stays on the mma.sync kernel (attention_prefill.cu).
+// (tcgen05, accumulators in tensor memory, operands brought by TMA).  bfloat16, head size 64 or 128, pages of a
+// multiple of 64 tokens; every other shape stays on the mma.sync kernel (attention_prefill.cu).  The description
+// below gives the numbers for heads of 64; with heads of 128 a tile is two blocks of 64 dims side by side, S takes
+// 8 products, PV 4 per block of output dims, O has 128 columns and the ring 6 stages.
 //
 // One CTA per (128 query tokens of one request's portion, query head), 11 warps:
 //   warp 0     one thread: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the Q tile once, then of the
@@ -41,18 +43,25 @@ using namespace lb200::tc;
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int kQ = 128, kKV = 64, kHD = 64;               // queries per CTA, keys per tile, head size
-constexpr int kStages = 8;                                // K|V tiles in shared memory: each group has three in use, the rest are on their way
+constexpr int kQ = 128, kKV = 64;                         // queries per CTA, keys per tile
 constexpr int kGroups = 2;                                // softmax groups of 128 threads
 constexpr int kFirstSoftmaxWarp = 1 + kGroups;            // warp 0: TMA; warps 1..kGroups: one issuing thread per group
 constexpr int kThreads = 32 * (kFirstSoftmaxWarp + 4 * kGroups);
-constexpr uint32_t kQBytes = kQ * kHD * 2, kTileBytes = kKV * kHD * 2;
-constexpr uint32_t kGroupCols = 192;                      // per group: S (then P) of even tiles 0..63, of odd tiles 64..127, O 128..191
 constexpr uint32_t kTmemCols = 512;
-static_assert(kGroups * kGroupCols <= kTmemCols, "tensor memory");
-constexpr uint32_t kMergeBytes = (kHD + 2) * kQ * 4;      // a group's partial result, [column][row] float32
 constexpr float kTau = 8.f;                               // log2 of the growth of a row's maximum that O is rescaled for
-static_assert((kGroups - 1) * kMergeBytes <= kStages * 2 * kTileBytes, "the partial results lie over the K|V ring");
+// Per head size (64 or 128).  A tile of shared memory is made of blocks of 64 dims (rows of 128 bytes, the width
+// of the 128-byte swizzle): one block for heads of 64, two side by side for heads of 128.
+template <int HD> struct Shape {
+    static constexpr int kBlocks = HD / 64;
+    // K|V tiles in shared memory: each group has three in use, the rest are on their way (6 x 32 KB + Q fill the SM at 128)
+    static constexpr int kStages = HD == 64 ? 8 : 6;
+    static constexpr uint32_t kQBlock = kQ * 128, kKVBlock = kKV * 128;          // bytes of one block of Q, of K or V
+    static constexpr uint32_t kQBytes = kQBlock * kBlocks, kTileBytes = kKVBlock * kBlocks;
+    static constexpr uint32_t kGroupCols = 128 + HD;      // per group: S (then P) of even tiles 0..63, of odd tiles 64..127, O from 128
+    static constexpr uint32_t kMergeBytes = (64 + 2) * kQ * 4;   // a group's partial result for 64 dims, [column][row] float32
+    static_assert(kGroups * kGroupCols <= kTmemCols, "tensor memory");
+    static_assert((kGroups - 1) * kMergeBytes <= kStages * 2 * kTileBytes, "the partial results lie over the K|V ring");
+};
 
 struct TcArgs {
     bf16* out;                                            // [tokens, Hq, 64]
@@ -69,13 +78,17 @@ __device__ __forceinline__ void report(int* error, int role, int tile) {
     if (error != nullptr) atomicCAS(error, 0, (role << 24) | ((blockIdx.x & 0xFFF) << 12) | (tile & 0xFFF) | 0x40000000);
 }
 
+template <int HD>
 __global__ void __launch_bounds__(kThreads)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, TcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* q_s = base;                                  // [128][128 B]
-    uint8_t* kv_s = q_s + kQBytes;                        // stages of K [64][128 B] | V [64][128 B]
+    typedef Shape<HD> Sh;
+    constexpr int kHD = HD, kStages = Sh::kStages, kBlocks = Sh::kBlocks;
+    constexpr uint32_t kQBytes = Sh::kQBytes, kTileBytes = Sh::kTileBytes, kGroupCols = Sh::kGroupCols;
+    uint8_t* q_s = base;                                  // blocks of [128][128 B]
+    uint8_t* kv_s = q_s + kQBytes;                        // stages of K (blocks of [64][128 B]) | V (the same)
     float* merge = reinterpret_cast<float*>(kv_s);        // at the end, over the ring: per group beyond the first [66][128]
     uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv_s + kStages * 2 * kTileBytes);
     uint64_t* kv_empty = kv_full + kStages;
@@ -124,7 +137,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (warp == 0) {
         if (lane == 0) {
             mbar_expect_tx(q_full, kQBytes);
-            tma_load_2d(q_s, &map_q, q_full, h * kHD, begin + q0);
+#pragma unroll
+            for (int blk = 0; blk < kBlocks; ++blk) tma_load_2d(q_s + blk * Sh::kQBlock, &map_q, q_full, h * kHD + blk * 64, begin + q0);
             int issued = 0;
             for (int i = 0; i < n_kt && !*failed; ++i, ++issued) {
                 const int s = i % kStages;
@@ -134,8 +148,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const int row = bt[page] * a.page_size + (j0 - page * a.page_size);
                 uint8_t* k_tile = kv_s + (size_t)s * 2 * kTileBytes;
                 mbar_expect_tx(kv_full + s, 2 * kTileBytes);
-                tma_load_2d(k_tile, &map_k, kv_full + s, kvh * kHD, row);
-                tma_load_2d(k_tile + kTileBytes, &map_v, kv_full + s, kvh * kHD, row);
+#pragma unroll
+                for (int blk = 0; blk < kBlocks; ++blk) {
+                    tma_load_2d(k_tile + blk * Sh::kKVBlock, &map_k, kv_full + s, kvh * kHD + blk * 64, row);
+                    tma_load_2d(k_tile + kTileBytes + blk * Sh::kKVBlock, &map_v, kv_full + s, kvh * kHD + blk * 64, row);
+                }
             }
             if (*failed) {                                 // let the copies already under way land before the CTA leaves
                 mbar_wait(q_full, 0);
@@ -150,16 +167,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // float32 accumulator, bfloat16 operands, N 64, M 128; the B operand of PV is MN-major (V)
             const uint32_t idesc_s = umma_idesc(kQ, kKV);
             const uint32_t idesc_o = idesc_s | kBMnMajor;
-            const uint64_t qdesc = umma_desc(q_s);
+            uint64_t qdesc[kBlocks];
+#pragma unroll
+            for (int blk = 0; blk < kBlocks; ++blk) qdesc[blk] = umma_desc(q_s + blk * Sh::kQBlock);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) { report(a.error, 2, 0xFFF); *failed = 1; }
             auto issue_s = [&](int i, int t) -> bool {     // S of tile i, the group's tile number t, into its S buffer t & 1
                 const int s = i % kStages;
                 if (!mbar_wait(kv_full + s, (i / kStages) & 1)) { report(a.error, 2, i); *failed = 1; return false; }
                 fence_after_sync();
-                const uint64_t kdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes);
 #pragma unroll
-                for (int k = 0; k < kHD / 16; ++k) umma_bf16(tmem + g * kGroupCols + (t & 1) * 64, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k != 0);
+                for (int blk = 0; blk < kBlocks; ++blk) {
+                    const uint64_t kdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + blk * Sh::kKVBlock);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)            // 16 dims per product, 64 per block
+                        umma_bf16(tmem + g * kGroupCols + (t & 1) * 64, qdesc[blk] + 2 * k, kdesc + 2 * k, idesc_s, (blk | k) != 0);
+                }
                 umma_commit(s_ready + 2 * g + (t & 1));
                 return true;
             };
@@ -173,11 +196,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // P of tile i is written (and O rescaled where a row's maximum grew): O += P V
                 if (!mbar_wait(p_ready + 2 * g + (t & 1), (t >> 1) & 1)) { report(a.error, 3, i); *failed = 1; break; }
                 fence_after_sync();
-                const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes);
                 const uint32_t p_tmem = tmem + g * kGroupCols + (t & 1) * 64;     // P lies over the S it was made from
 #pragma unroll
-                for (int k = 0; k < kKV / 16; ++k)         // 16 keys: 8 columns of P (two bfloat16 each), two 8-row groups of V = 2048 bytes
-                    umma_bf16_tmem_a(tmem + g * kGroupCols + 128, p_tmem + 8 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o, (t > 0 || k != 0) ? 1u : 0u);
+                for (int blk = 0; blk < kBlocks; ++blk) {  // 64 dims of O per block of V
+                    const uint64_t vdesc = umma_desc(kv_s + (size_t)s * 2 * kTileBytes + kTileBytes + blk * Sh::kKVBlock);
+#pragma unroll
+                    for (int k = 0; k < kKV / 16; ++k)     // 16 keys: 8 columns of P (two bfloat16 each), two 8-row groups of V = 2048 bytes
+                        umma_bf16_tmem_a(tmem + g * kGroupCols + 128 + blk * 64, p_tmem + 8 * k, vdesc + (uint64_t)(2048 >> 4) * k, idesc_o,
+                                         (t > 0 || k != 0) ? 1u : 0u);
+                }
                 umma_commit(o_ready + 2 * g + (t & 1));
                 umma_commit(kv_empty + s);                 // both products have read the stage
                 if (i + 2 * kGroups < n_kt) ok = issue_s(i + 2 * kGroups, t + 2);
@@ -213,8 +240,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (j0 + kKV - 1 > last_pos) {
                 uint8_t* v_tile = kv_s + (size_t)(i % kStages) * 2 * kTileBytes + kTileBytes;
                 const int first_bad = last_pos + 1 - j0;   // >= 1: the tile holds at least one key
-                for (int x = r; x < (kKV - first_bad) * 8; x += 128)
-                    *reinterpret_cast<uint4*>(v_tile + (size_t)(first_bad + x / 8) * 128 + (x % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                for (int x = r; x < (kKV - first_bad) * 8 * kBlocks; x += 128) {
+                    const int blk = x / ((kKV - first_bad) * 8), y = x - blk * (kKV - first_bad) * 8;
+                    *reinterpret_cast<uint4*>(v_tile + blk * Sh::kKVBlock + (size_t)(first_bad + y / 8) * 128 + (y % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
             const bool whole = j0 + kKV - 1 <= pos0 && (a.window <= 0 || j0 >= pos0 + kQ - a.window);
             uint32_t pk[32];                               // the row of P, two bfloat16 per word
@@ -247,12 +276,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (!wait_pv(t - 1, 6, i)) { ok = false; break; }
                     fence_after_sync();
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
+                    for (int piece = 0; piece < kHD / 32; ++piece) {
                         uint32_t ov[32];
-                        tmem_ld32(lane_addr + 128 + half * 32, ov);
+                        tmem_ld32(lane_addr + 128 + piece * 32, ov);
 #pragma unroll
                         for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
-                        tmem_st32(lane_addr + 128 + half * 32, ov);
+                        tmem_st32(lane_addr + 128 + piece * 32, ov);
                     }
                     tmem_st_wait();
                 }
@@ -281,65 +310,75 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(p_ready + 2 * grp + (t & 1));
             done = t + 1;
         }
-        // the row of O once the group's last product has landed
-        float o[kHD];
+        // The rows of O once the group's last product has landed, 64 dims at a time.  The groups' partial results meet
+        // in shared memory ([column][row]: a warp's rows lie side by side), over the K|V ring: every group's products
+        // have read it by now (each group waits for its own last one first).
+        if (ok && done > 0) ok = wait_pv(done - 1, 8, grp + (done - 1) * kGroups);
+        if (ok && done > 0) fence_after_sync();
+        float* theirs0 = merge;                            // per group beyond the first: [66][128] floats
+        float f0 = 1.f, l_all = l;
+        float fg[kGroups] = {};
+#pragma unroll 1
+        for (int piece = 0; piece < kHD / 64; ++piece) {
+            float o[64];
 #pragma unroll
-        for (int d = 0; d < kHD; ++d) o[d] = 0.f;
-        if (ok && done > 0) {
-            ok = wait_pv(done - 1, 8, grp + (done - 1) * kGroups);
-            if (ok) {
-                fence_after_sync();
+            for (int d = 0; d < 64; ++d) o[d] = 0.f;
+            if (ok && done > 0) {
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t ov[32];
-                    tmem_ld32(lane_addr + 128 + half * 32, ov);
+                    tmem_ld32(lane_addr + 128 + piece * 64 + half * 32, ov);
 #pragma unroll
                     for (int c = 0; c < 32; ++c) o[half * 32 + c] = __uint_as_float(ov[c]);
                 }
             }
-        }
-        // The groups' partial results meet in shared memory ([column][row]: a warp's rows lie side by side), over the
-        // K|V ring: every group's products have read it by now (each group has waited for its own last one above).
-        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");
-        if (grp > 0) {
-            float* mine = merge + (size_t)(grp - 1) * (kHD + 2) * kQ;
+            asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");       // the ring (or the piece before) is done with
+            if (grp > 0) {
+                float* mine = theirs0 + (size_t)(grp - 1) * (64 + 2) * kQ;
 #pragma unroll
-            for (int d = 0; d < kHD; ++d) mine[d * kQ + r] = o[d];
-            mine[kHD * kQ + r] = m_used;
-            mine[(kHD + 1) * kQ + r] = l;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");
-        if (grp == 0) {
-            float mt = m_used;
-#pragma unroll
-            for (int g = 1; g < kGroups; ++g) mt = fmaxf(mt, merge[(size_t)(g - 1) * (kHD + 2) * kQ + kHD * kQ + r]);
-            const float ref = mt == -INFINITY ? 0.f : mt;
-            const float f0 = exp2f(m_used - ref);
-            l *= f0;
-#pragma unroll
-            for (int d = 0; d < kHD; ++d) o[d] *= f0;
-#pragma unroll
-            for (int g = 1; g < kGroups; ++g) {
-                const float* theirs = merge + (size_t)(g - 1) * (kHD + 2) * kQ;
-                const float fg = exp2f(theirs[kHD * kQ + r] - ref);
-                l += theirs[(kHD + 1) * kQ + r] * fg;
-#pragma unroll
-                for (int d = 0; d < kHD; ++d) o[d] += theirs[d * kQ + r] * fg;
+                for (int d = 0; d < 64; ++d) mine[d * kQ + r] = o[d];
+                mine[64 * kQ + r] = m_used;
+                mine[(64 + 1) * kQ + r] = l;
             }
-        }
-        if (ok && grp == 0 && r < rows) {
-            const float inv = 1.f / l;
-            bf16* dst = a.out + ((size_t)(begin + q0 + r) * a.Hq + h) * kHD;
+            asm volatile("bar.sync 1, %0;" ::"n"(kGroups * 128) : "memory");
+            if (grp == 0) {
+                if (piece == 0) {
+                    float mt = m_used;
 #pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
-                uint4 piece;
-                uint32_t* pw = reinterpret_cast<uint32_t*>(&piece);
+                    for (int g = 1; g < kGroups; ++g) mt = fmaxf(mt, theirs0[(size_t)(g - 1) * (64 + 2) * kQ + 64 * kQ + r]);
+                    const float ref = mt == -INFINITY ? 0.f : mt;
+                    f0 = exp2f(m_used - ref);
+                    l_all = l * f0;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    __nv_bfloat162 pr = __floats2bfloat162_rn(o[c8 * 8 + 2 * e] * inv, o[c8 * 8 + 2 * e + 1] * inv);
-                    pw[e] = *reinterpret_cast<uint32_t*>(&pr);
+                    for (int g = 1; g < kGroups; ++g) {
+                        const float* theirs = theirs0 + (size_t)(g - 1) * (64 + 2) * kQ;
+                        fg[g] = exp2f(theirs[64 * kQ + r] - ref);
+                        l_all += theirs[(64 + 1) * kQ + r] * fg[g];
+                    }
                 }
-                *reinterpret_cast<uint4*>(dst + c8 * 8) = piece;
+#pragma unroll
+                for (int d = 0; d < 64; ++d) o[d] *= f0;
+#pragma unroll
+                for (int g = 1; g < kGroups; ++g) {
+                    const float* theirs = theirs0 + (size_t)(g - 1) * (64 + 2) * kQ;
+#pragma unroll
+                    for (int d = 0; d < 64; ++d) o[d] += theirs[d * kQ + r] * fg[g];
+                }
+                if (ok && r < rows) {
+                    const float inv = 1.f / l_all;
+                    bf16* dst = a.out + ((size_t)(begin + q0 + r) * a.Hq + h) * kHD + piece * 64;
+#pragma unroll
+                    for (int c8 = 0; c8 < 8; ++c8) {
+                        uint4 pc;
+                        uint32_t* pw = reinterpret_cast<uint32_t*>(&pc);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 pr = __floats2bfloat162_rn(o[c8 * 8 + 2 * e] * inv, o[c8 * 8 + 2 * e + 1] * inv);
+                            pw[e] = *reinterpret_cast<uint32_t*>(&pr);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c8 * 8) = pc;
+                    }
+                }
             }
         }
     }
@@ -352,10 +391,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
 // Does the tensor-core kernel take these sizes?  (Else: lb_attention_prefill.)
 extern "C" int lb_attention_prefill_tc_ok(int Hq, int Hkv, int hd, int page_size) {
-    return hd == kHD && page_size > 0 && page_size % kKV == 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 ? 1 : 0;
+    return (hd == 64 || hd == 128) && page_size > 0 && page_size % kKV == 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 ? 1 : 0;
 }
 
-// q, out: [tokens, Hq, 64] bfloat16 contiguous; caches [pages, page_size, Hkv, 64] contiguous; tiles: int32
+namespace {
+template <int HD>
+int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const TcArgs& a, cudaStream_t stream) {
+    typedef Shape<HD> Sh;
+    const size_t smem = Sh::kQBytes + (size_t)Sh::kStages * 2 * Sh::kTileBytes + 256 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured = true;
+    }
+    attn_prefill_tc_kernel<HD><<<(unsigned)a.n_items, kThreads, smem, stream>>>(map_q, map_k, map_v, a);
+    return launch_status();
+}
+}  // namespace
+
+// q, out: [tokens, Hq, hd] bfloat16 contiguous, hd 64 or 128; caches [pages, page_size, Hkv, hd] contiguous; tiles: int32
 // [n_tiles, 2] (request index, first token of the tile within the request's portion; 128 tokens per tile).
 // `error`: a device int that is 0 before the call; non-zero afterwards: a wait inside the kernel gave up.
 extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, long tokens,
@@ -373,12 +427,6 @@ extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const
     if (rc != 0) return rc;
     TcArgs a{(bf16*)out, block_table, bt_stride, cu_seqlens, start_pos, tiles, Hq, Hkv, page_size, window,
              scale * 1.4426950408889634f, n_tiles * Hq, error};
-    const size_t smem = kQBytes + (size_t)kStages * 2 * kTileBytes + 256 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        configured = true;
-    }
-    attn_prefill_tc_kernel<<<(unsigned)a.n_items, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_k, map_v, a);
-    return launch_status();
+    return hd == 64 ? launch_tc<64>(map_q, map_k, map_v, a, (cudaStream_t)stream)
+                    : launch_tc<128>(map_q, map_k, map_v, a, (cudaStream_t)stream);
 }

@@ -403,10 +403,10 @@ ATTENTION_TC = os.environ.get("LOGSSMS_B200_ATTN_TC", "1") != "0"
 
 
 def attention_prefill_tc_ok(q: torch.Tensor, k_cache: torch.Tensor) -> bool:
-    """Does the tcgen05 prompt-attention kernel take these operands (bfloat16, head size 64, pages of a multiple of
-    64 tokens)?  Else `attention_prefill`."""
-    return (ATTENTION_TC and q.dtype == torch.bfloat16 and q.dim() == 3 and q.shape[2] == 64 and k_cache.dim() == 4
-            and k_cache.shape[1] % 64 == 0 and k_cache.shape[3] == 64 and q.shape[1] % k_cache.shape[2] == 0
+    """Does the tcgen05 prompt-attention kernel take these operands (bfloat16, head size 64 or 128, pages of a
+    multiple of 64 tokens)?  Else `attention_prefill`."""
+    return (ATTENTION_TC and q.dtype == torch.bfloat16 and q.dim() == 3 and q.shape[2] in (64, 128) and k_cache.dim() == 4
+            and k_cache.shape[1] % 64 == 0 and k_cache.shape[3] == q.shape[2] and q.shape[1] % k_cache.shape[2] == 0
             and q.is_contiguous() and k_cache.is_contiguous())
 
 
@@ -416,7 +416,7 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     """`attention_prefill` on the tcgen05 tensor cores: the same arguments, but `tiles` lists 128-token tiles.
     `check_kernel_errors()` reports a kernel whose internal wait gave up."""
     _cuda(q, k_cache, v_cache, block_table, cu_seqlens, start_pos, tiles)
-    _need(attention_prefill_tc_ok(q, k_cache), "attention_prefill_tc takes bfloat16, head size 64 and pages of a multiple of 64 tokens")
+    _need(attention_prefill_tc_ok(q, k_cache), "attention_prefill_tc takes bfloat16, head size 64 or 128 and pages of a multiple of 64 tokens")
     tokens, Hq, hd = q.shape
     _need(v_cache.shape == k_cache.shape and v_cache.is_contiguous() and v_cache.dtype == k_cache.dtype == q.dtype,
           "caches must be contiguous [pages, page_size, kv_heads, head_dim] of q's dtype")

@@ -359,7 +359,7 @@ def test_attention_prefill_finds_a_far_key_honours_a_window_and_leaves_other_row
     assert bool((out[:lo] == 7.0).all()) and bool((out[hi:] == 7.0).all())
 
 
-@pytest.mark.parametrize("shape", [(8, 2, 64, 64), (3, 3, 64, 128), (4, 1, 64, 64)])
+@pytest.mark.parametrize("shape", [(8, 2, 64, 64), (3, 3, 64, 128), (4, 1, 64, 64), (6, 2, 128, 64), (3, 1, 128, 128)])
 def test_attention_prefill_on_tcgen05_over_pages_and_earlier_portions(shape):
     """The tcgen05 form (head size 64, pages of a multiple of 64 tokens): whole prompts and later portions, tiles
     that end inside a page whose other rows hold NaN (what a reused page holds in the replay tests), a planted far
