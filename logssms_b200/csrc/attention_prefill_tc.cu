@@ -72,6 +72,11 @@ struct TcArgs {
     float scale_log2;
     int n_items;                                          // tiles * query heads
     int* error;
+    // With `splits` > 1 the keys of a tile are cut into that many ranges, each a CTA of its own (a step of few
+    // query tiles over a long context would otherwise leave most SMs idle): a CTA then leaves its rows unnormalised
+    // in `part_o` [item][split][128][hd] with (maximum in log2 units, sum) in `part_ml` [item][split][128][2], and
+    // attn_prefill_merge_kernel puts the ranges together.
+    int splits; float* part_o; float* part_ml;
 };
 
 __device__ __forceinline__ void report(int* error, int role, int tile) {
@@ -106,7 +111,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // heaviest tiles first (the host lists them so); the query heads of a tile follow one another
-    const int item = blockIdx.x;
+    const int item = blockIdx.x / a.splits, split = blockIdx.x % a.splits;
     const int tile = item / a.Hq, h = item % a.Hq, kvh = h / (a.Hq / a.Hkv);
     const int b = a.tiles[2 * tile], q0 = a.tiles[2 * tile + 1];
     if (b < 0) return;                                  // a list entry without work: the lists of a step that was filled up to fixed sizes end in such entries
@@ -114,7 +119,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int rows = min(kQ, len - q0);
     const int pos0 = a.start_pos[b] + q0, last_pos = pos0 + rows - 1;
     const int lo = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-    const int kt_begin = lo / kKV, kt_end = last_pos / kKV + 1, n_kt = kt_end - kt_begin;
+    int kt_begin = lo / kKV, kt_end = last_pos / kKV + 1;
+    if (a.splits > 1) {                                   // this CTA's share of the key tiles
+        const int per = (kt_end - kt_begin + a.splits - 1) / a.splits;
+        kt_begin += split * per;
+        kt_end = min(kt_end, kt_begin + per);
+        if (kt_begin >= kt_end) {                         // a range without keys: the merge skips it
+            if (threadIdx.x < kQ) {
+                float* ml = a.part_ml + (((size_t)item * a.splits + split) * kQ + threadIdx.x) * 2;
+                ml[0] = -INFINITY; ml[1] = 0.f;
+            }
+            return;
+        }
+    }
+    const int n_kt = kt_end - kt_begin;
     const int* bt = a.block_table + (size_t)b * a.bt_stride;
 
     if (threadIdx.x == 0) {
@@ -316,7 +334,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok && done > 0) ok = wait_pv(done - 1, 8, grp + (done - 1) * kGroups);
         if (ok && done > 0) fence_after_sync();
         float* theirs0 = merge;                            // per group beyond the first: [66][128] floats
-        float f0 = 1.f, l_all = l;
+        float f0 = 1.f, l_all = l, m_all = m_used;
         float fg[kGroups] = {};
 #pragma unroll 1
         for (int piece = 0; piece < kHD / 64; ++piece) {
@@ -347,6 +365,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                     for (int g = 1; g < kGroups; ++g) mt = fmaxf(mt, theirs0[(size_t)(g - 1) * (64 + 2) * kQ + 64 * kQ + r]);
                     const float ref = mt == -INFINITY ? 0.f : mt;
+                    m_all = mt;
                     f0 = exp2f(m_used - ref);
                     l_all = l * f0;
 #pragma unroll
@@ -364,7 +383,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                     for (int d = 0; d < 64; ++d) o[d] += theirs[d * kQ + r] * fg[g];
                 }
-                if (ok && r < rows) {
+                if (a.splits > 1) {
+                    // unnormalised, relative to the maximum that the groups agreed on; the merge kernel does the rest
+                    const size_t at = ((size_t)item * a.splits + split) * kQ + r;
+                    float4* po = reinterpret_cast<float4*>(a.part_o + at * kHD + piece * 64);
+#pragma unroll
+                    for (int c4 = 0; c4 < 16; ++c4) po[c4] = make_float4(o[4 * c4], o[4 * c4 + 1], o[4 * c4 + 2], o[4 * c4 + 3]);
+                    if (piece == 0) { a.part_ml[at * 2] = ok ? m_all : -INFINITY; a.part_ml[at * 2 + 1] = ok ? l_all : 0.f; }
+                } else if (ok && r < rows) {
                     const float inv = 1.f / l_all;
                     bf16* dst = a.out + ((size_t)(begin + q0 + r) * a.Hq + h) * kHD + piece * 64;
 #pragma unroll
@@ -389,6 +415,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 }  // namespace
 
+namespace {
+// Puts the key ranges of every (tile, head) together: one thread per query row and 16 dims.
+__global__ void __launch_bounds__(kQ) attn_prefill_merge_kernel(TcArgs a, int hd) {
+    const int item = blockIdx.x, r = threadIdx.x, d0 = blockIdx.y * 16;
+    const int tile = item / a.Hq, h = item % a.Hq;
+    const int b = a.tiles[2 * tile], q0 = a.tiles[2 * tile + 1];
+    if (b < 0) return;
+    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
+    if (r >= min(kQ, len - q0)) return;
+    float mt = -INFINITY;
+    for (int s = 0; s < a.splits; ++s) mt = fmaxf(mt, a.part_ml[(((size_t)item * a.splits + s) * kQ + r) * 2]);
+    float acc[16], lsum = 0.f;
+#pragma unroll
+    for (int d = 0; d < 16; ++d) acc[d] = 0.f;
+    for (int s = 0; s < a.splits; ++s) {
+        const size_t at = ((size_t)item * a.splits + s) * kQ + r;
+        const float ms = a.part_ml[at * 2];
+        if (ms == -INFINITY) continue;                    // a range without keys left nothing to read
+        const float f = exp2f(ms - mt);
+        lsum += a.part_ml[at * 2 + 1] * f;
+        const float4* po = reinterpret_cast<const float4*>(a.part_o + at * hd + d0);
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+            const float4 v = po[c4];
+            acc[4 * c4] += v.x * f; acc[4 * c4 + 1] += v.y * f; acc[4 * c4 + 2] += v.z * f; acc[4 * c4 + 3] += v.w * f;
+        }
+    }
+    const float inv = 1.f / lsum;
+    bf16* dst = a.out + ((size_t)(begin + q0 + r) * a.Hq + h) * hd + d0;
+#pragma unroll
+    for (int c8 = 0; c8 < 2; ++c8) {
+        uint4 pc;
+        uint32_t* pw = reinterpret_cast<uint32_t*>(&pc);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 pr = __floats2bfloat162_rn(acc[c8 * 8 + 2 * e] * inv, acc[c8 * 8 + 2 * e + 1] * inv);
+            pw[e] = *reinterpret_cast<uint32_t*>(&pr);
+        }
+        *reinterpret_cast<uint4*>(dst + c8 * 8) = pc;
+    }
+}
+}  // namespace
+
 // Does the tensor-core kernel take these sizes?  (Else: lb_attention_prefill.)
 extern "C" int lb_attention_prefill_tc_ok(int Hq, int Hkv, int hd, int page_size) {
     return (hd == 64 || hd == 128) && page_size > 0 && page_size % kKV == 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 ? 1 : 0;
@@ -404,7 +473,8 @@ int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensor
         cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured = true;
     }
-    attn_prefill_tc_kernel<HD><<<(unsigned)a.n_items, kThreads, smem, stream>>>(map_q, map_k, map_v, a);
+    attn_prefill_tc_kernel<HD><<<(unsigned)a.n_items * a.splits, kThreads, smem, stream>>>(map_q, map_k, map_v, a);
+    if (a.splits > 1) attn_prefill_merge_kernel<<<dim3((unsigned)a.n_items, HD / 16), kQ, 0, stream>>>(a, HD);
     return launch_status();
 }
 }  // namespace
@@ -412,13 +482,17 @@ int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensor
 // q, out: [tokens, Hq, hd] bfloat16 contiguous, hd 64 or 128; caches [pages, page_size, Hkv, hd] contiguous; tiles: int32
 // [n_tiles, 2] (request index, first token of the tile within the request's portion; 128 tokens per tile).
 // `error`: a device int that is 0 before the call; non-zero afterwards: a wait inside the kernel gave up.
+// `splits` > 1: key ranges per tile, with float32 scratch part_o [n_tiles * Hq * splits * 128 * hd] and
+// part_ml [n_tiles * Hq * splits * 128 * 2] (see TcArgs).
 extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, long tokens,
                                        long pages, const int* block_table, int bt_stride, const int* cu_seqlens,
                                        const int* start_pos, const int* tiles, int n_tiles, int Hq, int Hkv, int hd,
-                                       int page_size, float scale, int window, int* error, void* stream) {
+                                       int page_size, float scale, int window, int* error, int splits, float* part_o,
+                                       float* part_ml, void* stream) {
     if (n_tiles <= 0) return kOk;
     if (!lb_attention_prefill_tc_ok(Hq, Hkv, hd, page_size)) return kBadSize;
-    if ((long)n_tiles * Hq > 0x7fffffffL) return kTooLarge;
+    if (splits < 1 || splits > 64 || (splits > 1 && (part_o == nullptr || part_ml == nullptr))) return kBadSize;
+    if ((long)n_tiles * Hq * splits > 0x7fffffffL) return kTooLarge;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return kBadSize;
     CUtensorMap map_q, map_k, map_v;
     int rc = make_tile_map(&map_q, q, tokens, (long)Hq * hd, (long)Hq * hd, kQ);
@@ -426,7 +500,7 @@ extern "C" int lb_attention_prefill_tc(const void* q, const void* k_cache, const
     if (rc == 0) rc = make_tile_map(&map_v, v_cache, pages * page_size, (long)Hkv * hd, (long)Hkv * hd, kKV);
     if (rc != 0) return rc;
     TcArgs a{(bf16*)out, block_table, bt_stride, cu_seqlens, start_pos, tiles, Hq, Hkv, page_size, window,
-             scale * 1.4426950408889634f, n_tiles * Hq, error};
+             scale * 1.4426950408889634f, n_tiles * Hq, error, splits, part_o, part_ml};
     return hd == 64 ? launch_tc<64>(map_q, map_k, map_v, a, (cudaStream_t)stream)
                     : launch_tc<128>(map_q, map_k, map_v, a, (cudaStream_t)stream);
 }

@@ -410,10 +410,22 @@ def attention_prefill_tc_ok(q: torch.Tensor, k_cache: torch.Tensor) -> bool:
             and q.is_contiguous() and k_cache.is_contiguous())
 
 
+def prefill_splits(num_tiles: int, num_heads: int, max_context: int) -> int:
+    """Key ranges per 128-query tile for `attention_prefill_tc`: a step of few tiles over a long context (a prompt
+    portion far into its prompt) would leave most SMs idle with one CTA per (tile, head), so the keys are shared out
+    until the grid fills the SMs, each range keeping at least 512 keys."""
+    items = max(1, num_tiles * num_heads)
+    return max(1, min(_SM_COUNT // items, max_context // 512, 16))
+
+
+_SM_COUNT = 148
+
+
 def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                          cu_seqlens: torch.Tensor, start_pos: torch.Tensor, tiles: torch.Tensor, num_tiles: int,
-                         scale: float, window: int = 0, *, out: torch.Tensor | None = None) -> torch.Tensor:
+                         scale: float, window: int = 0, *, out: torch.Tensor | None = None, splits: int = 1) -> torch.Tensor:
     """`attention_prefill` on the tcgen05 tensor cores: the same arguments, but `tiles` lists 128-token tiles.
+    `splits` > 1 cuts every tile's keys into that many ranges, each a CTA of its own, merged by a second kernel.
     `check_kernel_errors()` reports a kernel whose internal wait gave up."""
     _cuda(q, k_cache, v_cache, block_table, cu_seqlens, start_pos, tiles)
     _need(attention_prefill_tc_ok(q, k_cache), "attention_prefill_tc takes bfloat16, head size 64 or 128 and pages of a multiple of 64 tokens")
@@ -431,12 +443,17 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         out = torch.empty_like(q)
     _need(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
     err = error_word(q.device)
+    splits = max(1, int(splits))
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty(num_tiles * Hq * splits * ATTENTION_TC_TILE * hd, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(num_tiles * Hq * splits * ATTENTION_TC_TILE * 2, dtype=torch.float32, device=q.device)
     f = _fn("attention_prefill_tc", "lb_attention_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_long, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), tokens, pages, _ptr(block_table), block_table.stride(0),
              _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), num_tiles, Hq, Hkv, hd, page_size, scale, int(window or 0),
-             _ptr(err), _stream()), "attention_prefill_tc")
+             _ptr(err), splits, _ptr(part_o), _ptr(part_ml), _stream()), "attention_prefill_tc", launches=2 if splits > 1 else 1)
     return out
 
 

@@ -86,7 +86,7 @@ class Attention(Part):
             if K.attention_prefill_tc_ok(q, k_cache):
                 tiles, n_tiles = ctx.long_portion_tiles(K.ATTENTION_TC_TILE)
                 o = K.attention_prefill_tc(q, k_cache, v_cache, tables, ctx.cu_seqlens, ctx.start_pos, tiles, n_tiles,
-                                           self.scale, window)
+                                           self.scale, window, splits=K.prefill_splits(n_tiles, s.num_heads, ctx.max_context))
             else:
                 tiles, n_tiles = ctx.long_portion_tiles(K.ATTENTION_TILE)
                 o = K.attention_prefill(q, k_cache, v_cache, tables, ctx.cu_seqlens, ctx.start_pos, tiles, n_tiles,

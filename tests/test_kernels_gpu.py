@@ -386,9 +386,11 @@ def test_attention_prefill_on_tcgen05_over_pages_and_earlier_portions(shape):
     got = k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale)
     k.check_kernel_errors()
     close(got, rnd_of(dtype)(want), dtype)
+    close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale, splits=2), rnd_of(dtype)(want), dtype)   # ranges, some empty
     for window in (1, 64, 65, 300):
         want_w = rnd_of(dtype)(attention_reference(case, scale, window, rd))
         close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale, window), want_w, dtype)
+        close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale, window, splits=4), want_w, dtype)
     k.check_kernel_errors()
     # only one request's tiles: the other rows stay as they were
     out = torch.full_like(dev(case["q"]), 7.0)
@@ -987,6 +989,10 @@ def test_prompt_attention_kernels_over_thousands_of_keys(shape):
     if k.attention_prefill_tc_ok(args[0], args[1]):
         cu, start, tiles = prefill_inputs(case, lengths, new, k.ATTENTION_TC_TILE)
         close(k.attention_prefill_tc(*args, dev(cu), dev(start), dev(tiles), tiles.shape[0], scale), want, dtype)
+        # the keys of every tile cut into ranges with a CTA each, merged by a second kernel (few tiles, long contexts)
+        for splits in (3, 16):
+            close(k.attention_prefill_tc(*args, dev(cu), dev(start), dev(tiles), tiles.shape[0], scale, splits=splits), want, dtype)
+        assert k.prefill_splits(4, 6, 4096) == 6 and k.prefill_splits(40, 8, 4096) == 1 and k.prefill_splits(2, 4, 700) == 1
         k.check_kernel_errors()
 
 
