@@ -41,6 +41,10 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--mixed-prefill-tokens", type=int, default=None,
                    help="most prompt tokens in a step that also decodes (mixed policy; default: the step's budget)")
     p.add_argument("--no-graph", action="store_true", help="launch every step kernel by kernel (no CUDA graphs)")
+    p.add_argument("--profile", default=None, metavar="FILE",
+                   help="time every kernel with CUDA events and write the sums per kernel class to FILE (JSON) at exit; "
+                        "such a run launches every step kernel by kernel")
+    p.add_argument("--nvtx", action="store_true", help="NVTX ranges per layer and part, for a timeline tool")
     p.add_argument("--memory-ratio", type=float, default=0.9)
     p.add_argument("--num-pages", type=int, default=None)
     p.add_argument("--page-size", type=int, default=64)
@@ -177,13 +181,20 @@ def main(argv=None) -> int:
               max_seq_len_override=args.max_seq_len_override, page_size=args.page_size, num_pages=args.num_pages,
               memory_ratio=args.memory_ratio, max_prefill_tokens=args.max_prefill_tokens, seed=args.seed,
               scheduling_policy=args.scheduling_policy, mixed_prefill_tokens=args.mixed_prefill_tokens,
-              use_graphs=not args.no_graph)
+              use_graphs=not args.no_graph, profile=args.profile is not None, nvtx=args.nvtx)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             ignore_eos=args.ignore_eos, max_tokens=args.max_tokens)
+    def write_profile():
+        if args.profile is not None:
+            import json
+            with open(args.profile, "w") as f:
+                json.dump(llm.engine.profile_report(), f, indent=1)
+
     if args.prompt_ids is not None:
         ids = [int(t) for t in args.prompt_ids.replace(",", " ").split()]
         out = llm.generate([ids], params)[0]
         print(" ".join(map(str, out.token_ids)))
+        write_profile()
         return 0
     chat = Chat(llm, params, args.system)
     print("logssms_b200 chat; /help for commands", flush=True)
@@ -197,4 +208,5 @@ def main(argv=None) -> int:
             except KeyboardInterrupt:
                 print("\nCancelled. Use /exit or Ctrl-D to quit.")
     chat.loop(lines())
+    write_profile()
     return 0

@@ -29,7 +29,7 @@ class LLM:
                  memory_ratio: float = 0.9, max_prefill_tokens: int = 8192, seed: int = 0,
                  device: str = "cuda:0", tokenizer=None, eos_token_ids: Sequence[int] | None = None,
                  poison_on_free: bool = False, use_graphs: bool = True, scheduling_policy: str = "mixed",
-                 mixed_prefill_tokens: int | None = None):
+                 mixed_prefill_tokens: int | None = None, profile: bool = False, nvtx: bool = False):
         from ..config import load_model_config
         config = load_model_config(model_path)
         max_seq_len = max_seq_len_override or min(getattr(config, "max_position_embeddings", 8192), 8192)
@@ -37,7 +37,8 @@ class LLM:
             dtype = "float32" if getattr(config, "torch_dtype", "bfloat16") == "float32" else "bfloat16"
         self.engine = Engine(model_path, dtype, max_requests=max_running_requests, max_seq_len=max_seq_len,
                              page_size=page_size, num_pages=num_pages, memory_ratio=memory_ratio, device=device,
-                             poison_on_free=poison_on_free, max_step_tokens=max_prefill_tokens, use_graphs=use_graphs)
+                             poison_on_free=poison_on_free, max_step_tokens=max_prefill_tokens, use_graphs=use_graphs,
+                             profile=profile, nvtx=nvtx)
         self.tokenizer = tokenizer if tokenizer is not None else _maybe_tokenizer(model_path)
         if eos_token_ids is None:
             eos = getattr(self.tokenizer, "eos_token_id", None) if self.tokenizer is not None else None

@@ -22,6 +22,7 @@ from ..cache import CacheManager, RequestCache
 from ..config import load_model_config
 from ..models import build_model
 from ..ops import kernels as K
+from ..ops.profiler import PROFILER
 from ..parts import Runtime
 from ..weights import load_weights
 from .plan import StaticTables, StepEntry, StepPlanner, bucket_for
@@ -37,7 +38,7 @@ class Engine:
                  page_size: int = 64, num_pages: int | None = None, memory_ratio: float = 0.9,
                  device: str = "cuda:0", poison_on_free: bool = False, max_step_tokens: int = 1 << 30,
                  use_graphs: bool = True, max_graphs: int = 64, max_shape_graphs: int = 8, max_bucket_graphs: int = 32,
-                 max_graph_tokens: int = 4096):
+                 max_graph_tokens: int = 4096, profile: bool = False, nvtx: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("logssms_b200 needs a CUDA device (built for sm_100a); there is no CPU path")
         try:
@@ -61,7 +62,13 @@ class Engine:
                                   poison_on_free=poison_on_free, max_step_tokens=max_step_tokens)
         self.vocab_size = self.model.spec.vocab_size
         self.planner = StepPlanner(self.cache, self.device, self.vocab_size)
-        self.use_graphs = use_graphs
+        # `profile`: every kernel between two CUDA events, summed per kernel class (`profile_report`); such steps run
+        # kernel by kernel.  `nvtx`: named ranges per layer and part, for a timeline tool.
+        # (one profiler per process: the engine made last decides)
+        PROFILER.enabled, PROFILER.nvtx = bool(profile), bool(nvtx)
+        if profile:
+            PROFILER.reset()
+        self.use_graphs = use_graphs and not profile
         self.max_graphs = max_graphs
         self.max_shape_graphs = max_shape_graphs
         self.max_graph_tokens = max_graph_tokens
@@ -155,9 +162,14 @@ class Engine:
             ctx.token_ids.copy_(device_tokens)
         x, residual = self.model.forward(ctx)
         self.steps_run += 1
+        PROFILER.steps += PROFILER.enabled
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.logits(x, residual, ctx.logit_rows)
+
+    def profile_report(self) -> dict:
+        """Device time per kernel class and per kernel since the engine started (needs `profile=True`)."""
+        return PROFILER.report()
 
     def _graph_step(self, graphs: dict, key, most: int, capture_at: int, entries: Sequence[StepEntry],
                     device_tokens: torch.Tensor | None, bucket=None) -> torch.Tensor:

@@ -5,6 +5,7 @@ import torch
 
 from ..ops import build as kernel_build
 from ..ops import kernels as K
+from ..ops.profiler import PROFILER, nvtx_range
 from ..parts import Embedding, LMHead, Part
 from ..registry import BLOCKS, NORMS
 
@@ -78,7 +79,8 @@ class DecoderModel(Part):
 
     def forward(self, ctx):
         """Residual stream after all scheduled layers, as the pair (x, residual) whose sum it is."""
-        x = self.embedding.forward(ctx.token_ids)
+        with nvtx_range("embedding"):
+            x = self.embedding.forward(ctx.token_ids)
         residual = None
         for i, e in enumerate(self.schedule):
             # a block may hand its output on already joined with the residual (`SummedRows`) where the norm that
@@ -89,7 +91,11 @@ class DecoderModel(Part):
             # the one before the head
             ctx.extras["next_norm_takes_scaled"] = getattr(getattr(nxt, "mixer_norm", None) if nxt is not None else self.final_norm,
                                                            "takes_scaled_rows", False)
-            x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
+            if PROFILER.nvtx:                      # named ranges per layer (and per part inside it) for a timeline
+                with nvtx_range(f"layer {e.layer}"):
+                    x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
+            else:
+                x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
         ctx.extras.pop("next_norm_takes_summed", None)
         ctx.extras.pop("next_norm_takes_scaled", None)
         return x, residual
@@ -101,5 +107,6 @@ class DecoderModel(Part):
             residual = K.gather_rows(residual, rows)
         # The norm runs as a kernel of its own here: in the head's prologue every one of its vocabulary / 16 CTAs would
         # redo it (measured: a decode step 14-19 us longer).
-        (h,), _ = self.final_norm.forward(x, residual, want_residual=False)
-        return self.lm_head.forward(h)
+        with nvtx_range("final norm + head"):
+            (h,), _ = self.final_norm.forward(x, residual, want_residual=False)
+            return self.lm_head.forward(h)

@@ -19,6 +19,7 @@ from ctypes import c_float, c_int, c_long, c_void_p
 import torch
 
 from . import build
+from .profiler import PROFILER
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _ERRORS = {-1: "dtype is neither float32 nor bfloat16", -2: "a size the kernel does not take",
@@ -39,6 +40,8 @@ def _fn(lib: str, name: str, argtypes):
         f.argtypes = argtypes
         f.restype = c_int
         _fn_cache[key] = f
+    if PROFILER.enabled:                  # opt-in: every launch between two events, summed per kernel class
+        return lambda *args: PROFILER.timed(lib, name, lambda: f(*args))
     return f
 
 
@@ -1005,7 +1008,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
     else:
         # the library product, asked for as mm / addmm: the same cuBLAS call as `F.linear` makes, with 4 us less of
         # dispatch on the host per call (a prompt step of a new shape is bound by the host)
-        y = torch.mm(x, w.t()) if bias is None else torch.addmm(bias.to(x.dtype), x, w.t())
+        product = (lambda: torch.mm(x, w.t())) if bias is None else (lambda: torch.addmm(bias.to(x.dtype), x, w.t()))
+        y = PROFILER.timed("library", "mm", product) if PROFILER.enabled else product()
     if lazy_scale and not out_f32 and out_scale != 1.0:
         return ScaledRows(y, out_scale)
     if out_f32 or out_scale != 1.0:

@@ -4,6 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
+from ..ops.profiler import PROFILER, nvtx_range
 from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from .base import Part
 
@@ -57,6 +58,18 @@ class PreNormParallelBlock(Part):
             part.setup(rt)
 
     def forward(self, x: torch.Tensor, residual, ctx, cache_layer: int, writes_cache: bool = True):
+        if PROFILER.nvtx and not getattr(self, "_ranged", False):
+            # named ranges around the parts, put on once (only when ranges are switched on)
+            self._ranged = True
+            for part, label in [*((m, s.spec.kind) for m, s in zip(self.mixers, self.spec.mixers)),
+                                (self.feed_forward, self.spec.feed_forward.kind),
+                                (self.mixer_norm, "mixer norm"), (self.ff_norm, "feed-forward norm")]:
+                inner = part.forward
+
+                def ranged(*args, _inner=inner, _label=label, **kwargs):
+                    with nvtx_range(_label):
+                        return _inner(*args, **kwargs)
+                part.forward = ranged
         slots = self.spec.mixers
         # parts whose first step is a product say so (`takes_normed_rows`): the norm in front of them can then
         # ride in that product's prologue (decode steps: fewer dependent launches)

@@ -17,7 +17,9 @@ def test_reference_option_names_parse():
     assert (args.max_prefill_tokens, args.scheduling_policy, args.mixed_prefill_tokens) == (512, "prefill-first", 128)
     assert (args.num_pages, args.page_size) == (33, 128)
     assert (args.max_tokens, args.temperature, args.top_k, args.top_p, args.ignore_eos) == (9, 0.8, 40, 0.95, True)
-    assert args.system == "be brief" and not args.no_graph
+    assert args.system == "be brief" and not args.no_graph and args.profile is None and not args.nvtx
+    args = build_parser().parse_args(["--model", "/m", "--profile", "/tmp/p.json", "--nvtx", "--no-graph"])
+    assert args.profile == "/tmp/p.json" and args.nvtx and args.no_graph
 
 
 def test_model_path_has_both_spellings_and_defaults_follow_the_chat_client():

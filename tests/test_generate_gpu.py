@@ -214,3 +214,30 @@ def test_a_kernel_that_gave_up_ends_the_requests_of_its_step_with_an_error(tmp_p
     with pytest.raises(K.KernelError):
         K.check_kernel_errors(llm.engine.device)
     K.check_kernel_errors(llm.engine.device)        # cleared by the report
+
+
+def test_profile_times_every_kernel_by_class_and_changes_no_token(tmp_path):
+    """`profile=True`: CUDA events around every launch, summed per kernel class; `nvtx=True`: named ranges per layer
+    and part.  The tokens are those of an ordinary run."""
+    import json
+    from logssms_b200.engine import LLM
+    from logssms_b200.ops.profiler import PROFILER
+    from logssms_b200.sampling import SamplingParams
+    model_dir = make_model_dir(tmp_path / "m", TINY["D"], seed=26, dtype=torch.bfloat16)
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    prompts = [list(range(3, 150)), [7, 8, 9]]
+    plain_run = [o.token_ids for o in LLM(model_dir, "bfloat16", max_running_requests=2, max_seq_len_override=256,
+                                           num_pages=8).generate(prompts, sp)]
+    llm = LLM(model_dir, "bfloat16", max_running_requests=2, max_seq_len_override=256, num_pages=8, profile=True, nvtx=True)
+    assert not llm.engine.use_graphs and PROFILER.enabled and PROFILER.nvtx
+    assert [o.token_ids for o in llm.generate(prompts, sp)] == plain_run
+    report = llm.engine.profile_report()
+    assert report["steps"] >= 5
+    for cls in ("attention", "mamba2", "products", "norms and gates", "embedding", "sampling"):
+        assert report["classes"][cls]["launches"] > 0 and report["classes"][cls]["ms"] > 0, cls
+    assert any(k.startswith("attention_prefill_tc.") for k in report["kernels"])       # the prompt ran on the tcgen05 kernel
+    assert abs(sum(c["ms"] for c in report["classes"].values()) - sum(k["ms"] for k in report["kernels"].values())) < 1e-3
+    json.dumps(report)
+    # the engine made next switches the profiler off again
+    LLM(model_dir, "bfloat16", max_running_requests=2, max_seq_len_override=256, num_pages=8)
+    assert not PROFILER.enabled and not PROFILER.nvtx
