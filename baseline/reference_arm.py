@@ -95,9 +95,16 @@ def run(args, model: dict, context: int, max_seq_len: int) -> dict:
     batch = args.batch
     new_tokens = args.warmup + args.steps + 8
     rng = np.random.default_rng(1234)
-    msgs = [UserMsg(uid=i, input_ids=torch.from_numpy(rng.integers(0, model["vocab_size"], context - 1).astype(np.int32)),
-                    sampling_params=SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True))
-            for i in range(batch)]
+    next_uid = [0]
+
+    def messages(count: int, prompt_len: int, max_tokens: int) -> list:
+        out = []
+        for _ in range(count):
+            ids = torch.from_numpy(rng.integers(0, model["vocab_size"], prompt_len).astype(np.int32))
+            out.append(UserMsg(uid=next_uid[0], input_ids=ids,
+                               sampling_params=SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True)))
+            next_uid[0] += 1
+        return out
 
     class InProcessScheduler(Scheduler):
         def __init__(self, config, pending):
@@ -115,42 +122,81 @@ def run(args, model: dict, context: int, max_seq_len: int) -> dict:
                              use_dummy_weight=True, max_seq_len_override=max_seq_len,
                              max_prefill_tokens=args.prefill_budget)      # cache type, attention backend, graphs: the defaults
     t0 = time.time()
-    sched = InProcessScheduler(config, msgs)
+    sched = InProcessScheduler(config, messages(batch, context - 1, new_tokens))
     print(f"[bench] reference engine up in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
-    with torch.inference_mode():
-        data = None
+    state = {"data": None}
+
+    def pump():
+        state["data"] = sched.overlap_loop(state["data"])
+
+    def decode_point(count: int, first_uid: int) -> dict:
+        """The `count` requests already fed: prompts, W warm-up iterations, K timed ones, then the rest of their tokens."""
         deadline = time.time() + 600
-        # prompts first: iterate until every request has produced its first token
-        while len({m.uid for m in sched.results}) < batch:
-            data = sched.overlap_loop(data)
+        while len({m.uid for m in sched.results if m.uid >= first_uid}) < count:      # every request has its first token
+            pump()
             if time.time() > deadline:
                 raise RuntimeError("reference scheduler did not finish the prompts within 600 s")
         for _ in range(args.warmup):
-            data = sched.overlap_loop(data)
+            pump()
         torch.cuda.synchronize()
         before = len(sched.results)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         wall0 = time.perf_counter()
         start.record()
         for _ in range(args.steps):
-            data = sched.overlap_loop(data)
+            pump()
         stop.record()
         torch.cuda.synchronize()
         wall = time.perf_counter() - wall0
         produced = len(sched.results) - before
-    ms = start.elapsed_time(stop)
-    if produced < batch * (args.steps - 1):
-        raise RuntimeError(f"reference produced {produced} tokens in {args.steps} iterations of batch {batch}: not in steady decode")
-    return {
+        ms = start.elapsed_time(stop)
+        if produced < count * (args.steps - 1):
+            raise RuntimeError(f"reference produced {produced} tokens in {args.steps} iterations of batch {count}: not in steady decode")
+        for _ in range(16):                                # the requests end by length within a few more iterations
+            pump()
+        return {"tok_s": produced / (ms / 1e3), "ms_per_step": ms / args.steps, "wall_tok_s": produced / wall}
+
+    with torch.inference_mode():
+        main = decode_point(batch, 0)
+        points, prefill = {}, None
+        try:                                               # further points of the same benchmark; the headline stands without them
+            for count in (1, 64):
+                first = next_uid[0]
+                sched._pending.extend(messages(count, context - 1, new_tokens))
+                points[f"decode_b{count}"] = decode_point(count, first)["tok_s"]
+            times = []
+            for _ in range(4):                             # a 2,048-token prompt to its first token, through the scheduler
+                first = next_uid[0]
+                sched._pending.extend(messages(1, 2048, 1))
+                torch.cuda.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                deadline = time.time() + 120
+                while not any(m.uid == first for m in sched.results) and time.time() < deadline:
+                    pump()
+                stop.record()
+                torch.cuda.synchronize()
+                times.append(start.elapsed_time(stop))
+                for _ in range(4):
+                    pump()
+            prefill = {"tokens": 2048, "ms": min(times[1:]), "value": 2048 / (min(times[1:]) / 1e3),
+                       "path": "one prompt through Scheduler.overlap_loop until its first token"}
+        except Exception as exc:
+            print(f"[bench] reference: further points failed: {type(exc).__name__}: {exc}", file=sys.stderr, flush=True)
+    out = {
         "impl": "reference", "metric": "decode tok/s (batch 8, 2,048-token contexts; 0.5B-class Falcon-H1)",
-        "value": produced / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "value": main["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (seeded uniform token ids, the reference's dummy weights)",
         "config": {"model": "Falcon-H1-0.5B-class", "layers": model["num_hidden_layers"], "global_batch": batch,
                    "seq_len": context, "context_budget": max_seq_len, "parallelism": "single GPU",
                    "path": "Scheduler.overlap_loop, default cache type and attention backend"},
-        "e2e": {"value": produced / wall, "unit": "tokens/s"},
+        "e2e": {"value": main["wall_tok_s"], "unit": "tokens/s"},
+        "points": points,
     }
+    if prefill is not None:
+        out["prefill"] = prefill
+    return out
 
 
 def main() -> int:
