@@ -1,11 +1,11 @@
 // The chunk-scan step of the chunked selective scan (ssd.cu, kernel 3) on the 5th-generation tensor cores:
-// head size 64, state size a multiple of 64 up to 256, chunks of 128 tokens, bfloat16.  Other sizes stay on the
-// mma.sync kernel.
+// head size a multiple of 64 (a CTA takes 64 dims of a head), state size a multiple of 64 up to 256, chunks of 128
+// tokens, bfloat16.  Other sizes stay on the mma.sync kernel.
 //
 //   y_t = e^{a_t} C_t . S_in + sum_{s<=t} [(C_t . B_s) e^{a_t - a_s} dt_s] x_s + D x_t       (t, s: tokens of one chunk)
 //
 // (python/logssms/kernel/linear_attention/mamba2.py:148-194, vendor/fla/chunk_o.py:79-136 of the reference.)
-// One CTA per (chunk, head), 10 warps, two CTAs per SM:
+// One CTA per (chunk, 64 dims of a head), 10 warps, two CTAs per SM:
 //   warp 0    one thread: TMA loads (128-byte swizzle) of the chunk's rows of C and B (128 tokens x N, 64 columns
 //             per box), of x (128 x 64) and of the state the chunk starts from (64 x N, bfloat16)
 //   warp 1    allocates 256 columns of tensor memory; one thread issues
@@ -43,7 +43,7 @@ struct ScanArgs {
     const float* A_log; const float* dt_bias; const float* D;
     bf16* y;
     const int* cu_seqlens; const int* chunks;
-    int nh, N, G;
+    int nh, P, N, G;                                      // P: the head size, a multiple of 64 (a CTA takes 64 dims of it)
     float dt_scale;
     const bf16* gate; long gate_stride; float gate_scale;
     int gate16;                                           // the gate's rows start on 16-byte boundaries
@@ -79,13 +79,15 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    const int chunk = blockIdx.x, h = blockIdx.y;
+    // a head of more than 64 dims is run as pieces of 64 with a CTA each: they share the head's B, C, dt and decay
+    // (and each computes G = C B^T again), and own their columns of x, of the start state and of y
+    const int chunk = blockIdx.x, pieces = a.P / kP, h = blockIdx.y / pieces, col0 = h * a.P + (blockIdx.y % pieces) * kP;
     const int b = a.chunks[2 * chunk], t0 = a.chunks[2 * chunk + 1];
     if (b < 0) return;                                  // a list entry without work: the lists of a step that was filled up to fixed sizes end in such entries
     const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
     const int Lc = min(kL, len - t0);
     const int tok0 = begin + t0;
-    const int g = h / (a.nh / a.G), inner = a.nh * kP;
+    const int g = h / (a.nh / a.G), inner = a.nh * a.P;
 
     if (threadIdx.x == 0) {
         mbar_init(full_cb, 1); mbar_init(full_sx, 1); mbar_init(g_ready, 1); mbar_init(y_ready, 1);
@@ -108,10 +110,10 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
                 tma_load_2d(b_s + kb * kRowTile, &map_conv, full_cb, inner + g * a.N + kb * 64, tok0);
             }
             mbar_expect_tx(full_sx, kRowTile + NB * kSinTile);
-            tma_load_2d(x_s, &map_conv, full_sx, h * kP, tok0);
+            tma_load_2d(x_s, &map_conv, full_sx, col0, tok0);
 #pragma unroll
             for (int kb = 0; kb < NB; ++kb)
-                tma_load_2d(sin_s + kb * kSinTile, &map_sin, full_sx, kb * 64, (chunk * a.nh + h) * kP);
+                tma_load_2d(sin_s + kb * kSinTile, &map_sin, full_sx, kb * 64, chunk * inner + col0);
             // the CTA does not leave before its copies have landed, whatever the other roles do
             if (!mbar_wait(full_cb, 0)) { report(a.error, 1); *failed = 1; }
             if (!mbar_wait(full_sx, 0)) { report(a.error, 1); *failed = 1; }
@@ -185,7 +187,7 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
         uint4 zrow[4];
         const bool gated = a.gate != nullptr && r < Lc;
         if (gated) {
-            const bf16* zr = a.gate + (size_t)(tok0 + r) * a.gate_stride + h * kP + hf * 32;
+            const bf16* zr = a.gate + (size_t)(tok0 + r) * a.gate_stride + col0 + hf * 32;
             if (a.gate16) {
                 const uint4* zp = reinterpret_cast<const uint4*>(zr);
 #pragma unroll
@@ -266,7 +268,7 @@ ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap map_conv, const __g
             tmem_ld32(lane_addr + 192 + hf * 32, y1);
             if (r < Lc) {
                 const float ea = exp2f(at), Dh = a.D[h];
-                bf16* dst = a.y + (size_t)(tok0 + r) * inner + h * kP + hf * 32;
+                bf16* dst = a.y + (size_t)(tok0 + r) * inner + col0 + hf * 32;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint4 xv = *reinterpret_cast<const uint4*>(x_s + (size_t)r * 128 + (((hf * 4 + j) ^ (r & 7)) * 16));
@@ -309,14 +311,14 @@ int launch(const CUtensorMap& map_conv, const CUtensorMap& map_sin, const ScanAr
         cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured = true;
     }
-    ssd_chunk_scan_tc_kernel<NB><<<dim3(n_chunks, a.nh), kThreads, smem, s>>>(map_conv, map_sin, a);
+    ssd_chunk_scan_tc_kernel<NB><<<dim3(n_chunks, a.nh * (a.P / kP)), kThreads, smem, s>>>(map_conv, map_sin, a);
     return launch_status();
 }
 }  // namespace
 
 // Does the tensor-core chunk scan take these sizes?  (Else kernel 3 of lb_ssd_prefill.)
 extern "C" int lb_ssd_chunk_scan_tc_ok(int P, int N, int L) {
-    return P == kP && L == kL && N >= 64 && N <= 256 && N % 64 == 0 ? 1 : 0;
+    return P >= kP && P % kP == 0 && P <= 256 && L == kL && N >= 64 && N <= 256 && N % 64 == 0 ? 1 : 0;
 }
 
 // The third step of lb_ssd_prefill (which is then called with run_scan = 0) for chunks of 128 tokens: conv
@@ -331,13 +333,13 @@ extern "C" int lb_ssd_chunk_scan_tc(const void* conv, long tokens, int C, const 
                                     float gate_scale, int* error, void* stream) {
     if (n_chunks <= 0) return kOk;
     if (!lb_ssd_chunk_scan_tc_ok(P, N, L) || nh <= 0 || G <= 0 || nh % G || C != nh * P + 2 * G * N) return kBadSize;
-    if (nh > 65535 || (long)n_chunks * nh * P > 0x7fffffffL) return kTooLarge;
+    if ((long)nh * (P / kP) > 65535 || (long)n_chunks * nh * P > 0x7fffffffL) return kTooLarge;
     if (((uintptr_t)conv | (uintptr_t)s_in | (uintptr_t)y) & 15) return kBadSize;
     CUtensorMap map_conv, map_sin;
     int rc = make_tile_map(&map_conv, conv, tokens, C, C, kL);
     if (rc == 0) rc = make_tile_map(&map_sin, s_in, (long)n_chunks * nh * P, N, N, kP);
     if (rc != 0) return rc;
-    ScanArgs a{(const bf16*)dt, dt_stride, A_log, dt_bias, D, (bf16*)y, cu_seqlens, chunks, nh, N, G, dt_scale,
+    ScanArgs a{(const bf16*)dt, dt_stride, A_log, dt_bias, D, (bf16*)y, cu_seqlens, chunks, nh, P, N, G, dt_scale,
                (const bf16*)gate, gate_stride, gate_scale,
                (((uintptr_t)gate & 15) == 0 && gate_stride % 8 == 0) ? 1 : 0, error};
     cudaStream_t s = (cudaStream_t)stream;

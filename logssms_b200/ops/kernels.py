@@ -534,9 +534,10 @@ SSD_TC_CHUNK = 128
 
 
 def ssd_chunk_scan_tc_ok(head_dim: int, state_dim: int, chunk_len: int) -> bool:
-    """Does the tcgen05 chunk-scan kernel take these sizes (head size 64, state size 64..256 in steps of 64,
-    chunks of 128 tokens)?"""
-    return SSD_TC and head_dim == 64 and state_dim % 64 == 0 and 64 <= state_dim <= 256 and chunk_len == SSD_TC_CHUNK
+    """Does the tcgen05 chunk-scan kernel take these sizes (head size 64 or 128: the kernels that make the chunk
+    states before it take no larger heads; state size 64..256 in steps of 64, chunks of 128 tokens)?"""
+    return (SSD_TC and head_dim in (64, 128) and state_dim % 64 == 0 and 64 <= state_dim <= 256
+            and chunk_len == SSD_TC_CHUNK)
 
 
 def ssd_chunk_len(chunk_size: int, head_dim: int, state_dim: int) -> int:

@@ -530,7 +530,9 @@ def chunk_lists(lens, L):
 @pytest.mark.parametrize("shape", [(4, 16, 16, 1, 8), (6, 24, 32, 2, 16), (3, 64, 128, 1, 128), (2, 40, 256, 2, 64),
                                    (2, 128, 64, 1, 32), (5, 8, 24, 5, 256),
                                    # head size 64 with chunks of 128: the tcgen05 chunk scan, state sizes 64 to 256
-                                   (4, 64, 64, 2, 128), (2, 64, 192, 1, 128), (2, 64, 256, 2, 256), (3, 64, 128, 1, 64)])
+                                   (4, 64, 64, 2, 128), (2, 64, 192, 1, 128), (2, 64, 256, 2, 256), (3, 64, 128, 1, 64),
+                                   # ... and heads of 128 as two pieces of 64
+                                   (2, 128, 128, 1, 128), (3, 128, 256, 3, 128)])
 def test_ssd_prefill_in_chunks_resumes_from_state_and_matches_the_recurrence(shape):
     ssd_case(shape, [150, 40, 300], [70, 17, 129])
 
