@@ -648,7 +648,7 @@ def run_ours(args) -> dict:
 
 # --------------------------------------------------------------------------- a short run for profilers
 def run_probe(args) -> int:
-    """`--probe decode|prefill`: a few steps of one kind on a model of `--layers` layers (default 4), with
+    """`--probe decode|prefill|mixed`: a few steps of one kind on a model of `--layers` layers (default 4), with
     the CUDA profiler range switched on around the last ones, for `ncu --profile-from-start off`.  Prints a
     line with the device time of the unprofiled steps; nothing here is a benchmark value.  This is the one
     tracked way to reproduce the commands in the files under profiles/."""
@@ -685,6 +685,26 @@ def run_probe(args) -> int:
             torch.cuda.profiler.start()
             llm.step()
             llm.step()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        elif args.probe == "mixed":
+            # `--batch` requests decode from `context`-token contexts beside a prompt that comes in portions of changing
+            # length (none twice): such steps replay the graph of their bucket
+            decoding = [llm.engine.new_request() for _ in range(args.batch)]
+            for r in decoding:
+                llm.engine.step([StepEntry(r, rng.integers(0, cfg["vocab_size"], context).tolist(), [])])
+            prompt = llm.engine.new_request()
+
+            def mixed(n):
+                return [StepEntry(r, [5], [0]) for r in decoding] + [StepEntry(prompt, rng.integers(0, cfg["vocab_size"], n).tolist(), [n - 1])]
+            for n in (480, 481, 482, 483, 484):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                llm.engine.step(mixed(n))
+                torch.cuda.synchronize()
+                print(f"probe mixed: {args.batch} decoding + {n} prompt tokens, {cfg['num_hidden_layers']} layers, {(time.perf_counter() - t0) * 1e3:.3f} ms", flush=True)
+            torch.cuda.profiler.start()
+            llm.engine.step(mixed(485))
             torch.cuda.synchronize()
             torch.cuda.profiler.stop()
         else:
@@ -752,7 +772,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="--probe decode: tokens each request holds (default 2,048)")
     ap.add_argument("--prefill-budget", type=int, default=8192, help="token budget of one scheduled step")
     ap.add_argument("--reference-timeout", type=int, default=900, help="seconds the reference arm may take")
-    ap.add_argument("--probe", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--probe", choices=["decode", "prefill", "mixed"], default=None,
                     help="a short run of one kind of step for a profiler (see profiles/); prints no benchmark line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:

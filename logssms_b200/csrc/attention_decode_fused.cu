@@ -30,6 +30,9 @@ struct FusedArgs {
     float* part_o; float* part_ml; int* counters;
     int Hq, Hkv, hd, page_size, window, splits, head_tiles, write_kv;
     float scale, key_scale;
+    // the tensor-core form only: the step rows of the call's tokens (null: rows 0 .. tokens - 1), and whether the
+    // queries still have to be rotated (0: `qkv` holds rotated queries, [rows, Hq * hd]; then write_kv is 0 as well)
+    const int* token_list; int rotate;
 };
 
 // eight consecutive elements held raw in registers until they are needed
@@ -392,7 +395,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     float* cta_part = mrg + kWarps * 16 * (hd + 2);      // [16][hd + 2]: the CTA's own partial result (cluster form)
     __shared__ int last_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;
-    const size_t t = blockIdx.x;
+    // `ti`: which of the call's tokens; `t`: its row in the step (the same unless the call lists its tokens)
+    const size_t ti = blockIdx.x, t = a.token_list != nullptr ? (size_t)a.token_list[ti] : ti;
     const int kvh = blockIdx.y;
     const int G = a.Hq / a.Hkv, h0 = kvh * G;
     const int split = blockIdx.z;
@@ -467,6 +471,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     // Up to here only step tables and keys and values of earlier tokens were read: that may run under the tail of
     // the q|k|v projection before this kernel.  Its output is read from here on.
     pdl_wait();
+    const int rotary = a.rotate ? a.rotary_dim : 0;      // queries that come rotated already are only copied
     const int half = a.rotary_dim >> 1;
     if ((half & 7) == 0 && (a.row_stride & 7) == 0 && ((uintptr_t)a.qkv & 15) == 0) {
         // eight columns per thread: the piece, its partner half a rotation away, cos and sin come as 16-byte loads
@@ -477,7 +482,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
             if (g < G) {
                 const bf16* src = row + (size_t)(h0 + g) * hd;
                 packed = *reinterpret_cast<const uint4*>(src + c0);
-                if (c0 < a.rotary_dim) {
+                if (c0 < rotary) {
                     const bool low = c0 < half;
                     const int f0 = low ? c0 : c0 - half;
                     const uint4 other = *reinterpret_cast<const uint4*>(src + (low ? c0 + half : c0 - half));
@@ -504,7 +509,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     } else {
         for (int i = threadIdx.x; i < 16 * hd; i += kThreads) {
             const int g = i / hd, c = i % hd;
-            q_s[g * ld + c] = __float2bfloat16_rn(g < G ? rotated<bf16>(row + (size_t)(h0 + g) * hd, c, a.rotary_dim, cs, 1.f, false) : 0.f);
+            q_s[g * ld + c] = __float2bfloat16_rn(g < G ? rotated<bf16>(row + (size_t)(h0 + g) * hd, c, rotary, cs, 1.f, false) : 0.f);
         }
     }
     if (owns_new) {
@@ -625,7 +630,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
         mrg[(warp * 16 + lg + 8) * stride + hd] = m1 * ln2; mrg[(warp * 16 + lg + 8) * stride + hd + 1] = l1;
     }
     __syncthreads();
-    const size_t group = t * (size_t)a.Hkv + kvh;
+    const size_t group = ti * (size_t)a.Hkv + kvh;
     for (int i = threadIdx.x; i < G * hd; i += kThreads) {
         const int g = i / hd, d = i % hd;
         float mt = -INFINITY;
@@ -646,7 +651,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
             cta_part[g * stride + d] = osum;
             if (d == 0) { cta_part[g * stride + hd] = mt; cta_part[g * stride + hd + 1] = lsum; }
         } else {
-            const size_t slot = ((size_t)t * a.Hq + h) * a.splits + split;
+            const size_t slot = ((size_t)ti * a.Hq + h) * a.splits + split;
             a.part_o[slot * hd + d] = osum;
             if (d == 0) { a.part_ml[slot * 2] = mt; a.part_ml[slot * 2 + 1] = lsum; }
         }
@@ -697,7 +702,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     __threadfence();
     for (int i = threadIdx.x; i < G * hd; i += kThreads) {
         const int g = i / hd, d = i % hd;
-        const size_t base = ((size_t)t * a.Hq + h0 + g) * a.splits;
+        const size_t base = ((size_t)ti * a.Hq + h0 + g) * a.splits;
         float mt = -INFINITY;
         for (int s2 = 0; s2 < used; ++s2) mt = fmaxf(mt, __ldcg(a.part_ml + (base + s2) * 2));
         float lsum = 0.f, osum = 0.f;
@@ -773,7 +778,7 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
     if (splits > 65535 || (long)Hkv * ((Hq / Hkv + 7) / 8 + 1) > 65535) return kTooLarge;
     FusedArgs a{qkv, row_stride, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, slot_mapping,
                 cos_sin, table_rows, rotary_dim, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
-                write_kv, scale, key_scale};
+                write_kv, scale, key_scale, nullptr, 1};
     if (dtype == kBF16 && hd <= 128 && Hq / Hkv <= 16)
     {
         // Stages of a warp's tile ring: 3 for a small grid (two tiles on their way before the first is used), 2 for a
@@ -787,4 +792,31 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
     }
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, tokens, (cudaStream_t)stream));
     return kOk;
+}
+
+// Does lb_attention_decode_listed take these sizes (the tensor-core form of the kernel above)?
+extern "C" int lb_attention_decode_listed_ok(int Hq, int Hkv, int hd, int dtype) {
+    return dtype == kBF16 && hd > 0 && hd <= 128 && hd % 16 == 0 && Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 16 ? 1 : 0;
+}
+
+// The same attention for some tokens of a step that holds prompt portions as well: `token_list` names the `count` step
+// rows to run (each the newest token of its request: single decoded tokens, or the tokens of a short portion one by
+// one), `q` [rows, Hq, hd] holds the queries already rotated, and every key and value, the tokens' own included, is
+// already in the cache (the rotate-and-store kernel ran before).  Rows of `out` [rows, Hq, hd] that are not listed
+// are left as they are.  bfloat16, hd <= 128, group <= 16 (lb_attention_decode_listed_ok).
+extern "C" int lb_attention_decode_listed(const void* q, void* k_cache, void* v_cache, void* out, const int* block_table,
+                                          int bt_stride, const int* token_req, const int* positions, const int* token_list,
+                                          int count, int Hq, int Hkv, int hd, int page_size, float scale, int window,
+                                          int splits, float* part_o, float* part_ml, int* counters, void* stream) {
+    if (count <= 0) return kOk;
+    if (!lb_attention_decode_listed_ok(Hq, Hkv, hd, kBF16) || page_size <= 0 || splits < 1 || token_list == nullptr) return kBadSize;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return kBadSize;
+    if (splits > 65535 || Hkv > 65535) return kTooLarge;
+    FusedArgs a{q, (long)Hq * hd, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, nullptr,
+                nullptr, 1, 0, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
+                0, scale, 1.f, token_list, 0};
+    const bool small = (long)count * Hkv * splits <= 2 * 148;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (hd <= 64) return small ? launch_mma<4, 3>(a, count, st) : launch_mma<4, 2>(a, count, st);
+    return small ? launch_mma<8, 3>(a, count, st) : launch_mma<8, 2>(a, count, st);
 }

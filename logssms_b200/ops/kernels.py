@@ -366,6 +366,49 @@ def attention_decode_step(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, 
     return out
 
 
+def attention_decode_listed_ok(q: torch.Tensor, k_cache: torch.Tensor) -> bool:
+    """Does `attention_decode_listed` take these operands (bfloat16, head size up to 128, at most 16 query heads per
+    key/value head)?  Else `attention_decode`."""
+    return (q.dtype == torch.bfloat16 and q.dim() == 3 and k_cache.dim() == 4 and q.shape[2] <= 128 and q.shape[2] % 16 == 0
+            and q.shape[1] % k_cache.shape[2] == 0 and q.shape[1] // k_cache.shape[2] <= 16 and q.is_contiguous())
+
+
+def attention_decode_listed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                            token_req: torch.Tensor, positions: torch.Tensor, token_list: torch.Tensor, count: int,
+                            scale: float, window: int = 0, *, splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The decode-step attention kernel (tensor-core form: the query heads of a key/value head as one tile, key ranges
+    merged through the cluster's shared memory) for `count` listed rows of a step that holds prompt portions as well.
+    q [rows, Hq, hd]: rotated queries; every key and value, the rows' own included, is in the cache already.  Rows of
+    `out` that are not listed are left as they are."""
+    _cuda(q, k_cache, v_cache, block_table, token_req, positions, token_list, out)
+    _need(attention_decode_listed_ok(q, k_cache), "attention_decode_listed takes bfloat16, head sizes up to 128, groups up to 16")
+    rows, Hq, hd = q.shape
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape and k_cache.dtype == q.dtype
+          == v_cache.dtype and k_cache.shape[3] == hd, "caches must be contiguous [pages, page_size, kv_heads, head_dim] of q's dtype")
+    page_size, Hkv = k_cache.shape[1], k_cache.shape[2]
+    _need(block_table.dim() == 2 and block_table.dtype == torch.int32 and block_table.stride(1) == 1,
+          "block table must be a row-major int32 matrix")
+    for t_, n_ in ((token_req, "token_req"), (positions, "positions"), (token_list, "token_list")):
+        _i32(t_, n_)
+    _need(token_list.numel() >= count and token_req.numel() == rows == positions.numel(), "one entry per row; a list of `count` rows")
+    if out is None:
+        out = torch.empty_like(q)
+    _need(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+    part_o = part_ml = counters = None
+    splits = int(splits)
+    if splits > 1:
+        part_o = torch.empty(count * Hq * splits * hd, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(count * Hq * splits * 2, dtype=torch.float32, device=q.device)
+        counters = _counters_for(q.device, count * Hq)
+    f = _fn("attention_decode_fused", "lb_attention_decode_listed",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0), _ptr(token_req),
+             _ptr(positions), _ptr(token_list), count, Hq, Hkv, hd, page_size, scale, int(window or 0), splits, _ptr(part_o),
+             _ptr(part_ml), _ptr(counters), _stream()), "attention_decode_listed")
+    return out
+
+
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                       cu_seqlens: torch.Tensor, start_pos: torch.Tensor, tiles: torch.Tensor, num_tiles: int,
                       scale: float, window: int = 0, *, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -92,7 +92,12 @@ class Attention(Part):
                 o = K.attention_prefill(q, k_cache, v_cache, tables, ctx.cu_seqlens, ctx.start_pos, tiles, n_tiles,
                                         self.scale, window)
             token_list, n_short = ctx.short_portion_tokens()
-        if n_short > 0:
+        if n_short > 0 and token_list is not None and K.attention_decode_listed_ok(q, k_cache):
+            # decoded tokens and short portions beside prompt portions: the decode step's kernel, on the listed rows
+            splits = ctx.attention_splits or K.decode_step_splits(n_short, s.num_heads, s.num_kv_heads, ctx.max_context)
+            o = K.attention_decode_listed(q, k_cache, v_cache, tables, ctx.token_req, ctx.positions, token_list, n_short,
+                                          self.scale, window, splits=splits, out=o)
+        elif n_short > 0:
             splits = ctx.attention_splits or K.attention_splits(n_short, s.num_heads, s.num_kv_heads, ctx.max_context)
             o = K.attention_decode(q, k_cache, v_cache, tables, ctx.token_req, ctx.positions, self.scale, window,
                                    splits=splits, token_list=token_list, out=o)

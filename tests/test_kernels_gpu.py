@@ -1018,3 +1018,34 @@ def test_attention_prefill_on_tcgen05_when_only_some_warps_keep_rescaling():
     for _ in range(5):
         close(k.attention_prefill_tc(*args, dev(tiles), tiles.shape[0], scale), want, dtype)
     k.check_kernel_errors()
+
+
+@pytest.mark.parametrize("shape", [(8, 2, 64, 64), (12, 2, 128, 64), (3, 1, 32, 64), (16, 1, 80, 32), (6, 6, 48, 16)])
+@pytest.mark.parametrize("splits", [1, 5, 8, 20])
+def test_attention_decode_listed_runs_the_listed_rows_with_rotated_queries(shape, splits):
+    """The decode step's tensor-core kernel on some rows of a step (queries rotated and keys stored beforehand):
+    equal to the reference on the listed rows, other rows untouched; short and long contexts, a planted far key."""
+    Hq, Hkv, hd, page = shape
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(hd + 3 * Hq + splits)
+    lengths, new = [70, 1, 2065, 64, 129, 700], [3, 1, 1, 2, 1, 4]
+    case = paged_case(g, dtype, Hq, Hkv, hd, page, lengths, new, plant=True)
+    k = K()
+    scale = hd ** -0.5
+    assert k.attention_decode_listed_ok(dev(case["q"]), dev(case["kc"]))
+    want = rnd_of(dtype)(attention_reference(case, scale, 0, ref_dtype(dtype)))
+    rows = len(case["rows"])
+    listed = torch.tensor([r for r in range(rows) if r % 3 != 1], dtype=torch.int32)
+    out = torch.full_like(dev(case["q"]), 7.0)
+    k.attention_decode_listed(dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(case["token_req"]),
+                              dev(case["positions"]), dev(listed), listed.numel(), scale, splits=splits, out=out)
+    mask = torch.zeros(rows, dtype=torch.bool)
+    mask[listed.long()] = True
+    close(out[dev(mask)], want[mask], dtype)
+    assert bool((out[dev(~mask)] == 7.0).all())
+    for window in (1, 65, 300):
+        want_w = rnd_of(dtype)(attention_reference(case, scale, window, ref_dtype(dtype)))
+        got = k.attention_decode_listed(dev(case["q"]), dev(case["kc"]), dev(case["vc"]), dev(case["bt"]), dev(case["token_req"]),
+                                        dev(case["positions"]), dev(listed), listed.numel(), scale, window, splits=splits)
+        close(got[dev(mask)], want_w[mask], dtype)
+    assert int(k._counters_for(torch.device("cuda", torch.cuda.current_device()), 1).abs().sum()) == 0
