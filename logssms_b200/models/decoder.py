@@ -67,6 +67,8 @@ class DecoderModel(Part):
             for child in part.children().values():
                 walk(child)
         walk(self)
+        if K.GEMM_MODE != "tcgen05":          # the engine's own tcgen05 product is built only where it is switched on
+            names = [n for n in names if n != "gemm_tcgen05"]
         return list(dict.fromkeys(names))
 
     def setup(self, rt) -> None:
