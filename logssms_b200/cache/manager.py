@@ -180,16 +180,17 @@ class CacheManager:
         return rc
 
     # ------------------------------------------------------------------ growth
-    def extend(self, rc: RequestCache, new_length: int) -> None:
+    def extend(self, rc: RequestCache, new_length: int, first_pos: int | None = None) -> None:
         """Make room for positions [rc.length, new_length) in every group; for a group with a window,
-        first give back the pages that no token of this step can still see."""
+        first give back the pages that no token of this step can still see.  `first_pos`: the position of the
+        step's first token where that is not rc.length (a step planned once more after the cache has grown)."""
         if new_length < rc.length:
             raise ValueError("a request's cache never shrinks")
         if new_length > self.max_seq_len:
             raise OutOfPages(f"request grows to {new_length} tokens, beyond max_seq_len {self.max_seq_len}")
         for gi, g in enumerate(self.groups):
             if g.need.window is not None:
-                self._drop_behind(gi, rc, rc.length)        # the step's first token sits at rc.length
+                self._drop_behind(gi, rc, rc.length if first_pos is None else min(first_pos, rc.length))   # the step's first token
             want = g.pages_for(new_length)
             have = int(g.num_pages_of[rc.row])
             if want > have:

@@ -15,6 +15,7 @@
 // half-split pairing); attention: python/logssms/layers/attention_backend/fi.py:175-190.
 // Softmax statistics and accumulators are float32, exp is expf.  Head sizes: multiples of 16 up to 256.
 #include "lb200/common.cuh"
+#include "lb200/tcgen05.cuh"
 using namespace lb200;
 
 namespace {
@@ -33,6 +34,7 @@ struct FusedArgs {
     // the tensor-core form only: the step rows of the call's tokens (null: rows 0 .. tokens - 1), and whether the
     // queries still have to be rotated (0: `qkv` holds rotated queries, [rows, Hq * hd]; then write_kv is 0 as well)
     const int* token_list; int rotate;
+    int* error;                                    // the tile-copy form only: where a wait that gave up records itself
 };
 
 // eight consecutive elements held raw in registers until they are needed
@@ -383,16 +385,34 @@ __device__ __forceinline__ void cluster_barrier() {
 // CL: the key ranges of a token and key/value head are the CTAs of one thread-block cluster (2 to 8 of them): their
 // partial results meet through distributed shared memory and two cluster barriers instead of global memory, a
 // fence, an atomic counter and the loads of the last CTA - about 2 us off a kernel of 13.
-template <int HDT, int NS, bool CL>
-__global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int hd = a.hd, ld = hd + 8;                    // row stride: an odd number of 16-byte pieces
-    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [16][ld]   rotated queries (rows beyond the group: zeros)
+// TMA: a tile's keys and values come as boxes of 32 cache rows x 64 dims through the tensor maps (128-byte swizzle,
+// one lane asks, an mbarrier per stage tells the warp that they landed) instead of 16 cp.async per lane with their
+// address arithmetic: the loop of a 32-key tile was several hundred instructions, most of them not arithmetic, and
+// with two warps per scheduler it was the issue rate, not the memory system, that bounded a batch of 64 at
+// 4 TB/s.  Needs head_dim 64 or 128, pages of a multiple of 32 tokens, no window.
+template <int HDT, int NS, bool CL, bool TMA>
+__global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, const __grid_constant__ CUtensorMap map_k,
+                                                                   const __grid_constant__ CUtensorMap map_v) {
+    extern __shared__ __align__(16) unsigned char smem_dyn[];
+    // the tile-copy form wants its tiles on a 1024-byte boundary (the swizzle pattern repeats every 1024 bytes)
+    unsigned char* smem_raw = TMA ? smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u) : smem_dyn;
+    const int hd = a.hd, ld = hd + 8;                    // row stride of q (and of cp.async tiles): an odd number of 16-byte pieces
+    constexpr int kTileElems = kKT * HDT * 16;            // TMA: K (or V) of one tile: HDT / 4 blocks of 32 rows x 64 values
+    constexpr int kStageElems = 2 * kTileElems;          //      K and V of a stage
+    bf16* tiles;                                         // cp.async: [kWarps][NS stages][K, V][kKT][ld]; TMA: [kWarps][NS][K, V][blocks][32][64]
+    bf16* q_s;                                           // [16][ld]   rotated queries (rows beyond the group: zeros)
+    if (TMA) {
+        tiles = reinterpret_cast<bf16*>(smem_raw);
+        q_s = tiles + (size_t)kWarps * NS * kStageElems;
+    } else {
+        q_s = reinterpret_cast<bf16*>(smem_raw);
+        tiles = q_s + 18 * ld;
+    }
     bf16* kn_s = q_s + 16 * ld;                          // [ld]       the token's own key (rotated)
     bf16* vn_s = kn_s + ld;                              // [ld]       the token's own value
-    bf16* tiles = vn_s + ld;                             // [kWarps][NS stages][K, V][kKT][ld]
     float* mrg = reinterpret_cast<float*>(tiles);        // [kWarps][16][hd + 2], over the tiles once the keys are done
     float* cta_part = mrg + kWarps * 16 * (hd + 2);      // [16][hd + 2]: the CTA's own partial result (cluster form)
+    __shared__ __align__(8) uint64_t full[kWarps][NS];   // TMA: a stage's boxes have landed
     __shared__ int last_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;
     // `ti`: which of the call's tokens; `t`: its row in the step (the same unless the call lists its tokens)
@@ -417,10 +437,28 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     const float* cs = a.cos_sin + (size_t)min(max(pos, 0), a.table_rows - 1) * a.rotary_dim;
     const int pieces = hd / 8;
 
-    bf16* my_tiles = tiles + (size_t)warp * NS * 2 * kKT * ld;
+    bf16* my_tiles = TMA ? tiles + (size_t)warp * NS * kStageElems : tiles + (size_t)warp * NS * 2 * kKT * ld;
     const bf16* kc = (const bf16*)a.k_cache;
     const bf16* vc = (const bf16*)a.v_cache;
-    // Lane l looks up the cache row of key j0 + l once; the copies then run with consecutive lanes on
+    // TMA: the cache row at which the tile of key j0 starts (tiles never cross a page: pages are multiples of 32 keys,
+    // ranges start at multiples of 32), and the request for its boxes by one lane.
+    auto tile_row = [&](int j0) -> int {
+        if (j0 >= end) return 0;
+        const int page = j0 / a.page_size;
+        return __ldg(bt + page) * a.page_size + (j0 - page * a.page_size);
+    };
+    auto fetch_tma = [&](int cache_row, int stage) {
+        if (lane == 0) {
+            bf16* kd = my_tiles + (size_t)stage * kStageElems;           // K blocks, then V blocks
+            tc::mbar_expect_tx(&full[warp][stage], kStageElems * (int)sizeof(bf16));
+#pragma unroll
+            for (int blk = 0; blk < HDT / 4; ++blk) {
+                tc::tma_load_2d(kd + blk * (kKT * 64), &map_k, &full[warp][stage], kvh * hd + blk * 64, cache_row);
+                tc::tma_load_2d(kd + kTileElems + blk * (kKT * 64), &map_v, &full[warp][stage], kvh * hd + blk * 64, cache_row);
+            }
+        }
+    };
+    // cp.async: lane l looks up the cache row of key j0 + l once; the copies then run with consecutive lanes on
     // consecutive 16-byte pieces of the same row, so that one instruction covers whole 128-byte lines.
     // The block-table entry of a tile is read one iteration before its copies are issued, so that the warp
     // never waits on that load with tensor-core work behind it.
@@ -462,12 +500,27 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     // share of the memory system is what it keeps in flight, and a tile takes well over a microsecond to arrive
     const int first = begin + warp * kKT;
     constexpr int kStride = kWarps * kKT;
+    long long off_next = -1;
+    int row_next = 0;
+    if (TMA) {
+        if (lane == 0) {
 #pragma unroll
-    for (int p = 0; p < NS - 1; ++p) {
-        if (first + p * kStride < end) fetch(lookup(first + p * kStride), p);
-        cp_async_commit();
+            for (int p = 0; p < NS; ++p) tc::mbar_init(&full[warp][p], 1);
+            tc::mbar_fence_init();
+        }
+        __syncwarp();
+#pragma unroll
+        for (int p = 0; p < NS - 1; ++p)
+            if (first + p * kStride < end) fetch_tma(tile_row(first + p * kStride), p);
+        row_next = tile_row(first + (NS - 1) * kStride);
+    } else {
+#pragma unroll
+        for (int p = 0; p < NS - 1; ++p) {
+            if (first + p * kStride < end) fetch(lookup(first + p * kStride), p);
+            cp_async_commit();
+        }
+        off_next = lookup(first + (NS - 1) * kStride);
     }
-    long long off_next = lookup(first + (NS - 1) * kStride);
     // Up to here only step tables and keys and values of earlier tokens were read: that may run under the tail of
     // the q|k|v projection before this kernel.  Its output is read from here on.
     pdl_wait();
@@ -532,18 +585,51 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     for (int kk = 0; kk < HDT; ++kk)
         if (kk * 16 < hd) ldsm_x4(qa[kk], q_s + (lane & 15) * ld + kk * 16 + (lane >> 4) * 8);
     int stage = 0;
-    for (int j0 = first; j0 < end; j0 += kStride, stage = (stage + 1 == NS ? 0 : stage + 1)) {
+    unsigned phase = 0;                                  // TMA: parity of the stage ring's current round
+    // swizzled tiles: 16-byte piece c of row r lies at piece c ^ (r & 7); the rows a lane addresses have r & 7 == lane & 7
+    const int sw = lane & 7;
+    for (int j0 = first; j0 < end; j0 += kStride) {
         const int ahead = j0 + (NS - 1) * kStride;
-        if (ahead < end) fetch(off_next, (stage + NS - 1) % NS);       // into the stage that was used last iteration
-        cp_async_commit();
-        off_next = lookup(ahead + kStride);
-        cp_async_wait<NS - 1>();
-        __syncwarp();
-        bf16* kb = my_tiles + (size_t)(stage * 2) * kKT * ld;
-        bf16* vb = kb + kKT * ld;
-        if (use_new && pos >= j0 && pos < j0 + kKT) {     // the token's own key and value take their row of the tile
-            for (int c = lane; c < hd; c += 32) { kb[(pos - j0) * ld + c] = kn_s[c]; vb[(pos - j0) * ld + c] = vn_s[c]; }
+        bf16 *kb, *vb;
+        if (TMA) {
+            if (ahead < end) fetch_tma(row_next, (stage + NS - 1) % NS);       // into the stage that was used last iteration
+            row_next = tile_row(ahead + kStride);
+            const bool landed = tc::mbar_wait(&full[warp][stage], phase);
+            if (!__all_sync(0xffffffffu, landed)) {       // the copy engine never answered: give up, the step is invalid
+                if (lane == 0 && a.error != nullptr)
+                    atomicCAS(a.error, 0, 0x31000000 | ((blockIdx.x & 0xFFF) << 12) | ((blockIdx.y & 0x3F) << 6) | (blockIdx.z & 0x3F));
+                break;
+            }
+            kb = my_tiles + (size_t)stage * kStageElems;
+            vb = kb + kTileElems;
+            if (use_new && pos >= j0 && pos < j0 + kKT) { // the token's own key and value take their row of the tile
+                const int r = pos - j0;
+                for (int c = lane; c < hd; c += 32) {
+                    const int at = (c >> 6) * (kKT * 64) + r * 64 + ((((c & 63) >> 3) ^ (r & 7)) << 3) + (c & 7);
+                    kb[at] = kn_s[c]; vb[at] = vn_s[c];
+                }
+                __syncwarp();
+            }
+            if (j0 + kKT > end) {                         // rows of the page beyond the last key hold anything: their values
+                const int r0 = end - j0;                  // must not meet the zero weights as NaN or infinity
+                for (int i = lane; i < (kKT - r0) * (HDT * 2); i += 32) {
+                    const int r = r0 + i / (HDT * 2), c = i % (HDT * 2);
+                    *reinterpret_cast<uint4*>(vb + (c >> 3) * (kKT * 64) + r * 64 + (c & 7) * 8) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+            }
+        } else {
+            if (ahead < end) fetch(off_next, (stage + NS - 1) % NS);       // into the stage that was used last iteration
+            cp_async_commit();
+            off_next = lookup(ahead + kStride);
+            cp_async_wait<NS - 1>();
             __syncwarp();
+            kb = my_tiles + (size_t)(stage * 2) * kKT * ld;
+            vb = kb + kKT * ld;
+            if (use_new && pos >= j0 && pos < j0 + kKT) { // the token's own key and value take their row of the tile
+                for (int c = lane; c < hd; c += 32) { kb[(pos - j0) * ld + c] = kn_s[c]; vb[(pos - j0) * ld + c] = vn_s[c]; }
+                __syncwarp();
+            }
         }
         float s[4][4];
 #pragma unroll
@@ -554,7 +640,11 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
 #pragma unroll
                 for (int n2 = 0; n2 < 2; ++n2) {
                     unsigned kf[4];
-                    ldsm_x4(kf, kb + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * ld + kk * 16 + (mi & 1) * 8);
+                    if (TMA)
+                        ldsm_x4(kf, kb + (kk >> 2) * (kKT * 64) + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * 64
+                                        + ((((kk & 3) * 2 + (mi & 1)) ^ sw) << 3));
+                    else
+                        ldsm_x4(kf, kb + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * ld + kk * 16 + (mi & 1) * 8);
                     mma_bf16(s[2 * n2], qa[kk], kf[0], kf[1]);
                     mma_bf16(s[2 * n2 + 1], qa[kk], kf[2], kf[3]);
                 }
@@ -579,35 +669,46 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         mx0 = fmaxf(m0, mx0 * scale_log2);               // every tile of a warp holds at least one key: finite
         mx1 = fmaxf(m1, mx1 * scale_log2);
-        const float alpha0 = exp2f(m0 - mx0), alpha1 = exp2f(m1 - mx1);
-        m0 = mx0; m1 = mx1;
+        // a row's sums are rescaled only when some row of the warp met a larger score (the weights lie in [0, 1]
+        // and become bfloat16 operands next: the one-instruction 2^x is exact enough)
+        const bool grew = __any_sync(0xffffffffu, mx0 > m0 || mx1 > m1);
         float sum0 = 0.f, sum1 = 0.f;
         unsigned pa[2][4];
 #pragma unroll
         for (int nn = 0; nn < 4; ++nn) {
-            const float e0 = exp2f(fmaf(s[nn][0], scale_log2, -mx0)), e1 = exp2f(fmaf(s[nn][1], scale_log2, -mx0));
-            const float e2 = exp2f(fmaf(s[nn][2], scale_log2, -mx1)), e3 = exp2f(fmaf(s[nn][3], scale_log2, -mx1));
+            const float e0 = tc::ex2_approx(fmaf(s[nn][0], scale_log2, -mx0)), e1 = tc::ex2_approx(fmaf(s[nn][1], scale_log2, -mx0));
+            const float e2 = tc::ex2_approx(fmaf(s[nn][2], scale_log2, -mx1)), e3 = tc::ex2_approx(fmaf(s[nn][3], scale_log2, -mx1));
             sum0 += e0 + e1; sum1 += e2 + e3;
             pa[nn >> 1][(nn & 1) * 2] = pack_bf16(e0, e1);
             pa[nn >> 1][(nn & 1) * 2 + 1] = pack_bf16(e2, e3);
         }
-        l0 = l0 * alpha0 + sum0;
-        l1 = l1 * alpha1 + sum1;
+        if (grew) {
+            const float alpha0 = tc::ex2_approx(m0 - mx0), alpha1 = tc::ex2_approx(m1 - mx1);
+            m0 = mx0; m1 = mx1;
+            l0 *= alpha0; l1 *= alpha1;
 #pragma unroll
-        for (int i = 0; i < HDT * 2; ++i) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+            for (int i = 0; i < HDT * 2; ++i) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+        }
+        l0 += sum0;
+        l1 += sum1;
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
 #pragma unroll
             for (int d2 = 0; d2 < HDT; ++d2) {
                 if (d2 * 16 < hd) {
                     unsigned vf[4];
-                    ldsm_x4_t(vf, vb + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * ld + d2 * 16 + (mi >> 1) * 8);
+                    if (TMA)
+                        ldsm_x4_t(vf, vb + (d2 >> 2) * (kKT * 64) + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * 64
+                                          + ((((d2 & 3) * 2 + (mi >> 1)) ^ sw) << 3));
+                    else
+                        ldsm_x4_t(vf, vb + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * ld + d2 * 16 + (mi >> 1) * 8);
                     mma_bf16(o[2 * d2], pa[kk], vf[0], vf[1]);
                     mma_bf16(o[2 * d2 + 1], pa[kk], vf[2], vf[3]);
                 }
             }
         }
         __syncwarp();
+        if (++stage == NS) { stage = 0; phase ^= 1u; }
     }
     pdl_trigger();                                       // the output projection may fetch its weights under the merge
     cp_async_wait<0>();
@@ -715,15 +816,16 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a) 
     }
 }
 
-template <int HDT, int NS>
-int launch_mma(const FusedArgs& a, int tokens, cudaStream_t s) {
+template <int HDT, int NS, bool TMA>
+int launch_mma_form(const FusedArgs& a, int tokens, cudaStream_t s, const CUtensorMap& map_k, const CUtensorMap& map_v) {
     const int ld = a.hd + 8;
     // the per-warp partial results (kWarps * 16 * (hd + 2) floats) lie over the tiles, which are larger
-    const size_t smem = (size_t)(16 + 2 + kWarps * NS * 2 * kKT) * ld * sizeof(bf16);
+    const size_t smem = TMA ? 1024 + (size_t)kWarps * NS * 2 * kKT * HDT * 16 * sizeof(bf16) + (size_t)18 * ld * sizeof(bf16)
+                            : (size_t)(16 + 2 + kWarps * NS * 2 * kKT) * ld * sizeof(bf16);
     if (a.splits >= 2 && a.splits <= 8) {
         // the ranges of one (token, head) as one cluster along z
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(attn_decode_mma_kernel<HDT, NS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        static size_t have = 0;
+        ensure_dynamic_smem(attn_decode_mma_kernel<HDT, NS, true, TMA>, smem, have);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(tokens, a.Hkv, a.splits); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = s;
         cudaLaunchAttribute attr[2];
@@ -732,11 +834,28 @@ int launch_mma(const FusedArgs& a, int tokens, cudaStream_t s) {
         attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr; cfg.numAttrs = tokens <= kPdlMaxRows ? 2 : 1;
-        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HDT, NS, true>, a);
+        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HDT, NS, true, TMA>, a, map_k, map_v);
     }
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(attn_decode_mma_kernel<HDT, NS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_pdl_if(tokens <= kPdlMaxRows, attn_decode_mma_kernel<HDT, NS, false>, dim3(tokens, a.Hkv, a.splits), dim3(kThreads), smem, s, a);
+    static size_t have_plain = 0;
+    ensure_dynamic_smem(attn_decode_mma_kernel<HDT, NS, false, TMA>, smem, have_plain);
+    return launch_pdl_if(tokens <= kPdlMaxRows, attn_decode_mma_kernel<HDT, NS, false, TMA>, dim3(tokens, a.Hkv, a.splits),
+                         dim3(kThreads), smem, s, a, map_k, map_v);
+}
+
+// The tile-copy form where the sizes allow it (head_dim 64 or 128, pages of a multiple of 32 tokens, no window, caches
+// on 16-byte boundaries), else the cp.async form.  `pages`: pages of the caches (the tensor maps' extent).
+template <int HDT, int NS>
+int launch_mma(const FusedArgs& a, int tokens, long pages, cudaStream_t s) {
+    CUtensorMap map_k = {}, map_v = {};
+    const bool tma = a.hd == HDT * 16 && (a.hd == 64 || a.hd == 128) && a.page_size % kKT == 0 && a.window <= 0 && pages > 0 &&
+                     ((((uintptr_t)a.k_cache) | ((uintptr_t)a.v_cache)) & 15) == 0;
+    if (tma) {
+        int rc = tc::make_tile_map(&map_k, a.k_cache, pages * a.page_size, (long)a.Hkv * a.hd, (long)a.Hkv * a.hd, kKT);
+        if (rc == 0) rc = tc::make_tile_map(&map_v, a.v_cache, pages * a.page_size, (long)a.Hkv * a.hd, (long)a.Hkv * a.hd, kKT);
+        if (rc != 0) return rc;
+        return launch_mma_form<HDT, NS, true>(a, tokens, s, map_k, map_v);
+    }
+    return launch_mma_form<HDT, NS, false>(a, tokens, s, map_k, map_v);
 }
 
 template <typename T>
@@ -769,8 +888,8 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
                                          const int* positions, const int* slot_mapping, const float* cos_sin,
                                          int table_rows, int rotary_dim, int tokens, int Hq, int Hkv, int hd,
                                          int page_size, float scale, float key_scale, int window, int write_kv,
-                                         int splits, float* part_o, float* part_ml, int* counters, int dtype,
-                                         void* stream) {
+                                         int splits, float* part_o, float* part_ml, int* counters, long pages,
+                                         int* error, int dtype, void* stream) {
     if (tokens <= 0) return kOk;
     if (hd <= 0 || hd > 256 || hd % 16 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || splits < 1) return kBadSize;
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return kBadSize;
@@ -778,7 +897,7 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
     if (splits > 65535 || (long)Hkv * ((Hq / Hkv + 7) / 8 + 1) > 65535) return kTooLarge;
     FusedArgs a{qkv, row_stride, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, slot_mapping,
                 cos_sin, table_rows, rotary_dim, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
-                write_kv, scale, key_scale, nullptr, 1};
+                write_kv, scale, key_scale, nullptr, 1, error};
     if (dtype == kBF16 && hd <= 128 && Hq / Hkv <= 16)
     {
         // Stages of a warp's tile ring: 3 for a small grid (two tiles on their way before the first is used), 2 for a
@@ -787,8 +906,8 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
         // 147 KB per CTA delay the start of a cluster under the kernel before).
         const bool small = (long)tokens * Hkv * splits <= 2 * 148;
         cudaStream_t st = (cudaStream_t)stream;
-        if (hd <= 64) return small ? launch_mma<4, 3>(a, tokens, st) : launch_mma<4, 2>(a, tokens, st);
-        return small ? launch_mma<8, 3>(a, tokens, st) : launch_mma<8, 2>(a, tokens, st);
+        if (hd <= 64) return small ? launch_mma<4, 3>(a, tokens, pages, st) : launch_mma<4, 2>(a, tokens, pages, st);
+        return small ? launch_mma<8, 3>(a, tokens, pages, st) : launch_mma<8, 2>(a, tokens, pages, st);
     }
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, tokens, (cudaStream_t)stream));
     return kOk;
@@ -807,16 +926,17 @@ extern "C" int lb_attention_decode_listed_ok(int Hq, int Hkv, int hd, int dtype)
 extern "C" int lb_attention_decode_listed(const void* q, void* k_cache, void* v_cache, void* out, const int* block_table,
                                           int bt_stride, const int* token_req, const int* positions, const int* token_list,
                                           int count, int Hq, int Hkv, int hd, int page_size, float scale, int window,
-                                          int splits, float* part_o, float* part_ml, int* counters, void* stream) {
+                                          int splits, float* part_o, float* part_ml, int* counters, long pages,
+                                          int* error, void* stream) {
     if (count <= 0) return kOk;
     if (!lb_attention_decode_listed_ok(Hq, Hkv, hd, kBF16) || page_size <= 0 || splits < 1 || token_list == nullptr) return kBadSize;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return kBadSize;
     if (splits > 65535 || Hkv > 65535) return kTooLarge;
     FusedArgs a{q, (long)Hq * hd, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, nullptr,
                 nullptr, 1, 0, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
-                0, scale, 1.f, token_list, 0};
+                0, scale, 1.f, token_list, 0, error};
     const bool small = (long)count * Hkv * splits <= 2 * 148;
     cudaStream_t st = (cudaStream_t)stream;
-    if (hd <= 64) return small ? launch_mma<4, 3>(a, count, st) : launch_mma<4, 2>(a, count, st);
-    return small ? launch_mma<8, 3>(a, count, st) : launch_mma<8, 2>(a, count, st);
+    if (hd <= 64) return small ? launch_mma<4, 3>(a, count, pages, st) : launch_mma<4, 2>(a, count, pages, st);
+    return small ? launch_mma<8, 3>(a, count, pages, st) : launch_mma<8, 2>(a, count, pages, st);
 }

@@ -137,7 +137,7 @@ inline int make_tile_map(CUtensorMap* map, const void* ptr, long rows, long widt
     // The same few tensors come back step after step (caches; activations that the allocator hands out at the same
     // address): the last maps are kept, an encoding costs the host a few microseconds.
     struct Entry { const void* ptr; long rows, width, stride; int box_rows; CUtensorMap map; };
-    constexpr int kEntries = 16;
+    constexpr int kEntries = 256;                         // two caches per layer of a deep model and a few activations
     thread_local Entry cache[kEntries] = {};
     thread_local int next = 0;
     for (int i = 0; i < kEntries; ++i) {

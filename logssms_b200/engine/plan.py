@@ -22,10 +22,15 @@ from ..parts.context import SHORT_PORTION, Padding
 
 @dataclass
 class StepEntry:
-    """One request's share of a step: its next tokens and the places among them whose logits are wanted."""
+    """One request's share of a step: its next tokens and the places among them whose logits are wanted.
+
+    `start`: the position of the first of these tokens, when the caller keeps count itself (None: the length of the
+    request's cache).  With it a step can be planned a second time: a plan that was made ahead and then dropped has
+    grown the caches of its requests already, and planning the same tokens again at the same positions grows nothing."""
     request: RequestCache
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    start: int | None = None
 
 
 class _PinnedRing:
@@ -126,7 +131,10 @@ class StepPlanner:
             if self.cache.live.get(e.request.row) is not e.request:
                 raise ValueError("step entry names a request that is not live")
         lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
-        starts = np.fromiter((e.request.length for e in entries), dtype=np.int64, count=B)
+        starts = np.fromiter((e.request.length if e.start is None else e.start for e in entries), dtype=np.int64, count=B)
+        for e, s0, n in zip(entries, starts, lens):
+            if not s0 <= e.request.length <= s0 + n:
+                raise ValueError(f"an entry starts at position {int(s0)}, its request's cache holds {e.request.length} tokens")
         T = int(lens.sum())
         cu = np.zeros(B + 1, dtype=np.int64)
         np.cumsum(lens, out=cu[1:])
@@ -141,7 +149,7 @@ class StepPlanner:
         # extending may give back pages a window has passed
         self.cache.check_room([(e.request, int(s + n)) for e, s, n in zip(entries, starts, lens)])
         for e, s, n in zip(entries, starts, lens):
-            self.cache.extend(e.request, int(s + n))
+            self.cache.extend(e.request, int(s + n), first_pos=int(s))
         rows = np.fromiter((e.request.row for e in entries), dtype=np.int64, count=B)
         logit_rows = np.asarray([cu[b] + w for b, e in enumerate(entries) for w in e.want], dtype=np.int64)
         real_entries = B

@@ -35,6 +35,7 @@ from typing import Iterable, Sequence
 
 import torch
 
+from ..cache import OutOfPages
 from ..sampling import Sampler, SamplingParams
 from .step import StepEntry
 
@@ -111,6 +112,11 @@ class Scheduler:
         self._inflight: _InFlight | None = None
         self._pinned: list[torch.Tensor] = []
         self.overlap = True           # launch the next decode step before reading the previous step's ids
+        # without overlap (every id visits the host before it is fed back): the next decode step planned while the
+        # device still runs this one, (handle, requests); and the pinned buffer its ids go through
+        self._ahead: tuple | None = None
+        self.steps_ahead = 0          # steps that ran from a plan made ahead
+        self._ids_pinned: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ intake
     def add_request(self, prompt: Sequence[int], params: SamplingParams | None = None) -> Request:
@@ -169,10 +175,10 @@ class Scheduler:
     def step(self) -> list[Request]:
         """Run one step; return the requests that are known to have finished since the last call."""
         inflight = self._inflight
-        if inflight is not None and self.overlap and self._goes_on(inflight):
+        if inflight is not None and self.overlap and inflight.event is not None and self._goes_on(inflight):
             # the same requests decode on: launch their next step from the ids on the device, then read the previous ids
             reqs = inflight.requests
-            logits = self.engine.step([StepEntry(r.cache, [0], [0]) for r in reqs], device_tokens=inflight.tokens)
+            logits = self.engine.step([StepEntry(r.cache, [0], [0], r.computed) for r in reqs], device_tokens=inflight.tokens)
             self.steps += 1
             for r in reqs:
                 r.computed += 1
@@ -180,6 +186,20 @@ class Scheduler:
             return self._read(inflight)
         done = self._read(inflight) if inflight is not None else []
         self._inflight = None
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None and self._still_right(ahead[1]):
+            # the step was planned while the last one ran: its ids go to the device, nothing else is left to do
+            handle, reqs = ahead
+            n = len(reqs)
+            if self._ids_pinned is None or self._ids_pinned.numel() < n:
+                self._ids_pinned = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=self.engine.device.type == "cuda")
+            self._ids_pinned.numpy()[:n] = [r.output[-1] for r in reqs]
+            logits = self.engine.run_prepared(handle, self._ids_pinned[:n])
+            self.steps += 1
+            self.steps_ahead += 1
+            for r in reqs:
+                r.computed += 1
+            return done + self._after_step(logits, reqs)
         decision = self.schedule()
         if decision.num_tokens == 0:
             if self.waiting and not self.running:
@@ -187,10 +207,10 @@ class Scheduler:
             return done
         entries, sampled = [], []
         for r in decision.decodes:
-            entries.append(StepEntry(r.cache, [r.output[-1]], [0]))
+            entries.append(StepEntry(r.cache, [r.output[-1]], [0], r.computed))
             sampled.append(r)
         for r, first, n, last in decision.portions:
-            entries.append(StepEntry(r.cache, r.prompt[first:first + n], [n - 1] if last else []))
+            entries.append(StepEntry(r.cache, r.prompt[first:first + n], [n - 1] if last else [], r.computed))
             if last:
                 sampled.append(r)
         logits = self.engine.step(entries)
@@ -200,11 +220,34 @@ class Scheduler:
         for r, _, n, _ in decision.portions:
             r.computed += n
         if sampled:
-            self._inflight = self._sample(logits, sampled, pending=0)
-            if not (self.overlap and self._goes_on(self._inflight)):
-                done += self._read(self._inflight)         # nothing to overlap with: read at once
-                self._inflight = None
+            done += self._after_step(logits, sampled)
         return done
+
+    def _after_step(self, logits: torch.Tensor, sampled: list) -> list[Request]:
+        """Sample; then either leave the ids in flight (overlap), or read them at once, after planning the next
+        decode step while the device still works on this one."""
+        self._inflight = self._sample(logits, sampled, pending=0)
+        goes_on = self._goes_on(self._inflight)
+        if self.overlap and goes_on and self._inflight.event is not None:
+            return []
+        if goes_on and hasattr(self.engine, "prepare"):
+            try:
+                handle = self.engine.prepare([StepEntry(r.cache, [0], [0], r.computed) for r in sampled])
+            except OutOfPages:                             # (requests that reserved their pages never meet this)
+                handle = None
+            if handle is not None:
+                self._ahead = (handle, list(sampled))
+        inflight, self._inflight = self._inflight, None
+        return self._read(inflight)                        # nothing to overlap with: read at once
+
+    def _still_right(self, reqs: list) -> bool:
+        """Does the step that was planned ahead for `reqs` still stand: the same requests decode on, nobody new can
+        come in?  (Else it is dropped: its entries are planned again at their positions, which grows nothing twice.)"""
+        if len(reqs) != len(self.running) or any(r is not q or r.state != RUNNING for r, q in zip(reqs, self.running)):
+            return False
+        if any(len(r.output) >= r.max_tokens for r in reqs):
+            return False
+        return not (self.waiting and self.cache.can_admit(self.waiting[0].total_len))
 
     def _sample(self, logits: torch.Tensor, reqs: list, pending: int) -> _InFlight:
         """Sample one id per request and start its copy to pinned host memory; nobody waits here."""
@@ -228,8 +271,6 @@ class Scheduler:
     def _goes_on(self, inflight: _InFlight) -> bool:
         """Will the next step be exactly one more token for each of these requests, whatever their pending ids
         turn out to be (an end-of-sequence id aside)?  Then it can be launched before they are read."""
-        if inflight.event is None:
-            return False
         if self.waiting and self.cache.can_admit(self.waiting[0].total_len):
             return False
         decoding = [r for r in self.running if r.prompt_done]

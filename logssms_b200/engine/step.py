@@ -154,6 +154,40 @@ class Engine:
                 return self._graph_step(self._shape_graphs, key, self.max_shape_graphs, 3, entries, None)
         return self._run(self.planner.plan(entries), device_tokens)
 
+    # ------------------------------------------------------------------ a decode step planned ahead
+    @torch.inference_mode()
+    def prepare(self, entries: Sequence[StepEntry]):
+        """Plan a step of single decoded tokens before their ids are known: the caches grow, the step's tables go to
+        the device (behind whatever still runs there), and only the ids are missing.  `run_prepared` then costs the
+        host one small copy and one graph launch.  Returns a handle, or None where planning ahead is not on offer (no
+        captured graph of this batch size yet, other shapes of step): then `step` does it all.  A handle that is not
+        run is simply dropped; its entries must then come again with `start` set (see `StepEntry`)."""
+        if not self.use_graphs or not entries:
+            return None
+        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return None
+        slot = self._graphs.get(len(entries))
+        if slot is None or slot.graph is None:
+            return None
+        self._graphs[len(entries)] = self._graphs.pop(len(entries))       # most recently used last
+        self.planner.plan(entries, slot)
+        return (slot, len(entries))
+
+    @torch.inference_mode()
+    def run_prepared(self, handle, token_ids: torch.Tensor) -> torch.Tensor:
+        """Run the step that `prepare` planned on these ids (int32, one per entry, pinned host or device memory)."""
+        slot, n = handle
+        if token_ids.numel() != n or token_ids.dtype != torch.int32:
+            raise ValueError("run_prepared takes one int32 id per prepared entry")
+        slot.ctx.token_ids.copy_(token_ids, non_blocking=True)
+        if not token_ids.is_cuda:
+            self.planner.h2d_bytes += n * 4
+        slot.seen += 1
+        slot.graph.replay()
+        K.launch_count += slot.launches
+        self.steps_run += 1
+        return slot.logits
+
     def _run(self, ctx, device_tokens: torch.Tensor | None) -> torch.Tensor:
         """The planned step, kernel by kernel."""
         if device_tokens is not None:

@@ -358,11 +358,12 @@ def attention_decode_step(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, 
     f = _fn("attention_decode_fused", "lb_attention_decode_fused",
             [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
-             c_void_p, c_int, c_void_p])
+             c_void_p, c_long, c_void_p, c_int, c_void_p])
     _check(f(_ptr(qkv), row_stride, _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
              _ptr(token_req), _ptr(positions), _ptr(slot_mapping), _ptr(cos_sin), cos_sin.shape[0], rotary_dim, tokens,
              Hq, Hkv, hd, page_size, scale, key_scale, int(window or 0), int(write_kv), splits, _ptr(part_o),
-             _ptr(part_ml), _ptr(counters), _code(qkv), _stream()), "attention_decode_step")
+             _ptr(part_ml), _ptr(counters), k_cache.shape[0], _ptr(error_word(qkv.device)), _code(qkv), _stream()),
+           "attention_decode_step")
     return out
 
 
@@ -402,10 +403,10 @@ def attention_decode_listed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         counters = _counters_for(q.device, count * Hq)
     f = _fn("attention_decode_fused", "lb_attention_decode_listed",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+             c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p])
     _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0), _ptr(token_req),
              _ptr(positions), _ptr(token_list), count, Hq, Hkv, hd, page_size, scale, int(window or 0), splits, _ptr(part_o),
-             _ptr(part_ml), _ptr(counters), _stream()), "attention_decode_listed")
+             _ptr(part_ml), _ptr(counters), k_cache.shape[0], _ptr(error_word(q.device)), _stream()), "attention_decode_listed")
     return out
 
 

@@ -79,6 +79,28 @@ def test_window_group_gives_pages_back_as_the_window_passes():
     assert win.pool.num_held == 0 and full.pool.num_held == 0
 
 
+def test_extending_again_to_the_same_length_from_the_same_first_position_changes_nothing():
+    """A step planned ahead and then dropped has grown its requests; the same step planned again names the position
+    of its first token, and neither takes pages nor gives back a page that this token still sees."""
+    m = manager([CacheNeeds(kv=FULL), CacheNeeds(kv=WINDOW)], pages=16)
+    a = m.admit(reserve_tokens=200)
+    m.extend(a, 103)
+    full, win = m.groups
+    for pos in range(103, 140):                   # position 103: the window's oldest key, 64, is the first of page 4
+        m.extend(a, pos + 1, first_pos=pos)
+        held = (full.pool.num_held, win.pool.num_held, a.length, dict(a.reserved))
+        table = win.block_table[a.row].copy()
+        oldest_seen = pos - 40 + 1
+        assert win.block_table[a.row, oldest_seen // 16] >= 0
+        m.extend(a, pos + 1, first_pos=pos)       # once more: the cache already holds pos + 1 tokens
+        assert (full.pool.num_held, win.pool.num_held, a.length, dict(a.reserved)) == held
+        assert (win.block_table[a.row] == table).all()
+        m.check_room([(a, pos + 1)])
+        m.check_integrity()
+    m.release(a)
+    m.check_integrity()
+
+
 def test_reservation_blocks_admission_not_running_requests():
     m = manager([CacheNeeds(kv=FULL)], pages=10)
     a = m.admit(reserve_tokens=100)               # 7 pages set aside

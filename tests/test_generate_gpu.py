@@ -94,6 +94,9 @@ def test_overlapped_decoding_gives_the_same_tokens_and_notices_eos_one_step_late
         outs = llm.generate(prompts, params)
         results[overlap] = [(o.token_ids, o.finish_reason) for o in outs]
         assert llm.scheduler.steps > 0 and not llm.engine.cache.live
+        # without overlap the next decode step is planned while the device runs this one; some of those plans are
+        # dropped here (a request ends, by its end-of-sequence id too), the others run once their ids have come
+        assert (llm.scheduler.steps_ahead > 0) == (not overlap)
         llm.engine.cache.check_integrity()
         del llm
     assert results[True] == results[False]

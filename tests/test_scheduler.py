@@ -25,7 +25,8 @@ class FakeEngine:
         self.batches.append([(e.request.row, e.request.length, list(e.tokens), list(e.want)) for e in entries])
         rows = []
         for e in entries:
-            self.cache.extend(e.request, e.request.length + len(e.tokens))
+            first = e.request.length if e.start is None else e.start
+            self.cache.extend(e.request, first + len(e.tokens), first_pos=first)
             for w in e.want:
                 row = torch.zeros(VOCAB)
                 row[(e.tokens[w] + 1) % VOCAB] = 1.0
@@ -174,3 +175,76 @@ def test_unknown_policy_is_refused():
     import pytest
     with pytest.raises(ValueError, match="scheduling policy"):
         make(policy="decode-first")
+
+
+# --------------------------------------------------------------------------- the next decode step planned ahead
+class AheadEngine(FakeEngine):
+    """An engine that can plan a decode step before its ids are known, as the GPU engine does."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.prepared = self.used = 0
+
+    def prepare(self, entries):
+        assert all(list(e.tokens) == [0] and list(e.want) == [0] and e.start == e.request.length for e in entries)
+        self.prepared += 1
+        for e in entries:
+            self.cache.extend(e.request, e.start + 1, first_pos=e.start)
+        self.cache.check_integrity()
+        return [e.request.row for e in entries]
+
+    def run_prepared(self, handle, ids):
+        self.used += 1
+        self.batches.append([(row, None, [int(t)], [0]) for row, t in zip(handle, ids.tolist())])
+        rows = torch.zeros(len(handle), VOCAB)
+        for i, t in enumerate(ids.tolist()):
+            rows[i, (t + 1) % VOCAB] = 1.0
+        return rows
+
+
+def ahead(**kw):
+    eos = kw.pop("eos", ())
+    eng = AheadEngine(**kw)
+    s = Scheduler(eng, max_step_tokens=32, sampler=ArgmaxSampler(), eos_token_ids=eos)
+    s.overlap = False
+    return eng, s
+
+
+def test_decode_steps_are_planned_ahead_and_dropped_when_the_batch_changes():
+    eng, s = ahead(eos=(9,))
+    a = s.add_request([1], SamplingParams(max_tokens=20))                 # stops at the id 9, planned ahead or not
+    b = s.add_request([30], SamplingParams(max_tokens=6, ignore_eos=True))
+    s.run()
+    assert a.output == list(range(2, 10)) and a.finish_reason == "stop"
+    assert b.output == list(range(31, 37)) and b.finish_reason == "length"
+    # steps 2..5 ran from plans made ahead; the plan made before b's last id is not made (its end was known), the
+    # one made before a's end-of-sequence id is dropped, and a's remaining steps alone are planned ahead again
+    assert eng.used >= 4 and eng.prepared > eng.used
+    assert eng.cache.rows.num_free == 3 and eng.cache.groups[0].pool.num_free == 8
+    eng.cache.check_integrity()
+
+
+def test_a_newcomer_makes_the_plan_ahead_void():
+    eng, s = ahead()
+    a = s.add_request([1], SamplingParams(max_tokens=8))
+    for _ in range(3):
+        s.step()
+    used = eng.used
+    c = s.add_request([40, 41, 42], SamplingParams(max_tokens=3))         # can be admitted: the planned step is dropped
+    s.step()
+    assert eng.used == used and len(eng.batches[-1]) == 2                  # a's token and c's prompt in one step
+    s.run()
+    assert a.output == list(range(2, 10)) and c.output == [43, 44, 45]
+    assert eng.cache.rows.num_free == 3 and eng.cache.groups[0].pool.num_free == 8
+
+
+def test_an_abort_makes_the_plan_ahead_void():
+    eng, s = ahead()
+    a = s.add_request([1], SamplingParams(max_tokens=8))
+    b = s.add_request([20], SamplingParams(max_tokens=8))
+    for _ in range(3):
+        s.step()
+    s.abort(a)
+    s.run()
+    assert b.output == list(range(21, 29)) and a.finish_reason == "abort"
+    assert eng.cache.rows.num_free == 3 and eng.cache.groups[0].pool.num_free == 8
