@@ -513,7 +513,10 @@ def run_1p5b_deep(args, clocks, layers: int | None = None) -> dict:
         llm.engine.step = recording_step
         once(99)                                   # warm-up with other prompts and lengths: builds kernels,
         once(98)                                   # captures the graphs of the buckets that such steps fall into
-        run = once(4321)
+        # three timed passes over requests that were never seen before (other prompts and lengths each time); the
+        # median pass is reported: a pass is seconds of host-driven serving on a machine that other jobs share
+        passes = sorted((once(seed) for seed in (4321, 4322, 4323)), key=lambda r: r["ms"])
+        run = passes[1]
         ck = clocks.summary(*run["clock_span"])
         gen = requests * new_tokens
         del llm
@@ -529,7 +532,7 @@ def run_1p5b_deep(args, clocks, layers: int | None = None) -> dict:
                                   seq_len="128..4096 + 128", prefill_tokens_per_step=budget, temperature=0.8,
                                   parallelism="single GPU"),
             "total_tok_s": (gen + run["prompt_tokens"]) / (run["ms"] / 1e3), "prompt_tokens": run["prompt_tokens"],
-            "generated_tokens": gen, "total_ms": run["ms"],
+            "generated_tokens": gen, "total_ms": run["ms"], "passes_ms": [round(r["ms"], 1) for r in passes],
             "e2e": {"value": gen / run["wall"], "unit": "tokens/s", "path": "LLM.add_request / Scheduler.run, wall clock"},
             "roofline": {"bound": "per step max(bytes / copy bandwidth, FLOPs / bf16 peak), summed", "bound_ms": run["bound_s"] * 1e3,
                          "frac": run["bound_s"] * 1e3 / run["ms"], "peaks": pk_src},

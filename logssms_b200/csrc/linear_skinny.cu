@@ -123,8 +123,9 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
     const int chunks = (K + kChunk - 1) / kChunk;
     const int per_warp = (chunks + kWarps - 1) / kWarps;
     const int c_begin = warp * per_warp, c_end = min(chunks, c_begin + per_warp);
-    uint4 wv[kUnroll][HALVES][2];
-    auto load_w = [&](int c0) {
+    // two batches of weights in registers: one is multiplied while the other is on its way
+    uint4 wa[kUnroll][HALVES][2], wb[kUnroll][HALVES][2];
+    auto load_w = [&](uint4 (&wv)[kUnroll][HALVES][2], int c0) {
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int k = (c0 + u) * kChunk + t * 8;
@@ -135,9 +136,10 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
                 for (int r = 0; r < 2; ++r) wv[u][h][r] = ok ? load_stream(wrow[h][r] + k) : zero;
         }
     };
-    // The weights do not depend on the kernel before this one: their first batch is on its way while
-    // that kernel still runs; x (its output) is touched only after the wait.
-    load_w(c_begin);
+    // The weights do not depend on the kernel before this one: their first two batches (all of them up to
+    // K = 2048) are on their way while that kernel still runs; x (its output) is touched only after the wait.
+    load_w(wa, c_begin);
+    load_w(wb, c_begin + kUnroll);
     pdl_wait();
     if (NORM == 1) {
         // one warp per row; a lane keeps its 8-element pieces of the row in registers between the two passes
@@ -250,8 +252,7 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
         }
         return outv;
     };
-    for (int c0 = c_begin; c0 < c_end; c0 += kUnroll) {
-        if (c0 != c_begin) load_w(c0);
+    auto multiply = [&](const uint4 (&wv)[kUnroll][HALVES][2], int c0) {
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int k = (c0 + u) * kChunk + t * 8;
@@ -267,6 +268,12 @@ __global__ void __launch_bounds__(kThreads) skinny_linear_kernel(SkinnyArgs a) {
                 }
             }
         }
+    };
+    for (int c0 = c_begin; c0 < c_end; c0 += 2 * kUnroll) {
+        multiply(wa, c0);
+        if (c0 + 2 * kUnroll < c_end) load_w(wa, c0 + 2 * kUnroll);
+        if (c0 + kUnroll < c_end) multiply(wb, c0 + kUnroll);
+        if (c0 + 3 * kUnroll < c_end) load_w(wb, c0 + 3 * kUnroll);
     }
     // The next kernel may start once every CTA here has streamed its weights: it fetches its own under this
     // kernel's reduction and stores.  (A trigger at the start lets a whole chain of waiting kernels pile up

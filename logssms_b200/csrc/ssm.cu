@@ -76,6 +76,9 @@ __global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
     }
     const T* conv = (const T*)a.conv;
     const T* dtp = (const T*)a.dt;
+    // Up to here only step tables, constants and the saved state were read: with a programmatic launch that runs
+    // under the kernel before (the projection and conv that make x, B, C and dt), whose results are read from here on.
+    pdl_wait();
 #pragma unroll 2
     for (int t = 0; t < len; ++t) {
         const size_t tok = (size_t)(begin + t);
@@ -132,8 +135,10 @@ __global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
 template <typename T, int NPT>
 void launch_npt(const SsmArgs& a, int B, bool aligned, cudaStream_t s) {
     dim3 grid(a.nh, B, (a.P + kPTile - 1) / kPTile);
-    if (aligned) ssm_scan_kernel<T, NPT, true><<<grid, kPTile * kLanesN, 0, s>>>(a);
-    else ssm_scan_kernel<T, NPT, false><<<grid, kPTile * kLanesN, 0, s>>>(a);
+    // few requests: the kernel starts under the one before it and has its state in registers when that one ends
+    const bool early = B <= kPdlMaxRows;
+    if (aligned) launch_pdl_if(early, ssm_scan_kernel<T, NPT, true>, grid, dim3(kPTile * kLanesN), 0, s, a);
+    else launch_pdl_if(early, ssm_scan_kernel<T, NPT, false>, grid, dim3(kPTile * kLanesN), 0, s, a);
 }
 
 template <typename T>
