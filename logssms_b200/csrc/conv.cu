@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
 // flight together; a thread then walks 4 consecutive tokens of 8 channels.  One thread per 32 outputs instead of
 // per 64 with the rows shared through shared memory: four times the warps of the register form above, which at
 // 2,048 tokens left the SMs a dozen warps each.
-constexpr int kTileTokens = 32, kTileGroups = 32, kTileThreads = 256;
+constexpr int kTileTokens = 64, kTileGroups = 32, kTileThreads = 256;
 
 template <int K>
 __global__ void __launch_bounds__(kTileThreads, 3) conv_forward_tile_kernel(ConvArgs a) {
