@@ -141,6 +141,8 @@ class ModelSpec:
     final_norm_name: str
     layers: tuple[BlockSpec, ...]
     schedule: tuple[ScheduleEntry, ...] = field(default=())
+    embedding_kind: str = "embedding"       # registry.EMBEDDINGS: built as cls(vocab_size, hidden_size, multiplier)
+    lm_head_kind: str = "lm_head"           # registry.HEADS: built as cls(vocab_size, hidden_size, multiplier, tied_to)
 
     def resolved_schedule(self) -> tuple[ScheduleEntry, ...]:
         if self.schedule:

@@ -6,8 +6,8 @@ import torch
 from ..ops import build as kernel_build
 from ..ops import kernels as K
 from ..ops.profiler import PROFILER, nvtx_range
-from ..parts import Embedding, LMHead, Part
-from ..registry import BLOCKS, NORMS
+from ..parts import Part
+from ..registry import BLOCKS, EMBEDDINGS, HEADS, NORMS
 
 
 class DecoderModel(Part):
@@ -20,11 +20,11 @@ class DecoderModel(Part):
     def __init__(self, spec, perturb_init: bool = False):
         self.spec = spec
         shared: dict = {}
-        self.embedding = Embedding(spec.vocab_size, spec.hidden_size, spec.embedding_multiplier)
+        self.embedding = EMBEDDINGS.get(spec.embedding_kind)(spec.vocab_size, spec.hidden_size, spec.embedding_multiplier)
         self.layers = [BLOCKS.get(b.kind)(b, perturb_init=perturb_init, shared=shared) for b in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, perturb_init)
-        self.lm_head = LMHead(spec.vocab_size, spec.hidden_size, spec.lm_head_multiplier,
-                              self.embedding if spec.tie_word_embeddings else None)
+        self.lm_head = HEADS.get(spec.lm_head_kind)(spec.vocab_size, spec.hidden_size, spec.lm_head_multiplier,
+                                                    self.embedding if spec.tie_word_embeddings else None)
         self.schedule = spec.resolved_schedule()
         for e in self.schedule:
             if not 0 <= e.layer < len(self.layers):
@@ -86,12 +86,13 @@ class DecoderModel(Part):
         residual = None
         for i, e in enumerate(self.schedule):
             # a block may hand its output on already joined with the residual (`SummedRows`) where the norm that
-            # comes next takes it: the next block's first norm (the rows before the head are gathered first)
+            # comes next takes it: the next block's first norm, which a block names as `input_norm` (a block that
+            # names none is handed plain tensors; the rows before the head are gathered first)
             nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
-            ctx.extras["next_norm_takes_summed"] = getattr(getattr(nxt, "mixer_norm", None), "takes_summed_rows", False)
+            ctx.extras["next_norm_takes_summed"] = getattr(getattr(nxt, "input_norm", None), "takes_summed_rows", False)
             # ... or with its output multiplier still to be applied (`ScaledRows`); after the last block that norm is
             # the one before the head
-            ctx.extras["next_norm_takes_scaled"] = getattr(getattr(nxt, "mixer_norm", None) if nxt is not None else self.final_norm,
+            ctx.extras["next_norm_takes_scaled"] = getattr(getattr(nxt, "input_norm", None) if nxt is not None else self.final_norm,
                                                            "takes_scaled_rows", False)
             if PROFILER.nvtx:                      # named ranges per layer (and per part inside it) for a timeline
                 with nvtx_range(f"layer {e.layer}"):

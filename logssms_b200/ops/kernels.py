@@ -19,6 +19,7 @@ from ctypes import c_float, c_int, c_long, c_void_p
 import torch
 
 from . import build
+from .fusion import NormedRows, ResidualJoin, ScaledRows, SummedRows      # the fusion protocol (re-exported here)
 from .profiler import PROFILER
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -662,37 +663,6 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
-class ResidualJoin:
-    """A request to a part: let your last product join the residual stream in its epilogue, i.e. leave
-    v = [round(round(y * in_scales[0]) + round(other * in_scales[1])) or y] + residual instead of its output y.
-    `other` may be a callable that returns the tensor (and first waits for whatever produces it)."""
-    __slots__ = ("residual", "other", "in_scales")
-
-    def __init__(self, residual, other=None, in_scales=(1.0, 1.0)):
-        self.residual, self.other, self.in_scales = residual, other, in_scales
-
-    def other_tensor(self):
-        return self.other() if callable(self.other) else self.other
-
-
-class SummedRows:
-    """What a product with a residual join leaves (`linear_join`): the float32 sums `vsum` [M, N], their rounded
-    copy `residual` (the new residual), and `partial` [N / 16, M], the sums of squares over blocks of 16 columns:
-    everything the next RMSNorm needs, so that its consumers can norm their own columns where they load them."""
-    __slots__ = ("vsum", "residual", "partial")
-
-    def __init__(self, vsum, residual, partial):
-        self.vsum, self.residual, self.partial = vsum, residual, partial
-
-    @property
-    def shape(self):
-        return self.vsum.shape
-
-    @property
-    def dtype(self):
-        return self.residual.dtype
-
-
 def linear_join_ok(x, w: torch.Tensor, bias, join: ResidualJoin | None) -> bool:
     """Can `linear_join` take this product?  Few bfloat16 rows (the consumers norm at most 16), whole blocks of 16
     output columns, a residual of the output's shape."""
@@ -740,66 +710,6 @@ def summed_rmsnorm(rows: SummedRows, weight: torch.Tensor, eps: float, out_scale
     _check(f(_ptr(v), _ptr(weight), _ptr(out0), _ptr(out1), M, H, eps, out_scales[0], out_scales[-1],
              _DTYPE_CODE[act], _stream()), "summed_rmsnorm")
     return (out0,) if out1 is None else (out0, out1)
-
-
-class ScaledRows:
-    """Rows whose output multiplier is still to be applied: round(rows * scale).  The product that made them ran in
-    the library, which has no such epilogue; the norm that reads them next applies the multiplier while it loads
-    them (`add_rmsnorm` with `in_scales[0]`: the same rounding), which saves a pass over the rows.  `tensor()` is
-    the scaled tensor for any other use."""
-    __slots__ = ("rows", "scale")
-
-    def __init__(self, rows: torch.Tensor, scale: float):
-        self.rows, self.scale = rows, float(scale)
-
-    @property
-    def shape(self):
-        return self.rows.shape
-
-    @property
-    def dtype(self):
-        return self.rows.dtype
-
-    def tensor(self) -> torch.Tensor:
-        return scale(self.rows, self.scale)
-
-
-class NormedRows:
-    """Rows that are still to be normalised: what `add_rmsnorm` would compute, handed to the product that
-    consumes them so that the few-row kernel can do the norm in its prologue (a decode step is bound by the
-    number of dependent launches).  `residual_out` is shared by all consumers of one norm; the first product
-    that runs writes it.  `tensor()` falls back to the norm kernel for any other use."""
-    __slots__ = ("x", "other", "residual", "weight", "eps", "in_scales", "scale", "shared", "_tensor")
-
-    def __init__(self, x, other, residual, weight, eps, in_scales, scale, shared):
-        # x may be `SummedRows` (the product before has joined the residual already): other and residual are None then
-        self.x, self.other, self.residual, self.weight, self.eps = x, other, residual, weight, eps
-        self.in_scales, self.scale, self.shared = in_scales, scale, shared
-        self._tensor = None
-
-    @property
-    def summed(self) -> bool:
-        return isinstance(self.x, SummedRows)
-
-    @property
-    def shape(self):
-        return self.x.shape
-
-    @property
-    def dtype(self):
-        return self.x.dtype
-
-    def tensor(self) -> torch.Tensor:
-        if self._tensor is None and self.summed:
-            (self._tensor,) = summed_rmsnorm(self.x, self.weight, self.eps, (self.scale,))
-        if self._tensor is None:
-            write = self.shared["residual_out"] is not None and not self.shared["written"]
-            (self._tensor,), res = add_rmsnorm(self.x, self.weight, self.eps, self.residual, other=self.other,
-                                               in_scales=self.in_scales, out_scales=(self.scale,), want_residual=write,
-                                               residual_out=self.shared["residual_out"] if write else None, in_place=False)
-            if write:
-                self.shared["written"] = True
-        return self._tensor
 
 
 def deferred_norm_ok(x) -> bool:
@@ -940,7 +850,8 @@ def error_word(device) -> torch.Tensor:
         device = torch.device(device.type, torch.cuda.current_device())
     err = _gemm_error.get(device)
     if err is None:
-        err = _gemm_error[device] = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):      # an ordinary tensor, whoever asks first: the host may set and clear it anywhere
+            err = _gemm_error[device] = torch.zeros(1, dtype=torch.int32, device=device)
     return err
 
 

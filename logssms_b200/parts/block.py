@@ -29,6 +29,12 @@ class PreNormParallelBlock(Part):
         self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, perturb_init=perturb_init,
                                                                       shared=shared)
 
+    @property
+    def input_norm(self):
+        """The norm that reads this block's input: the block before may hand it rows in the form it takes
+        (`takes_summed_rows`, `takes_scaled_rows`).  A block kind that names none is handed plain tensors."""
+        return self.mixer_norm
+
     def children(self):
         s = self.spec
         kids = {s.mixer_norm_name: self.mixer_norm, s.feed_forward_norm_name: self.ff_norm,

@@ -4,9 +4,11 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
+from ..registry import EMBEDDINGS, HEADS
 from .base import MATRIX, ParamSpec, Part
 
 
+@EMBEDDINGS.register("embedding")
 class Embedding(Part):
     """out = round(table[id] * multiplier), one kernel (python/logssms/models/falcon_h1.py:213)."""
     kernels = ("embed",)
@@ -27,6 +29,7 @@ class Embedding(Part):
         return K.embed_gather(self.weight, ids, self.multiplier, self.bad_ids)
 
 
+@HEADS.register("lm_head")
 class LMHead(Part):
     """logits = float32((h W^T) * multiplier); W is the embedding table when the model ties them
     (python/logssms/layers/embedding.py:94-106, python/logssms/models/falcon_h1.py:237)."""

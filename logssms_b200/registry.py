@@ -1,7 +1,7 @@
 """Name -> object registries.
 
 Every pluggable kind of thing in the engine (architectures, mixers, feed-forwards,
-norms, position encodings, blocks) lives in one `Registry`.  A test or a user
+norms, position encodings, blocks, embeddings, output heads) lives in one `Registry`.  A test or a user
 package adds an entry with `registry.register("name")(cls)`; nothing inside the
 framework has to change.  The same shape as the reference's `Registry[T]`
 (python/logssms/utils/registry.py:5-37) and its architecture table
@@ -54,3 +54,5 @@ FEED_FORWARDS: Registry = Registry("Feed-forward")
 NORMS: Registry = Registry("Norm")
 POSITION_ENCODINGS: Registry = Registry("Position encoding")
 BLOCKS: Registry = Registry("Block")
+EMBEDDINGS: Registry = Registry("Embedding")
+HEADS: Registry = Registry("Output head")

@@ -1,5 +1,6 @@
 """Parts that the framework has never seen, defined HERE and registered from outside the package: a feed-forward
-with routing (top-1 over small experts), another position encoding (rotation with linearly spaced frequencies), and
+with routing (top-1 over small experts), another position encoding (rotation with linearly spaced frequencies), an
+output head of another kind (its own matrix and a bias per vocabulary entry), and
 a stateful mixer whose scan is a CUDA kernel of its own that lies beside this test.  They are chosen layer by layer
 in one toy architecture (layer 0: the toy mixer + the built-in gated MLP; layer 1: attention with the toy encoding
 + the routed feed-forward, last, so that a token whose two best experts nearly tie moves its own logits only), built from a config.json, given random weights, stepped in portions and single
@@ -130,7 +131,23 @@ def define_toys():
             assert rc == 0
             return K.linear(y.to(x.dtype), self.proj_weight)
 
-    for reg, name, cls in ((registry.POSITION_ENCODINGS, "toy_linear_rope", LinearRope),
+    class BiasedHead(Part):
+        """An output head of another kind: never tied to the embedding, and with a bias per vocabulary entry."""
+        kernels = ("linear_skinny",)
+
+        def __init__(self, vocab_size, hidden_size, multiplier, tied_to):
+            assert tied_to is None
+            self.vocab_size, self.hidden_size, self.multiplier = vocab_size, hidden_size, multiplier
+
+        def param_specs(self):
+            return {"weight": ParamSpec((self.vocab_size, self.hidden_size), MATRIX),
+                    "bias": ParamSpec((self.vocab_size,), MATRIX, normal_init(0.5))}
+
+        def forward(self, h):
+            return K.linear(h, self.weight, self.bias, out_scale=self.multiplier, out_f32=True)
+
+    for reg, name, cls in ((registry.HEADS, "toy_biased_head", BiasedHead),
+                           (registry.POSITION_ENCODINGS, "toy_linear_rope", LinearRope),
                            (registry.FEED_FORWARDS, "toy_routed", RoutedFeedForward),
                            (registry.MIXERS, "toy_ema_cuda", EmaCudaMixer)):
         if name not in reg:
@@ -161,8 +178,8 @@ def define_toys():
                 BlockSpec(prefix="layers.1.", mixers=(MixerSlot(attention, "attn."),), feed_forward=RoutedSpec(H, EXPERTS, EI), **common),
             )
             return ModelSpec(vocab_size=V, hidden_size=H, embedding_name="embed.", embedding_multiplier=1.0, lm_head_name="head.",
-                             lm_head_multiplier=1.0, tie_word_embeddings=True, final_norm=norm, final_norm_name="final_norm.",
-                             layers=layers)
+                             lm_head_multiplier=1.0, tie_word_embeddings=False, final_norm=norm, final_norm_name="final_norm.",
+                             layers=layers, lm_head_kind="toy_biased_head")
 
     register_architecture(ARCH, ToyConfig, replace=True)
     return ToyConfig
@@ -201,7 +218,7 @@ def toy_reference(tensors, ids, rd, rnd):
         x = x + rnd(y * weights[:, e:e + 1]) * (top == e).to(rd)[:, None]
     x = rnd(x)
     (hN,), _ = P.rms_norm_branches(x, w["final_norm.weight"], 1e-5, res, rnd=rnd)
-    return lin(hN, w["embed.weight"]).float()
+    return rnd(hN @ w["head.weight"].T + w["head.bias"]).float()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
