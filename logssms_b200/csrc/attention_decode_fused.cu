@@ -389,17 +389,19 @@ __device__ __forceinline__ void cluster_barrier() {
 // one lane asks, an mbarrier per stage tells the warp that they landed) instead of 16 cp.async per lane with their
 // address arithmetic: the loop of a 32-key tile was several hundred instructions, most of them not arithmetic, and
 // with two warps per scheduler it was the issue rate, not the memory system, that bounded a batch of 64 at
-// 4 TB/s.  Needs head_dim 64 or 128, pages of a multiple of 32 tokens, no window.
-template <int HDT, int NS, bool CL, bool TMA>
+// 4 TB/s.  Needs head_dim 64 or 128, pages of a multiple of the tile, no window.
+// KT: keys per tile, 32, or 16 for heads of 128 by TMA: a stage is then 8 KB as for heads of 64, and two CTAs
+// share an SM instead of one with its four warps.
+template <int HDT, int NS, bool CL, bool TMA, int KT>
 __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ __align__(16) unsigned char smem_dyn[];
     // the tile-copy form wants its tiles on a 1024-byte boundary (the swizzle pattern repeats every 1024 bytes)
     unsigned char* smem_raw = TMA ? smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u) : smem_dyn;
     const int hd = a.hd, ld = hd + 8;                    // row stride of q (and of cp.async tiles): an odd number of 16-byte pieces
-    constexpr int kTileElems = kKT * HDT * 16;            // TMA: K (or V) of one tile: HDT / 4 blocks of 32 rows x 64 values
+    constexpr int kTileElems = KT * HDT * 16;            // TMA: K (or V) of one tile: HDT / 4 blocks of KT rows x 64 values
     constexpr int kStageElems = 2 * kTileElems;          //      K and V of a stage
-    bf16* tiles;                                         // cp.async: [kWarps][NS stages][K, V][kKT][ld]; TMA: [kWarps][NS][K, V][blocks][32][64]
+    bf16* tiles;                                         // cp.async: [kWarps][NS stages][K, V][KT][ld]; TMA: [kWarps][NS][K, V][blocks][KT][64]
     bf16* q_s;                                           // [16][ld]   rotated queries (rows beyond the group: zeros)
     if (TMA) {
         tiles = reinterpret_cast<bf16*>(smem_raw);
@@ -424,7 +426,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int n = pos - lo + 1;
     // a range is at least two tiles per warp: shorter ranges only add partial results to merge
-    const int chunk = (max((n + a.splits - 1) / a.splits, 2 * kWarps * kKT) + kKT - 1) / kKT * kKT;
+    const int chunk = (max((n + a.splits - 1) / a.splits, 2 * kWarps * KT) + KT - 1) / KT * KT;
     const int used = (n + chunk - 1) / chunk;
     const bool idle = split >= used;                     // a range without keys
     if (idle && (!CL || used == 1)) return;              // in a cluster it still meets the others at the barriers
@@ -437,7 +439,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
     const float* cs = a.cos_sin + (size_t)min(max(pos, 0), a.table_rows - 1) * a.rotary_dim;
     const int pieces = hd / 8;
 
-    bf16* my_tiles = TMA ? tiles + (size_t)warp * NS * kStageElems : tiles + (size_t)warp * NS * 2 * kKT * ld;
+    bf16* my_tiles = TMA ? tiles + (size_t)warp * NS * kStageElems : tiles + (size_t)warp * NS * 2 * KT * ld;
     const bf16* kc = (const bf16*)a.k_cache;
     const bf16* vc = (const bf16*)a.v_cache;
     // TMA: the cache row at which the tile of key j0 starts (tiles never cross a page: pages are multiples of 32 keys,
@@ -453,8 +455,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
             tc::mbar_expect_tx(&full[warp][stage], kStageElems * (int)sizeof(bf16));
 #pragma unroll
             for (int blk = 0; blk < HDT / 4; ++blk) {
-                tc::tma_load_2d(kd + blk * (kKT * 64), &map_k, &full[warp][stage], kvh * hd + blk * 64, cache_row);
-                tc::tma_load_2d(kd + kTileElems + blk * (kKT * 64), &map_v, &full[warp][stage], kvh * hd + blk * 64, cache_row);
+                tc::tma_load_2d(kd + blk * (KT * 64), &map_k, &full[warp][stage], kvh * hd + blk * 64, cache_row);
+                tc::tma_load_2d(kd + kTileElems + blk * (KT * 64), &map_v, &full[warp][stage], kvh * hd + blk * 64, cache_row);
             }
         }
     };
@@ -469,12 +471,12 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
         return (((long long)__ldg(bt + page) * a.page_size + (j - page * a.page_size)) * a.Hkv + kvh) * hd;
     };
     auto fetch = [&](long long off, int stage) {
-        bf16* kd = my_tiles + (size_t)(stage * 2) * kKT * ld;
-        bf16* vd = kd + kKT * ld;
+        bf16* kd = my_tiles + (size_t)(stage * 2) * KT * ld;
+        bf16* vd = kd + KT * ld;
         if (hd == HDT * 16) {                             // the usual case: shifts for the divisions, copies unrolled
             constexpr int kPieces = HDT * 2;
 #pragma unroll
-            for (int it = 0; it < kKT * kPieces / 32; ++it) {
+            for (int it = 0; it < KT * kPieces / 32; ++it) {
                 const int i = it * 32 + lane, r = i / kPieces, c = i % kPieces;
                 const long long roff = __shfl_sync(0xffffffffu, off, r);
                 const bool valid = roff >= 0;
@@ -482,7 +484,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
                 cp_async16(vd + r * ld + c * 8, vc + (valid ? roff : 0) + c * 8, valid);
             }
         } else {
-            for (int i = lane; i < kKT * pieces; i += 32) {
+            for (int i = lane; i < KT * pieces; i += 32) {
                 const int r = i / pieces, c = i - r * pieces;
                 const long long roff = __shfl_sync(0xffffffffu, off, r);
                 const bool valid = roff >= 0;
@@ -498,8 +500,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
     const float scale_log2 = a.scale * 1.4426950408889634f;
     // NS - 1 tiles are on their way before the first one is used (and while the queries are prepared): a warp's
     // share of the memory system is what it keeps in flight, and a tile takes well over a microsecond to arrive
-    const int first = begin + warp * kKT;
-    constexpr int kStride = kWarps * kKT;
+    const int first = begin + warp * KT;
+    constexpr int kStride = kWarps * KT;
     long long off_next = -1;
     int row_next = 0;
     if (TMA) {
@@ -602,19 +604,19 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
             }
             kb = my_tiles + (size_t)stage * kStageElems;
             vb = kb + kTileElems;
-            if (use_new && pos >= j0 && pos < j0 + kKT) { // the token's own key and value take their row of the tile
+            if (use_new && pos >= j0 && pos < j0 + KT) { // the token's own key and value take their row of the tile
                 const int r = pos - j0;
                 for (int c = lane; c < hd; c += 32) {
-                    const int at = (c >> 6) * (kKT * 64) + r * 64 + ((((c & 63) >> 3) ^ (r & 7)) << 3) + (c & 7);
+                    const int at = (c >> 6) * (KT * 64) + r * 64 + ((((c & 63) >> 3) ^ (r & 7)) << 3) + (c & 7);
                     kb[at] = kn_s[c]; vb[at] = vn_s[c];
                 }
                 __syncwarp();
             }
-            if (j0 + kKT > end) {                         // rows of the page beyond the last key hold anything: their values
+            if (j0 + KT > end) {                         // rows of the page beyond the last key hold anything: their values
                 const int r0 = end - j0;                  // must not meet the zero weights as NaN or infinity
-                for (int i = lane; i < (kKT - r0) * (HDT * 2); i += 32) {
+                for (int i = lane; i < (KT - r0) * (HDT * 2); i += 32) {
                     const int r = r0 + i / (HDT * 2), c = i % (HDT * 2);
-                    *reinterpret_cast<uint4*>(vb + (c >> 3) * (kKT * 64) + r * 64 + (c & 7) * 8) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(vb + (c >> 3) * (KT * 64) + r * 64 + (c & 7) * 8) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 __syncwarp();
             }
@@ -624,24 +626,24 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
             off_next = lookup(ahead + kStride);
             cp_async_wait<NS - 1>();
             __syncwarp();
-            kb = my_tiles + (size_t)(stage * 2) * kKT * ld;
-            vb = kb + kKT * ld;
-            if (use_new && pos >= j0 && pos < j0 + kKT) { // the token's own key and value take their row of the tile
+            kb = my_tiles + (size_t)(stage * 2) * KT * ld;
+            vb = kb + KT * ld;
+            if (use_new && pos >= j0 && pos < j0 + KT) { // the token's own key and value take their row of the tile
                 for (int c = lane; c < hd; c += 32) { kb[(pos - j0) * ld + c] = kn_s[c]; vb[(pos - j0) * ld + c] = vn_s[c]; }
                 __syncwarp();
             }
         }
-        float s[4][4];
+        float s[KT / 8][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < HDT; ++kk) {
             if (kk * 16 < hd) {
 #pragma unroll
-                for (int n2 = 0; n2 < 2; ++n2) {
+                for (int n2 = 0; n2 < KT / 16; ++n2) {
                     unsigned kf[4];
                     if (TMA)
-                        ldsm_x4(kf, kb + (kk >> 2) * (kKT * 64) + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * 64
+                        ldsm_x4(kf, kb + (kk >> 2) * (KT * 64) + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * 64
                                         + ((((kk & 3) * 2 + (mi & 1)) ^ sw) << 3));
                     else
                         ldsm_x4(kf, kb + (n2 * 16 + (mi >> 1) * 8 + (lane & 7)) * ld + kk * 16 + (mi & 1) * 8);
@@ -651,15 +653,15 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
             }
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
-        if (j0 + kKT > end) {                            // only a range's last tile has keys beyond its end
+        if (j0 + KT > end) {                            // only a range's last tile has keys beyond its end
 #pragma unroll
-            for (int nn = 0; nn < 4; ++nn)
+            for (int nn = 0; nn < KT / 8; ++nn)
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     if (j0 + nn * 8 + 2 * lt + (e & 1) >= end) s[nn][e] = -INFINITY;
         }
 #pragma unroll
-        for (int nn = 0; nn < 4; ++nn) {
+        for (int nn = 0; nn < KT / 8; ++nn) {
             mx0 = fmaxf(mx0, fmaxf(s[nn][0], s[nn][1]));
             mx1 = fmaxf(mx1, fmaxf(s[nn][2], s[nn][3]));
         }
@@ -673,9 +675,9 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
         // and become bfloat16 operands next: the one-instruction 2^x is exact enough)
         const bool grew = __any_sync(0xffffffffu, mx0 > m0 || mx1 > m1);
         float sum0 = 0.f, sum1 = 0.f;
-        unsigned pa[2][4];
+        unsigned pa[KT / 16][4];
 #pragma unroll
-        for (int nn = 0; nn < 4; ++nn) {
+        for (int nn = 0; nn < KT / 8; ++nn) {
             const float e0 = tc::ex2_approx(fmaf(s[nn][0], scale_log2, -mx0)), e1 = tc::ex2_approx(fmaf(s[nn][1], scale_log2, -mx0));
             const float e2 = tc::ex2_approx(fmaf(s[nn][2], scale_log2, -mx1)), e3 = tc::ex2_approx(fmaf(s[nn][3], scale_log2, -mx1));
             sum0 += e0 + e1; sum1 += e2 + e3;
@@ -692,13 +694,13 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
         l0 += sum0;
         l1 += sum1;
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
+        for (int kk = 0; kk < KT / 16; ++kk) {
 #pragma unroll
             for (int d2 = 0; d2 < HDT; ++d2) {
                 if (d2 * 16 < hd) {
                     unsigned vf[4];
                     if (TMA)
-                        ldsm_x4_t(vf, vb + (d2 >> 2) * (kKT * 64) + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * 64
+                        ldsm_x4_t(vf, vb + (d2 >> 2) * (KT * 64) + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * 64
                                           + ((((d2 & 3) * 2 + (mi >> 1)) ^ sw) << 3));
                     else
                         ldsm_x4_t(vf, vb + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * ld + d2 * 16 + (mi >> 1) * 8);
@@ -816,16 +818,16 @@ __global__ void __launch_bounds__(kThreads) attn_decode_mma_kernel(FusedArgs a, 
     }
 }
 
-template <int HDT, int NS, bool TMA>
+template <int HDT, int NS, bool TMA, int KT>
 int launch_mma_form(const FusedArgs& a, int tokens, cudaStream_t s, const CUtensorMap& map_k, const CUtensorMap& map_v) {
     const int ld = a.hd + 8;
     // the per-warp partial results (kWarps * 16 * (hd + 2) floats) lie over the tiles, which are larger
-    const size_t smem = TMA ? 1024 + (size_t)kWarps * NS * 2 * kKT * HDT * 16 * sizeof(bf16) + (size_t)18 * ld * sizeof(bf16)
+    const size_t smem = TMA ? 1024 + (size_t)kWarps * NS * 2 * KT * HDT * 16 * sizeof(bf16) + (size_t)18 * ld * sizeof(bf16)
                             : (size_t)(16 + 2 + kWarps * NS * 2 * kKT) * ld * sizeof(bf16);
     if (a.splits >= 2 && a.splits <= 8) {
         // the ranges of one (token, head) as one cluster along z
         static size_t have = 0;
-        ensure_dynamic_smem(attn_decode_mma_kernel<HDT, NS, true, TMA>, smem, have);
+        ensure_dynamic_smem(attn_decode_mma_kernel<HDT, NS, true, TMA, KT>, smem, have);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(tokens, a.Hkv, a.splits); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = s;
         cudaLaunchAttribute attr[2];
@@ -834,28 +836,40 @@ int launch_mma_form(const FusedArgs& a, int tokens, cudaStream_t s, const CUtens
         attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr; cfg.numAttrs = tokens <= kPdlMaxRows ? 2 : 1;
-        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HDT, NS, true, TMA>, a, map_k, map_v);
+        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HDT, NS, true, TMA, KT>, a, map_k, map_v);
     }
     static size_t have_plain = 0;
-    ensure_dynamic_smem(attn_decode_mma_kernel<HDT, NS, false, TMA>, smem, have_plain);
-    return launch_pdl_if(tokens <= kPdlMaxRows, attn_decode_mma_kernel<HDT, NS, false, TMA>, dim3(tokens, a.Hkv, a.splits),
+    ensure_dynamic_smem(attn_decode_mma_kernel<HDT, NS, false, TMA, KT>, smem, have_plain);
+    return launch_pdl_if(tokens <= kPdlMaxRows, attn_decode_mma_kernel<HDT, NS, false, TMA, KT>, dim3(tokens, a.Hkv, a.splits),
                          dim3(kThreads), smem, s, a, map_k, map_v);
 }
 
 // The tile-copy form where the sizes allow it (head_dim 64 or 128, pages of a multiple of 32 tokens, no window, caches
 // on 16-byte boundaries), else the cp.async form.  `pages`: pages of the caches (the tensor maps' extent).
-template <int HDT, int NS>
-int launch_mma(const FusedArgs& a, int tokens, long pages, cudaStream_t s) {
+template <int HDT, int NS, int KT>
+int launch_mma_tiles(const FusedArgs& a, int tokens, long pages, cudaStream_t s) {
     CUtensorMap map_k = {}, map_v = {};
-    const bool tma = a.hd == HDT * 16 && (a.hd == 64 || a.hd == 128) && a.page_size % kKT == 0 && a.window <= 0 && pages > 0 &&
+    const bool tma = a.hd == HDT * 16 && (a.hd == 64 || a.hd == 128) && a.page_size % KT == 0 && a.window <= 0 && pages > 0 &&
                      ((((uintptr_t)a.k_cache) | ((uintptr_t)a.v_cache)) & 15) == 0;
     if (tma) {
-        int rc = tc::make_tile_map(&map_k, a.k_cache, pages * a.page_size, (long)a.Hkv * a.hd, (long)a.Hkv * a.hd, kKT);
-        if (rc == 0) rc = tc::make_tile_map(&map_v, a.v_cache, pages * a.page_size, (long)a.Hkv * a.hd, (long)a.Hkv * a.hd, kKT);
+        int rc = tc::make_tile_map(&map_k, a.k_cache, pages * a.page_size, (long)a.Hkv * a.hd, (long)a.Hkv * a.hd, KT);
+        if (rc == 0) rc = tc::make_tile_map(&map_v, a.v_cache, pages * a.page_size, (long)a.Hkv * a.hd, (long)a.Hkv * a.hd, KT);
         if (rc != 0) return rc;
-        return launch_mma_form<HDT, NS, true>(a, tokens, s, map_k, map_v);
+        return launch_mma_form<HDT, NS, true, KT>(a, tokens, s, map_k, map_v);
     }
-    return launch_mma_form<HDT, NS, false>(a, tokens, s, map_k, map_v);
+    return launch_mma_form<HDT, NS, false, kKT>(a, tokens, s, map_k, map_v);
+}
+
+// The tile-copy form where the sizes allow it (head_dim 64 or 128, pages of a multiple of the tile, no window, caches
+// on 16-byte boundaries), else the cp.async form.  `pages`: pages of the caches (the tensor maps' extent).
+// Heads of 128 take 16-key tiles up to 32 tokens, where the kernel is bound by the chains of its few warps and two
+// CTAs per SM help (24 tokens of 2,048 keys: 27 -> 17 us); with more tokens it runs beside the state update and is
+// bound by the memory both share, and the 32-key form leaves that kernel more room (a 7B-size step of 64 tokens:
+// 2.08 against 2.17 ms).
+template <int HDT, int NS>
+int launch_mma(const FusedArgs& a, int tokens, long pages, cudaStream_t s) {
+    if (HDT == 8 && tokens <= 32) return launch_mma_tiles<HDT, NS, 16>(a, tokens, pages, s);
+    return launch_mma_tiles<HDT, NS, kKT>(a, tokens, pages, s);
 }
 
 template <typename T>
