@@ -114,33 +114,53 @@ __global__ void __launch_bounds__(kStateThreads) ssd_chunk_state_kernel(SsdArgs 
     float* tot = a_s + Lpad;                                    // [32]
     bf16* x_s = reinterpret_cast<bf16*>(tot + 32);              // [Lpad][ldx]  u_s * e^{a_L - a_s}
     bf16* b_s = x_s + Lpad * ldx;                               // [Lpad][ldb]
-    chunk_decay(a, tok0, Lc, Lpad, h, dt_s, a_s, tot);
-    const float aL = a_s[Lc - 1];
+    // Everything the CTA reads is asked for before anything is waited for: B goes straight to shared memory
+    // (cp.async, rows beyond the chunk and columns beyond N as zeros), the thread's pieces of x wait in registers
+    // for the decay factors, which come from dt last.  One after the other these three were the kernel's time.
     const int g = h / (a.nh / a.G), inner = a.nh * P;
-    const int ppieces = Ppad / 8;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < Lpad * ppieces; i += kStateThreads) {
-        const int s = i / ppieces, p = (i % ppieces) * 8;
-        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-        if (s < Lc && p < P) {
-            float f[8];
-            unpack8(*reinterpret_cast<const uint4*>(a.conv + (size_t)(tok0 + s) * a.C + h * P + p), f);
-            const float dts = dt_s[s], wgt = expf(aL - a_s[s]);
-            unsigned* o = reinterpret_cast<unsigned*>(&packed);
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                o[e] = pack_bf16(round_to<bf16>(f[2 * e] * dts) * wgt, round_to<bf16>(f[2 * e + 1] * dts) * wgt);
-        }
-        *reinterpret_cast<uint4*>(x_s + s * ldx + p) = packed;
-    }
     const int npieces = Npad / 8;
-#pragma unroll 4
     for (int i = threadIdx.x; i < Lpad * npieces; i += kStateThreads) {
         const int s = i / npieces, c = i % npieces;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (s < Lc && c * 8 < N) v = *reinterpret_cast<const uint4*>(a.conv + (size_t)(tok0 + s) * a.C + inner + g * N + c * 8);
-        *reinterpret_cast<uint4*>(b_s + s * ldb + c * 8) = v;
+        const bool valid = s < Lc && c * 8 < N;
+        cp_async16(b_s + s * ldb + c * 8, a.conv + (size_t)(tok0 + (valid ? s : 0)) * a.C + inner + g * N + (valid ? c * 8 : 0), valid);
     }
+    asm volatile("cp.async.commit_group;");
+    const int ppieces = Ppad / 8;
+    constexpr int kXAhead = 4;                                  // pieces of x a thread holds while the decay is computed
+    uint4 xv[kXAhead];
+#pragma unroll
+    for (int u = 0; u < kXAhead; ++u) {
+        const int i = threadIdx.x + u * kStateThreads, s = i / ppieces, p = (i % ppieces) * 8;
+        xv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < Lpad * ppieces && s < Lc && p < P)
+            xv[u] = *reinterpret_cast<const uint4*>(a.conv + (size_t)(tok0 + s) * a.C + h * P + p);
+    }
+    chunk_decay(a, tok0, Lc, Lpad, h, dt_s, a_s, tot);
+    const float aL = a_s[Lc - 1];
+    for (int i0 = 0; i0 < Lpad * ppieces; i0 += kXAhead * kStateThreads) {
+#pragma unroll
+        for (int u = 0; u < kXAhead; ++u) {
+            const int i = i0 + threadIdx.x + u * kStateThreads;
+            if (i >= Lpad * ppieces) break;
+            const int s = i / ppieces, p = (i % ppieces) * 8;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            const bool live = s < Lc && p < P;
+            if (i0 == 0) raw = xv[u];
+            else if (live) raw = *reinterpret_cast<const uint4*>(a.conv + (size_t)(tok0 + s) * a.C + h * P + p);
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (live) {
+                float f[8];
+                unpack8(raw, f);
+                const float dts = dt_s[s], wgt = expf(aL - a_s[s]);
+                unsigned* o = reinterpret_cast<unsigned*>(&packed);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    o[e] = pack_bf16(round_to<bf16>(f[2 * e] * dts) * wgt, round_to<bf16>(f[2 * e + 1] * dts) * wgt);
+            }
+            *reinterpret_cast<uint4*>(x_s + s * ldx + p) = packed;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;");
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, lg = lane >> 2, lt = lane & 3, mi = lane >> 3;
     const int ptiles = Ppad / 16, nchunks = (Npad + 63) / 64;
