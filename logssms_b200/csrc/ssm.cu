@@ -31,6 +31,7 @@ struct SsmArgs {
     int nh, P, N, G; float dt_scale;
     const void* gate; long gate_stride; float gate_scale;   // optional [tokens, nh * P] view: y *= silu(gate * scale)
     const int* req_list;                         // optional: the requests (indices in the batch) to run
+    int beside;                                  // the launch shares the GPU with other kernels of the step: leave them SM slots
 };
 
 template <typename T> __device__ __forceinline__ void load4(const T* p, float* f);
@@ -45,40 +46,17 @@ template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bflo
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 
-// NPT: state values per thread (N <= 8 * NPT).  ALIGNED: 4-element vector loads of B and C are legal.
+// The tokens of one portion through the state values S that the thread holds (thread (pi, nl): row p of head h, the
+// state columns i * 32 + nl * 4 .. + 3): y for its row, S updated.
 template <typename T, int NPT, bool ALIGNED>
-__global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
-    pdl_trigger();
-    const int h = blockIdx.x, b = a.req_list ? a.req_list[blockIdx.y] : blockIdx.y;
-    const int pi = threadIdx.x / kLanesN, nl = threadIdx.x % kLanesN;
-    const int p = blockIdx.z * kPTile + pi;
-    const bool p_ok = p < a.P;
-    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
-    if (len <= 0) return;
+__device__ __forceinline__ void scan_tokens(const SsmArgs& a, int h, int p, bool p_ok, int nl, int begin, int len, float (&S)[NPT]) {
     const int g = h / (a.nh / a.G);
     const int inner = a.nh * a.P;
     const int N = a.N;
     const float negA = -expf(a.A_log[h]);
     const float dt_bias = a.dt_bias[h], Dh = a.D[h];
-    float* sp = a.state + (((size_t)a.slots[b] * a.nh + h) * a.P + (p_ok ? p : 0)) * N;
-
-    float S[NPT];
-    const bool fresh = a.start_pos[b] <= 0;
-#pragma unroll
-    for (int i = 0; i < NPT / 4; ++i) {
-        const int n0 = i * 32 + nl * 4;
-        if (!fresh && p_ok && n0 < N) {
-            const float4 v = *reinterpret_cast<const float4*>(sp + n0);
-            S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
-        } else {
-            S[4 * i] = S[4 * i + 1] = S[4 * i + 2] = S[4 * i + 3] = 0.f;
-        }
-    }
     const T* conv = (const T*)a.conv;
     const T* dtp = (const T*)a.dt;
-    // Up to here only step tables, constants and the saved state were read: with a programmatic launch that runs
-    // under the kernel before (the projection and conv that make x, B, C and dt), whose results are read from here on.
-    pdl_wait();
 #pragma unroll 2
     for (int t = 0; t < len; ++t) {
         const size_t tok = (size_t)(begin + t);
@@ -122,6 +100,37 @@ __global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
             ((T*)a.y)[tok * inner + h * a.P + p] = from_f32<T>(yv);
         }
     }
+}
+
+// NPT: state values per thread (N <= 8 * NPT).  ALIGNED: 4-element vector loads of B and C are legal.
+template <typename T, int NPT, bool ALIGNED>
+__global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
+    pdl_trigger();
+    const int h = blockIdx.x, b = a.req_list ? a.req_list[blockIdx.y] : blockIdx.y;
+    const int pi = threadIdx.x / kLanesN, nl = threadIdx.x % kLanesN;
+    const int p = blockIdx.z * kPTile + pi;
+    const bool p_ok = p < a.P;
+    const int begin = a.cu_seqlens[b], len = a.cu_seqlens[b + 1] - begin;
+    if (len <= 0) return;
+    const int N = a.N;
+    float* sp = a.state + (((size_t)a.slots[b] * a.nh + h) * a.P + (p_ok ? p : 0)) * N;
+
+    float S[NPT];
+    const bool fresh = a.start_pos[b] <= 0;
+#pragma unroll
+    for (int i = 0; i < NPT / 4; ++i) {
+        const int n0 = i * 32 + nl * 4;
+        if (!fresh && p_ok && n0 < N) {
+            const float4 v = *reinterpret_cast<const float4*>(sp + n0);
+            S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+        } else {
+            S[4 * i] = S[4 * i + 1] = S[4 * i + 2] = S[4 * i + 3] = 0.f;
+        }
+    }
+    // Up to here only step tables, constants and the saved state were read: with a programmatic launch that runs
+    // under the kernel before (the projection and conv that make x, B, C and dt), whose results are read from here on.
+    pdl_wait();
+    scan_tokens<T, NPT, ALIGNED>(a, h, p, p_ok, nl, begin, len, S);
     if (p_ok) {
 #pragma unroll
         for (int i = 0; i < NPT / 4; ++i) {
@@ -132,9 +141,88 @@ __global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_kernel(SsmArgs a) {
     }
 }
 
+// The same work as a grid that is resident all at once: every CTA walks (request, head, tile of p) items, the state of
+// its next item on its way while it works on this one.  For the listed requests of a step that also holds prompt
+// portions: the one-CTA-per-item grid above is thousands of CTAs that take every SM slot that frees up before any
+// kernel launched after it gets one, so nothing could run beside it; this form leaves the other kernels of the step
+// (the chunked kernels of the prompt portion, on another stream) their share of the SMs, while it streams the states.
+constexpr int kPersistCtasPerSm = 3, kSmCount = 148;
+
+template <typename T, int NPT, bool ALIGNED>
+__global__ void __launch_bounds__(kPTile * kLanesN) ssm_scan_persistent_kernel(SsmArgs a, int B, int ptiles) {
+    extern __shared__ int facts[];                       // per listed request: state slot, starts from zeros?, first token, tokens
+    pdl_trigger();
+    for (int i = threadIdx.x; i < B; i += blockDim.x) {
+        const int b = a.req_list ? a.req_list[i] : i;
+        const int begin = b >= 0 ? a.cu_seqlens[b] : 0;
+        facts[4 * i] = b >= 0 ? a.slots[b] : 0;
+        facts[4 * i + 1] = b >= 0 ? (a.start_pos[b] <= 0) : 1;
+        facts[4 * i + 2] = begin;
+        facts[4 * i + 3] = b >= 0 ? a.cu_seqlens[b + 1] - begin : 0;      // an entry that names no request: no tokens
+    }
+    __syncthreads();
+    const int pi = threadIdx.x / kLanesN, nl = threadIdx.x % kLanesN;
+    const int N = a.N, per_request = a.nh * ptiles, total = B * per_request;
+    // item -> (request index in the list, head, tile of p): tiles of a head, heads of a request follow one another, as
+    // the state lies in memory
+    auto state_of = [&](int item, int& bi, int& h, int& p, bool& p_ok) -> float* {
+        bi = item / per_request;
+        const int r = item - bi * per_request;
+        h = r / ptiles;
+        p = (r - h * ptiles) * kPTile + pi;
+        p_ok = p < a.P;
+        return a.state + (((size_t)facts[4 * bi] * a.nh + h) * a.P + (p_ok ? p : 0)) * N;
+    };
+    auto fetch = [&](int item, float (&S)[NPT]) {
+        int bi, h, p; bool p_ok;
+        const float* sp = state_of(item, bi, h, p, p_ok);
+        const bool read = p_ok && !facts[4 * bi + 1] && facts[4 * bi + 3] > 0;
+#pragma unroll
+        for (int i = 0; i < NPT / 4; ++i) {
+            const int n0 = i * 32 + nl * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (read && n0 < N) v = *reinterpret_cast<const float4*>(sp + n0);
+            S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+        }
+    };
+    float S[NPT], Sn[NPT];
+    int item = blockIdx.x;
+    if (item < total) fetch(item, S);
+    pdl_wait();
+    while (item < total) {
+        const int next = item + gridDim.x;
+        if (next < total) fetch(next, Sn);               // on its way while this item is worked on
+        int bi, h, p; bool p_ok;
+        float* sp = state_of(item, bi, h, p, p_ok);
+        const int len = facts[4 * bi + 3];
+        if (len > 0) {
+            scan_tokens<T, NPT, ALIGNED>(a, h, p, p_ok, nl, facts[4 * bi + 2], len, S);
+            if (p_ok) {
+#pragma unroll
+                for (int i = 0; i < NPT / 4; ++i) {
+                    const int n0 = i * 32 + nl * 4;
+                    if (n0 < N)
+                        *reinterpret_cast<float4*>(sp + n0) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) S[i] = Sn[i];
+        item = next;
+    }
+}
+
 template <typename T, int NPT>
 void launch_npt(const SsmArgs& a, int B, bool aligned, cudaStream_t s) {
-    dim3 grid(a.nh, B, (a.P + kPTile - 1) / kPTile);
+    const int ptiles = (a.P + kPTile - 1) / kPTile;
+    if (a.beside && (long)B * a.nh * ptiles > kPersistCtasPerSm * kSmCount && B <= 4096) {
+        const int ctas = kPersistCtasPerSm * kSmCount;
+        const size_t smem = (size_t)B * 4 * sizeof(int);
+        if (aligned) ssm_scan_persistent_kernel<T, NPT, true><<<ctas, kPTile * kLanesN, smem, s>>>(a, B, ptiles);
+        else ssm_scan_persistent_kernel<T, NPT, false><<<ctas, kPTile * kLanesN, smem, s>>>(a, B, ptiles);
+        return;
+    }
+    dim3 grid(a.nh, B, ptiles);
     // few requests: the kernel starts under the one before it and has its state in registers when that one ends
     const bool early = B <= kPdlMaxRows;
     if (aligned) launch_pdl_if(early, ssm_scan_kernel<T, NPT, true>, grid, dim3(kPTile * kLanesN), 0, s, a);
@@ -159,12 +247,12 @@ extern "C" int lb_ssm_scan(const void* conv, int C, long conv_stride, const void
                            const float* dt_bias, const float* D, float* state, void* y, const int* cu_seqlens,
                            const int* start_pos, const int* slots, int B, int nh, int P, int N, int G,
                            float dt_scale, const void* gate, long gate_stride, float gate_scale,
-                           const int* req_list, int dtype, void* stream) {
+                           const int* req_list, int beside, int dtype, void* stream) {
     if (B <= 0) return kOk;
     if (nh <= 0 || P <= 0 || N <= 0 || G <= 0 || nh % G || N % 4) return kBadSize;
     if (C != nh * P + 2 * G * N) return kBadSize;
     SsmArgs a{conv, C, conv_stride, dt, dt_stride, A_log, dt_bias, D, state, y, cu_seqlens, start_pos, slots, nh, P, N, G, dt_scale,
-              gate, gate_stride, gate_scale, req_list};
+              gate, gate_stride, gate_scale, req_list, beside};
     LB_DISPATCH_DTYPE(dtype, return launch<T>(a, B, (cudaStream_t)stream));
     return kOk;
 }

@@ -78,8 +78,14 @@ class Engine:
         self._bucket_graphs: dict[tuple, _StepGraph] = {}     # other steps filled up to a bucket of sizes, by bucket
         self._sightings: dict[tuple, int] = {}               # shapes seen once: (which kind of graph, key) -> count
         self._often: dict[tuple, int] = {}                   # how often a shape has gone through its bucket's graph
-        self.exact_after = 4                                 # ... before it gets a graph of its own
+        # ... before it gets a graph of its own.  A graph of its own costs a shape three slow steps (two kernel by
+        # kernel, one captured: tens of milliseconds on a deep model) and saves it the bucket's filling, a few per cent
+        # of a step: it pays after dozens of replays.  (With 4, a serving run of 32 requests spent a third of its time
+        # on such steps: a 512-token budget beside a changing number of decoding requests keeps making shapes that
+        # come back a dozen times.)
+        self.exact_after = 32
         self._side_stream: torch.cuda.Stream | None = None
+        self._aux_streams: list | None = None
         self.steps_run = 0
 
     def _pages_that_fit(self, needs, max_requests: int, memory_ratio: float) -> int:
@@ -256,6 +262,10 @@ class Engine:
             # blocks may fork their mixers onto a second stream while capturing (measured: without it a batch-8 decode
             # step takes 30 % longer, a 2,048-token prompt 8.3 instead of 6.4 ms)
             ctx.extras["side_stream"] = self._side_stream
+            # ... and a part may put work of its own beside the rest of its branch (`StepContext.fork`)
+            if self._aux_streams is None:
+                self._aux_streams = [torch.cuda.Stream(self.device) for _ in range(2)]
+            ctx.extras["aux_streams"] = self._aux_streams
             with torch.cuda.graph(graph):
                 x, residual = self.model.forward(ctx)
                 if ctx.logit_rows.numel() == 0:
@@ -263,6 +273,8 @@ class Engine:
                 else:
                     slot.logits = self.model.logits(x, residual, ctx.logit_rows)
             ctx.extras.pop("side_stream", None)
+            ctx.extras.pop("aux_streams", None)
+            ctx.extras.pop("aux_turn", None)
             slot.launches = K.launch_count - before
             K.launch_count = before
             slot.graph = graph

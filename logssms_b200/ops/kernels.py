@@ -538,12 +538,14 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
              num_requests: int, num_heads: int, head_dim: int, state_dim: int, num_groups: int,
              dt_scale: float, gate: torch.Tensor | None = None, gate_scale: float = 1.0, *,
              request_list: torch.Tensor | None = None, num_listed: int = 0,
-             out: torch.Tensor | None = None) -> torch.Tensor:
+             out: torch.Tensor | None = None, beside: bool = False) -> torch.Tensor:
     """conv: [tokens, nh*P + 2*G*N] (x | B | C; a column view is fine); dt: [tokens, nh] view; state: float32
     [slots, nh, P, N], updated in place.  Returns y [tokens, nh*P]; with `gate` ([tokens, nh*P] view)
     the result is y * silu(gate * gate_scale), the gate of a mixer that has no norm.  `request_list`
     (int32 indices into the batch, `num_listed` of them) restricts the call to those requests; the rows
-    of `out` that belong to other requests are left as they are."""
+    of `out` that belong to other requests are left as they are.  `beside`: other kernels of the step run at the same
+    time (on another stream): the launch then takes a grid that is resident at once and walks its items, instead of one
+    CTA per item that would take every SM slot before them."""
     _cuda(conv, dt, A_log, dt_bias, D, state, cu_seqlens, start_pos, slots, gate, request_list, out)
     if request_list is not None:
         _i32(request_list, "request_list")
@@ -566,11 +568,11 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
     _need(y.shape == (tokens, num_heads * head_dim) and y.dtype == conv.dtype and y.is_contiguous(), "out must be [tokens, heads * head_dim]")
     f = _fn("ssm", "lb_ssm_scan", [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                   c_long, c_float, c_void_p, c_int, c_void_p])
+                                   c_long, c_float, c_void_p, c_int, c_int, c_void_p])
     _check(f(_ptr(conv), C, conv.stride(0) if tokens > 1 else C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D),
              _ptr(state), _ptr(y), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), num_requests, num_heads, head_dim,
              state_dim, num_groups, dt_scale, _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale,
-             _ptr(request_list), _code(conv), _stream()), "ssm_scan")
+             _ptr(request_list), int(bool(beside)), _code(conv), _stream()), "ssm_scan")
     return y
 
 

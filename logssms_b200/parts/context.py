@@ -190,6 +190,31 @@ class StepContext:
         (t,) = self._lists(("tiles", tile), lambda: (tile_list(self.host_lens, self.host_starts, tile, cap),))
         return t, t.shape[0]
 
+    def fork(self):
+        """Mark this point of the caller's stream and return `run(work)`, or None where the step has no stream to spare.
+        `run(work)` launches `work()` (kernels that depend only on what was launched before the mark) on a spare stream
+        of the captured step (`extras["aux_streams"]`, set by the engine while it captures), beside whatever the caller
+        has launched since the mark, and returns a function that makes the caller's stream wait for it.  Launch the
+        chain that the step waits for first and the side work after it; the side work should take a grid that is
+        resident at once, or its waiting CTAs take every SM slot before the chain's later kernels get one.  Whatever
+        `work` reads or writes must stay alive until the join."""
+        pool = self.extras.get("aux_streams")
+        if not pool:
+            return None
+        turn = self.extras["aux_turn"] = (self.extras.get("aux_turn", -1) + 1) % len(pool)
+        aux, cur = pool[turn], torch.cuda.current_stream()
+        mark = torch.cuda.Event()
+        mark.record(cur)
+
+        def run(work):
+            aux.wait_event(mark)
+            with torch.cuda.stream(aux):
+                work()
+                done = torch.cuda.Event()
+                done.record(aux)
+            return lambda: cur.wait_event(done)
+        return run
+
     def short_portion_tokens(self) -> tuple[torch.Tensor, int]:
         """int32 token indices (rows of this step's batch) of all portions of at most SHORT_PORTION tokens."""
         if self.padding is None:

@@ -107,15 +107,24 @@ class Mamba2(Part):
         gate = None if s.gated_norm else z          # the bare gate rides in the scan's epilogue
         head = (conv, dt, self.A_log, self.dt_bias, self.D, states["ssm"], ctx.cu_seqlens, ctx.start_pos, ctx.slots)
         sizes = (s.num_heads, s.head_dim, s.state_dim, s.num_groups, m[4])
-        y = None
-        short_list, n_short = None, ctx.num_requests
         if x.dtype == torch.bfloat16 and ctx.has_long_portions and self._chunk_len:
-            # long portions in chunks on the tensor cores; decoded tokens and short portions token by token
+            # long portions in chunks on the tensor cores; decoded tokens and short portions token by token: other
+            # requests, other rows of y.  In a captured step the token-by-token kernel, which is bound by the states it
+            # streams, runs beside the chunked kernels, which are not, on a stream to spare.
             chunks, n_chunks, per_request, n_long = ctx.long_portion_chunks(self._chunk_len)
-            y = K.ssd_prefill(*head, chunks, n_chunks, per_request, n_long, self._chunk_len, *sizes, gate, m[0])
             _, _, short_list, n_short = ctx.requests_by_portion()
-        if n_short > 0:
-            y = K.ssm_scan(*head, ctx.num_requests, *sizes, gate, m[0], request_list=short_list, num_listed=n_short, out=y)
+            y = torch.empty((conv.shape[0], inner), dtype=conv.dtype, device=conv.device)
+            beside = ctx.fork() if n_short > 0 else None
+            K.ssd_prefill(*head, chunks, n_chunks, per_request, n_long, self._chunk_len, *sizes, gate, m[0], out=y)
+            if n_short > 0:
+                short = lambda: K.ssm_scan(*head, ctx.num_requests, *sizes, gate, m[0], request_list=short_list,
+                                           num_listed=n_short, out=y, beside=beside is not None)
+                if beside is not None:
+                    beside(short)()
+                else:
+                    short()
+        else:
+            y = K.ssm_scan(*head, ctx.num_requests, *sizes, gate, m[0])
         if s.gated_norm:
             mode = K.NORM_BEFORE_GATE if s.norm_before_gate else K.NORM_AFTER_GATE
             y = K.gated_rmsnorm(y, z, self.norm_w, s.norm_eps, s.num_groups, m[0], mode)

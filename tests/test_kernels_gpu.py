@@ -622,6 +622,45 @@ def test_ssm_scan_request_list_leaves_other_rows():
     assert torch.equal(st_some[[0, 2]], st_all[[0, 2]]) and bool((st_some[1] == 0).all())
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(24, 64, 128, 1, 9), (20, 40, 256, 2, 12), (37, 24, 20, 1, 20)])
+def test_ssm_scan_beside_other_kernels_gives_the_same_bits(dtype, shape):
+    """The form for listed requests that shares the GPU with other kernels (a grid that is resident at once, every CTA
+    walking its items with the next state on its way) against one CTA per item: the same threads, the same order of
+    sums, the same outputs and states; a list entry that names no request is skipped."""
+    nh, Pd, N, G, B = shape
+    g = torch.Generator().manual_seed(B * 3 + N)
+    k = K()
+    inner, C = nh * Pd, nh * Pd + 2 * G * N
+    lens = [1 + (r * 5) % 4 for r in range(B)]
+    starts = [0 if r % 4 == 1 else 11 for r in range(B)]
+    n = sum(lens)
+    conv = dev(randn(g, n, C + 8, dtype=dtype))[:, :C]
+    dt = dev(randn(g, n, nh, dtype=dtype))
+    consts = [dev(torch.log(1 + 15 * torch.rand(nh, generator=g))), dev(randn(g, nh, scale=0.5) - 2.0),
+              dev(1 + 0.1 * torch.randn(nh, generator=g))]
+    cu, sp = packed_batch(lens, starts)
+    slots = torch.randperm(B + 3, generator=g)[:B].to(torch.int32)
+    state = randn(g, B + 3, nh, Pd, N)
+    for r in range(B):
+        if starts[r] == 0:
+            state[int(slots[r])] = float("nan")          # a request at position 0 never reads its slot
+    listed = [r for r in range(B) if r % 3 != 2]          # some requests of the batch only
+    st_a, st_b = dev(state), dev(state)
+    y_a = torch.full((n, inner), 7.0, dtype=dtype, device="cuda")
+    y_b = y_a.clone()
+    common = (conv, dt, *consts)
+    k.ssm_scan(*common, st_a, dev(cu), dev(sp), dev(slots), B, nh, Pd, N, G, 0.8,
+               request_list=dev(torch.tensor(listed, dtype=torch.int32)), num_listed=len(listed), out=y_a)
+    with_gap = listed[:2] + [-1] + listed[2:]
+    k.ssm_scan(*common, st_b, dev(cu), dev(sp), dev(slots), B, nh, Pd, N, G, 0.8,
+               request_list=dev(torch.tensor(with_gap, dtype=torch.int32)), num_listed=len(with_gap), out=y_b, beside=True)
+    assert torch.equal(y_a, y_b)
+    assert torch.equal(st_a.nan_to_num(nan=-1.0), st_b.nan_to_num(nan=-1.0))
+    rows = torch.cat([torch.arange(int(cu[r]), int(cu[r + 1])) for r in listed])
+    assert not bool(torch.isnan(y_b[rows.cuda()].float()).any()) and bool((y_b[rows.cuda()] != 7.0).any())
+
+
 # --------------------------------------------------------------------------- 32-bit matrix product
 def test_gemm_f32_is_true_32_bit():
     g = torch.Generator().manual_seed(9)
