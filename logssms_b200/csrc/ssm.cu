@@ -14,6 +14,7 @@
 // the batch (B then counts the list).  Grid (head, request, P tile of 16); 128 threads
 // = 16 values of p x 8 lanes over N; each lane owns N/8 state values in registers (float4 strided),
 // the sum over N ends with three shuffles.
+// A second form (`beside`) walks the same items with a grid that is resident at once; see ssm_scan_persistent_kernel.
 #include "lb200/common.cuh"
 using namespace lb200;
 
