@@ -29,7 +29,8 @@ class LLM:
                  memory_ratio: float = 0.9, max_prefill_tokens: int = 8192, seed: int = 0,
                  device: str = "cuda:0", tokenizer=None, eos_token_ids: Sequence[int] | None = None,
                  poison_on_free: bool = False, use_graphs: bool = True, scheduling_policy: str = "mixed",
-                 mixed_prefill_tokens: int | None = None, profile: bool = False, nvtx: bool = False):
+                 mixed_prefill_tokens: int | None = None, profile: bool = False, nvtx: bool = False,
+                 cuda_graph_max_bs: int | None = None):
         from ..config import load_model_config
         config = load_model_config(model_path)
         max_seq_len = max_seq_len_override or min(getattr(config, "max_position_embeddings", 8192), 8192)
@@ -38,7 +39,10 @@ class LLM:
         self.engine = Engine(model_path, dtype, max_requests=max_running_requests, max_seq_len=max_seq_len,
                              page_size=page_size, num_pages=num_pages, memory_ratio=memory_ratio, device=device,
                              poison_on_free=poison_on_free, max_step_tokens=max_prefill_tokens, use_graphs=use_graphs,
-                             profile=profile, nvtx=nvtx)
+                             profile=profile, nvtx=nvtx, cuda_graph_max_bs=cuda_graph_max_bs)
+        if cuda_graph_max_bs:
+            # asked for by size: the decode graphs are captured now, before the first request (as the reference does)
+            self.engine.capture_decode_graphs()
         self.tokenizer = tokenizer if tokenizer is not None else _maybe_tokenizer(model_path)
         if eos_token_ids is None:
             eos = getattr(self.tokenizer, "eos_token_id", None) if self.tokenizer is not None else None

@@ -38,7 +38,8 @@ class Engine:
                  page_size: int = 64, num_pages: int | None = None, memory_ratio: float = 0.9,
                  device: str = "cuda:0", poison_on_free: bool = False, max_step_tokens: int = 1 << 30,
                  use_graphs: bool = True, max_graphs: int = 64, max_shape_graphs: int = 8, max_bucket_graphs: int = 32,
-                 max_graph_tokens: int = 4096, profile: bool = False, nvtx: bool = False):
+                 max_graph_tokens: int = 4096, profile: bool = False, nvtx: bool = False,
+                 cuda_graph_max_bs: int | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("logssms_b200 needs a CUDA device (built for sm_100a); there is no CPU path")
         try:
@@ -68,7 +69,12 @@ class Engine:
         PROFILER.enabled, PROFILER.nvtx = bool(profile), bool(nvtx)
         if profile:
             PROFILER.reset()
-        self.use_graphs = use_graphs and not profile
+        # `cuda_graph_max_bs` (the reference's --cuda-graph-max-bs / --graph, python/logssms/server/args.py:133-143): 0
+        # switches all graphs off; a number is the largest decode batch that gets a graph, and `capture_decode_graphs`
+        # captures the batch sizes 1, 2, 4, 8, 16, ... up to it ahead of the first request, as the reference does at
+        # start (python/logssms/engine/decode_graph.py:52-68); None: every batch size, captured when it first comes twice
+        self.cuda_graph_max_bs = cuda_graph_max_bs
+        self.use_graphs = use_graphs and not profile and cuda_graph_max_bs != 0
         self.max_graphs = max_graphs
         self.max_shape_graphs = max_shape_graphs
         self.max_graph_tokens = max_graph_tokens
@@ -135,6 +141,8 @@ class Engine:
         if self.use_graphs:
             lens = tuple(len(e.tokens) for e in entries)
             if all(n == 1 for n in lens) and all(list(e.want) == [0] for e in entries):
+                if self.cuda_graph_max_bs is not None and len(entries) > self.cuda_graph_max_bs:
+                    return self._run(self.planner.plan(entries), device_tokens)
                 return self._graph_step(self._graphs, len(entries), self.max_graphs, 2, entries, device_tokens)
             if device_tokens is None and sum(lens) <= self.max_graph_tokens:
                 # The graph of exactly this shape, if the shape has come before (no padding: a prompt length that
@@ -159,6 +167,36 @@ class Engine:
                     return logits[:wanted]
                 return self._graph_step(self._shape_graphs, key, self.max_shape_graphs, 3, entries, None)
         return self._run(self.planner.plan(entries), device_tokens)
+
+    def capture_decode_graphs(self, sizes: Sequence[int] | None = None) -> list[int]:
+        """Capture the decode graphs of these batch sizes now (default: 1, 2, 4, 8, 16, 24, ... up to
+        `cuda_graph_max_bs`, or up to the number of request rows), with requests made for the purpose that decode a few
+        dummy tokens and are released again.  A server calls this before its first request so that no request pays for
+        a capture; without the call every batch size is captured when it comes for the second time.  Returns the sizes
+        that now have a graph."""
+        if not self.use_graphs:
+            return []
+        most = min(self.cuda_graph_max_bs or self.cache.max_requests, self.cache.max_requests, self.max_graphs)
+        if sizes is None:
+            sizes = [b for b in [1, 2, 4] + list(range(8, most + 1, 8)) if b <= most]
+        done = []
+        for n in sizes:
+            slot = self._graphs.get(n)
+            if n < 1 or n > most or (slot is not None and slot.graph is not None):
+                continue
+            if self.cache.rows.num_free < n or not self.cache.can_admit(4 * n):
+                break
+            requests = [self.cache.admit(4) for _ in range(n)]
+            try:
+                for _ in range(3):                       # kernel by kernel, captured, replayed
+                    self.step([StepEntry(r, [0], [0]) for r in requests])
+                torch.cuda.synchronize(self.device)
+            finally:
+                for r in requests:
+                    self.cache.release(r)
+            if self._graphs.get(n) is not None and self._graphs[n].graph is not None:
+                done.append(n)
+        return done
 
     # ------------------------------------------------------------------ a decode step planned ahead
     @torch.inference_mode()

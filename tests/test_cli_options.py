@@ -18,8 +18,12 @@ def test_reference_option_names_parse():
     assert (args.num_pages, args.page_size) == (33, 128)
     assert (args.max_tokens, args.temperature, args.top_k, args.top_p, args.ignore_eos) == (9, 0.8, 40, 0.95, True)
     assert args.system == "be brief" and not args.no_graph and args.profile is None and not args.nvtx
+    assert args.cuda_graph_max_bs is None
     args = build_parser().parse_args(["--model", "/m", "--profile", "/tmp/p.json", "--nvtx", "--no-graph"])
     assert args.profile == "/tmp/p.json" and args.nvtx and args.no_graph
+    # the reference's two spellings of the graph option (0: no graphs; a number: the largest decode batch with a graph)
+    assert build_parser().parse_args(["--model", "/m", "--cuda-graph-max-bs", "16"]).cuda_graph_max_bs == 16
+    assert build_parser().parse_args(["--model", "/m", "--graph", "0"]).cuda_graph_max_bs == 0
 
 
 def test_model_path_has_both_spellings_and_defaults_follow_the_chat_client():

@@ -162,3 +162,26 @@ def test_steps_of_new_shapes_replay_the_graph_of_their_bucket(tmp_path, name, dt
     ends = [sum(portions_p[:i + 1]) - 1 for i in range(len(portions_p))]
     got = torch.stack([results[True][1 + i][3] for i in range(len(portions_p))])
     assert rel_err(got, want[ends]) <= TOL[dtype]
+
+
+def test_decode_graphs_captured_ahead_and_the_largest_batch_with_a_graph(tmp_path):
+    """`cuda_graph_max_bs` as the reference has it: the decode graphs of batch sizes 1, 2, 4, 8, ... up to it can be
+    captured before the first request; a larger decode batch runs kernel by kernel; 0 switches graphs off.  Tokens are
+    the same either way."""
+    from logssms_b200.engine import LLM
+    from logssms_b200.sampling import SamplingParams
+    model_dir = make_model_dir(tmp_path / "m", TINY["B"], seed=3)
+    prompts = [[3 + i, 9, 27 + i] for i in range(6)]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    plain = LLM(model_dir, "float32", max_running_requests=8, max_seq_len_override=128, num_pages=12, cuda_graph_max_bs=0)
+    assert not plain.engine.use_graphs
+    want = [o.token_ids for o in plain.generate(prompts, sp)]
+    del plain
+    llm = LLM(model_dir, "float32", max_running_requests=8, max_seq_len_override=128, num_pages=12, cuda_graph_max_bs=4)
+    assert sorted(n for n, g in llm.engine._graphs.items() if g.graph is not None) == [1, 2, 4]      # captured at start
+    assert not llm.engine.cache.live
+    llm.engine.cache.check_integrity()
+    assert [o.token_ids for o in llm.generate(prompts, sp)] == want          # six decode together: beyond 4, no graph
+    assert 6 not in llm.engine._graphs
+    assert [o.token_ids for o in llm.generate(prompts[:2], sp)] == want[:2]  # two: the graph captured at start
+    assert llm.engine.capture_decode_graphs([3]) == [3] and llm.engine.capture_decode_graphs([7]) == []
