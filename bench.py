@@ -58,7 +58,7 @@ _COMMON = {
     "projectors_bias": False, "mamba_rms_norm": False, "mamba_norm_before_gate": False,
     "hidden_act": "silu", "attention_bias": False, "mlp_bias": False, **_MUP,
 }
-# BASELINE.json configs[2], [3], [4]
+# the three benchmark configurations: 0.5B-class (the default line), 1.5B-Deep-class, 7B-class layer sizes
 MODELS = {
     "0p5b": {**_COMMON, "num_hidden_layers": 36, "hidden_size": 1024, "num_attention_heads": 8, "num_key_value_heads": 2,
              "head_dim": 64, "intermediate_size": 2048, "vocab_size": 32784, "max_position_embeddings": 8192,
