@@ -113,7 +113,7 @@ class StepPlanner:
         self.h2d_bytes = 0          # bytes of step tables copied host -> device so far
 
     def plan(self, entries: Sequence[StepEntry], static: StaticTables | None = None,
-             bucket: Bucket | None = None) -> StepContext:
+             bucket: Bucket | None = None, pad_singles: int = 0) -> StepContext:
         """Host side of a step: checks, room in the cache, and every per-step integer packed into one
         pinned buffer and copied to the device at once.  With `static` (a captured step's slot) the
         tables keep a fixed width and a fixed place on the device, so that a captured graph finds them;
@@ -121,7 +121,9 @@ class StepPlanner:
         places, request by request, or, with `bucket`, fit the same bucket: the step is then filled up
         with dummy requests (single tokens and one portion, on a state slot and a cache page of their
         own) to the bucket's numbers of requests, tokens and wanted places, and the context's work lists
-        have the bucket's fixed lengths."""
+        have the bucket's fixed lengths.  `pad_singles` (a step of single decoded tokens replayed from the graph of a
+        larger batch): that many dummy requests of one token each, which want their logits like the others, follow
+        the real ones."""
         B = len(entries)
         seen = set()
         for e in entries:
@@ -167,6 +169,15 @@ class StepPlanner:
             cu = np.zeros(B + 1, dtype=np.int64)
             np.cumsum(lens, out=cu[1:])
             logit_rows = np.concatenate([logit_rows, np.full(bucket.requests - len(logit_rows), T - 1, dtype=np.int64)])
+        elif pad_singles > 0:
+            lens = np.concatenate([lens, np.ones(pad_singles, dtype=np.int64)])
+            starts = np.concatenate([starts, np.zeros(pad_singles, dtype=np.int64)])
+            rows = np.concatenate([rows, np.full(pad_singles, self.cache.dummy_row, dtype=np.int64)])
+            tokens = np.concatenate([tokens, np.zeros(pad_singles, dtype=np.int64)])
+            logit_rows = np.concatenate([logit_rows, T + np.arange(pad_singles, dtype=np.int64)])
+            B, T = B + pad_singles, T + pad_singles
+            cu = np.zeros(B + 1, dtype=np.int64)
+            np.cumsum(lens, out=cu[1:])
         token_req = np.repeat(np.arange(B, dtype=np.int64), lens)
         positions = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1], lens) + np.repeat(starts, lens)
         groups = self.cache.groups

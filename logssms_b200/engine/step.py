@@ -84,6 +84,7 @@ class Engine:
         self._bucket_graphs: dict[tuple, _StepGraph] = {}     # other steps filled up to a bucket of sizes, by bucket
         self._sightings: dict[tuple, int] = {}               # shapes seen once: (which kind of graph, key) -> count
         self._often: dict[tuple, int] = {}                   # how often a shape has gone through its bucket's graph
+        self._decode_seen: dict[int, int] = {}               # ... and a decode batch size through a larger batch's graph
         # ... before it gets a graph of its own.  A graph of its own costs a shape three slow steps (two kernel by
         # kernel, one captured: tens of milliseconds on a deep model) and saves it the bucket's filling, a few per cent
         # of a step: it pays after dozens of replays.  (With 4, a serving run of 32 requests spent a third of its time
@@ -141,9 +142,21 @@ class Engine:
         if self.use_graphs:
             lens = tuple(len(e.tokens) for e in entries)
             if all(n == 1 for n in lens) and all(list(e.want) == [0] for e in entries):
-                if self.cuda_graph_max_bs is not None and len(entries) > self.cuda_graph_max_bs:
+                n = len(entries)
+                if self.cuda_graph_max_bs is not None and n > self.cuda_graph_max_bs:
                     return self._run(self.planner.plan(entries), device_tokens)
-                return self._graph_step(self._graphs, len(entries), self.max_graphs, 2, entries, device_tokens)
+                own = self._graphs.get(n)
+                if own is None or own.graph is None:
+                    # No graph of this batch size yet.  Until the size has come `exact_after` times it is replayed from
+                    # the graph of the next larger batch that has one, filled up with dummy requests (the reference
+                    # pads its decode batches to graph buckets the same way, python/logssms/engine/decode_graph.py:185-193):
+                    # a graph of its own costs two slow steps.
+                    seen = self._decode_seen[n] = self._decode_seen.get(n, 0) + 1
+                    wider = min((b for b, g in self._graphs.items() if b > n and g.graph is not None and b <= max(2 * n, n + 8)),
+                                default=None)
+                    if wider is not None and seen <= self.exact_after:
+                        return self._padded_decode(self._graphs[wider], wider, entries, device_tokens)
+                return self._graph_step(self._graphs, n, self.max_graphs, 2, entries, device_tokens)
             if device_tokens is None and sum(lens) <= self.max_graph_tokens:
                 # The graph of exactly this shape, if the shape has come before (no padding: a prompt length that
                 # recurs, equal portions of a long prompt).  A shape that is new goes through the graph of its bucket:
@@ -189,7 +202,8 @@ class Engine:
             requests = [self.cache.admit(4) for _ in range(n)]
             try:
                 for _ in range(3):                       # kernel by kernel, captured, replayed
-                    self.step([StepEntry(r, [0], [0]) for r in requests])
+                    with torch.inference_mode():
+                        self._graph_step(self._graphs, n, self.max_graphs, 2, [StepEntry(r, [0], [0]) for r in requests], None)
                 torch.cuda.synchronize(self.device)
             finally:
                 for r in requests:
@@ -231,6 +245,21 @@ class Engine:
         K.launch_count += slot.launches
         self.steps_run += 1
         return slot.logits
+
+    def _padded_decode(self, slot, size: int, entries: Sequence[StepEntry], device_tokens) -> torch.Tensor:
+        """A decode step of fewer requests than `size` through the captured graph of that size."""
+        n = len(entries)
+        self._graphs[size] = self._graphs.pop(size)        # most recently used last
+        ctx = self.planner.plan(entries, slot, pad_singles=size - n)
+        if device_tokens is not None:
+            if device_tokens.numel() != n:
+                raise ValueError("device_tokens feeds steps of one token per entry only")
+            ctx.token_ids[:n].copy_(device_tokens)
+        slot.seen += 1
+        slot.graph.replay()
+        K.launch_count += slot.launches
+        self.steps_run += 1
+        return slot.logits[:n]
 
     def _run(self, ctx, device_tokens: torch.Tensor | None) -> torch.Tensor:
         """The planned step, kernel by kernel."""

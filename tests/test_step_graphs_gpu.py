@@ -185,3 +185,50 @@ def test_decode_graphs_captured_ahead_and_the_largest_batch_with_a_graph(tmp_pat
     assert 6 not in llm.engine._graphs
     assert [o.token_ids for o in llm.generate(prompts[:2], sp)] == want[:2]  # two: the graph captured at start
     assert llm.engine.capture_decode_graphs([3]) == [3] and llm.engine.capture_decode_graphs([7]) == []
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_decode_batch_without_a_graph_rides_in_the_graph_of_a_larger_one(tmp_path, dtype):
+    """With the usual batch sizes captured at start, a decode batch of another size is filled up with dummy requests
+    and replayed from the next larger graph: no step of the run is launched kernel by kernel or captured, the dummy
+    requests change nobody's tokens, and only a size that keeps coming earns a graph of its own."""
+    from logssms_b200.engine import LLM
+    from logssms_b200.sampling import SamplingParams
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    model_dir = make_model_dir(tmp_path / "m", TINY["B"], seed=5, dtype=store)
+    prompts = [[3 + i, 9, 27 + i] for i in range(7)]
+    sp = SamplingParams(max_tokens=7, ignore_eos=True)
+    plain = LLM(model_dir, dtype, max_running_requests=8, max_seq_len_override=128, num_pages=12, cuda_graph_max_bs=0)
+    want = {k: [o.token_ids for o in plain.generate(prompts[:k], sp)] for k in (3, 5, 6, 7)}
+    del plain
+
+    def same(got, ref):
+        # float32: the very tokens.  bfloat16: the key ranges of the attention follow the batch size of the graph, so
+        # sums round differently and a greedy choice between near-equal logits of a random model may flip later on:
+        # the first tokens must agree, and most of all tokens
+        if dtype == "float32":
+            return got == ref
+        flat = [(a, b) for g, r in zip(got, ref) for a, b in zip(g, r)]
+        return all(g[:2] == r[:2] for g, r in zip(got, ref)) and sum(a == b for a, b in flat) >= 0.6 * len(flat)
+    llm = LLM(model_dir, dtype, max_running_requests=8, max_seq_len_override=128, num_pages=12, cuda_graph_max_bs=8)
+    eng = llm.engine
+    assert sorted(n for n, g in eng._graphs.items() if g.graph is not None) == [1, 2, 4, 8]
+    eager = {"n": 0}
+    run = eng._run
+
+    def counting(ctx, device_tokens):
+        eager["n"] += ctx.max_len == 1                      # decode steps only: the prompts' own steps do not count
+        return run(ctx, device_tokens)
+    eng._run = counting
+    for overlap in (True, False):
+        llm.scheduler.overlap = overlap
+        for k in (3, 5, 6, 7):
+            assert same([o.token_ids for o in llm.generate(prompts[:k], sp)], want[k]), (overlap, k)
+    assert eager["n"] == 0
+    assert sorted(n for n, g in eng._graphs.items() if g.graph is not None) == [1, 2, 4, 8]
+    assert not eng.cache.live
+    eng.cache.check_integrity()
+    eng.exact_after = 2                                     # now a size that keeps coming gets a graph of its own
+    for _ in range(2):
+        assert same([o.token_ids for o in llm.generate(prompts[:3], sp)], want[3])
+    assert eng._graphs.get(3) is not None and eng._graphs[3].graph is not None
