@@ -164,6 +164,51 @@ def test_steps_of_new_shapes_replay_the_graph_of_their_bucket(tmp_path, name, dt
     assert rel_err(got, want[ends]) <= TOL[dtype]
 
 
+def test_decoded_tokens_state_update_beside_the_chunked_kernels_of_a_portion(tmp_path):
+    """In a captured step the Mamba2 mixer puts the token-by-token state update of the decoded tokens on a stream of
+    its own beside the chunked kernels of the prompt portion, as a grid that is resident at once.  That form is taken
+    only with hundreds of (request, head) items: a model with 40 small SSM heads and a dozen decoding requests.  The
+    replayed steps must give the logits of the same steps run kernel by kernel on one stream, and the plain model's."""
+    import copy
+    from logssms_b200.engine import Engine
+    from tiny import plain_logits, rel_err
+    raw = copy.deepcopy(TINY["D"])
+    raw.update({"mamba_n_heads": 40, "mamba_d_head": 16, "mamba_d_ssm": 640, "mamba_d_state": 64})
+    dtype = "bfloat16"
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=47, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(23)
+    decoders = [f"d{i}" for i in range(12)]
+    portions_p = [100, 101, 99, 102, 98, 103]
+    sizes = {"p": sum(portions_p), **{d: 20 + 3 * i + len(portions_p) for i, d in enumerate(decoders)}}
+    prompts = {k: torch.randint(0, raw["vocab_size"], (n,), generator=g).tolist() for k, n in sizes.items()}
+    plan = [[(d, 20 + 3 * i, [19 + 3 * i]) for i, d in enumerate(decoders)]]
+    for n in portions_p:
+        plan.append([*((d, 1, [0]) for d in decoders), ("p", n, [n - 1])])
+    results = {}
+    for graphs in (False, True):
+        engine = Engine(model_dir, dtype, max_requests=16, max_seq_len=1024, num_pages=40, use_graphs=graphs, poison_on_free=True)
+        results[graphs] = run_steps(engine, plan, prompts)
+        engine.cache.check_integrity()
+        if graphs:
+            replayed = sum(max(0, slot.seen - 1) for slot in engine._bucket_graphs.values() if slot.graph is not None)
+            assert replayed >= 3 and engine._aux_streams is not None, {k: slot.seen for k, slot in engine._bucket_graphs.items()}
+        del engine
+    for i, (a, b) in enumerate(zip(results[False], results[True])):
+        assert a.shape == b.shape and bool(torch.isfinite(b).all()), f"step {i}"
+        scale = float(a.abs().max()) or 1.0
+        assert float((a - b).abs().max()) <= TOL[dtype] * scale, f"step {i}: the graph differs from the kernel-by-kernel run"
+    want_p = plain_logits(model_dir, prompts["p"], dtype)
+    ends = [sum(portions_p[:i + 1]) - 1 for i in range(len(portions_p))]
+    got_p = torch.stack([results[True][1 + i][len(decoders)] for i in range(len(portions_p))])
+    assert rel_err(got_p, want_p[ends]) <= TOL[dtype]
+    for j in (0, 7, 11):                                   # ... and the decoded tokens of some of the decoding requests
+        d = decoders[j]
+        want_d = plain_logits(model_dir, prompts[d], dtype)
+        first = 20 + 3 * j
+        got_d = torch.stack([results[True][1 + i][j] for i in range(len(portions_p))])
+        assert rel_err(got_d, want_d[first:first + len(portions_p)]) <= TOL[dtype]
+
+
 def test_decode_graphs_captured_ahead_and_the_largest_batch_with_a_graph(tmp_path):
     """`cuda_graph_max_bs` as the reference has it: the decode graphs of batch sizes 1, 2, 4, 8, ... up to it can be
     captured before the first request; a larger decode batch runs kernel by kernel; 0 switches graphs off.  Tokens are
