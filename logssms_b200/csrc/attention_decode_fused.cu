@@ -914,11 +914,11 @@ extern "C" int lb_attention_decode_fused(const void* qkv, long row_stride, void*
                 write_kv, scale, key_scale, nullptr, 1, error};
     if (dtype == kBF16 && hd <= 128 && Hq / Hkv <= 16)
     {
-        // Stages of a warp's tile ring: 3 for a small grid (two tiles on their way before the first is used), 2 for a
-        // large one, which then keeps three CTAs per SM.  Measured on 8-layer decode steps at batch 1 / 8 / 64:
-        // 2 stages 0.304 / 0.366 / 0.674 ms, 3 stages 0.305 / 0.361 / 0.676 ms, 4 stages 0.301 / 0.406 / 0.749 ms (their
-        // 147 KB per CTA delay the start of a cluster under the kernel before).
-        const bool small = (long)tokens * Hkv * splits <= 2 * 148;
+        // Stages of a warp's tile ring: 3 for a grid of up to 96 CTAs (two tiles on their way before the first is used:
+        // a lone request), 2 beyond, which keeps three CTAs per SM instead of two.  Measured on 36-layer decode steps
+        // with the tile-copy form at batch 8 / 64: 1.262 / 2.552 ms with 2 stages, 1.283 / 2.606 ms with 3 (batch 1,
+        // 64 CTAs: no difference).
+        const bool small = (long)tokens * Hkv * splits <= 96;
         cudaStream_t st = (cudaStream_t)stream;
         if (hd <= 64) return small ? launch_mma<4, 3>(a, tokens, pages, st) : launch_mma<4, 2>(a, tokens, pages, st);
         return small ? launch_mma<8, 3>(a, tokens, pages, st) : launch_mma<8, 2>(a, tokens, pages, st);
