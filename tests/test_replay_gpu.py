@@ -81,7 +81,7 @@ def replayed(tmp_path_factory, name, dtype):
 
 @pytest.mark.parametrize("scenario", SCENARIOS)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "Bl", "C", "D", "E", "B-sharp", "D-sharp"])
+@pytest.mark.parametrize("name", ["A", "B", "Bl", "C", "D", "E", "B-sharp", "D-sharp", "R5", "R10", "R11-sharp", "R14"])
 def test_replay_matches_plain(tmp_path_factory, name, dtype, scenario):
     got, want, ids_of, trace = replayed(tmp_path_factory, name, dtype)
     checked = 0

@@ -26,7 +26,7 @@ pytestmark = pytest.mark.gpu
 
 LONG = 2200
 SCENARIOS = ("whole", "equal", "tail", "rows40", "rows24")
-PAGE_OF = {"E": 128}                   # one configuration replays through pages of 128 tokens
+PAGE_OF = {"E": 128, "T5": 128}        # two configurations replay through pages of 128 tokens
 
 _cache: dict = {}
 
@@ -78,7 +78,7 @@ def replayed(tmp_path_factory, name, dtype):
 
 @pytest.mark.parametrize("scenario", SCENARIOS)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["D", "D-sharp", "E"])
+@pytest.mark.parametrize("name", ["D", "D-sharp", "E", "T5"])
 def test_long_requests_and_many_rows_match_plain(tmp_path_factory, name, dtype, scenario):
     got, want, ids_of, trace = replayed(tmp_path_factory, name, dtype)
     checked = 0

@@ -101,3 +101,64 @@ def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     assert got.shape == want.shape, (got.shape, want.shape)
     assert torch.isfinite(got).all(), "engine produced non-finite logits"
     return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def random_tiny(seed: int, tensor_core_sizes: bool = False) -> dict:
+    """A small configuration with every size and option drawn at random within what config.json allows: head sizes in
+    steps of 16, any number of heads and groups, widths and vocabularies that are multiples of nothing in particular.
+    `tensor_core_sizes` then redraws the mixers' head sizes, the state size and the chunk length among those that the
+    tcgen05 prompt kernels take."""
+    import random
+    rng = random.Random(seed)
+    kv, group = rng.randint(1, 3), rng.randint(1, 5)
+    head_dim = rng.choice([16, 32, 48, 64, 80, 96, 112, 128])
+    partial = rng.choice([1.0, 1.0, 0.5, 0.75])
+    if int(head_dim * partial) % 2:
+        partial = 1.0
+    scaling = rng.choice([None, None,
+                          {"rope_type": "llama3", "factor": rng.choice([2.0, 8.0]), "low_freq_factor": 1.0,
+                           "high_freq_factor": 4.0, "original_max_position_embeddings": rng.choice([32, 64, 128])},
+                          {"rope_type": "yarn", "factor": rng.choice([2.0, 4.0]),
+                           "original_max_position_embeddings": rng.choice([64, 128])}])
+    groups = rng.randint(1, 3)
+    m_heads = groups * rng.randint(1, 3)
+    m_head = rng.choice([8, 16, 24, 32, 40, 64, 128])
+    mult = lambda: round(rng.uniform(0.5, 1.5), 3)
+    raw = {
+        "architectures": ["FalconH1ForCausalLM"], "model_type": "falcon_h1",
+        "num_hidden_layers": rng.randint(1, 3), "hidden_size": 2 * rng.randint(24, 90),
+        "num_attention_heads": kv * group, "num_key_value_heads": kv, "head_dim": head_dim,
+        "intermediate_size": 2 * rng.randint(20, 130), "vocab_size": rng.randint(100, 700),
+        "rms_norm_eps": rng.choice([1e-4, 1e-5, 1e-6]), "max_position_embeddings": rng.choice([1024, 2048, 4096]),
+        "rope_theta": rng.choice([1e4, 1e5, 1e6, 1e11]), "partial_rotary_factor": partial, "rope_scaling": scaling,
+        "tie_word_embeddings": rng.random() < 0.5,
+        "mamba_d_ssm": m_heads * m_head, "mamba_n_heads": m_heads, "mamba_d_head": m_head,
+        "mamba_d_state": rng.choice([8, 16, 32, 48, 64, 128, 256]), "mamba_n_groups": groups,
+        "mamba_d_conv": rng.choice([2, 3, 4]), "mamba_chunk_size": rng.choice([8, 16, 32, 64, 128, 256]),
+        "mamba_conv_bias": rng.random() < 0.5, "mamba_proj_bias": rng.random() < 0.5,
+        "projectors_bias": rng.random() < 0.5, "mamba_rms_norm": rng.random() < 0.5,
+        "mamba_norm_before_gate": rng.random() < 0.5,
+        "embedding_multiplier": mult(), "lm_head_multiplier": mult(), "attention_in_multiplier": mult(),
+        "attention_out_multiplier": mult(), "key_multiplier": mult(), "ssm_in_multiplier": mult(),
+        "ssm_out_multiplier": mult(), "ssm_multipliers": [mult() for _ in range(5)],
+        "mlp_multipliers": [mult(), mult()],
+        "hidden_act": "silu", "attention_bias": False, "mlp_bias": False,
+    }
+    if tensor_core_sizes:
+        rng = random.Random(1000 + seed)
+        raw["head_dim"] = rng.choice([64, 128])
+        raw["partial_rotary_factor"] = rng.choice([1.0, 0.5])
+        raw["mamba_d_head"] = rng.choice([64, 128])
+        raw["mamba_d_ssm"] = raw["mamba_n_heads"] * raw["mamba_d_head"]
+        raw["mamba_d_state"] = rng.choice([64, 128, 192, 256])
+        raw["mamba_chunk_size"] = rng.choice([128, 256])
+        raw["max_position_embeddings"] = 4096
+    return raw
+
+
+# four of them as configurations of the replay tests (heads of 96 / 112 / 128 / 64, groups of 3 / 1 / 5 / 5 query heads,
+# SSM heads of 128 / 8 / 16 / 128, state sizes 48 / 256 / 256 / 32, conv kernels of 2 to 4 taps)
+TINY.update({f"R{seed}": random_tiny(seed) for seed in (5, 10, 11, 14)})
+# and one for the long replays: 9 query heads of 128 on 3 KV heads with half of each head rotated, 4 SSM heads of 128
+# with a state of 192, chunks of 256 (run as 128), a conv of 3 taps
+TINY["T5"] = random_tiny(5, tensor_core_sizes=True)
