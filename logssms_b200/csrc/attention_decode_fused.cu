@@ -949,7 +949,7 @@ extern "C" int lb_attention_decode_listed(const void* q, void* k_cache, void* v_
     FusedArgs a{q, (long)Hq * hd, k_cache, v_cache, out, block_table, bt_stride, token_req, positions, nullptr,
                 nullptr, 1, 0, part_o, part_ml, counters, Hq, Hkv, hd, page_size, window, splits, 1,
                 0, scale, 1.f, token_list, 0, error};
-    const bool small = (long)count * Hkv * splits <= 2 * 148;
+    const bool small = (long)count * Hkv * splits <= 96;
     cudaStream_t st = (cudaStream_t)stream;
     if (hd <= 64) return small ? launch_mma<4, 3>(a, count, pages, st) : launch_mma<4, 2>(a, count, pages, st);
     return small ? launch_mma<8, 3>(a, count, pages, st) : launch_mma<8, 2>(a, count, pages, st);
