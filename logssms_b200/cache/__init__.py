@@ -1,4 +1,4 @@
-from .manager import CacheManager, CacheNeeds, KVNeed, PageGroup, RequestCache, StateNeed
+from .manager import CacheManager, CacheNeeds, KVNeed, PagedNeed, PagedTensor, PageGroup, RequestCache, StateNeed
 from .pools import FreeList, OutOfPages
 
-__all__ = ["CacheManager", "CacheNeeds", "KVNeed", "PageGroup", "RequestCache", "StateNeed", "FreeList", "OutOfPages"]
+__all__ = ["CacheManager", "CacheNeeds", "KVNeed", "PagedNeed", "PagedTensor", "PageGroup", "RequestCache", "StateNeed", "FreeList", "OutOfPages"]

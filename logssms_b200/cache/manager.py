@@ -1,10 +1,11 @@
 """The cache manager: paged keys/values per layer group, state slots per request.
 
 What a model needs is collected from its mixers (`CacheNeeds` per cache layer):
-  * `KVNeed`: keys and values per token, in pages.  Cache layers whose needs are
-    equal (heads, head size, window) form one *group*; each group has its own
-    page pool, its own storage and, per request, its own block table.  A group
-    with a window gives pages back as soon as the window has passed them.
+  * `PagedNeed`: tensors of a fixed shape per token, in pages (`KVNeed(heads, head size, window)` writes the
+    common one: keys and values of one shape; a cache of latents has one tensor, keys and values of different
+    head sizes two of different shapes).  Cache layers whose needs are equal form one *group*; each group has its
+    own page pool, its own storage and, per request, its own block table.  A group with a window gives pages back
+    as soon as the window has passed them.
   * `StateNeed`: a tensor of fixed size per request (a conv window, an SSM
     state).  One slot per live request; the slot index is the request's row.
 
@@ -30,10 +31,23 @@ from .pools import FreeList, OutOfPages
 
 
 @dataclass(frozen=True)
-class KVNeed:
-    num_kv_heads: int
-    head_dim: int
+class PagedTensor:
+    name: str
+    shape: tuple[int, ...]                # per token
+    dtype: torch.dtype | None = None      # None: the engine's activation dtype
+
+
+@dataclass(frozen=True)
+class PagedNeed:
+    """What a cache layer keeps per token, in pages: named tensors; `window`: only the last so many tokens are read."""
+    tensors: tuple[PagedTensor, ...]
     window: int | None = None
+
+
+def KVNeed(num_kv_heads: int, head_dim: int, window: int | None = None, value_head_dim: int | None = None) -> PagedNeed:
+    """Keys "k" and values "v" of [num_kv_heads, head_dim] per token (values of another head size if given)."""
+    return PagedNeed((PagedTensor("k", (num_kv_heads, head_dim)),
+                      PagedTensor("v", (num_kv_heads, value_head_dim or head_dim))), window)
 
 
 @dataclass(frozen=True)
@@ -45,35 +59,39 @@ class StateNeed:
 
 @dataclass(frozen=True)
 class CacheNeeds:
-    kv: KVNeed | None = None
+    kv: PagedNeed | None = None           # the layer's paged tensors (keys and values, mostly)
     states: tuple[StateNeed, ...] = ()
 
 
 class PageGroup:
-    """Cache layers with equal key/value needs: one page pool, one storage, one block table per request."""
+    """Cache layers with equal paged needs: one page pool, one storage, one block table per request."""
 
-    def __init__(self, need: KVNeed, layers: list[int], num_pages: int, page_size: int, max_requests: int,
+    def __init__(self, need: PagedNeed, layers: list[int], num_pages: int, page_size: int, max_requests: int,
                  max_pages_per_request: int, dtype, device):
         self.need = need
         self.layers = layers
         self.page_size = page_size
         self.pool = FreeList(num_pages, "page")
         self.layer_index = {layer: i for i, layer in enumerate(layers)}
-        # [2 (k, v), layers, pages, page_size, kv_heads, head_dim]
+        # per tensor of the need: [layers, pages, page_size, *shape per token]
         # one page more than the pool hands out: the dummy page (index `num_pages`), where the dummy requests of a
         # padded step keep their keys and values; its block-table row is the last one
-        self.storage = torch.zeros((2, len(layers), num_pages + 1, page_size, need.num_kv_heads, need.head_dim),
-                                   dtype=dtype, device=device)
+        self.storage = {t.name: torch.zeros((len(layers), num_pages + 1, page_size, *t.shape), dtype=t.dtype or dtype,
+                                            device=device) for t in need.tensors}
         self.block_table = np.full((max_requests + 1, max_pages_per_request), -1, dtype=np.int32)
         self.block_table[max_requests, :] = num_pages
         self.first_page = np.zeros(max_requests, dtype=np.int64)     # pages below are given back (window)
         self.num_pages_of = np.zeros(max_requests, dtype=np.int64)    # logical pages handed out so far
 
+    def tensor(self, name: str, layer: int) -> torch.Tensor:
+        """[pages, page_size, *shape per token] of one cache layer."""
+        return self.storage[name][self.layer_index[layer]]
+
     def k_cache(self, layer: int) -> torch.Tensor:
-        return self.storage[0, self.layer_index[layer]]
+        return self.tensor("k", layer)
 
     def v_cache(self, layer: int) -> torch.Tensor:
-        return self.storage[1, self.layer_index[layer]]
+        return self.tensor("v", layer)
 
     def pages_for(self, length: int) -> int:
         return -(-length // self.page_size)
@@ -112,7 +130,7 @@ class CacheManager:
         # (`engine.plan.Bucket`) lets its dummy requests read and write there.
         self.dummy_row = max_requests
 
-        by_need: dict[KVNeed, list[int]] = {}
+        by_need: dict[PagedNeed, list[int]] = {}
         for layer, need in enumerate(needs):
             if need.kv is not None:
                 by_need.setdefault(need.kv, []).append(layer)
@@ -131,8 +149,8 @@ class CacheManager:
     # ------------------------------------------------------------------ sizes
     @staticmethod
     def bytes_per_page(needs: list[CacheNeeds], page_size: int, dtype) -> int:
-        item = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * page_size * n.kv.num_kv_heads * n.kv.head_dim * item for n in needs if n.kv is not None)
+        size = lambda t: int(np.prod(t.shape)) * torch.empty((), dtype=t.dtype or dtype).element_size()
+        return sum(page_size * size(t) for n in needs if n.kv is not None for t in n.kv.tensors)
 
     @staticmethod
     def bytes_per_request_state(needs: list[CacheNeeds], dtype) -> int:
@@ -254,7 +272,8 @@ class CacheManager:
         g = self.groups[gi]
         if self.poison_on_free and pages:
             idx = torch.tensor(pages, device=self.device, dtype=torch.long)
-            g.storage[:, :, idx] = float("nan")
+            for t in g.storage.values():
+                t[:, idx] = float("nan") if t.is_floating_point() else -1
         g.pool.free(pages)
 
     # ------------------------------------------------------------------ end of life

@@ -4,7 +4,7 @@ import random
 import pytest
 import torch
 
-from logssms_b200.cache import CacheManager, CacheNeeds, FreeList, KVNeed, OutOfPages, StateNeed
+from logssms_b200.cache import CacheManager, CacheNeeds, FreeList, KVNeed, OutOfPages, PagedNeed, PagedTensor, StateNeed
 
 FULL = KVNeed(2, 16)
 WINDOW = KVNeed(2, 16, window=40)
@@ -35,7 +35,7 @@ def test_groups_are_formed_by_need():
     m = manager(needs)
     assert len(m.groups) == 2
     assert m.groups[0].layers == [0, 2] and m.groups[1].layers == [1]
-    assert m.groups[0].storage.shape == (2, 2, 13, 16, 2, 16)        # 12 pages and the dummy page
+    assert {n: tuple(t.shape) for n, t in m.groups[0].storage.items()} == {"k": (2, 13, 16, 2, 16), "v": (2, 13, 16, 2, 16)}   # 12 pages and the dummy page
     assert m.states[2]["s"].shape == (5, 3, 2) and m.states[3]["only"].dtype == torch.float32
     k, v, gi = m.kv(2)
     assert gi == 0 and k.shape == (13, 16, 2, 16)
@@ -181,7 +181,7 @@ def test_poison_marks_freed_memory():
     m.extend(a, 5)
     page = int(m.groups[0].block_table[a.row, 0])
     m.release(a)
-    assert torch.isnan(m.groups[0].storage[:, :, page]).all() and torch.isnan(m.states[0]["s"][a.row]).all()
+    assert all(torch.isnan(t[:, page]).all() for t in m.groups[0].storage.values()) and torch.isnan(m.states[0]["s"][a.row]).all()
 
 
 def test_check_room_refuses_a_step_whose_third_request_runs_dry_and_changes_nothing():
@@ -233,3 +233,29 @@ def test_check_room_agrees_with_what_extend_does():
                 break
         assert fits != ran_dry, (trial, fits, ran_dry)
         m.check_integrity()
+
+
+def test_paged_needs_other_than_equal_keys_and_values():
+    """A cache of latents (one tensor per token, of its own dtype), keys and values of different head sizes, and the
+    usual pair: three groups with their own pools, storage shapes and block tables, paged alike."""
+    latent = PagedNeed((PagedTensor("latent", (40,), torch.float32), PagedTensor("rope_key", (8,))), window=None)
+    uneven = KVNeed(2, 24, value_head_dim=16)
+    needs = [CacheNeeds(kv=latent), CacheNeeds(kv=uneven), CacheNeeds(kv=FULL), CacheNeeds(kv=latent)]
+    m = CacheManager(needs, page_size=16, num_pages=6, max_requests=2, max_seq_len=64, dtype=torch.bfloat16, device="cpu",
+                     poison_on_free=True)
+    assert len(m.groups) == 3 and m.groups[0].layers == [0, 3]
+    g = m.groups[0]
+    assert g.tensor("latent", 3).shape == (7, 16, 40) and g.tensor("latent", 3).dtype == torch.float32
+    assert g.tensor("rope_key", 0).shape == (7, 16, 8) and g.tensor("rope_key", 0).dtype == torch.bfloat16
+    k, v, gi = m.kv(1)
+    assert gi == 1 and k.shape == (7, 16, 2, 24) and v.shape == (7, 16, 2, 16)
+    item = 2
+    assert CacheManager.bytes_per_page(needs, 16, torch.bfloat16) == 16 * (2 * (40 * 4 + 8 * item) + (48 + 32) * item + 64 * item)
+    a = m.admit()
+    m.extend(a, 40)
+    assert all(int(gr.num_pages_of[a.row]) == 3 for gr in m.groups)
+    pages = [int(p) for p in g.block_table[a.row, :3]]
+    g.tensor("latent", 0)[pages[0]] = 1.0
+    m.release(a)
+    m.check_integrity()
+    assert torch.isnan(g.tensor("latent", 0)[pages[0]]).all() and torch.isnan(g.tensor("rope_key", 3)[pages[2]]).all()
