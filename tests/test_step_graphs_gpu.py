@@ -4,7 +4,7 @@ the ones the graph was captured with."""
 import pytest
 import torch
 
-from tiny import TINY, TOL, make_model_dir
+from tiny import TINY, TOL, make_model_dir, plain_logits
 
 pytestmark = pytest.mark.gpu
 
@@ -250,12 +250,16 @@ def test_a_decode_batch_without_a_graph_rides_in_the_graph_of_a_larger_one(tmp_p
     def same(got, ref):
         # float32: the very tokens.  bfloat16: the key ranges of the attention follow the batch size of the graph, so
         # sums round differently and a greedy choice between near-equal logits of a random model may flip, after
-        # which that request goes its own way: every request's first token (from its prompt's step) must agree, and
-        # half of all tokens; the float32 run is the one that proves the mechanism
+        # which that request goes its own way: every token must be the plain implementation's choice after the
+        # request's own tokens so far, or within the tolerance of it; the float32 run is the one that proves the mechanism
         if dtype == "float32":
             return got == ref
-        flat = [(a, b) for g, r in zip(got, ref) for a, b in zip(g, r)]
-        return all(g[:1] == r[:1] for g, r in zip(got, ref)) and sum(a == b for a, b in flat) >= 0.5 * len(flat)
+        for prompt, toks in zip(prompts, got):
+            logits = plain_logits(model_dir, prompt + toks[:-1], dtype)[len(prompt) - 1:]
+            for tok, row in zip(toks, logits):
+                if float(row.max() - row[tok]) / float(row.abs().max()) > TOL[dtype]:
+                    return False
+        return len(got) == len(ref) and all(len(g) == len(r) for g, r in zip(got, ref))
     llm = LLM(model_dir, dtype, max_running_requests=8, max_seq_len_override=128, num_pages=12, cuda_graph_max_bs=8)
     eng = llm.engine
     assert sorted(n for n, g in eng._graphs.items() if g.graph is not None) == [1, 2, 4, 8]
