@@ -54,6 +54,56 @@ def test_greedy_generation_of_several_prompts_through_a_small_pool(tmp_path, nam
     assert [o.token_ids for o in again] == [o.token_ids for o in outs[:2]]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("policy", [("prefill-first", None), ("mixed", 8)])
+def test_the_other_scheduling_policies_drive_the_real_engine(tmp_path, policy, dtype):
+    """`prefill-first` (a step is prompt portions or decoded tokens, never both) and a cap on the prompt tokens of a step
+    that also decodes, through the real engine and a small pool: the steps have the promised shapes and every token
+    is the plain implementation's choice."""
+    from logssms_b200.engine import LLM
+    from logssms_b200.sampling import SamplingParams
+    name, cap = policy
+    raw = TINY["B"]
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=27, dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, raw["vocab_size"], (n,), generator=g).tolist() for n in (40, 3, 61, 17, 29)]
+    new = 10
+    llm = LLM(model_dir, dtype, max_running_requests=3, max_seq_len_override=128, num_pages=4, max_prefill_tokens=24,
+              poison_on_free=True, scheduling_policy=name, mixed_prefill_tokens=cap)
+    steps = []
+    inner = llm.engine.step
+
+    def recording(entries, device_tokens=None):
+        steps.append([len(e.tokens) if e.tokens is not None else 1 for e in entries])
+        return inner(entries, device_tokens)
+    llm.engine.step = recording
+    planned = llm.engine.run_prepared
+
+    def recording_planned(handle, token_ids):     # a decode step that was planned ahead: single tokens only
+        steps.append([1] * len(token_ids))
+        return planned(handle, token_ids)
+    llm.engine.run_prepared = recording_planned
+    llm.scheduler.overlap = False                  # every step with its ids through the host: all of them are recorded
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True))
+    assert [o.finish_reason for o in outs] == ["length"] * len(prompts) and all(len(o.token_ids) == new for o in outs)
+    for p, o in zip(prompts, outs):
+        check_greedy(model_dir, dtype, p, o.token_ids)
+    portions = [[n for n in st if n > 1] for st in steps]
+    singles = [sum(n == 1 for n in st) for st in steps]
+    assert any(portions) and any(singles)
+    if name == "prefill-first":
+        # a 1-token rest of a prompt looks like a decoded token: steps with portions hold at most such rests beside them
+        assert all(not (pt and sg) or sum(pt) + sg <= 24 for pt, sg in zip(portions, singles))
+        assert all(sum(st) <= 24 for st in steps)
+        mixed_steps = sum(1 for pt, sg in zip(portions, singles) if pt and sg)
+        assert mixed_steps <= len(prompts)          # only where a prompt's last portion is a single token
+    else:
+        assert all(sum(pt) <= cap for pt, sg in zip(portions, singles) if sg and pt), steps
+        assert any(sum(pt) > cap for pt, sg in zip(portions, singles) if not sg), steps
+    llm.engine.cache.check_integrity()
+    assert not llm.engine.cache.live
+
+
 def test_eos_and_max_tokens_end_requests(tmp_path):
     from logssms_b200.engine import LLM
     from logssms_b200.sampling import SamplingParams
