@@ -304,19 +304,31 @@ def _counters_for(device: torch.device, n: int) -> torch.Tensor:
     return t
 
 
-def decode_step_splits(num_tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
-    """Most key ranges per token for `attention_decode_step`: about two CTAs per SM, never more ranges than
-    256-key pieces of the longest context (the kernel itself uses fewer ranges for a short context)."""
+def decode_step_splits(num_tokens: int, num_heads: int, num_kv_heads: int, max_context: int, listed: bool = False,
+                       head_dim: int = 64) -> int:
+    """Most key ranges per token for `attention_decode_step` (about one CTA per SM with heads of up to 64, about two
+    with larger ones) or, `listed`, for `attention_decode_listed` (about two), never more ranges than 256-key pieces of
+    the longest context (the kernel itself uses fewer ranges for a short context)."""
     G = num_heads // num_kv_heads
     tile = 8 if G >= 8 else (4 if G > 2 else G)
     items = max(1, num_tokens * num_kv_heads * (-(-G // tile)))
-    splits = max(1, min(_STEP_TARGET_CTAS // items, -(-max_context // 256), 256))
+    target = _WIDE_TARGET_CTAS if (listed or head_dim > 64) else _STEP_TARGET_CTAS
+    splits = max(1, min(target // items, -(-max_context // 256), 256))
     # up to 8 ranges are the CTAs of one cluster and merge through distributed shared memory (about 2 us off the
     # kernel); with a dozen (token, head) items that many ranges fill the GPU, so more would only cost that path
     return min(splits, 8) if items >= 12 else splits
 
 
-_STEP_TARGET_CTAS = 296         # two CTAs per SM (three fit): measured best at 1, 8 and 64 tokens of 2,048 and 8,000 keys
+# Heads of up to 64: about one CTA per SM.  Up to 9 tokens the 256-key pieces of the context set the number of ranges,
+# not this; from 10 tokens on fewer, longer ranges win, the more so beside the state update that shares the SMs:
+# 36-layer decode steps over 2,048-key contexts (head 64) with 296 / 160 took 1.66 / 1.62 ms at batch 16, 1.92 / 1.90 ms
+# at 32, 2.56 / 2.39 ms at 64 (444: 2.68 ms).
+_STEP_TARGET_CTAS = 160
+# Heads of 128 (a CTA's chain per key is twice as long), and the listed rows of a step that also holds a prompt portion
+# (the last link of the attention branch, with little beside them): shorter ranges win.  16 layers of 1.5B-Deep size
+# (head 128) with 296 / 160: 1.38 / 1.42 ms at batch 24, 1.52 / 1.62 ms at 32; the 1.5B-Deep serving run 2,220 / 1,970
+# generated tok/s; 64 tokens of 4,096 keys at 7B size (one range either way): no difference.
+_WIDE_TARGET_CTAS = 296
 
 
 def attention_decode_step(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,

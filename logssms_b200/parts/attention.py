@@ -65,7 +65,8 @@ class Attention(Part):
         k_cache, v_cache, group = ctx.cache.kv(cache_layer)
         if ctx.max_len == 1:
             # a decode step: rotation, cache store, attention over the pages and the merge of key ranges in one launch
-            splits = ctx.attention_splits or K.decode_step_splits(T, s.num_heads, s.num_kv_heads, ctx.max_context)
+            splits = ctx.attention_splits or K.decode_step_splits(T, s.num_heads, s.num_kv_heads, ctx.max_context,
+                                                                  head_dim=s.head_dim)
             o = K.attention_decode_step(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions,
                                         ctx.slot_mappings[group], self.position.table, k_cache, v_cache,
                                         ctx.block_tables[group], ctx.token_req, self.scale, s.key_scale, s.window or 0,
@@ -94,7 +95,8 @@ class Attention(Part):
             token_list, n_short = ctx.short_portion_tokens()
         if n_short > 0 and token_list is not None and K.attention_decode_listed_ok(q, k_cache):
             # decoded tokens and short portions beside prompt portions: the decode step's kernel, on the listed rows
-            splits = ctx.attention_splits or K.decode_step_splits(n_short, s.num_heads, s.num_kv_heads, ctx.max_context)
+            splits = ctx.attention_splits or K.decode_step_splits(n_short, s.num_heads, s.num_kv_heads, ctx.max_context,
+                                                                  listed=True)
             o = K.attention_decode_listed(q, k_cache, v_cache, tables, ctx.token_req, ctx.positions, token_list, n_short,
                                           self.scale, window, splits=splits, out=o)
         elif n_short > 0:
