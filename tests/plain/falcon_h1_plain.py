@@ -9,7 +9,10 @@ It rests on the formulas of the reference (dakingffo/LogSSMs); every function
 cites the file:line it was written from.  Where the reference's own kernels can
 run on the CPU (its Triton kernels under the Triton interpreter), the functions
 here were compared with them once: see tests/golden/make_golden.py and the
-stored outputs next to it.
+stored outputs next to it.  The whole model was compared once with the
+reference's own bfloat16 engine on a GPU, on tiny models with real weights:
+tests/golden/make_reference_model_golden.py and the logits stored next to it
+(tests/test_plain.py checks both).
 
 Two knobs, both about arithmetic only:
   * `compute`: the dtype all maths runs in (float64 for an oracle of the 32-bit

@@ -3,10 +3,17 @@
 `tests/golden/reference_blocks.safetensors` holds what the parts of dakingffo/LogSSMs that run on a
 CPU produced for the seeded inputs of `tests/golden/make_golden.py` (its Triton kernels under the
 Triton interpreter: both norms, both gates, the packed conv; its rotary tables; the recurrence oracle
-of its kernel tests).  The functions of tests/plain must reproduce them.  The rest of the plain
-implementation (attention, the whole model) rests on the reference's formulas; here it is checked for
-what must hold whatever the weights are: causality, and the cache-free recomputation being
-independent of what follows a position.
+of its kernel tests).  The functions of tests/plain must reproduce them.
+
+`tests/golden/reference_model_*.safetensors` hold whole-model logits of the unmodified reference, run on a GPU
+through its own scheduler and engine on tiny Falcon-H1 models with real (seeded random) weights and every
+multiplier off its default (`tests/golden/make_reference_model_golden.py`): the last prompt position and the
+decoded tokens of three prompts each.  The plain implementation, given the same weights, must give the same
+logits: this pins what no part alone shows (where each multiplier sits, the key multiplier before the rotation,
+the feed-forward's output joining the residual in the next norm, attention over the cache, the chunked scan).
+
+Beyond that the plain implementation is checked for what must hold whatever the weights are: causality, and the
+cache-free recomputation being independent of what follows a position.
 """
 import os
 import sys
@@ -19,7 +26,7 @@ sys.path.insert(0, os.path.join(HERE, "golden"))
 
 import make_golden                                        # noqa: E402
 from plain import falcon_h1_plain as P                    # noqa: E402
-from tiny import TINY, make_model_dir, plain_logits       # noqa: E402
+from tiny import TINY, TOL, make_model_dir, plain_logits, rel_err       # noqa: E402
 
 # The Triton interpreter converts float32 to bfloat16 by dropping the low bits where a GPU rounds to
 # nearest, so the stored bfloat16 outputs sit up to one unit in the last place off per conversion; the
@@ -134,3 +141,26 @@ def test_whole_model_logits_do_not_depend_on_later_tokens(tmp_path, name):
     # bfloat16 rounding points move the result a little, not a lot
     rounded = plain_logits(model_dir, ids, "bfloat16")
     assert float((rounded - whole).abs().max() / whole.abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("name", ["gate", "gated_norm"])
+def test_whole_model_logits_match_the_reference_engine(tmp_path, name):
+    """The reference's own bfloat16 engine on a GPU against the plain implementation on the same weights."""
+    import json
+    from safetensors import safe_open
+    with safe_open(os.path.join(HERE, "golden", f"reference_model_{name}.safetensors"), "pt") as f:
+        meta = f.metadata()
+        data = {k: f.get_tensor(k) for k in f.keys()}
+    raw, seed = json.loads(meta["config"]), int(meta["seed"])
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=seed, dtype=torch.bfloat16)
+    requests = sorted(int(k.split("_")[1]) for k in data if k.startswith("prompt_"))
+    assert len(requests) == 3
+    for i in requests:
+        prompt, tokens, want = data[f"prompt_{i}"].tolist(), data[f"tokens_{i}"].tolist(), data[f"logits_{i}"]
+        got = plain_logits(model_dir, prompt + tokens[:-1], "bfloat16")[len(prompt) - 1:]
+        assert got.shape == want.shape
+        err = rel_err(got, want)
+        assert err <= TOL["bfloat16"], f"{name}, prompt of {len(prompt)} tokens: error {err:.3g}"
+        # the reference's greedy choice is the plain model's, or within the tolerance of it
+        for row, tok in zip(got, tokens):
+            assert float(row.max() - row[tok]) / float(row.abs().max()) <= TOL["bfloat16"]
