@@ -294,3 +294,31 @@ def test_profile_times_every_kernel_by_class_and_changes_no_token(tmp_path):
     # the engine made next switches the profiler off again
     LLM(model_dir, "bfloat16", max_running_requests=2, max_seq_len_override=256, num_pages=8)
     assert not PROFILER.enabled and not PROFILER.nvtx
+
+
+@pytest.mark.parametrize("name", ["gate", "gated_norm"])
+def test_engine_logits_match_the_reference_engines_golden_logits(tmp_path, name):
+    """The stored whole-model logits of the unmodified reference (tests/golden/make_reference_model_golden.py): this
+    engine on the same weights, the prompt in one step and the reference's own tokens decoded one by one."""
+    import json
+    import os
+    from safetensors import safe_open
+    from logssms_b200.engine import Engine, StepEntry
+    from tiny import rel_err
+    here = os.path.dirname(os.path.abspath(__file__))
+    with safe_open(os.path.join(here, "golden", f"reference_model_{name}.safetensors"), "pt") as f:
+        meta = f.metadata()
+        data = {k: f.get_tensor(k) for k in f.keys()}
+    raw, seed = json.loads(meta["config"]), int(meta["seed"])
+    model_dir = make_model_dir(tmp_path / "m", raw, seed=seed, dtype=torch.bfloat16)
+    engine = Engine(model_dir, "bfloat16", max_requests=2, max_seq_len=512, num_pages=8, poison_on_free=True)
+    for i in range(3):
+        prompt, tokens, want = data[f"prompt_{i}"].tolist(), data[f"tokens_{i}"].tolist(), data[f"logits_{i}"]
+        r = engine.new_request()
+        rows = [engine.step([StepEntry(r, prompt, [len(prompt) - 1])]).float().cpu()]
+        for tok in tokens[:-1]:
+            rows.append(engine.step([StepEntry(r, [tok], [0])]).float().cpu())
+        engine.release(r)
+        err = rel_err(torch.cat(rows), want)
+        assert err <= TOL["bfloat16"], f"{name}, prompt of {len(prompt)} tokens: error {err:.3g}"
+    engine.cache.check_integrity()
