@@ -10,7 +10,7 @@ The reference runs as it does in the benchmark: its own `Scheduler` and `Engine`
 and `overlap_loop` (python/logssms/scheduler/scheduler.py), real weights read by its own loader
 (python/logssms/models/weight.py), bfloat16, default cache type, attention backend and graphs.  One request at a
 time, greedy: every call of the engine's sampling step then holds one row of logits, the last prompt position
-first and one decoded token per call after it.  Only that one bound method of the engine OBJECT is wrapped here to
+first (after one call per earlier portion of a prompt that is cut) and one decoded token per call after it.  Only that one bound method of the engine OBJECT is wrapped here to
 copy the logits out; no file of the reference is changed.
 """
 from __future__ import annotations
@@ -45,8 +45,11 @@ CONFIGS = {
     "gated_norm": {**_BASE, "mamba_rms_norm": True, "mamba_n_groups": 2, "tie_word_embeddings": False,
                    "num_hidden_layers": 3, "mamba_proj_bias": True, "projectors_bias": True},
 }
-SEEDS = {"gate": 71, "gated_norm": 72}
-PROMPT_LENGTHS = (150, 37, 300)         # the first and the last cross a 128-token chunk of the SSD form
+# the same model again for long prompts that the reference cuts into portions of 512 tokens
+CONFIGS["long"] = {**_BASE, "max_position_embeddings": 4096, "rope_theta": 1e4, "num_key_value_heads": 1}
+SEEDS = {"gate": 71, "gated_norm": 72, "long": 73}
+# prompt lengths and the reference's `max_prefill_tokens`; 150 and 300 cross a 128-token chunk of the SSD form
+RUNS = {"gate": ((150, 37, 300), 1024), "gated_norm": ((150, 37, 300), 1024), "long": ((1100, 2200, 700), 512)}
 NEW_TOKENS = 8
 
 
@@ -86,7 +89,8 @@ def run_reference(name: str) -> dict:
             return out
 
     config = SchedulerConfig(model_path=tmp, tp_info=DistributedInfo(0, 1), dtype=torch.bfloat16, max_running_req=4,
-                             use_dummy_weight=False, max_seq_len_override=1024, max_prefill_tokens=1024)
+                             use_dummy_weight=False, max_seq_len_override=4096 if name == "long" else 1024,
+                             max_prefill_tokens=RUNS[name][1])
     sched = InProcessScheduler(config)
     seen: list = []
     inner = sched.engine._sample_batch
@@ -100,7 +104,7 @@ def run_reference(name: str) -> dict:
     out: dict = {}
     state = None
     with torch.inference_mode():
-        for i, n in enumerate(PROMPT_LENGTHS):
+        for i, n in enumerate(RUNS[name][0]):
             ids = rng.integers(0, raw["vocab_size"], n).astype(np.int32)
             seen.clear()
             first = len(sched.results)
@@ -118,7 +122,10 @@ def run_reference(name: str) -> dict:
             for m in sched.results[first:]:
                 if m.uid == i:
                     tokens += m.next_token if isinstance(m.next_token, list) else [m.next_token]
-            rows = [t for t in seen if t.shape[0] == 1][:NEW_TOKENS]
+            # a prompt that is cut into portions passes the sampling step once per portion: the rows before the
+            # last portion's are not this request's tokens (the check below holds the alignment)
+            earlier = -(-n // RUNS[name][1]) - 1
+            rows = [t for t in seen if t.shape[0] == 1][earlier:earlier + NEW_TOKENS]
             if len(tokens) != NEW_TOKENS or len(rows) != NEW_TOKENS:
                 raise RuntimeError(f"{name}: request {i}: {len(tokens)} tokens, {len(rows)} rows of logits")
             logits = torch.cat(rows)

@@ -296,7 +296,7 @@ def test_profile_times_every_kernel_by_class_and_changes_no_token(tmp_path):
     assert not PROFILER.enabled and not PROFILER.nvtx
 
 
-@pytest.mark.parametrize("name", ["gate", "gated_norm"])
+@pytest.mark.parametrize("name", ["gate", "gated_norm", "long"])
 def test_engine_logits_match_the_reference_engines_golden_logits(tmp_path, name):
     """The stored whole-model logits of the unmodified reference (tests/golden/make_reference_model_golden.py): this
     engine on the same weights, the prompt in one step and the reference's own tokens decoded one by one."""
@@ -311,7 +311,7 @@ def test_engine_logits_match_the_reference_engines_golden_logits(tmp_path, name)
         data = {k: f.get_tensor(k) for k in f.keys()}
     raw, seed = json.loads(meta["config"]), int(meta["seed"])
     model_dir = make_model_dir(tmp_path / "m", raw, seed=seed, dtype=torch.bfloat16)
-    engine = Engine(model_dir, "bfloat16", max_requests=2, max_seq_len=512, num_pages=8, poison_on_free=True)
+    engine = Engine(model_dir, "bfloat16", max_requests=2, max_seq_len=2560, num_pages=40, poison_on_free=True)
     for i in range(3):
         prompt, tokens, want = data[f"prompt_{i}"].tolist(), data[f"tokens_{i}"].tolist(), data[f"logits_{i}"]
         r = engine.new_request()
