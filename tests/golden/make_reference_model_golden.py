@@ -47,9 +47,17 @@ CONFIGS = {
 }
 # the same model again for long prompts that the reference cuts into portions of 512 tokens
 CONFIGS["long"] = {**_BASE, "max_position_embeddings": 4096, "rope_theta": 1e4, "num_key_value_heads": 1}
-SEEDS = {"gate": 71, "gated_norm": 72, "long": 73}
+# heads of 128 in both mixers, three query heads per KV head, a state of 256, the norm before the gate, llama3
+# frequency scaling
+CONFIGS["wide"] = {**_BASE, "hidden_size": 384, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128,
+                   "intermediate_size": 512, "mamba_d_ssm": 384, "mamba_n_heads": 3, "mamba_d_head": 128,
+                   "mamba_d_state": 256, "mamba_rms_norm": True, "mamba_norm_before_gate": True, "rope_theta": 1e5,
+                   "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                    "original_max_position_embeddings": 64}}
+SEEDS = {"gate": 71, "gated_norm": 72, "long": 73, "wide": 74}
 # prompt lengths and the reference's `max_prefill_tokens`; 150 and 300 cross a 128-token chunk of the SSD form
-RUNS = {"gate": ((150, 37, 300), 1024), "gated_norm": ((150, 37, 300), 1024), "long": ((1100, 2200, 700), 512)}
+RUNS = {"gate": ((150, 37, 300), 1024), "gated_norm": ((150, 37, 300), 1024), "long": ((1100, 2200, 700), 512),
+        "wide": ((150, 37, 300), 1024)}
 NEW_TOKENS = 8
 
 

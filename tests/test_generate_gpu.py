@@ -296,7 +296,7 @@ def test_profile_times_every_kernel_by_class_and_changes_no_token(tmp_path):
     assert not PROFILER.enabled and not PROFILER.nvtx
 
 
-@pytest.mark.parametrize("name", ["gate", "gated_norm", "long"])
+@pytest.mark.parametrize("name", ["gate", "gated_norm", "long", "wide"])
 def test_engine_logits_match_the_reference_engines_golden_logits(tmp_path, name):
     """The stored whole-model logits of the unmodified reference (tests/golden/make_reference_model_golden.py): this
     engine on the same weights, the prompt in one step and the reference's own tokens decoded one by one."""

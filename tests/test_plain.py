@@ -144,7 +144,7 @@ def test_whole_model_logits_do_not_depend_on_later_tokens(tmp_path, name):
     assert float((rounded - whole).abs().max() / whole.abs().max()) < 0.05
 
 
-@pytest.mark.parametrize("name", ["gate", "gated_norm", "long"])
+@pytest.mark.parametrize("name", ["gate", "gated_norm", "long", "wide"])
 def test_whole_model_logits_match_the_reference_engine(tmp_path, name):
     """The reference's own bfloat16 engine on a GPU against the plain implementation on the same weights."""
     import json
