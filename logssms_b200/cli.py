@@ -44,6 +44,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--cuda-graph-max-bs", "--graph", type=int, default=None, dest="cuda_graph_max_bs",
                    help="largest decode batch that gets a CUDA graph; the batch sizes 1, 2, 4, 8, 16, ... up to it are "
                         "captured at start.  0 disables all graphs; default: every batch size, captured when it comes twice")
+    p.add_argument("--ssm-state-dtype", choices=["float32", "activation"], default="float32",
+                   help="dtype in which recurrent states are kept between steps: float32, or the model's dtype (as the "
+                        "reference keeps them: half the bytes of a decode step's state update, one rounding per step)")
     p.add_argument("--profile", default=None, metavar="FILE",
                    help="time every kernel with CUDA events and write the sums per kernel class to FILE (JSON) at exit; "
                         "such a run launches every step kernel by kernel")
@@ -185,7 +188,7 @@ def main(argv=None) -> int:
               memory_ratio=args.memory_ratio, max_prefill_tokens=args.max_prefill_tokens, seed=args.seed,
               scheduling_policy=args.scheduling_policy, mixed_prefill_tokens=args.mixed_prefill_tokens,
               use_graphs=not args.no_graph, profile=args.profile is not None, nvtx=args.nvtx,
-              cuda_graph_max_bs=args.cuda_graph_max_bs)
+              cuda_graph_max_bs=args.cuda_graph_max_bs, ssm_state_dtype=args.ssm_state_dtype)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             ignore_eos=args.ignore_eos, max_tokens=args.max_tokens)
     def write_profile():

@@ -26,7 +26,7 @@ struct SsdArgs {
     const bf16* conv; int C;                     // [tokens, C]: x | B | C after the conv
     const bf16* dt; long dt_stride;              // [tokens, nh] view
     const float* A_log; const float* dt_bias; const float* D;
-    float* state;                                // [slots, nh, P, N]
+    void* state;                                 // [slots, nh, P, N]: float32, or bfloat16 with `state_bf16`
     bf16* y;                                     // [tokens, nh * P]
     const int* cu_seqlens; const int* start_pos; const int* slots;
     const int* chunks;                           // [n_chunks][2]: request index, first token of the chunk in its portion
@@ -37,6 +37,7 @@ struct SsdArgs {
     int nh, P, N, G, L;
     float dt_scale;
     const bf16* gate; long gate_stride; float gate_scale;
+    int state_bf16;
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -205,9 +206,20 @@ __global__ void __launch_bounds__(256) ssd_state_pass_kernel(SsdArgs a) {
     const size_t per_head = (size_t)a.P * a.N;
     const size_t i = ((size_t)blockIdx.z * blockDim.x + threadIdx.x) * 4;
     if (i >= per_head) return;
-    float* sp = a.state + ((size_t)a.slots[b] * a.nh + h) * per_head + i;
+    const size_t at = ((size_t)a.slots[b] * a.nh + h) * per_head + i;
+    float* sp = (float*)a.state + at;
+    bf16* sph = (bf16*)a.state + at;                    // the state as bfloat16 (state_bf16): four values are 8 bytes
     float4 S = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (a.start_pos[b] > 0) S = *reinterpret_cast<const float4*>(sp);
+    if (a.start_pos[b] > 0) {
+        if (a.state_bf16) {
+            const uint2 v = *reinterpret_cast<const uint2*>(sph);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            S = make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else {
+            S = *reinterpret_cast<const float4*>(sp);
+        }
+    }
     constexpr int kAhead = 4;                                    // chunks whose dS and decay are fetched together
     for (int c = c0; c < c0 + nc; c += kAhead) {
         float4 d[kAhead];
@@ -230,7 +242,8 @@ __global__ void __launch_bounds__(256) ssd_state_pass_kernel(SsdArgs a) {
             }
         }
     }
-    *reinterpret_cast<float4*>(sp) = S;
+    if (a.state_bf16) *reinterpret_cast<uint2*>(sph) = make_uint2(pack_bf16(S.x, S.y), pack_bf16(S.z, S.w));
+    else *reinterpret_cast<float4*>(sp) = S;
 }
 
 // ---------------------------------------------------------------------------------------------- kernel 3
@@ -430,11 +443,11 @@ extern "C" int lb_ssd_chunk_len(int chunk, int P, int N) {
 }
 
 extern "C" int lb_ssd_prefill(const void* conv, int C, const void* dt, long dt_stride, const float* A_log,
-                              const float* dt_bias, const float* D, float* state, void* y, const int* cu_seqlens,
+                              const float* dt_bias, const float* D, void* state, void* y, const int* cu_seqlens,
                               const int* start_pos, const int* slots, const int* chunks, int n_chunks,
                               const int* req_chunks, int n_long, float* scratch, void* s_in, float* chunk_a, int nh, int P, int N,
                               int G, int L, float dt_scale, const void* gate, long gate_stride, float gate_scale,
-                              int run_scan, int dtype, void* stream) {
+                              int run_scan, int state_bf16, int dtype, void* stream) {
     if (n_chunks <= 0 || n_long <= 0) return kOk;
     if (dtype != kBF16) return kBadDType;
     if (nh <= 0 || G <= 0 || nh % G || P <= 0 || N <= 0 || P % 8 || N % 8 || L <= 0) return kBadSize;
@@ -443,7 +456,7 @@ extern "C" int lb_ssd_prefill(const void* conv, int C, const void* dt, long dt_s
     if ((run_scan && scan_smem(L, P, N) > kSmemLimit) || state_smem(L, P, N) > kSmemLimit) return kTooLarge;
     SsdArgs a{(const bf16*)conv, C, (const bf16*)dt, dt_stride, A_log, dt_bias, D, state, (bf16*)y, cu_seqlens,
               start_pos, slots, chunks, req_chunks, scratch, (bf16*)s_in, chunk_a, nh, P, N, G, L, dt_scale,
-              (const bf16*)gate, gate_stride, gate_scale};
+              (const bf16*)gate, gate_stride, gate_scale, state_bf16};
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem1 = state_smem(L, P, N);
     static size_t have1 = 0;

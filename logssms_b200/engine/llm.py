@@ -30,7 +30,7 @@ class LLM:
                  device: str = "cuda:0", tokenizer=None, eos_token_ids: Sequence[int] | None = None,
                  poison_on_free: bool = False, use_graphs: bool = True, scheduling_policy: str = "mixed",
                  mixed_prefill_tokens: int | None = None, profile: bool = False, nvtx: bool = False,
-                 cuda_graph_max_bs: int | None = None):
+                 cuda_graph_max_bs: int | None = None, ssm_state_dtype: str = "float32"):
         from ..config import load_model_config
         config = load_model_config(model_path)
         max_seq_len = max_seq_len_override or min(getattr(config, "max_position_embeddings", 8192), 8192)
@@ -39,7 +39,8 @@ class LLM:
         self.engine = Engine(model_path, dtype, max_requests=max_running_requests, max_seq_len=max_seq_len,
                              page_size=page_size, num_pages=num_pages, memory_ratio=memory_ratio, device=device,
                              poison_on_free=poison_on_free, max_step_tokens=max_prefill_tokens, use_graphs=use_graphs,
-                             profile=profile, nvtx=nvtx, cuda_graph_max_bs=cuda_graph_max_bs)
+                             profile=profile, nvtx=nvtx, cuda_graph_max_bs=cuda_graph_max_bs,
+                             ssm_state_dtype=ssm_state_dtype)
         if cuda_graph_max_bs:
             # asked for by size: the decode graphs are captured now, before the first request (as the reference does)
             self.engine.capture_decode_graphs()

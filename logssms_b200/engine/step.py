@@ -39,7 +39,7 @@ class Engine:
                  device: str = "cuda:0", poison_on_free: bool = False, max_step_tokens: int = 1 << 30,
                  use_graphs: bool = True, max_graphs: int = 64, max_shape_graphs: int = 8, max_bucket_graphs: int = 32,
                  max_graph_tokens: int = 4096, profile: bool = False, nvtx: bool = False,
-                 cuda_graph_max_bs: int | None = None):
+                 cuda_graph_max_bs: int | None = None, ssm_state_dtype: str = "float32"):
         if not torch.cuda.is_available():
             raise RuntimeError("logssms_b200 needs a CUDA device (built for sm_100a); there is no CPU path")
         try:
@@ -54,7 +54,8 @@ class Engine:
         self.max_seq_len = max_seq_len
         with torch.inference_mode():
             load_weights(self.model, model_dir, self.dtype, self.device)
-            self.model.setup(Runtime(self.device, self.dtype, max_seq_len, page_size))
+            # `ssm_state_dtype`: "float32" (the default), or "activation" to keep recurrent states in the model's dtype
+            self.model.setup(Runtime(self.device, self.dtype, max_seq_len, page_size, {"ssm_state_dtype": ssm_state_dtype}))
         needs = self.model.cache_needs()
         if num_pages is None:
             num_pages = self._pages_that_fit(needs, max_requests, memory_ratio)

@@ -545,14 +545,18 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
     return out
 
 
+def _ssm_state_ok(state: torch.Tensor, act: torch.dtype) -> bool:
+    return state.is_contiguous() and (state.dtype == torch.float32 or (state.dtype == torch.bfloat16 == act))
+
+
 def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
              state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor,
              num_requests: int, num_heads: int, head_dim: int, state_dim: int, num_groups: int,
              dt_scale: float, gate: torch.Tensor | None = None, gate_scale: float = 1.0, *,
              request_list: torch.Tensor | None = None, num_listed: int = 0,
              out: torch.Tensor | None = None, beside: bool = False) -> torch.Tensor:
-    """conv: [tokens, nh*P + 2*G*N] (x | B | C; a column view is fine); dt: [tokens, nh] view; state: float32
-    [slots, nh, P, N], updated in place.  Returns y [tokens, nh*P]; with `gate` ([tokens, nh*P] view)
+    """conv: [tokens, nh*P + 2*G*N] (x | B | C; a column view is fine); dt: [tokens, nh] view; state: float32 (or,
+    with bfloat16 activations, bfloat16: rounded once per call) [slots, nh, P, N], updated in place.  Returns y [tokens, nh*P]; with `gate` ([tokens, nh*P] view)
     the result is y * silu(gate * gate_scale), the gate of a mixer that has no norm.  `request_list`
     (int32 indices into the batch, `num_listed` of them) restricts the call to those requests; the rows
     of `out` that belong to other requests are left as they are.  `beside`: other kernels of the step run at the same
@@ -571,8 +575,8 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
     _need(dt.shape == (tokens, num_heads) and dt.stride(1) == 1 and dt.dtype == conv.dtype, "dt must be a [tokens, heads] view")
     for t, n in ((A_log, "A_log"), (dt_bias, "dt_bias"), (D, "D")):
         _need(t.dtype == torch.float32 and t.shape == (num_heads,) and t.is_contiguous(), f"{n} must be float32 [heads]")
-    _need(state.dtype == torch.float32 and state.is_contiguous()
-          and state.shape[1:] == (num_heads, head_dim, state_dim), "SSM state must be float32 [slots, heads, P, N]")
+    _need(_ssm_state_ok(state, conv.dtype) and state.shape[1:] == (num_heads, head_dim, state_dim),
+          "SSM state must be contiguous float32 (or bfloat16 beside bfloat16 activations) [slots, heads, P, N]")
     _need(state_dim % 4 == 0 and state_dim <= 256, f"state sizes in steps of 4 up to 256 are built, got {state_dim}")
     for t, n in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
         _i32(t, n)
@@ -580,11 +584,11 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias:
     _need(y.shape == (tokens, num_heads * head_dim) and y.dtype == conv.dtype and y.is_contiguous(), "out must be [tokens, heads * head_dim]")
     f = _fn("ssm", "lb_ssm_scan", [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                   c_long, c_float, c_void_p, c_int, c_int, c_void_p])
+                                   c_long, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(conv), C, conv.stride(0) if tokens > 1 else C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D),
              _ptr(state), _ptr(y), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), num_requests, num_heads, head_dim,
              state_dim, num_groups, dt_scale, _ptr(gate), gate.stride(0) if gate is not None else 0, gate_scale,
-             _ptr(request_list), int(bool(beside)), _code(conv), _stream()), "ssm_scan")
+             _ptr(request_list), int(bool(beside)), int(state.dtype == torch.bfloat16), _code(conv), _stream()), "ssm_scan")
     return y
 
 
@@ -625,8 +629,8 @@ def ssd_prefill(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bi
     _need(dt.shape == (tokens, num_heads) and dt.stride(1) == 1 and dt.dtype == conv.dtype, "dt must be a [tokens, heads] view")
     for t, n in ((A_log, "A_log"), (dt_bias, "dt_bias"), (D, "D")):
         _need(t.dtype == torch.float32 and t.shape == (num_heads,) and t.is_contiguous(), f"{n} must be float32 [heads]")
-    _need(state.dtype == torch.float32 and state.is_contiguous()
-          and state.shape[1:] == (num_heads, head_dim, state_dim), "SSM state must be float32 [slots, heads, P, N]")
+    _need(_ssm_state_ok(state, conv.dtype) and state.shape[1:] == (num_heads, head_dim, state_dim),
+          "SSM state must be contiguous float32 or bfloat16 [slots, heads, P, N]")
     for t, n in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots"), (chunks, "chunks"), (req_chunks, "req_chunks")):
         _i32(t, n)
     _need(chunks.numel() >= 2 * num_chunks and req_chunks.numel() >= 3 * num_long, "work lists are shorter than their counts")
@@ -643,11 +647,12 @@ def ssd_prefill(conv: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bi
     tc = ssd_chunk_scan_tc_ok(head_dim, state_dim, chunk_len) and conv.data_ptr() % 16 == 0 and y.data_ptr() % 16 == 0
     f = _fn("ssd", "lb_ssd_prefill", [c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                      c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_float, c_int, c_int, c_void_p])
+                                      c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_float, c_int, c_int, c_int,
+                                      c_void_p])
     _check(f(_ptr(conv), C, _ptr(dt), dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(D), _ptr(state), _ptr(y),
              _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(req_chunks), num_long,
              _ptr(scratch), _ptr(s_in), _ptr(chunk_a), num_heads, head_dim, state_dim, num_groups, chunk_len, dt_scale,
-             _ptr(gate), gate_stride, gate_scale, 0 if tc else 1, _code(conv), _stream()),
+             _ptr(gate), gate_stride, gate_scale, 0 if tc else 1, int(state.dtype == torch.bfloat16), _code(conv), _stream()),
            "ssd_prefill", f"(head_dim {head_dim}, state_dim {state_dim}, chunk {chunk_len})", launches=2 if tc else 3)
     if tc:
         err = error_word(conv.device)

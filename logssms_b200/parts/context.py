@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any
+from typing import Any, Mapping
 
 import numpy as np
 import torch
@@ -17,6 +17,8 @@ class Runtime:
     dtype: torch.dtype
     max_seq_len: int
     page_size: int
+    # choices of the engine's user that a part may honour, by name ("ssm_state_dtype": "float32" | "activation")
+    options: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -80,12 +80,19 @@ class Mamba2(Part):
     def setup(self, rt) -> None:
         s = self.spec
         self._chunk_len = K.ssd_chunk_len(s.chunk_size, s.head_dim, s.state_dim) if rt.dtype == torch.bfloat16 else 0
+        # The recurrent state between steps: 32-bit unless the engine's user asks for the activation dtype, in which
+        # the reference keeps it (python/logssms/cache/naive/manager.py:445-451): half the bytes of a decode step's
+        # state update, one rounding of the state per step.
+        choice = rt.options.get("ssm_state_dtype", "float32")
+        if choice not in ("float32", "activation"):
+            raise ValueError(f"ssm_state_dtype must be float32 or activation, got {choice!r}")
+        self._state_dtype = torch.float32 if choice == "float32" else None
 
     def cache_needs(self) -> CacheNeeds:
         s = self.spec
         return CacheNeeds(states=(
             StateNeed("conv", (s.conv_dim, s.conv_kernel - 1), None),
-            StateNeed("ssm", (s.num_heads, s.head_dim, s.state_dim), torch.float32),
+            StateNeed("ssm", (s.num_heads, s.head_dim, s.state_dim), getattr(self, "_state_dtype", torch.float32)),
         ))
 
     def forward(self, x: torch.Tensor, ctx, cache_layer: int, writes_cache: bool = True) -> torch.Tensor:

@@ -24,6 +24,11 @@ def test_reference_option_names_parse():
     # the reference's two spellings of the graph option (0: no graphs; a number: the largest decode batch with a graph)
     assert build_parser().parse_args(["--model", "/m", "--cuda-graph-max-bs", "16"]).cuda_graph_max_bs == 16
     assert build_parser().parse_args(["--model", "/m", "--graph", "0"]).cuda_graph_max_bs == 0
+    # an option of this engine alone: the dtype in which recurrent states are kept between steps
+    assert build_parser().parse_args(["--model", "/m"]).ssm_state_dtype == "float32"
+    assert build_parser().parse_args(["--model", "/m", "--ssm-state-dtype", "activation"]).ssm_state_dtype == "activation"
+    with pytest.raises(SystemExit):
+        build_parser().parse_args(["--model", "/m", "--ssm-state-dtype", "float16"])
 
 
 def test_model_path_has_both_spellings_and_defaults_follow_the_chat_client():

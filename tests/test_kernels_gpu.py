@@ -661,6 +661,46 @@ def test_ssm_scan_beside_other_kernels_gives_the_same_bits(dtype, shape):
     assert not bool(torch.isnan(y_b[rows.cuda()].float()).any()) and bool((y_b[rows.cuda()] != 7.0).any())
 
 
+@pytest.mark.parametrize("shape", [(6, 64, 128, 1, 128), (3, 128, 256, 1, 128), (4, 24, 20, 2, 16)])
+def test_a_state_kept_in_bfloat16_is_the_float32_state_rounded_once_per_call(shape):
+    """The recurrent state kept in the activation dtype between steps (as the reference keeps it): every kernel that
+    reads or writes it (the chunked prompt kernels, the token-by-token kernel in both of its forms) must give the very
+    outputs of the 32-bit-state run whose state is rounded to bfloat16 by hand after each call."""
+    nh, Pd, N, G, chunk = shape
+    dtype = torch.bfloat16
+    k = K()
+    L = k.ssd_chunk_len(chunk, Pd, N)
+    g = torch.Generator().manual_seed(nh + N)
+    inner, C = nh * Pd, nh * Pd + 2 * G * N
+    consts = [dev(torch.log(1 + 15 * torch.rand(nh, generator=g))), dev(torch.randn(nh, generator=g) - 3.0),
+              dev(torch.randn(nh, generator=g))]
+    B = 3
+    slots = dev(torch.tensor([2, 0, 3], dtype=torch.int32))
+    st16 = torch.full((5, nh, Pd, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    st32 = torch.full((5, nh, Pd, N), float("nan"), dtype=torch.float32, device="cuda")
+    pos = [0, 0, 0]
+    # a prompt portion each (chunked where the sizes allow), a second portion, then single tokens in both scan forms
+    for step, lens in enumerate([[150, 40, 300], [129, 17, 33], [1, 1, 1], [1, 1, 1], [3, 1, 2]]):
+        n = sum(lens)
+        conv, dt = dev(randn(g, n, C, dtype=dtype)), dev(randn(g, n, nh, dtype=dtype))
+        cu, sp = packed_batch(lens, pos)
+        args = (dev(cu), dev(sp), slots)
+        outs = []
+        for st in (st16, st32):
+            if step < 2 and L > 0:
+                chunks, per_request = chunk_lists(lens, L)
+                outs.append(k.ssd_prefill(conv, dt, *consts, st, *args, dev(chunks), chunks.shape[0], dev(per_request),
+                                          per_request.shape[0], L, nh, Pd, N, G, 0.8))
+            else:
+                outs.append(k.ssm_scan(conv, dt, *consts, st, *args, B, nh, Pd, N, G, 0.8, beside=step == 3))
+        live = [2, 0, 3]
+        st32[live] = st32[live].bfloat16().float()          # what keeping the state in bfloat16 does, by hand
+        assert torch.equal(outs[0], outs[1]), f"step {step}"
+        assert torch.equal(st16[live].float(), st32[live]), f"step {step}"
+        pos = [p + m for p, m in zip(pos, lens)]
+    assert bool(torch.isnan(st16[[1, 4]].float()).all())      # nobody else's slot was touched
+
+
 # --------------------------------------------------------------------------- 32-bit matrix product
 def test_gemm_f32_is_true_32_bit():
     g = torch.Generator().manual_seed(9)

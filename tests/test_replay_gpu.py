@@ -35,13 +35,13 @@ def sharpen(model_dir):
 _cache: dict = {}
 
 
-def replayed(tmp_path_factory, name, dtype):
-    key = (name, dtype)
+def replayed(tmp_path_factory, name, dtype, state="float32"):
+    key = (name, dtype, state)
     if key in _cache:
         return _cache[key]
     base_name = name.split("-")[0]
     raw = TINY[base_name]
-    tmp = tmp_path_factory.mktemp(f"replay_{name}_{dtype}")
+    tmp = tmp_path_factory.mktemp(f"replay_{name}_{dtype}_{state}")
     model_dir = make_model_dir(tmp / "model", raw, seed=11 + len(name),
                                dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
     if name.endswith("-sharp"):
@@ -74,7 +74,8 @@ def replayed(tmp_path_factory, name, dtype):
     for n in (1, 2, 3):
         whole(trace, uid(f"first_tokens{n}", "r1"), seqs["r1"][:n])
     assert trace.peak_tokens <= MAX_TOKENS, trace.peak_tokens
-    got = run_trace(model_dir, dtype, trace, str(tmp / "out"), MAX_TOKENS, raw["vocab_size"], extra_args=["--poison"])
+    got = run_trace(model_dir, dtype, trace, str(tmp / "out"), MAX_TOKENS, raw["vocab_size"],
+                    extra_args=["--poison", "--ssm-state-dtype", state])
     _cache[key] = (got, want, ids_of, trace)
     return _cache[key]
 
@@ -108,3 +109,15 @@ def test_mixed_scenario_really_mixes_and_reuses_pages(tmp_path_factory, dtype):
     assert any(len(e["tokens"]) == 2 for s in mixed_steps for e in s["entries"]), "no two-token portion"
     total = sum(-(-n // PAGE) for n in LENGTHS.values())
     assert total * 2 > MAX_TOKENS // PAGE, "the pool is not small enough to force reuse"
+
+
+@pytest.mark.parametrize("name", ["D", "R14"])
+def test_replay_with_the_recurrent_state_kept_in_bfloat16(tmp_path_factory, name):
+    """`--ssm-state-dtype activation` (the reference's way of keeping the state): every cutting of the same requests
+    within the same tolerance of the plain implementation, which never rounds the state."""
+    got, want, ids_of, trace = replayed(tmp_path_factory, name, "bfloat16", state="activation")
+    for u, rid in ids_of.items():
+        g = got[u]
+        assert not torch.isnan(g).any(), f"{u}: positions without logits"
+        err = rel_err(g, want[rid][:g.shape[0]])
+        assert err <= TOL["bfloat16"], f"{name} {u}: error {err:.3g}"
